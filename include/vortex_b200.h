@@ -1,0 +1,140 @@
+/*
+ * vortex_b200 — C ABI of the B200-native (sm_100a) kernels behind the Vortex
+ * vFlow sparse-attention decode path.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless said otherwise.
+ *   - No entry point allocates, synchronises the host, or throws.  Every entry
+ *     point enqueues its work on `stream` (a cudaStream_t passed as void*) and
+ *     returns a status: VTX_OK or one of the VTX_ERR_* codes below.
+ *   - `dtype` selects the element type of q / caches / scores: VTX_BF16 or VTX_F32.
+ *   - "segment" = one (request, KV head) pair, numbered request * num_kv_heads + head.
+ *   - Citations name the interface of the reference project that each entry point
+ *     replaces (path:line inside that project).
+ */
+#ifndef VORTEX_B200_H
+#define VORTEX_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VTX_OK 0
+#define VTX_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, bad enum */
+#define VTX_ERR_UNSUPPORTED 2      /* shape outside what the kernels are built for */
+#define VTX_ERR_CUDA 3             /* the CUDA runtime reported an error at launch */
+
+#define VTX_BF16 0
+#define VTX_F32 1
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int vtx_version(void);
+
+/* Static, NUL-terminated description of a status code. */
+const char* vtx_status_string(int status);
+
+/* Text of the last CUDA runtime error seen by this thread's most recent failing call. */
+const char* vtx_last_cuda_error(void);
+
+/*
+ * Block-table builder for one decode step.
+ * Replaces `sglang_plan_decode` (csrc/register.h:15-36, csrc/utils_sglang.cu:313-460;
+ * kernels :123-184, :188-254, :257-309) and, when the four trailing table pointers
+ * are non-null, `sglang_plan_decode_fa3` (csrc/register.h, csrc/utils_sglang.cu:949-1239).
+ *
+ *   cached_seq_lens [bs] i32, req_to_token [pool, req_to_token_stride] i32,
+ *   req_indices [bs] i64.
+ *   dense/sparse_kv_indptr [bs*H + 1], dense/sparse_kv_indices (packed),
+ *   kv_last_page_len [bs*H], winfo_* workload arrays and two device scalars.
+ *   dense/sparse_page_table [bs*H, page_table_stride] and dense/sparse_cache_seqlens
+ *   [bs*H] are written only when all four are non-null; in that form kv_last_page_len
+ *   may be null (the reference's block-table planner has no such output).
+ * One kernel launch; no limit on bs (the reference stops at 1024).
+ */
+int vtx_plan_decode(const int32_t* cached_seq_lens, const int32_t* req_to_token,
+                    int64_t req_to_token_stride, const int64_t* req_indices,
+                    int32_t* dense_kv_indptr, int32_t* dense_kv_indices,
+                    int32_t* sparse_kv_indptr, int32_t* sparse_kv_indices,
+                    int32_t* kv_last_page_len, int32_t* winfo_q_indices,
+                    int32_t* winfo_kv_offsets, int32_t* winfo_kv_lens,
+                    int32_t* winfo_num_workloads, int32_t* winfo_chunk_size,
+                    int32_t* dense_page_table, int32_t* dense_cache_seqlens,
+                    int32_t* sparse_page_table, int32_t* sparse_cache_seqlens,
+                    int64_t page_table_stride, int batch_size, int page_size,
+                    int num_kv_heads, int topk_val, int page_reserved_bos,
+                    int page_reserved_eos, int max_chunk_size, int min_chunk_size,
+                    void* stream);
+
+/*
+ * Scatter new tokens into the paged K and V caches.
+ * Replaces `set_kv_buffer_launcher` (cache/triton_kernels/set_kv.py:5-62).
+ * Cache layout [num_pages, H, page_size, D]; new_k/new_v [nnz, H, D]; loc [nnz] i64.
+ */
+int vtx_set_kv(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
+               const int64_t* loc, int64_t nnz, int num_kv_heads, int head_dim,
+               int page_size, int dtype, void* stream);
+
+/*
+ * Page-completion mean over the token axis: the cache-side `Mean(dim=1)` op.
+ * Replaces `reduce_pp` with ReduceType.Mean, DIM=1 (cache/triton_kernels/reduce_impl.py:7-89).
+ * x [num_pages*H, rows, cols]; out [num_pages*H, 1, cols]; loc [nnz] i64.  A slot t does
+ * work only when (t + 1) % page_size == 0.  fp32 accumulation in row order, one rounding.
+ */
+int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads,
+              int rows, int cols, int page_size, int dtype, void* stream);
+
+/*
+ * Centroid GeMV: score of every non-reserved candidate page of every segment that has
+ * more than topk_val candidates, stored at the candidate's packed dense position.
+ * Replaces `mv_bpr` (indexer/triton_kernels/mv_impl.py:6-81).
+ * q_mean [eff_bs, 1, D]; centroids [num_pages*H, 1, D]; scores [>= dense_indptr[eff_bs]].
+ */
+int vtx_gemv(const void* q_mean, const void* centroids, void* scores,
+             const int32_t* dense_kv_indptr, const int32_t* dense_kv_indices, int eff_batch_size,
+             int head_dim, int topk_val, int page_reserved_bos, int page_reserved_eos,
+             int dtype, void* stream);
+
+/*
+ * Top-k page selection from packed scores into the sparse page list.
+ * Replaces `topk_output` (csrc/topk.cu:117-203; kernel :56-113).  Order: score descending,
+ * ties by ascending candidate position; output = that sorted prefix of dense row ids.
+ * max_num_pages_per_request bounds the candidates of one segment (sizes shared memory).
+ */
+int vtx_topk(const void* scores, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+             const int32_t* dense_kv_indices, int32_t* sparse_kv_indices, int eff_batch_size,
+             int topk_val, int page_reserved_bos, int page_reserved_eos,
+             int max_num_pages_per_request, int dtype, void* stream);
+
+/*
+ * Fused indexer: grouped-query mean + centroid GeMV + top-k, one CTA per segment, scores
+ * never leave the SM.  Same results as mean -> vtx_gemv -> vtx_topk.
+ * Replaces the chain flow/algorithms.py:168-170 (torch mean, mv_bpr, topk_output).
+ * q [eff_bs, group, D].  sparse_page_table (optional, may be null) receives the same ids at
+ * [segment, bos + j] for block-table consumers.
+ */
+int vtx_indexer_fused(const void* q, const void* centroids, const int32_t* dense_kv_indptr,
+                      const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                      int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                      int64_t page_table_stride, int eff_batch_size, int group_size, int head_dim,
+                      int topk_val, int page_reserved_bos, int page_reserved_eos,
+                      int max_num_pages_per_request, int dtype, void* stream);
+
+/*
+ * Paged grouped-query decode attention over each segment's page list (sparse or dense).
+ * Takes the place of the flashinfer paged-decode call the SGLang fork makes on
+ * sparse_kv_indptr / sparse_kv_indices / kv_last_page_len (data contract:
+ * indexer/context.py:117-121, csrc/utils_sglang.cu:148-151).
+ * q, out [eff_bs, group, D]; k_cache, v_cache [num_pages*H, page_size, D].
+ * softmax(q . K^T * sm_scale) . V with fp32 softmax and accumulation.
+ */
+int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void* out,
+                   const int32_t* kv_indptr, const int32_t* kv_indices,
+                   const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                   int head_dim, int page_size, float sm_scale, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VORTEX_B200_H */

@@ -1,0 +1,453 @@
+"""CPU oracle for the Vortex sparse-attention decode path (TEST INFRASTRUCTURE, not product).
+
+This module restates, in PyTorch eager on CPU tensors, the arithmetic of the
+reference's vFlow decode path: block-table planning, centroid maintenance,
+the indexer (grouped-query mean, centroid GeMV, top-k page selection) and the
+paged sparse decode attention.  Only the tests, the smoke check and the
+CPU-baseline leg of the benchmark may import it; the product path never does.
+
+Parity status
+-------------
+* Integer planning (`plan_decode`), top-k ordering and the KV layout follow the
+  reference sources line by line (citations on each function) and are pinned
+  by hand-derived known-answer cases plus, on a GPU box, by the reference's own
+  CUDA kernels compiled into ``oracle/_ref`` (when that build is present).
+* Floating-point order: the reference's GeMV/CMean reduction order is whatever
+  Triton's layout produced and is pinned by no reference test.  The oracle
+  fixes one canonical order (documented on `canonical_dot`), and the CUDA
+  kernels implement exactly that order, so selections are bit-exact between the
+  two.  Against the reference's Triton kernels the agreement is within one
+  bf16 ulp of the score (checked by fixtures generated under the Triton
+  interpreter), not bit-exact: **parity unpinned** for the reduction order.
+* Paged attention and MLA decode are not in the reference tree at all (they
+  live in a third-party dependency, flashinfer-python 0.2.7.post1, called from
+  an un-vendored SGLang fork).  The oracle restates textbook softmax attention
+  over the listed pages: **parity unpinned**.
+
+All citations are paths inside the reference project.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+NEG_FILL = -1  # value used for "never written" integer slots in oracle outputs
+
+
+# --------------------------------------------------------------------------- #
+# numeric helpers
+# --------------------------------------------------------------------------- #
+def bf16_rne(x: torch.Tensor) -> torch.Tensor:
+    """Round an fp32 tensor to bf16 (round-to-nearest-even) and return it as fp32."""
+    return x.to(torch.float32).to(torch.bfloat16).to(torch.float32)
+
+
+def _pow2_ceil(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+def canonical_lanes(head_dim: int) -> int:
+    """Number of partial accumulators ("lanes") of the canonical dot product."""
+    assert head_dim % 8 == 0, "head_dim must be a multiple of 8"
+    return min(32, _pow2_ceil(head_dim // 8))
+
+
+def canonical_dot(rows: torch.Tensor, vec: torch.Tensor, bf16_products: bool) -> torch.Tensor:
+    """Dot product of every row of ``rows`` [R, D] with ``vec`` [D] in the canonical order.
+
+    The reference computes ``sum((y_tile * x_i).to(float32), axis=1)`` where the
+    product is formed in the input dtype (indexer/triton_kernels/mv_impl.py:60):
+    for bf16 inputs each product is rounded to bf16 before the fp32 sum.  The
+    order of that sum is not specified by the reference; this build fixes it:
+
+    * the D dims are cut into chunks of 8 consecutive dims;
+    * L = min(32, pow2ceil(D/8)) lanes; lane l owns chunks l, l+L, l+2L, ...
+      and adds their products one at a time, in ascending dim order, into one
+      fp32 accumulator that starts at +0.0 (separate multiply and add, no FMA);
+    * the L lane sums are folded in halves: v[i] += v[i + w] for w = L/2 ... 1.
+
+    ``rows`` and ``vec`` are fp32 tensors (bf16 values already widened).
+    """
+    R, D = rows.shape
+    L = canonical_lanes(D)
+    nch = D // 8
+    prod = rows * vec.unsqueeze(0)                      # fp32 multiply, one rounding
+    if bf16_products:
+        prod = bf16_rne(prod)                           # exact product, RNE to bf16
+    prod = prod.view(R, nch, 8)
+    lane = torch.zeros(R, L, dtype=torch.float32)
+    for c0 in range(0, nch, L):
+        n = min(L, nch - c0)
+        for j in range(8):
+            lane[:, :n] = lane[:, :n] + prod[:, c0:c0 + n, j]
+    w = L // 2
+    while w >= 1:
+        lane = lane[:, :w] + lane[:, w:2 * w]
+        w //= 2
+    return lane[:, 0]
+
+
+# --------------------------------------------------------------------------- #
+# KV layout and centroid maintenance
+# --------------------------------------------------------------------------- #
+def set_kv(k_cache, v_cache, new_k, new_v, loc, page_size: int) -> None:
+    """Scatter new tokens into the paged caches.
+
+    Follows cache/triton_kernels/set_kv.py:28-33: token slot ``t`` of head ``h``
+    lives at flattened row ``(t // P) * H + h`` (caches are ``[num_pages*H, P, D]``)
+    and token offset ``t % P``.
+    """
+    nnz, H, D = new_k.shape
+    for i in range(nnz):
+        t = int(loc[i])
+        for h in range(H):
+            row = (t // page_size) * H + h
+            k_cache[row, t % page_size] = new_k[i, h]
+            v_cache[row, t % page_size] = new_v[i, h]
+
+
+def cmean(x: torch.Tensor, out: torch.Tensor, loc: torch.Tensor, page_size: int, num_kv_heads: int) -> None:
+    """Page-completion mean over the token axis (the ``CMean(dim=1)`` cache op).
+
+    Trigger and addressing follow cache/triton_kernels/reduce_impl.py:21-47: a new
+    token at slot ``t`` does work only if ``(t + 1) % P == 0``; it then reduces the
+    block ``x[(t // P) * H + h]`` of shape [rows, D] for every head h and writes
+    ``out[(t // P) * H + h, 0, :]``.
+
+    Arithmetic: fp32 accumulation over the rows in ascending order starting from
+    +0.0, one division by the row count, one rounding to the cache dtype.  (The
+    reference sums in bf16, reduce_impl.py:37; this build follows the fp32 rule.)
+    """
+    rows = x.shape[1]
+    for t in loc.tolist():
+        if (t + 1) % page_size != 0:
+            continue
+        for h in range(num_kv_heads):
+            pid = (t // page_size) * num_kv_heads + h
+            acc = torch.zeros(x.shape[2], dtype=torch.float32)
+            blk = x[pid].to(torch.float32)
+            for r in range(rows):
+                acc = acc + blk[r]
+            out[pid, 0] = (acc / float(rows)).to(out.dtype)
+
+
+def cmean_pages(x: torch.Tensor, page_rows: torch.Tensor) -> torch.Tensor:
+    """Vectorised form of the `cmean` arithmetic for many flattened rows at once (same order)."""
+    blk = x[page_rows].to(torch.float32)
+    acc = torch.zeros(blk.shape[0], blk.shape[2], dtype=torch.float32)
+    for r in range(blk.shape[1]):
+        acc = acc + blk[:, r]
+    return (acc / float(blk.shape[1])).to(x.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# block-table builder
+# --------------------------------------------------------------------------- #
+def plan_decode(
+    cached_seq_lens,
+    req_to_token,
+    req_indices,
+    page_size: int,
+    num_kv_heads: int,
+    topk_val: int,
+    bos: int,
+    eos: int,
+    max_chunk_size: int,
+    min_chunk_size: int = 1,
+    page_table_stride: Optional[int] = None,
+) -> Dict[str, np.ndarray]:
+    """Block-table builder for one decode step.
+
+    Restates csrc/utils_sglang.cu: indptr scan :257-309 (segments ordered
+    (request, head); every head of a request has the same length), index fill
+    :123-184 (dense row id ``(slot // P) * H + head``; sparse list = copy when
+    pages <= budget, else BOS pages in front and EOS pages in the last slots,
+    middle left for top-k), ``kv_last_page_len`` :148-151, workload chunks
+    :188-254.  With ``page_table_stride`` set it also produces the block-table
+    form of :949-1083 (page tables ``[bs*H, stride]`` and per-segment sequence
+    lengths, sparse length ``min((budget-1)*P + last_len, seq_len)``).
+
+    Slots the reference never writes hold ``NEG_FILL``.
+    """
+    seq = np.asarray(cached_seq_lens, dtype=np.int64)
+    r2t = np.asarray(req_to_token, dtype=np.int64)
+    ridx = np.asarray(req_indices, dtype=np.int64)
+    bs = seq.shape[0]
+    H, P, K = num_kv_heads, page_size, topk_val
+    budget = K + bos + eos
+    n = (seq + P - 1) // P
+    m = np.minimum(budget, n)
+    S = bs * H
+    dense_indptr = np.zeros(S + 1, dtype=np.int32)
+    sparse_indptr = np.zeros(S + 1, dtype=np.int32)
+    cn = np.concatenate([[0], np.cumsum(n)])
+    cm = np.concatenate([[0], np.cumsum(m)])
+    for r in range(bs):
+        for j in range(H + 1):
+            dense_indptr[r * H + j] = H * cn[r] + j * n[r]
+            sparse_indptr[r * H + j] = H * cm[r] + j * m[r]
+    dense = np.full(int(dense_indptr[-1]), NEG_FILL, dtype=np.int32)
+    sparse = np.full(int(sparse_indptr[-1]), NEG_FILL, dtype=np.int32)
+    last = np.zeros(S, dtype=np.int32)
+    out: Dict[str, np.ndarray] = {}
+    if page_table_stride is not None:
+        dpt = np.full((S, page_table_stride), NEG_FILL, dtype=np.int32)
+        spt = np.full((S, page_table_stride), NEG_FILL, dtype=np.int32)
+        dsl = np.zeros(S, dtype=np.int32)
+        ssl = np.zeros(S, dtype=np.int32)
+    for r in range(bs):
+        toks = r2t[ridx[r]]
+        nr = int(n[r])
+        ll = int(seq[r] % P)
+        ll = P if ll == 0 else ll
+        for h in range(H):
+            s = r * H + h
+            last[s] = ll
+            rows = (toks[np.arange(nr) * P] // P) * H + h
+            d0 = dense_indptr[s]
+            dense[d0:d0 + nr] = rows
+            s0 = sparse_indptr[s]
+            if nr <= budget:
+                sparse[s0:s0 + nr] = rows
+            else:
+                sparse[s0:s0 + bos] = rows[:bos]
+                for e in range(eos):
+                    sparse[s0 + budget - e - 1] = rows[nr - e - 1]
+            if page_table_stride is not None:
+                dpt[s, :nr] = rows
+                if nr <= budget:
+                    spt[s, :nr] = rows
+                else:
+                    spt[s, :bos] = rows[:bos]
+                    for e in range(eos):
+                        spt[s, budget - e - 1] = rows[nr - e - 1]
+                dsl[s] = seq[r]
+                ssl[s] = min((budget - 1) * P + ll, int(seq[r]))
+    # workload list (csrc/utils_sglang.cu:219-251)
+    wq, woff, wlen = [], [], []
+    for s in range(S):
+        w = int(dense_indptr[s + 1] - dense_indptr[s]) - bos - eos
+        cnt = w if w > K else 0
+        nchunk = (cnt + max_chunk_size - 1) // max_chunk_size
+        ll = cnt % max_chunk_size
+        ll = max_chunk_size if ll == 0 else ll
+        for j in range(nchunk):
+            wq.append(s)
+            wlen.append(max_chunk_size if j != nchunk - 1 else ll)
+            woff.append(int(dense_indptr[s]) + j * max_chunk_size + bos)
+    out.update(
+        dense_kv_indptr=dense_indptr,
+        sparse_kv_indptr=sparse_indptr,
+        dense_kv_indices=dense,
+        sparse_kv_indices=sparse,
+        kv_last_page_len=last,
+        winfo_q_indices=np.asarray(wq, dtype=np.int32),
+        winfo_kv_offsets=np.asarray(woff, dtype=np.int32),
+        winfo_kv_lens=np.asarray(wlen, dtype=np.int32),
+        winfo_num_workloads=np.asarray([len(wq)], dtype=np.int32),
+        winfo_chunk_size=np.asarray([max_chunk_size], dtype=np.int32),
+    )
+    if page_table_stride is not None:
+        out.update(dense_page_table=dpt, sparse_page_table=spt,
+                   dense_cache_seqlens=dsl, sparse_cache_seqlens=ssl)
+    return out
+
+
+# --------------------------------------------------------------------------- #
+# indexer
+# --------------------------------------------------------------------------- #
+def q_group_mean(q: torch.Tensor) -> torch.Tensor:
+    """Grouped-query mean ``q.mean(dim=1, keepdim=True)`` (flow/algorithms.py:168).
+
+    fp32 accumulation over the group in ascending order from +0.0, one division
+    by the group size, one rounding to q's dtype.
+    """
+    S, G, D = q.shape
+    acc = torch.zeros(S, D, dtype=torch.float32)
+    qf = q.to(torch.float32)
+    for g in range(G):
+        acc = acc + qf[:, g]
+    return (acc / float(G)).to(q.dtype).view(S, 1, D)
+
+
+def gemv_scores(q_mean, centroids, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Centroid scores at packed dense positions (the ``GeMV`` indexer op).
+
+    Follows indexer/triton_kernels/mv_impl.py:53-62 driven by the workload list of
+    csrc/utils_sglang.cu:219-251: only the non-reserved candidates
+    ``[indptr[s]+bos, indptr[s+1]-eos)`` of segments with more than ``topk_val``
+    candidates are scored; the score of candidate position p is stored at
+    ``out[p]`` in the input dtype.  Other positions are left untouched.
+    """
+    total = int(dense_indptr[eff_bs])
+    dt = q_mean.dtype
+    if out is None:
+        out = torch.zeros(total, dtype=dt)
+    is_bf16 = dt == torch.bfloat16
+    cf = centroids.view(centroids.shape[0], -1)
+    for s in range(eff_bs):
+        a = int(dense_indptr[s]) + bos
+        b = int(dense_indptr[s + 1]) - eos
+        if b - a <= topk_val:
+            continue
+        rows = cf[torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)].to(torch.float32)
+        sc = canonical_dot(rows, q_mean[s, 0].to(torch.float32), is_bf16)
+        out.view(-1)[a:b] = sc.to(dt)
+    return out
+
+
+def _sortable(scores_f32: np.ndarray) -> np.ndarray:
+    """Map fp32 values to uint32 keys whose unsigned order is the float order (-0.0 == +0.0)."""
+    x = scores_f32.astype(np.float32) + np.float32(0.0)  # -0.0 + 0.0 = +0.0
+    b = x.view(np.uint32)
+    return np.where(b & 0x80000000, ~b, b | 0x80000000).astype(np.uint32)
+
+
+def topk_select(scores, dense_indptr, sparse_indptr, dense_indices, sparse_indices,
+                eff_bs, topk_val, bos, eos) -> None:
+    """Top-k page selection (the ``topK`` indexer op), writing into ``sparse_indices``.
+
+    Follows csrc/topk.cu:70-77, 97-112: candidates are the dense positions
+    ``[indptr[s]+bos, indptr[s+1]-eos)``; segments with ``candidates <= topk_val``
+    are skipped; keys are the scores widened to fp32, values the dense row ids;
+    a stable descending sort (ties keep ascending candidate order) and the
+    first ``topk_val`` values go to ``sparse[sparse_indptr[s] + bos + j]``.
+    """
+    sc = scores.detach().to(torch.float32).view(-1).numpy()
+    for s in range(eff_bs):
+        a = int(dense_indptr[s]) + bos
+        b = int(dense_indptr[s + 1]) - eos
+        if b - a <= topk_val:
+            continue
+        seg = sc[a:b]
+        assert np.isfinite(seg).all(), "oracle defines ordering for finite scores only"
+        keys = _sortable(seg).astype(np.int64)
+        order = np.argsort(-keys, kind="stable")[:topk_val]
+        o0 = int(sparse_indptr[s]) + bos
+        sparse_indices[o0:o0 + topk_val] = np.asarray(dense_indices)[a + order]
+
+
+def forward_indexer(q, centroids, plan, topk_val, bos, eos):
+    """``q.mean -> GeMV -> topK`` of the block-sparse flow (flow/algorithms.py:168-170).
+
+    ``plan`` is the dict returned by `plan_decode`; its ``sparse_kv_indices`` array
+    is completed in place.  Returns the packed score tensor.
+    """
+    eff_bs = q.shape[0]
+    qm = q_group_mean(q)
+    scores = gemv_scores(qm, centroids, plan["dense_kv_indptr"], plan["dense_kv_indices"],
+                         eff_bs, topk_val, bos, eos)
+    topk_select(scores, plan["dense_kv_indptr"], plan["sparse_kv_indptr"], plan["dense_kv_indices"],
+                plan["sparse_kv_indices"], eff_bs, topk_val, bos, eos)
+    if "sparse_page_table" in plan:
+        spt = plan["sparse_page_table"]
+        for s in range(eff_bs):
+            a, b = int(plan["sparse_kv_indptr"][s]), int(plan["sparse_kv_indptr"][s + 1])
+            spt[s, : b - a] = plan["sparse_kv_indices"][a:b]
+    return scores
+
+
+# --------------------------------------------------------------------------- #
+# decode attention
+# --------------------------------------------------------------------------- #
+def decode_gqa(q, k_cache, v_cache, indptr, indices, last_page_len, scale: Optional[float] = None):
+    """Paged decode attention over each segment's page list.
+
+    q ``[S, G, D]``; caches ``[num_pages*H, P, D]``; segment s attends to every
+    token of the rows ``indices[indptr[s]:indptr[s+1]]`` except that the last
+    listed row contributes only ``last_page_len[s]`` tokens (the data contract of
+    csrc/utils_sglang.cu:148-151, 175-180).  fp32 softmax and accumulation,
+    ``scale`` defaults to ``1/sqrt(D)``; output is rounded once to q's dtype.
+    The attention kernel itself is third-party in the reference (flashinfer
+    inside the SGLang fork): parity unpinned.
+    """
+    S, G, D = q.shape
+    P = k_cache.shape[1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    out = torch.zeros(S, G, v_cache.shape[2], dtype=torch.float32)
+    for s in range(S):
+        a, b = int(indptr[s]), int(indptr[s + 1])
+        if b <= a:
+            continue
+        rows = torch.as_tensor(np.asarray(indices[a:b]), dtype=torch.long)
+        ntok = (b - a - 1) * P + int(last_page_len[s])
+        kk = k_cache[rows].to(torch.float32).reshape(-1, D)[:ntok]
+        vv = v_cache[rows].to(torch.float32).reshape(-1, v_cache.shape[2])[:ntok]
+        logits = (q[s].to(torch.float32) @ kk.T) * scale
+        p = torch.softmax(logits, dim=-1)
+        out[s] = p @ vv
+    return out.to(q.dtype)
+
+
+def decode_mla(q, latent_cache, page_table, cache_seqlens, kv_lora_rank: int, scale: float):
+    """Block-table decode over a shared compressed latent (no counterpart in the reference).
+
+    q ``[B, Hq, Dl]`` (Dl = kv_lora_rank + rope dims); ``latent_cache`` ``[pages, P, Dl]``;
+    ``page_table`` ``[B, stride]`` row ids and ``cache_seqlens`` ``[B]`` token counts in the
+    block-table form of csrc/utils_sglang.cu:968-976.  Keys are the full latent row,
+    values its first ``kv_lora_rank`` dims.  fp32 softmax/accumulation, output
+    ``[B, Hq, kv_lora_rank]`` rounded once to q's dtype.  Parity unpinned.
+    """
+    B, Hq, Dl = q.shape
+    P = latent_cache.shape[1]
+    out = torch.zeros(B, Hq, kv_lora_rank, dtype=torch.float32)
+    for b in range(B):
+        ntok = int(cache_seqlens[b])
+        npg = (ntok + P - 1) // P
+        rows = torch.as_tensor(np.asarray(page_table[b, :npg]), dtype=torch.long)
+        kv = latent_cache[rows].to(torch.float32).reshape(-1, Dl)[:ntok]
+        logits = (q[b].to(torch.float32) @ kv.T) * scale
+        p = torch.softmax(logits, dim=-1)
+        out[b] = p @ kv[:, :kv_lora_rank]
+    return out.to(q.dtype)
+
+
+# --------------------------------------------------------------------------- #
+# seeded synthetic workload (shared by tests, smoke and the benchmark's CPU leg)
+# --------------------------------------------------------------------------- #
+def make_paged_problem(seed: int, seq_lens, num_kv_heads: int, group: int, head_dim: int,
+                       page_size: int, dtype=torch.bfloat16, pool_pages: Optional[int] = None,
+                       permute: bool = True, v_dim: Optional[int] = None):
+    """Seeded paged-KV problem: N(0,1) q/K/V, random physical page order, centroids by `cmean_pages`."""
+    g = torch.Generator().manual_seed(seed)
+    seq = np.asarray(seq_lens, dtype=np.int32)
+    bs = len(seq)
+    n = (seq.astype(np.int64) + page_size - 1) // page_size
+    max_pages = int(n.max())
+    total = int(n.sum())
+    pool_pages = total if pool_pages is None else pool_pages
+    assert pool_pages >= total
+    perm = torch.randperm(pool_pages, generator=g).numpy() if permute else np.arange(pool_pages)
+    stride = max_pages * page_size
+    r2t = np.zeros((bs, stride), dtype=np.int32)
+    off = 0
+    for r in range(bs):
+        for j in range(int(n[r])):
+            r2t[r, j * page_size:(j + 1) * page_size] = perm[off + j] * page_size + np.arange(page_size)
+        off += int(n[r])
+    H, D = num_kv_heads, head_dim
+    vd = D if v_dim is None else v_dim
+    k = torch.randn(pool_pages * H, page_size, D, generator=g).to(dtype)
+    v = torch.randn(pool_pages * H, page_size, vd, generator=g).to(dtype)
+    q = torch.randn(bs * H, group, D, generator=g).to(dtype)
+    cent = torch.zeros(pool_pages * H, 1, D, dtype=dtype)
+    full_rows = []
+    off = 0
+    for r in range(bs):
+        nfull = int(seq[r]) // page_size
+        for j in range(nfull):
+            for h in range(H):
+                full_rows.append(int(perm[off + j]) * H + h)
+        off += int(n[r])
+    if full_rows:
+        fr = torch.as_tensor(full_rows, dtype=torch.long)
+        cent[fr, 0] = cmean_pages(k, fr)
+    return dict(seq_lens=seq, req_to_token=r2t, req_indices=np.arange(bs, dtype=np.int64),
+                k=k, v=v, q=q, centroids=cent, perm=perm)

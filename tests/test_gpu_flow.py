@@ -1,0 +1,146 @@
+"""The vFlow plugin API end to end on the GPU: user-visible calls only, checked against the oracle."""
+import math
+import textwrap
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import vortex_oracle as vo
+
+pytestmark = pytest.mark.gpu
+
+
+def _runtime(prob, seq, L, H, G, D, P, K, bos, eos, dtype, flow=None, skip=(0,)):
+    from vortex_torch.runtime import ServerArgs, VortexDecodeRuntime
+
+    sa = ServerArgs(page_size=P, vortex_topk_val=K, vortex_page_reserved_bos=bos, vortex_page_reserved_eos=eos,
+                    vortex_layers_skip=list(skip), vortex_max_seq_lens=int(max(seq)))
+    pages = prob["k"].shape[0] // H
+    rt = VortexDecodeRuntime(L, H * G, H, D, num_pages=pages, max_bs=len(seq), context_len=int(max(seq)),
+                             server_args=sa, dtype=dtype, flow=flow)
+    rt.model_runner.req_to_token_pool.req_to_token.copy_(torch.as_tensor(prob["req_to_token"]))
+    return rt
+
+
+@pytest.mark.parametrize("dtype,seq", [(torch.float32, [4096]), (torch.bfloat16, [2048, 1000, 8192, 300])])
+def test_runtime_step_matches_oracle(dtype, seq):
+    """Two layers (layer 0 dense, layer 1 sparse), the new token closes a page when seq % P == 0."""
+    L, H, G, D, P, K, bos, eos = 2, 8, 2, 128, 16, 30, 1, 1
+    prob = vo.make_paged_problem(7, seq, H, G, D, P, dtype=dtype)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, bos, eos, dtype)
+    bs = len(seq)
+    g = torch.Generator().manual_seed(1)
+    # caches hold everything except the newest token of each request; the step writes it
+    loc = torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)], dtype=torch.int64)
+    ks, vs, cents, qs, nks, nvs = [], [], [], [], [], []
+    for l in range(L):
+        pl = vo.make_paged_problem(100 + l, seq, H, G, D, P, dtype=dtype)
+        k, v, cent = pl["k"], pl["v"], pl["centroids"]
+        nk = torch.stack([k[(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)])
+        nv = torch.stack([v[(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)])
+        k0, v0, c0 = k.clone(), v.clone(), cent.clone()
+        for r in range(bs):
+            rows = (loc[r] // P) * H + torch.arange(H)
+            k0[rows, loc[r] % P] = 0
+            v0[rows, loc[r] % P] = 0
+            c0[rows] = 0  # the centroid of a page closed by this step must come from forward_cache
+        rt.pool.buffers[l]["k"].copy_(k0)
+        rt.pool.buffers[l]["v"].copy_(v0)
+        rt.pool.buffers[l]["centroids"].copy_(c0)
+        ks.append(k); vs.append(v); cents.append(cent)
+        qs.append(torch.randn(bs, H * G, D, generator=g).to(dtype)); nks.append(nk); nvs.append(nv)
+    outs = [torch.empty(bs, H * G, D, dtype=dtype, device="cuda") for _ in range(L)]
+    rt.step(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(),
+            [q.cuda() for q in qs], [x.cuda() for x in nks], [x.cuda() for x in nvs], loc.cuda(), outs)
+    torch.cuda.synchronize()
+    ref = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+    for l in range(L):
+        assert torch.equal(rt.pool.buffers[l]["k"].cpu(), ks[l])
+        full = [r for r in range(bs) if seq[r] % P == 0]
+        for r in full:
+            rows = (loc[r] // P) * H + torch.arange(H)
+            assert torch.equal(rt.pool.buffers[l]["centroids"].cpu()[rows], cents[l][rows])
+        qv = qs[l].view(bs * H, G, D)
+        if l == 0:
+            want = vo.decode_gqa(qv, ks[l], vs[l], ref["dense_kv_indptr"], ref["dense_kv_indices"], ref["kv_last_page_len"])
+        else:
+            plan = {k_: v_.copy() for k_, v_ in ref.items()}
+            vo.forward_indexer(qv, cents[l], plan, K, bos, eos)
+            ns = int(plan["sparse_kv_indptr"][-1])
+            np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], plan["sparse_kv_indices"])
+            want = vo.decode_gqa(qv, ks[l], vs[l], plan["sparse_kv_indptr"], plan["sparse_kv_indices"], plan["kv_last_page_len"])
+        got = outs[l].view(bs * H, G, D).cpu().float()
+        assert bool(((got - want.float()).abs() <= tol * want.float().abs().clamp(min=1)).all())
+    # the fused indexer path was taken: the GeMV never wrote its score buffer
+    assert rt.flow.gemv._fused_consumer is rt.flow.output_func
+
+
+def test_user_flow_file_runs_unfused_when_scores_are_read(tmp_path):
+    """A user flow that touches the scores with a torch op must fall back to GeMV + topK, same selection."""
+    from vortex_torch.flow import build_vflow
+
+    src = textwrap.dedent('''
+        import torch
+        from vortex_torch.flow import vFlow, register
+        from vortex_torch.indexer import GeMV, topK
+        from vortex_torch.cache import Mean as CMean
+
+        @register("probe_reads_scores")
+        class Probe(vFlow):
+            def __init__(self, shift=0.0):
+                super().__init__()
+                self.gemv, self.output_func, self.reduction, self.shift = GeMV(), topK(), CMean(dim=1), shift
+                self.seen = None
+            def forward_indexer(self, q, o, cache, ctx):
+                score = self.gemv(q.mean(dim=1, keepdim=True), cache["centroids"], ctx=ctx)
+                self.seen = score.abs().sum()            # plain torch read of the scores
+                self.output_func(score, o, ctx=ctx)
+            def forward_cache(self, cache, loc, ctx):
+                self.reduction(cache["k"], cache["centroids"], loc=loc, ctx=ctx)
+            def create_cache(self, page_size, head_dim):
+                return {"centroids": (1, head_dim)}
+    ''')
+    f = tmp_path / "probe_flow.py"
+    f.write_text(src)
+    flow = build_vflow("probe_reads_scores", {"shift": 1.0}, str(f))
+    seq, L, H, G, D, P, K = [2048, 900], 1, 4, 2, 128, 16, 10
+    prob = vo.make_paged_problem(3, seq, H, G, D, P)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16, flow=flow, skip=())
+    assert flow.gemv._score_read_elsewhere
+    for name in ("k", "v", "centroids"):
+        rt.pool.buffers[0][name].copy_(prob[name])
+    rt.plan(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda())
+    q = prob["q"].cuda()
+    flow.forward_indexer(q, rt.backend.kv_indices_decode[1].view(-1, 1, 1), rt.pool.buffers[0], ctx=rt.ictx)
+    ref = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, 1, 1, 64, 16)
+    vo.forward_indexer(prob["q"], prob["centroids"], ref, K, 1, 1)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], ref["sparse_kv_indices"])
+    assert float(flow.seen) > 0
+
+
+def test_vortex_torch_C_shim_signatures():
+    """The pybind-module names of the reference, called with its positional argument order."""
+    import vortex_torch_C as C
+
+    P, H, K, bos, eos = 16, 2, 4, 1, 1
+    prob = vo.make_paged_problem(1, [700, 40], H, 2, 128, P)
+    ref = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)
+    i32 = dict(dtype=torch.int32, device="cuda")
+    S = 2 * H
+    dip, sip = torch.zeros(S + 1, **i32), torch.zeros(S + 1, **i32)
+    din, sin_ = torch.zeros(4096, **i32), torch.full((256,), -1, **i32)
+    last = torch.zeros(S, **i32)
+    w = [torch.zeros(512, **i32) for _ in range(3)] + [torch.zeros(1, **i32), torch.zeros(1, **i32)]
+    C.sglang_plan_decode(torch.as_tensor(prob["seq_lens"]).cuda(), dip, din, sip, sin_, last,
+                         torch.as_tensor(prob["req_to_token"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(),
+                         *w, P, H, K, bos, eos, 64, 16)
+    np.testing.assert_array_equal(dip.cpu().numpy(), ref["dense_kv_indptr"])
+    scores = vo.forward_indexer(prob["q"], prob["centroids"], ref, K, bos, eos)
+    C.topk_output(scores.cuda(), dip, sip, din, sin_, S, K, bos, eos, 64)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(sin_.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+    with pytest.raises(NotImplementedError):
+        C.sglang_plan_prefill()

@@ -1,0 +1,207 @@
+"""Parity of the sm_100a kernels (called through the C ABI) against the CPU oracle.
+
+Integer outputs (block tables, selected pages) and centroids must be bit-exact; attention outputs
+must be within 2e-2 (abs or rel) for bf16 and 1e-5 for fp32.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import vortex_oracle as vo
+from vortex_torch import _cabi
+
+from _util import DevicePlan, assert_plan_equal, close, to_dev
+
+pytestmark = pytest.mark.gpu
+BF16_TOL, F32_TOL = 2e-2, 1e-5
+
+
+# ------------------------------------------------------------------ block tables
+@pytest.mark.parametrize("tables", [False, True])
+@pytest.mark.parametrize("case", [
+    dict(seq=[9, 18], P=4, H=2, K=1, bos=1, eos=1, mc=2),
+    dict(seq=[24], P=4, H=1, K=1, bos=1, eos=2, mc=4),
+    dict(seq=[16], P=4, H=1, K=1, bos=1, eos=2, mc=4),
+    dict(seq=[1, 2, 3, 4, 5, 600, 77, 16, 1023, 31], P=16, H=8, K=3, bos=0, eos=1, mc=8),
+    dict(seq=[4096] * 3 + [17, 512, 513], P=16, H=4, K=30, bos=1, eos=1, mc=64),
+    dict(seq=[300] * 300, P=16, H=2, K=5, bos=2, eos=2, mc=4),          # more than one scan tile of requests
+])
+def test_plan_decode_bit_exact(case, tables):
+    prob = vo.make_paged_problem(3, case["seq"], case["H"], 1, 8, case["P"], dtype=torch.float32)
+    # shuffle request slots so req_indices is exercised
+    bs = len(case["seq"])
+    order = np.random.default_rng(0).permutation(bs)
+    r2t = np.zeros_like(prob["req_to_token"])
+    r2t[order] = prob["req_to_token"]
+    prob["req_to_token"], prob["req_indices"] = r2t, order.astype(np.int64)
+    dp = DevicePlan(prob, case["P"], case["H"], case["K"], case["bos"], case["eos"], max_chunk=case["mc"],
+                    min_chunk=1, tables=tables)
+    assert_plan_equal(dp, dp.oracle(prob))
+
+
+def test_plan_decode_rejects_bad_arguments():
+    z = torch.zeros(4, dtype=torch.int32, device="cuda")
+    r2t = torch.zeros(1, 4, dtype=torch.int32, device="cuda")
+    ridx = torch.zeros(1, dtype=torch.int64, device="cuda")
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        _cabi.plan_decode(z[:1], r2t, ridx, z, z, z, z, z, z, z, z, z, z, 4, 1, 1, 0, 0, 4, 1)  # eos must be >= 1
+    with pytest.raises(TypeError):
+        _cabi.plan_decode(z[:1].long(), r2t, ridx, z, z, z, z, z, z, z, z, z, z, 4, 1, 1, 0, 1, 4, 1)
+
+
+# ------------------------------------------------------------------ cache side
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_set_kv_layout(dtype):
+    P, H, D, pages = 16, 8, 128, 12
+    g = torch.Generator().manual_seed(0)
+    k = torch.zeros(pages * H, P, D, dtype=dtype)
+    v = torch.zeros(pages * H, P, D, dtype=dtype)
+    loc = torch.randperm(pages * P, generator=g)[:50]
+    nk = torch.randn(50, H, D, generator=g).to(dtype)
+    nv = torch.randn(50, H, D, generator=g).to(dtype)
+    kd, vd = k.cuda(), v.cuda()
+    _cabi.set_kv(kd, vd, nk.cuda(), nv.cuda(), loc.cuda(), P)
+    vo.set_kv(k, v, nk, nv, loc, P)
+    assert torch.equal(kd.cpu(), k) and torch.equal(vd.cpu(), v)
+
+
+@pytest.mark.parametrize("dtype,P,H,D", [(torch.bfloat16, 16, 8, 128), (torch.float32, 16, 8, 128),
+                                         (torch.bfloat16, 64, 1, 576), (torch.bfloat16, 4, 2, 64),
+                                         (torch.bfloat16, 12, 3, 128)])
+def test_cmean_bit_exact(dtype, P, H, D):
+    pages = 40
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(pages * H, P, D, generator=g).to(dtype)
+    out = torch.zeros(pages * H, 1, D, dtype=dtype)
+    closing = torch.randperm(pages, generator=g)[:17] * P + (P - 1)
+    others = torch.randperm(pages, generator=g)[:9] * P + (P // 2 - 1 if P > 2 else 0)
+    loc = torch.cat([closing, others])[torch.randperm(26, generator=g)]
+    od = out.cuda()
+    _cabi.cmean(x.cuda(), od, loc.cuda(), H, P)
+    vo.cmean(x, out, loc, P, H)
+    assert torch.equal(od.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       out.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+
+
+def test_cmean_prefill_shape():
+    """Config 4b scaled down: every slot of a long request; only page-closing slots work."""
+    P, H, D, pages = 16, 8, 128, 128
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(pages * H, P, D, generator=g).bfloat16()
+    loc = torch.arange(pages * P - 5)  # last page left incomplete
+    od = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16, device="cuda")
+    _cabi.cmean(x.cuda(), od, loc.cuda(), H, P)
+    want = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16)
+    rows = torch.arange((pages - 1) * H)
+    want[rows, 0] = vo.cmean_pages(x, rows)
+    assert torch.equal(od.cpu().view(torch.int16), want.view(torch.int16))
+
+
+# ------------------------------------------------------------------ indexer
+def _indexer_case(seed, seq, H, G, D, P, K, bos, eos, dtype):
+    prob = vo.make_paged_problem(seed, seq, H, G, D, P, dtype=dtype)
+    dp = DevicePlan(prob, P, H, K, bos, eos)
+    ref = dp.oracle(prob)
+    scores_ref = vo.forward_indexer(prob["q"], prob["centroids"], ref, K, bos, eos)
+    return prob, dp, ref, scores_ref
+
+
+INDEXER_CASES = [
+    # seq lens, H, G, D, P, K, bos, eos, dtype
+    ([4096], 8, 2, 128, 16, 30, 1, 1, torch.float32),                       # config 1
+    ([2048, 2048, 1000, 600], 8, 2, 128, 16, 30, 1, 1, torch.bfloat16),     # config 2 shape, small batch
+    ([1024, 5000, 333, 16, 17, 2500], 8, 4, 128, 16, 64, 1, 1, torch.bfloat16),  # config 3 shape, ragged
+    ([700, 130], 2, 4, 64, 8, 5, 0, 2, torch.bfloat16),
+    ([4096, 1300], 1, 16, 576, 64, 32, 1, 1, torch.bfloat16),               # config 5 shape (latent rows)
+    ([1500], 2, 2, 256, 16, 7, 2, 1, torch.float32),
+]
+
+
+@pytest.mark.parametrize("case", INDEXER_CASES, ids=lambda c: f"H{c[1]}G{c[2]}D{c[3]}P{c[4]}K{c[5]}-{str(c[8])[6:]}")
+def test_indexer_fused_and_split_match_oracle(case):
+    seq, H, G, D, P, K, bos, eos, dtype = case
+    prob, dp, ref, scores_ref = _indexer_case(11, seq, H, G, D, P, K, bos, eos, dtype)
+    d = to_dev(prob)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    # fused
+    sparse_fused = dp.sparse_indices.clone()
+    _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sparse_fused,
+                        dp.S, K, bos, eos, dp.max_pages)
+    np.testing.assert_array_equal(sparse_fused.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+    # operator by operator: mean (oracle order) -> gemv -> topk
+    qm = vo.q_group_mean(prob["q"]).cuda()
+    scores = torch.zeros(max(1, int(ref["dense_kv_indptr"][-1])), dtype=dtype, device="cuda")
+    _cabi.gemv(qm, d["centroids"], scores, dp.dense_indptr, dp.dense_indices, dp.S, K, bos, eos)
+    itype = torch.int16 if dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(scores.cpu().view(itype), scores_ref.view(itype)), "GeMV scores differ in bits"
+    sparse_split = dp.sparse_indices.clone()
+    _cabi.topk(scores, dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sparse_split, dp.S, K, bos, eos,
+               dp.max_pages)
+    np.testing.assert_array_equal(sparse_split.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+
+
+def test_topk_heavy_ties():
+    """Scores drawn from four values: selection must follow candidate order inside each tie class."""
+    H, K, bos, eos, P = 2, 30, 1, 1, 16
+    prob = vo.make_paged_problem(5, [8192, 3000], H, 2, 128, P)
+    dp = DevicePlan(prob, P, H, K, bos, eos)
+    ref = dp.oracle(prob)
+    g = torch.Generator().manual_seed(9)
+    total = int(ref["dense_kv_indptr"][-1])
+    scores = torch.tensor([-1.0, 0.0, -0.0, 2.5])[torch.randint(0, 4, (total,), generator=g)].bfloat16()
+    vo.topk_select(scores, ref["dense_kv_indptr"], ref["sparse_kv_indptr"], ref["dense_kv_indices"],
+                   ref["sparse_kv_indices"], dp.S, K, bos, eos)
+    out = dp.sparse_indices.clone()
+    _cabi.topk(scores.cuda(), dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, out, dp.S, K, bos, eos,
+               dp.max_pages)
+    np.testing.assert_array_equal(out.cpu().numpy()[:int(ref["sparse_kv_indptr"][-1])], ref["sparse_kv_indices"])
+
+
+# ------------------------------------------------------------------ decode attention
+DECODE_CASES = [
+    ([4096], 8, 2, 128, 16, 30, 1, 1, torch.float32),
+    ([2048, 777, 100, 16, 15, 1], 8, 2, 128, 16, 30, 1, 1, torch.bfloat16),
+    ([1024, 5000, 333], 8, 4, 128, 16, 64, 1, 1, torch.bfloat16),
+    ([700, 130, 9], 2, 4, 64, 8, 5, 0, 2, torch.bfloat16),
+    ([513, 64], 4, 1, 128, 32, 4, 1, 1, torch.bfloat16),
+    ([300], 1, 8, 128, 16, 4, 1, 1, torch.bfloat16),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=lambda c: f"H{c[1]}G{c[2]}D{c[3]}P{c[4]}-{str(c[8])[6:]}")
+@pytest.mark.parametrize("sparse", [True, False])
+def test_decode_gqa_matches_oracle(case, sparse):
+    seq, H, G, D, P, K, bos, eos, dtype = case
+    prob, dp, ref, _ = _indexer_case(21, seq, H, G, D, P, K, bos, eos, dtype)
+    d = to_dev(prob)
+    key = "sparse" if sparse else "dense"
+    indptr, indices = ref[f"{key}_kv_indptr"], ref[f"{key}_kv_indices"]
+    want = vo.decode_gqa(prob["q"], prob["k"], prob["v"], indptr, indices, ref["kv_last_page_len"])
+    out = torch.empty_like(d["q"])
+    _cabi.decode_gqa(d["q"], d["k"], d["v"], out, torch.as_tensor(indptr).cuda(), torch.as_tensor(indices).cuda(),
+                     dp.last_page_len, dp.S, P, 1.0 / math.sqrt(D))
+    tol = BF16_TOL if dtype == torch.bfloat16 else F32_TOL
+    assert close(out, want, tol), f"max err {(out.float().cpu() - want.float()).abs().max()}"
+
+
+def test_decode_is_invariant_to_page_order():
+    """Size-independent property: permuting the middle pages of a list changes nothing beyond fp32 re-association."""
+    seq, H, G, D, P, K = [3000], 4, 2, 128, 16, 30
+    prob, dp, ref, _ = _indexer_case(4, seq, H, G, D, P, K, 1, 1, torch.bfloat16)
+    d = to_dev(prob)
+    ind = torch.as_tensor(ref["sparse_kv_indices"]).clone()
+    ptr = ref["sparse_kv_indptr"]
+    shuffled = ind.clone()
+    g = torch.Generator().manual_seed(0)
+    for s in range(dp.S):
+        a, b = int(ptr[s]) + 1, int(ptr[s + 1]) - 1
+        shuffled[a:b] = ind[a:b][torch.randperm(b - a, generator=g)]
+    outs = []
+    for lst in (ind, shuffled):
+        o = torch.empty_like(d["q"])
+        _cabi.decode_gqa(d["q"], d["k"], d["v"], o, torch.as_tensor(ptr).cuda(), lst.cuda(), dp.last_page_len, dp.S, P,
+                         1.0 / math.sqrt(D))
+        outs.append(o)
+    assert close(outs[0], outs[1], 1e-2)

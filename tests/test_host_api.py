@@ -1,0 +1,137 @@
+"""Host-side logic that needs no GPU: registry, loader, format-tagged tensors, contexts, the profile pass,
+the sharding helper, and that the C-ABI library exports every symbol the header declares."""
+import re
+import textwrap
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_cabi_exports_every_declared_symbol():
+    from vortex_torch import _cabi
+
+    header = (ROOT / "include" / "vortex_b200.h").read_text()
+    declared = sorted(set(re.findall(r"\b(vtx_[a-z0-9_]+)\s*\(", header)))
+    assert declared, "no declarations found in the header"
+    for name in declared:
+        assert hasattr(_cabi.lib, name), f"{name} declared in include/vortex_b200.h but not exported"
+    assert set(_cabi.EXPORTED) == set(declared)
+    assert _cabi.version() >= 100
+    assert _cabi.status_string(0) == "ok" and "invalid" in _cabi.status_string(1)
+
+
+def test_no_cpu_fallback():
+    from vortex_torch import _cabi
+
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _cabi.ptr(torch.zeros(4))
+
+
+def test_registry_and_loader(tmp_path):
+    from vortex_torch.flow import build_vflow, register, vFlow
+    from vortex_torch.flow import registry
+    from vortex_torch.flow.loader import FlowInitError, FlowLoadError
+
+    assert {"block_sparse_attention", "gqa_block_sparse_attention", "gqa_quest_sparse_attention"} <= set(registry.list_keys())
+    with pytest.raises(registry.RegistryError, match="must inherit"):
+        register("not_a_flow")(int)
+    with pytest.raises(registry.RegistryError, match="already exists"):
+        register("block_sparse_attention")(registry.get("block_sparse_attention"))
+    with pytest.raises(FlowLoadError, match="not found"):
+        build_vflow("does_not_exist")
+    with pytest.raises(FlowLoadError, match="does not exist"):
+        build_vflow("block_sparse_attention", None, str(tmp_path / "missing.py"))
+    with pytest.raises(FlowInitError, match="mismatch"):
+        build_vflow("block_sparse_attention", {"bogus": 1})
+    f = tmp_path / "user_flow.py"
+    f.write_text(textwrap.dedent('''
+        from vortex_torch.flow import vFlow, register
+        @register("tmp_user_flow")
+        class F(vFlow):
+            def __init__(self, k=3):
+                super().__init__(); self.k = k
+            def forward_indexer(self, q, o, cache, ctx): pass
+            def forward_cache(self, cache, loc, ctx): pass
+            def create_cache(self, page_size, head_dim): return {"s": (2, head_dim)}
+    '''))
+    flow = build_vflow("tmp_user_flow", {"k": 5}, str(f))
+    assert flow.k == 5 and isinstance(flow, vFlow)
+    meta = flow.get_cache_meta_info(16, 128)
+    assert meta == {"s": (2, 128), "k": (16, 128), "v": (16, 128)}
+    assert flow.get_token_ratio(16, 128) == pytest.approx(2.0 + 2 / 16)
+    bad = tmp_path / "bad_flow.py"
+    bad.write_text("raise ValueError('boom')")
+    with pytest.raises(FlowLoadError, match="boom"):
+        build_vflow("tmp_user_flow", None, str(bad))
+
+
+def test_vtensor_rules():
+    from vortex_torch.abs import FORMAT, as_vtensor, vTensor
+
+    a = as_vtensor(torch.randn(2, 3), FORMAT.RAGGED)
+    b = as_vtensor(torch.ones(2, 3), FORMAT.RAGGED)
+    assert isinstance(a + 2.0, vTensor) and (a + 2.0)._format == FORMAT.RAGGED
+    assert (a * b)._format == FORMAT.RAGGED
+    with pytest.raises(RuntimeError, match="plain torch.Tensor"):
+        _ = a + torch.randn(2, 3)
+    with pytest.raises(RuntimeError, match="mismatch"):
+        _ = a + as_vtensor(torch.randn(2, 3), FORMAT.PAGED)
+    assert as_vtensor(a, FORMAT.PAGED) is a and a._format == FORMAT.PAGED
+    import pickle
+    c = pickle.loads(pickle.dumps(b))
+    assert isinstance(c, vTensor) and c._format == FORMAT.RAGGED and torch.equal(torch.Tensor(c), torch.Tensor(b))
+
+
+def test_lazy_group_mean_is_invisible():
+    from vortex_torch.abs import FORMAT, as_vtensor
+    from vortex_torch.abs.tensor import lazy_group_mean_source, materialize
+
+    q = as_vtensor(torch.randn(5, 4, 16), FORMAT.BATCHED)
+    real = q.mean(dim=1, keepdim=True)
+    q._vtx_allow_lazy_mean = True
+    lazy = q.mean(dim=1, keepdim=True)
+    assert lazy_group_mean_source(lazy) is q and lazy.shape == real.shape
+    assert torch.equal(torch.Tensor(lazy * 1.0), torch.Tensor(real))           # any torch op sees the real mean
+    assert torch.equal(torch.Tensor(materialize(lazy)), torch.Tensor(real))
+    assert lazy_group_mean_source(q.mean(dim=2, keepdim=True)) is None           # other reductions are untouched
+    assert lazy_group_mean_source(q.mean(dim=1)) is None
+
+
+def test_profile_pass_allocates_and_detects_fusion():
+    from vortex_torch.runtime import VortexDecodeRuntime
+    from vortex_torch.utils import Mode
+
+    rt = VortexDecodeRuntime(2, 16, 8, 128, num_pages=32, max_bs=3, context_len=512, device="cpu")
+    assert rt.ictx.mode == Mode.execute and rt.cctx.mode == Mode.execute
+    assert rt.ictx.max_num_pages_per_request == 32 and rt.ictx.max_num_pages == 32 * 3 * 8
+    assert rt.flow.gemv.output_buffer.shape == (32 * 3 * 8, 1, 1)
+    assert rt.ictx._aux_total_bytes == 32 * 3 * 8 * 2 and rt.ictx._aux_total_flops == 128
+    assert rt.flow.gemv._fused_consumer is rt.flow.output_func and rt.flow.gemv._x_is_group_mean
+    assert rt.ictx.missing() == [] and rt.cctx.missing() == []
+    with pytest.raises(RuntimeError, match="already called"):
+        rt.ictx.create(rt.backend, rt.model_runner)
+    assert rt.flow.run_indexer_virtual(2, 16, 128, device="cpu") == 128
+
+
+def test_unbuilt_ops_fail_loudly():
+    from vortex_torch.flow import build_vflow
+    from vortex_torch.indexer import Context
+
+    flow = build_vflow("gqa_quest_sparse_attention")
+    with pytest.raises(NotImplementedError, match="no sm_100a kernel"):
+        flow.mul_max(None, None, ctx=Context())
+
+
+def test_balance_requests():
+    from vortex_torch.runtime import balance_requests
+
+    pages = [64, 2048, 100, 1500, 900, 31, 777, 1200]
+    for w in (1, 2, 4, 8):
+        parts = balance_requests(pages, w)
+        assert sorted(sum(parts, [])) == list(range(len(pages)))
+        loads = [sum(pages[i] for i in p) for p in parts]
+        assert max(loads) - min(loads) <= max(pages)
+    assert balance_requests(pages, 2) == balance_requests(pages, 2)

@@ -1,0 +1,30 @@
+// Library-level entry points of the C ABI: version, status strings, last CUDA error text.
+#include <string.h>
+
+#include "vtx_common.cuh"
+
+namespace {
+thread_local char g_last_error[256] = "";
+}
+
+namespace vtx {
+void note_cuda_error(cudaError_t e) {
+    const char* s = cudaGetErrorString(e);
+    strncpy(g_last_error, s ? s : "unknown CUDA error", sizeof(g_last_error) - 1);
+    g_last_error[sizeof(g_last_error) - 1] = '\0';
+}
+}  // namespace vtx
+
+extern "C" int vtx_version(void) { return 100; /* 0.1.0 */ }
+
+extern "C" const char* vtx_status_string(int status) {
+    switch (status) {
+        case VTX_OK: return "ok";
+        case VTX_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size or bad enum)";
+        case VTX_ERR_UNSUPPORTED: return "shape or size not supported by the sm_100a kernels";
+        case VTX_ERR_CUDA: return "CUDA runtime error at launch (see vtx_last_cuda_error)";
+        default: return "unknown status";
+    }
+}
+
+extern "C" const char* vtx_last_cuda_error(void) { return g_last_error; }

@@ -1,0 +1,130 @@
+// Cache-side kernels: KV scatter (defines the paged layout) and the page-completion mean.
+//
+// Layout (cache/triton_kernels/set_kv.py:28-33 of the reference): K and V are separate
+// buffers [num_pages, H, page_size, D]; token slot t of head h sits in flattened row
+// (t / P) * H + h at token offset t % P, so one (page, head) block is contiguous.
+#include <algorithm>
+
+#include "vtx_common.cuh"
+
+namespace {
+
+// One thread moves 16 bytes of K and 16 bytes of V.
+__global__ void __launch_bounds__(256) set_kv_kernel(uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
+                                                    const uint4* __restrict__ new_k,
+                                                    const uint4* __restrict__ new_v,
+                                                    const int64_t* __restrict__ loc, int64_t nnz, int H,
+                                                    int vec_per_row, int P) {
+    const int64_t total = nnz * H * vec_per_row;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % vec_per_row);
+        const int64_t th = i / vec_per_row;
+        const int h = (int)(th % H);
+        const int64_t tok = th / H;
+        const int64_t t = loc[tok];
+        const int64_t dst = (((t / P) * H + h) * P + (t % P)) * vec_per_row + c;
+        k_cache[dst] = new_k[i];
+        v_cache[dst] = new_v[i];
+    }
+}
+
+// A group of LANES threads owns one (new token, head) item; each lane owns chunks of eight
+// columns and adds the page's rows in ascending order into fp32 accumulators that start at
+// +0.0, divides once by the row count and rounds once to T.
+template <typename T, int LANES>
+__global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                   const int64_t* __restrict__ loc, int64_t nnz, int H,
+                                                   int rows, int cols, int P) {
+    constexpr int GROUPS = 256 / LANES;
+    const int lane = threadIdx.x % LANES;
+    const int64_t items = nnz * H;
+    const int nchunk = cols / 8;
+    const float denom = (float)rows;
+    for (int64_t it = (int64_t)blockIdx.x * GROUPS + threadIdx.x / LANES; it < items;
+         it += (int64_t)gridDim.x * GROUPS) {
+        const int64_t t = loc[it / H];
+        if ((t + 1) % P != 0) continue;
+        const int h = (int)(it % H);
+        const int64_t pid = (t / P) * H + h;
+        const T* src = x + pid * (int64_t)rows * cols;
+        for (int c = lane; c < nchunk; c += LANES) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            int r = 0;
+            for (; r + 8 <= rows; r += 8) {
+                vtx::Vec8<T> v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) v[u].load(src + (int64_t)(r + u) * cols + c * 8);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    float f[8];
+                    v[u].unpack(f);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                }
+            }
+            for (; r < rows; ++r) {
+                vtx::Vec8<T> v;
+                v.load(src + (int64_t)r * cols + c * 8);
+                float f[8];
+                v.unpack(f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], denom);
+            vtx::store8(out + pid * (int64_t)cols + c * 8, acc);
+        }
+    }
+}
+
+template <typename T>
+int launch_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int H, int rows, int cols, int P,
+                 cudaStream_t st) {
+    const int64_t items = nnz * H;
+    if (cols <= 128) {
+        const int64_t blocks = (items + 15) / 16;
+        cmean_kernel<T, 16><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
+            (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+    } else {
+        const int64_t blocks = (items + 7) / 8;
+        cmean_kernel<T, 32><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
+            (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+    }
+    return vtx::finish_launch();
+}
+
+}  // namespace
+
+extern "C" int vtx_set_kv(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
+                          const int64_t* loc, int64_t nnz, int num_kv_heads, int head_dim, int page_size,
+                          int dtype, void* stream) {
+    if (!k_cache || !v_cache || !new_k || !new_v || !loc) return VTX_ERR_INVALID_ARGUMENT;
+    if (nnz < 0 || num_kv_heads < 1 || head_dim < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    const int esize = dtype == VTX_BF16 ? 2 : 4;
+    if ((head_dim * esize) % 16 != 0) return VTX_ERR_UNSUPPORTED;
+    if (nnz == 0) return VTX_OK;
+    const int vec_per_row = head_dim * esize / 16;
+    const int64_t total = nnz * num_kv_heads * vec_per_row;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 1 << 20);
+    set_kv_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)k_cache, (uint4*)v_cache,
+                                                            (const uint4*)new_k, (const uint4*)new_v, loc, nnz,
+                                                            num_kv_heads, vec_per_row, page_size);
+    return vtx::finish_launch();
+}
+
+extern "C" int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads, int rows,
+                         int cols, int page_size, int dtype, void* stream) {
+    if (!x || !out || !loc) return VTX_ERR_INVALID_ARGUMENT;
+    if (nnz < 0 || num_kv_heads < 1 || rows < 1 || cols < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (cols % 8 != 0) return VTX_ERR_UNSUPPORTED;
+    if (nnz == 0) return VTX_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == VTX_BF16)
+        return launch_cmean<__nv_bfloat16>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
+    if (dtype == VTX_F32) return launch_cmean<float>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
+    return VTX_ERR_INVALID_ARGUMENT;
+}

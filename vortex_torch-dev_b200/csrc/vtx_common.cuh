@@ -1,0 +1,113 @@
+// Shared device/host helpers for the vortex_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "vortex_b200.h"
+
+namespace vtx {
+
+// Records the text of a failing CUDA runtime call for vtx_last_cuda_error().
+void note_cuda_error(cudaError_t e);
+
+inline int finish_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
+    return VTX_OK;
+}
+
+__host__ __device__ inline int pow2_ceil(int n) {
+    int p = 1;
+    while (p < n) p <<= 1;
+    return p;
+}
+
+// ---- streaming 16-byte loads (read-only path, no L1 allocation) ----
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Eight consecutive elements widened to fp32.
+template <typename T>
+struct Vec8;
+
+template <>
+struct Vec8<__nv_bfloat16> {
+    uint4 raw;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = ld_stream16(p); }
+    __device__ __forceinline__ void load_cached(const __nv_bfloat16* p) {
+        raw = *reinterpret_cast<const uint4*>(p);
+    }
+    __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = bf16lo(raw.x); f[1] = bf16hi(raw.x);
+        f[2] = bf16lo(raw.y); f[3] = bf16hi(raw.y);
+        f[4] = bf16lo(raw.z); f[5] = bf16hi(raw.z);
+        f[6] = bf16lo(raw.w); f[7] = bf16hi(raw.w);
+    }
+};
+
+template <>
+struct Vec8<float> {
+    uint4 raw0, raw1;
+    __device__ __forceinline__ void load(const float* p) {
+        raw0 = ld_stream16(p);
+        raw1 = ld_stream16(p + 4);
+    }
+    __device__ __forceinline__ void load_cached(const float* p) {
+        raw0 = *reinterpret_cast<const uint4*>(p);
+        raw1 = *reinterpret_cast<const uint4*>(p + 4);
+    }
+    __device__ __forceinline__ void zero() {
+        raw0 = make_uint4(0, 0, 0, 0);
+        raw1 = raw0;
+    }
+    __device__ __forceinline__ void unpack(float (&f)[8]) const {
+        f[0] = __uint_as_float(raw0.x); f[1] = __uint_as_float(raw0.y);
+        f[2] = __uint_as_float(raw0.z); f[3] = __uint_as_float(raw0.w);
+        f[4] = __uint_as_float(raw1.x); f[5] = __uint_as_float(raw1.y);
+        f[6] = __uint_as_float(raw1.z); f[7] = __uint_as_float(raw1.w);
+    }
+};
+
+// Round fp32 to T (RNE) and store eight consecutive elements.
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 o;
+    __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(f[2], f[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(f[4], f[5]);
+    __nv_bfloat162 d = __floats2bfloat162_rn(f[6], f[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&a);
+    o.y = *reinterpret_cast<uint32_t*>(&b);
+    o.z = *reinterpret_cast<uint32_t*>(&c);
+    o.w = *reinterpret_cast<uint32_t*>(&d);
+    *reinterpret_cast<uint4*>(p) = o;
+}
+__device__ __forceinline__ void store8(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
+// Value of x after one rounding to T, widened back to fp32.
+template <typename T>
+__device__ __forceinline__ float round_to(float x);
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+}
+template <>
+__device__ __forceinline__ float round_to<float>(float x) { return x; }
+
+}  // namespace vtx

@@ -1,0 +1,186 @@
+"""ctypes binding of ``libvortex_b200.so`` (the C ABI declared in ``include/vortex_b200.h``).
+
+There is no fallback: if the library is missing the import fails, and every wrapper raises
+``RuntimeError`` on a non-zero status.  Tensors are passed as raw device pointers and the
+work is enqueued on torch's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+VTX_BF16, VTX_F32 = 0, 1
+
+_PKG_ROOT = Path(__file__).resolve().parent.parent
+LIB_PATH = Path(os.environ.get("VORTEX_B200_LIB", _PKG_ROOT / "lib" / "libvortex_b200.so"))
+
+if not LIB_PATH.exists():
+    raise ImportError(
+        f"vortex_torch: CUDA library {LIB_PATH} not found. Build it first with "
+        f"`python {_PKG_ROOT / 'build.py'}` (needs nvcc with sm_100a support); there is no CPU fallback."
+    )
+
+lib = C.CDLL(str(LIB_PATH))
+
+_p, _i, _i64, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
+
+# name -> argument types, in header order
+SIGNATURES = {
+    "vtx_plan_decode": [_p, _p, _i64, _p] + [_p] * 10 + [_p] * 4 + [_i64] + [_i] * 8 + [_p],
+    "vtx_set_kv": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _p],
+    "vtx_cmean": [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _p],
+    "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
+}
+for _name, _args in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.argtypes = _args
+    _fn.restype = _i
+lib.vtx_version.restype = _i
+lib.vtx_status_string.argtypes = [_i]
+lib.vtx_status_string.restype = C.c_char_p
+lib.vtx_last_cuda_error.restype = C.c_char_p
+
+EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error"])
+
+
+def version() -> int:
+    return int(lib.vtx_version())
+
+
+def status_string(code: int) -> str:
+    return lib.vtx_status_string(int(code)).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        extra = ""
+        if code == 3:
+            extra = ": " + lib.vtx_last_cuda_error().decode()
+        raise RuntimeError(f"{what} failed with status {code} ({status_string(code)}{extra})")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return VTX_BF16
+    if dt == torch.float32:
+        return VTX_F32
+    raise TypeError(f"vortex_b200 kernels take bfloat16 or float32 tensors, got {dt}")
+
+
+def ptr(t) -> int:
+    """Device pointer of a contiguous CUDA tensor (or 0 for None)."""
+    if t is None:
+        return 0
+    if not t.is_cuda:
+        raise RuntimeError("vortex_b200 kernels need CUDA tensors; there is no CPU fallback")
+    if not t.is_contiguous():
+        raise RuntimeError("vortex_b200 kernels need contiguous tensors")
+    return t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def want(t: torch.Tensor, dt: torch.dtype, name: str) -> None:
+    if t.dtype != dt:
+        raise TypeError(f"{name} must be {dt}, got {t.dtype}")
+
+
+# --------------------------------------------------------------------------- wrappers
+def plan_decode(cached_seq_lens, req_to_token, req_indices, dense_kv_indptr, dense_kv_indices,
+                sparse_kv_indptr, sparse_kv_indices, kv_last_page_len, winfo_q_indices, winfo_kv_offsets,
+                winfo_kv_lens, winfo_num_workloads, winfo_chunk_size, page_size, num_kv_heads, topk_val,
+                bos, eos, max_chunk_size, min_chunk_size, dense_page_table=None, dense_cache_seqlens=None,
+                sparse_page_table=None, sparse_cache_seqlens=None) -> None:
+    want(cached_seq_lens, torch.int32, "cached_seq_lens")
+    want(req_to_token, torch.int32, "req_to_token")
+    want(req_indices, torch.int64, "req_indices")
+    for n, t in (("dense_kv_indptr", dense_kv_indptr), ("dense_kv_indices", dense_kv_indices),
+                 ("sparse_kv_indptr", sparse_kv_indptr), ("sparse_kv_indices", sparse_kv_indices),
+                 ("winfo_q_indices", winfo_q_indices),
+                 ("winfo_kv_offsets", winfo_kv_offsets), ("winfo_kv_lens", winfo_kv_lens),
+                 ("winfo_num_workloads", winfo_num_workloads), ("winfo_chunk_size", winfo_chunk_size)):
+        want(t, torch.int32, n)
+    if kv_last_page_len is not None:
+        want(kv_last_page_len, torch.int32, "kv_last_page_len")
+    stride = 0
+    if dense_page_table is not None:
+        for n, t in (("dense_page_table", dense_page_table), ("dense_cache_seqlens", dense_cache_seqlens),
+                     ("sparse_page_table", sparse_page_table), ("sparse_cache_seqlens", sparse_cache_seqlens)):
+            want(t, torch.int32, n)
+        stride = dense_page_table.shape[1]
+        if sparse_page_table.shape[1] != stride:
+            raise ValueError("dense and sparse page tables must have the same row stride")
+    rc = lib.vtx_plan_decode(
+        ptr(cached_seq_lens), ptr(req_to_token), req_to_token.shape[1], ptr(req_indices),
+        ptr(dense_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indptr), ptr(sparse_kv_indices),
+        ptr(kv_last_page_len), ptr(winfo_q_indices), ptr(winfo_kv_offsets), ptr(winfo_kv_lens),
+        ptr(winfo_num_workloads), ptr(winfo_chunk_size), ptr(dense_page_table), ptr(dense_cache_seqlens),
+        ptr(sparse_page_table), ptr(sparse_cache_seqlens), stride, cached_seq_lens.shape[0],
+        int(page_size), int(num_kv_heads), int(topk_val), int(bos), int(eos), int(max_chunk_size),
+        int(min_chunk_size), stream_of(cached_seq_lens))
+    check(rc, "vtx_plan_decode")
+
+
+def set_kv(k_cache, v_cache, new_k, new_v, loc, page_size) -> None:
+    want(loc, torch.int64, "loc")
+    nnz, H, D = new_k.shape
+    rc = lib.vtx_set_kv(ptr(k_cache), ptr(v_cache), ptr(new_k), ptr(new_v), ptr(loc), nnz, H, D,
+                        int(page_size), dtype_code(k_cache.dtype), stream_of(k_cache))
+    check(rc, "vtx_set_kv")
+
+
+def cmean(x, out, loc, num_kv_heads, page_size) -> None:
+    want(loc, torch.int64, "loc")
+    if out.dtype != x.dtype:
+        raise TypeError("cmean: x and out must share a dtype")
+    rc = lib.vtx_cmean(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
+                       int(page_size), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_cmean")
+
+
+def gemv(q_mean, centroids, scores, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos) -> None:
+    if not (q_mean.dtype == centroids.dtype == scores.dtype):
+        raise TypeError("gemv: q_mean, centroids and scores must share a dtype")
+    rc = lib.vtx_gemv(ptr(q_mean), ptr(centroids), ptr(scores), ptr(dense_kv_indptr), ptr(dense_kv_indices),
+                      int(eff_bs), q_mean.shape[-1], int(topk_val), int(bos), int(eos),
+                      dtype_code(q_mean.dtype), stream_of(q_mean))
+    check(rc, "vtx_gemv")
+
+
+def topk(scores, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices, eff_bs, topk_val,
+         bos, eos, max_pages_per_request) -> None:
+    want(sparse_kv_indices, torch.int32, "sparse_kv_indices")
+    rc = lib.vtx_topk(ptr(scores), ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
+                      ptr(sparse_kv_indices), int(eff_bs), int(topk_val), int(bos), int(eos),
+                      int(max_pages_per_request), dtype_code(scores.dtype), stream_of(scores))
+    check(rc, "vtx_topk")
+
+
+def indexer_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                  eff_bs, topk_val, bos, eos, max_pages_per_request, sparse_page_table=None) -> None:
+    if q.dtype != centroids.dtype:
+        raise TypeError("indexer_fused: q and centroids must share a dtype")
+    stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    rc = lib.vtx_indexer_fused(ptr(q), ptr(centroids), ptr(dense_kv_indptr), ptr(sparse_kv_indptr),
+                               ptr(dense_kv_indices), ptr(sparse_kv_indices), ptr(sparse_page_table), stride,
+                               int(eff_bs), q.shape[1], q.shape[2], int(topk_val), int(bos), int(eos),
+                               int(max_pages_per_request), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_indexer_fused")
+
+
+def decode_gqa(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len, eff_bs, page_size,
+               sm_scale) -> None:
+    if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
+        raise TypeError("decode_gqa: q, caches and out must share a dtype")
+    rc = lib.vtx_decode_gqa(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(kv_indptr), ptr(kv_indices),
+                            ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size),
+                            float(sm_scale), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_decode_gqa")

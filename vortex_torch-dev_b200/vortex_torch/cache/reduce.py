@@ -1,0 +1,64 @@
+"""Page-completion reductions (reference ops: ``cache/reduce.py:10-525``).
+
+``Mean(dim=1)(x, output, loc=loc, ctx=ctx)`` — the ``CMean`` of the shipped flows: for every new
+token slot in ``loc`` that closes a page, and every KV head, reduce that page's block of ``x``
+(``[rows, cols]``) over its rows and write ``output[row, 0, :]``.  Accumulation is fp32 in row
+order with one rounding to the cache dtype.  Only PAGED -> PAGED with ``dim=1`` has an sm_100a
+kernel; other layouts raise ``NotImplementedError`` in the profile pass.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _cabi
+from ..abs import FORMAT, vOp, vTensor
+from ..utils import ReduceType
+from .context import Context
+
+
+class Reduce(vOp):
+    def __init__(self, dim: int = 1):
+        super().__init__()
+        assert dim in (1, 2), f"{type(self).__name__}.__init__: dim must be 1 or 2, got dim={dim}"
+        self.dim = dim
+        self.reduce_type: Optional[ReduceType] = None
+        self.impl = None
+        self.output_format: Optional[FORMAT] = None
+        self.output_buffer: Optional[torch.Tensor] = None
+
+    def profile(self, x: vTensor, output: Optional[vTensor], loc: torch.Tensor, ctx: Context) -> vTensor:
+        p = self._prefix()
+        assert isinstance(x, vTensor), f"{p}x must be vTensor, got {type(x)}"
+        assert isinstance(loc, torch.Tensor), f"{p}loc must be torch.Tensor, got {type(loc)}"
+        assert x.dim() == 3, f"{p}x must be 3D, got ndim={x.dim()} shape={tuple(x.shape)}"
+        if output is None:
+            raise NotImplementedError(f"{p}RAGGED-output reductions have no sm_100a kernel in this build")
+        assert isinstance(output, vTensor), f"{p}output must be vTensor, got {type(output)}"
+        assert output.dim() == 3, f"{p}output must be 3D, got ndim={output.dim()} shape={tuple(output.shape)}"
+        if (x._format, output._format) != (FORMAT.PAGED, FORMAT.PAGED) or self.dim != 1 \
+                or self.reduce_type != ReduceType.Mean:
+            raise NotImplementedError(
+                f"{p}only Mean(dim=1) PAGED->PAGED has an sm_100a kernel; got {self.reduce_type}, dim={self.dim}, "
+                f"({x._format}, {output._format})")
+        assert output.shape[1] == 1, f"{p}profile(dim=1): expected output.shape[1] == 1, got {tuple(output.shape)}"
+        assert output.shape[2] == x.shape[2], (
+            f"{p}profile(dim=1): expected output.shape[2] == x.shape[2], got {output.shape[2]} vs {x.shape[2]}")
+        assert x.device == output.device, (
+            f"{p}x and output must be on the same device (x.device={x.device}, output.device={output.device})")
+        self.impl = _cabi.cmean
+        self.output_format = FORMAT.PAGED
+        return output
+
+    def execute(self, x: torch.Tensor, output: Optional[torch.Tensor], loc: torch.Tensor,
+                ctx: Context) -> torch.Tensor:
+        assert self.impl is not None, f"{self._prefix()}called before profile() (impl is None)"
+        self.impl(x, output, loc, ctx.head_num, ctx.page_size)
+        return output
+
+
+class Mean(Reduce):
+    def __init__(self, dim: int = 1):
+        super().__init__(dim)
+        self.reduce_type = ReduceType.Mean

@@ -1,0 +1,26 @@
+"""Indexer-side operators: score pages against the query and pick the sparse page set.
+
+Export list of the reference's ``indexer/__init__.py:49-71``.  Built on sm_100a: ``GeMV``,
+``topK``, ``Context``/``get_ctx`` and ``utils_sglang``; the other names are placeholders that
+raise ``NotImplementedError`` when used.
+"""
+from ._unbuilt import unbuilt as _unbuilt
+from .context import Context, get_ctx
+from .matmul import GeMV
+from .output_func import topK
+from . import utils_sglang
+
+_W = "indexer"
+GeMM = _unbuilt("GeMM", _W)
+Max, Mean, Min, L2Norm, Sum = (_unbuilt(n, _W) for n in ("Max", "Mean", "Min", "L2Norm", "Sum"))
+Softmax, Normalize = _unbuilt("Softmax", _W), _unbuilt("Normalize", _W)
+Transpose = _unbuilt("Transpose", _W)
+Maximum, Minimum, Multiply, Add = (_unbuilt(n, _W) for n in ("Maximum", "Minimum", "Multiply", "Add"))
+Relu, Sigmoid, Silu, Add_Mul, Abs = (_unbuilt(n, _W) for n in ("Relu", "Sigmoid", "Silu", "Add_Mul", "Abs"))
+Save, Load = _unbuilt("Save", _W), _unbuilt("Load", _W)
+
+__all__ = [
+    "GeMM", "GeMV", "topK", "Max", "Mean", "Min", "L2Norm", "Sum", "Softmax", "Normalize", "Transpose",
+    "Maximum", "Minimum", "Multiply", "Add", "Relu", "Sigmoid", "Silu", "Add_Mul", "Abs", "Save", "Load",
+    "utils_sglang", "Context", "get_ctx",
+]

@@ -1,0 +1,92 @@
+"""Indexer context: the per-step page lists and the static sizes every indexer operator reads.
+
+Field names and the ``create(parent, model_runner)`` contract are those of the reference's
+``indexer/context.py:8-170``.  ``parent`` is the attention backend (it owns the index buffers);
+``model_runner.server_args`` carries the ``vortex_*`` flags.
+"""
+from __future__ import annotations
+
+from typing import Any, Final
+
+import torch
+
+from ..abs import ContextBase
+
+
+class Context(ContextBase):
+    __slots__ = ContextBase.__slots__ + (
+        # page lists (int32 device tensors) and the active batch size
+        "dense_kv_indices", "sparse_kv_indices", "dense_kv_indptr", "sparse_kv_indptr", "kv_last_page_len",
+        "batch_size",
+        # workload list for chunk-scheduled operators
+        "winfo_q_indices", "winfo_kv_offsets", "winfo_kv_lens", "winfo_num_workloads", "winfo_chunk_size",
+        "max_num_workloads", "max_chunk_size", "min_chunk_size",
+        # attention shape
+        "group_size", "num_kv_heads", "num_qo_heads", "head_dim",
+        # device / paging
+        "num_sms", "page_size", "max_num_pages", "max_num_pages_per_request",
+        # selection parameters
+        "indexer_dtype", "topk_val", "page_reserved_bos", "page_reserved_eos",
+        # profile-pass counters
+        "_aux_total_bytes", "_aux_total_flops",
+    )
+
+    def __init__(self) -> None:
+        self._reset_slots("Indexer", {"batch_size": 0})
+
+    def set_batch_size(self, n: int) -> None:
+        self.batch_size = n
+
+    def create(self, parent: Any, model_runner: Any, *, overwrite: bool = False) -> "Context":
+        """Fill the context once (single caller thread; pass ``overwrite=True`` to redo it)."""
+        if self._created and not overwrite:
+            raise RuntimeError("Context.create() already called; pass overwrite=True to reinitialize.")
+        sa = model_runner.server_args
+        P = sa.page_size
+        longest = model_runner.model_config.context_len if sa.vortex_max_seq_lens < 0 else sa.vortex_max_seq_lens
+        pages_per_req = (longest + P - 1) // P
+        max_bs = int(model_runner.req_to_token_pool.size)
+
+        self.dense_kv_indices, self.sparse_kv_indices = parent.kv_indices_decode[0], parent.kv_indices_decode[1]
+        self.dense_kv_indptr, self.sparse_kv_indptr = parent.kv_indptr_decode[0], parent.kv_indptr_decode[1]
+        self.kv_last_page_len = parent.kv_last_page_len_decode
+
+        self.max_chunk_size = sa.vortex_lb_max_chunk_size
+        self.min_chunk_size = sa.vortex_lb_min_chunk_size
+        self.group_size = parent.group_size
+        self.num_kv_heads = parent.num_kv_heads
+        self.num_qo_heads = parent.num_qo_heads
+        self.head_dim = parent.head_dim
+
+        device = getattr(model_runner, "device", "cpu")
+        dev = torch.device(device)
+        self.num_sms = (torch.cuda.get_device_properties(dev).multi_processor_count
+                        if dev.type == "cuda" and torch.cuda.is_available() else 0)
+        self.page_size = P
+        self.max_num_pages_per_request = pages_per_req
+        self.max_num_pages = pages_per_req * max_bs * self.num_kv_heads
+
+        self.topk_val = sa.vortex_topk_val
+        dt = getattr(sa, "vortex_indexer_dtype", "float32")
+        self.indexer_dtype = getattr(torch, dt, torch.float32) if isinstance(dt, str) else dt
+        self.page_reserved_bos = sa.vortex_page_reserved_bos
+        self.page_reserved_eos = sa.vortex_page_reserved_eos
+
+        self.max_num_workloads = self.max_num_pages // max(1, sa.vortex_lb_min_chunk_size) + max_bs * self.num_kv_heads
+        for slot in ("winfo_q_indices", "winfo_kv_offsets", "winfo_kv_lens"):
+            setattr(self, slot, torch.zeros((self.max_num_workloads,), dtype=torch.int32, device=device))
+        self.winfo_num_workloads = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.winfo_chunk_size = torch.zeros((1,), dtype=torch.int32, device=device)
+        self._created = True
+        return self
+
+
+# Process-wide instance used by the serving hook (one attention backend per process).
+ctx: Final[Context] = Context()
+
+
+def get_ctx() -> Context:
+    return ctx
+
+
+__all__ = ["Context", "ctx", "get_ctx"]

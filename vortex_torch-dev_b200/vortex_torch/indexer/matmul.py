@@ -1,0 +1,73 @@
+"""``GeMV``: centroid scores for every candidate page (reference op: ``indexer/matmul.py:10-189``).
+
+``GeMV()(x, y, ctx=ctx)`` with ``x`` BATCHED ``[S, 1, D]`` and ``y`` PAGED ``[num_pages*H, 1, D]``
+returns a RAGGED ``[ctx.max_num_pages, 1, 1]`` buffer holding, at each candidate's packed dense
+position, the dot product of the segment's query vector with that page's row of ``y``.
+
+When the profile pass shows that the scores feed nothing but a ``topK`` the launch is deferred
+and the ``topK`` runs the fused sm_100a indexer kernel instead (same bits, no score round trip
+through HBM).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _cabi
+from ..abs import FORMAT, as_vtensor, vOp, vTensor
+from ..abs.tensor import lazy_group_mean_source, materialize
+from .context import Context
+
+
+class GeMV(vOp):
+    _supported = {(FORMAT.BATCHED, FORMAT.PAGED): FORMAT.RAGGED}
+
+    def __init__(self):
+        super().__init__()
+        self.impl = None
+        self.output_format: Optional[FORMAT] = None
+        self.output_buffer: Optional[torch.Tensor] = None
+        # fusion bookkeeping (see output_func.topK.profile)
+        self._x_is_group_mean = False
+        self._score_read_elsewhere = False
+        self._fused_consumer = None
+        self._pending = None
+
+    def profile(self, x: vTensor, y: vTensor, ctx: Context) -> vTensor:
+        p = self._prefix()
+        assert isinstance(x, vTensor), f"{p}profile expects x to be vTensor, got {type(x)}"
+        assert isinstance(y, vTensor), f"{p}profile expects y to be vTensor, got {type(y)}"
+        assert x.dim() == 3 and y.dim() == 3, f"{p}expected 3D inputs; got x.ndim={x.dim()}, y.ndim={y.dim()}"
+        assert x.shape[1] == 1, f"{p}expected x.shape[1] == 1, got {tuple(x.shape)}"
+        assert y.shape[1] == 1, f"{p}expected y.shape[1] == 1, got {tuple(y.shape)}"
+        assert x.shape[2] == y.shape[2], (
+            f"{p}last dimension mismatch: x.shape[2]={x.shape[2]} vs y.shape[2]={y.shape[2]}")
+        key = (x._format, y._format)
+        assert key in self._supported, (
+            f"{p}no implementation for (x_fmt={x._format}, y_fmt={y._format}). "
+            f"Available: {list(self._supported)}")
+        self.impl = _cabi.gemv
+        self.output_format = self._supported[key]
+        self.output_buffer = torch.empty((ctx.max_num_pages, 1, 1), device=x.device, dtype=x.dtype)
+        ctx.add_aux_memory(self.output_buffer)
+        ctx.add_aux_flops(y.shape[1] * y.shape[2])  # one multiply-add row per page of the PAGED operand
+        self._x_is_group_mean = getattr(x, "_vtx_origin", None) == "group_mean"
+        out = as_vtensor(self.output_buffer, self.output_format)
+        out._vtx_producer = self
+        return out
+
+    def execute(self, x: torch.Tensor, y: torch.Tensor, ctx: Context) -> torch.Tensor:
+        p = self._prefix()
+        assert self.impl is not None, f"{p}execute called before profile() (impl is None)"
+        assert x.device == y.device == self.output_buffer.device, (
+            f"{p}device mismatch: x={x.device}, y={y.device}, o={self.output_buffer.device}")
+        if self._fused_consumer is not None and not self._score_read_elsewhere:
+            src = lazy_group_mean_source(x)
+            self._pending = (src if src is not None else x, y)
+            return self.output_buffer
+        x = materialize(x)
+        eff_bs = ctx.batch_size * ctx.num_kv_heads
+        self.impl(x, y, self.output_buffer, ctx.dense_kv_indptr, ctx.dense_kv_indices, eff_bs, ctx.topk_val,
+                  ctx.page_reserved_bos, ctx.page_reserved_eos)
+        return self.output_buffer

@@ -1,0 +1,58 @@
+"""``topK``: complete each segment's sparse page list with its best-scoring pages
+(reference op: ``indexer/output_func.py:8-235`` over ``csrc/topk.cu:117-203``).
+
+``topK()(x, o, ctx=ctx)``: ``x`` RAGGED ``[S_pack, 1, 1]`` scores at packed dense positions,
+``o`` the packed sparse list (``ctx.sparse_kv_indices``).  For every segment with more than
+``topk_val`` candidates the ``topk_val`` best rows (score descending, ties by position) are
+written behind the reserved BOS pages.  Returns ``o``.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _cabi
+from ..abs import FORMAT, vOp, vTensor
+from .context import Context
+
+
+class topK(vOp):
+    _supported = (FORMAT.RAGGED,)
+
+    def __init__(self):
+        super().__init__()
+        self.impl = None
+        self._fused_producer = None
+
+    def profile(self, x: vTensor, o: vTensor, ctx: Context) -> None:
+        p = self._prefix()
+        assert isinstance(x, vTensor), f"{p}profile expects x to be vTensor, got {type(x)}"
+        assert isinstance(o, vTensor), f"{p}profile expects o to be vTensor, got {type(o)}"
+        assert x.dim() == 3, f"{p}expected x to be 3D, got ndim={x.dim()} shape={tuple(x.shape)}"
+        assert o.dim() == 3, f"{p}expected o to be 3D, got ndim={o.dim()} shape={tuple(o.shape)}"
+        assert x.shape[1] == 1 and x.shape[2] == 1, (
+            f"{p}expected x.shape[1] == x.shape[2] == 1, got {tuple(x.shape)}")
+        assert x._format in self._supported, (
+            f"{p}no implementation for x._format={x._format}. Available: {list(self._supported)}")
+        assert x.device == o.device, (
+            f"{p}x and o must be on the same device (x.device={x.device}, o.device={o.device})")
+        self.impl = _cabi.topk
+        # Fuse with the producing GeMV when its scores are read by this operator only.
+        producer = getattr(x, "_vtx_producer", None)
+        if producer is not None and getattr(producer, "_fused_consumer", None) is None:
+            producer._fused_consumer = self
+            self._fused_producer = producer
+
+    def execute(self, x: torch.Tensor, o: torch.Tensor, ctx: Context) -> torch.Tensor:
+        assert self.impl is not None, f"{self._prefix()}execute called before profile() (impl is None)"
+        eff_bs = ctx.batch_size * ctx.num_kv_heads
+        prod = self._fused_producer
+        if prod is not None and prod._pending is not None and x.data_ptr() == prod.output_buffer.data_ptr():
+            q, y = prod._pending
+            prod._pending = None
+            _cabi.indexer_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
+                                o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
+                                ctx.max_num_pages_per_request)
+            return o
+        self.impl(x, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o, eff_bs, ctx.topk_val,
+                  ctx.page_reserved_bos, ctx.page_reserved_eos, ctx.max_num_pages_per_request)
+        return o
