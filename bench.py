@@ -1,0 +1,411 @@
+"""Benchmark of the sparse-decode hot path.
+
+Workload (one "step"): a Qwen3-1.7B-shaped decode step — 28 attention layers, 16 query heads,
+8 KV heads, head_dim 128, bf16 KV, batch 64, every request at 8192 tokens, page_size 16,
+top-k 30 + 1 BOS + 1 EOS page, layer 0 dense and layers 1-27 sparse.  Per step: block-table
+build, then per layer KV write, centroid maintenance (the new token closes a page), fused
+indexer and paged decode attention.  Data are seeded synthetic N(0,1) values; each layer has its
+own 2.1 GB K/V pool in seeded random physical page order, so a step touches far more than L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank runs the same
+workload on its own shard of requests (weak scaling, no hot-path communication); NCCL is used
+for the barrier, the max-over-ranks time and to gather verification verdicts.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT), str(ROOT / "vortex_torch-dev_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np
+import torch
+
+METRIC = "sparse-decode steps/s (Qwen3-1.7B-shape, bs64 per GPU, 8k ctx)"
+CFG = dict(layers=28, Hq=16, Hkv=8, D=128, bs=64, ctx=8192, P=16, K=30, bos=1, eos=1, skip=[0])
+
+
+def algorithmic_bytes(cfg):
+    """Centroid rows scanned + K/V bytes of the attended pages (q, outputs, index lists excluded)."""
+    S = cfg["bs"] * cfg["Hkv"]
+    pages = cfg["ctx"] // cfg["P"]
+    row = cfg["D"] * 2
+    page_kv = 2 * cfg["P"] * cfg["D"] * 2
+    budget = cfg["K"] + cfg["bos"] + cfg["eos"]
+    cent = S * (pages - cfg["bos"] - cfg["eos"]) * row
+    sparse_kv = S * budget * page_kv
+    dense_kv = S * pages * page_kv
+    n_sparse = cfg["layers"] - len(cfg["skip"])
+    return dict(centroids_per_layer=cent, sparse_kv_per_layer=sparse_kv, dense_kv_per_layer=dense_kv,
+                step=n_sparse * (cent + sparse_kv) + len(cfg["skip"]) * dense_kv)
+
+
+def measured_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return json.loads(f.read_text()), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU baseline (oracle port)
+def cpu_baseline(cfg, sample_requests: int = 2, repeats: int = 1):
+    """Time the CPU port of the path on a bounded sample and scale it to one full step.
+
+    Sample: ``sample_requests`` requests of the workload (all 8 KV heads each); one dense layer and
+    one sparse layer (plan + indexer + decode) are timed and scaled by batch and layer counts.
+    """
+    from oracle import vortex_oracle as vo
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    P, H, G, D, K = cfg["P"], cfg["Hkv"], cfg["Hq"] // cfg["Hkv"], cfg["D"], cfg["K"]
+    seq = [cfg["ctx"]] * sample_requests
+    prob = vo.make_paged_problem(0, seq, H, G, D, P)
+    best_sparse, best_dense = float("inf"), float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, cfg["bos"],
+                              cfg["eos"], 64, 16)
+        t_plan = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        vo.forward_indexer(prob["q"], prob["centroids"], plan, K, cfg["bos"], cfg["eos"])
+        vo.decode_gqa(prob["q"], prob["k"], prob["v"], plan["sparse_kv_indptr"], plan["sparse_kv_indices"],
+                      plan["kv_last_page_len"])
+        best_sparse = min(best_sparse, time.perf_counter() - t0)
+        t0 = time.perf_counter()
+        vo.decode_gqa(prob["q"], prob["k"], prob["v"], plan["dense_kv_indptr"], plan["dense_kv_indices"],
+                      plan["kv_last_page_len"])
+        best_dense = min(best_dense, time.perf_counter() - t0)
+    scale = cfg["bs"] / sample_requests
+    n_sparse = cfg["layers"] - len(cfg["skip"])
+    step_s = scale * (t_plan + n_sparse * best_sparse + len(cfg["skip"]) * best_dense)
+    return dict(value=1.0 / step_s, unit="steps/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"{sample_requests} of {cfg['bs']} requests x (plan + 1 sparse layer + 1 dense layer), "
+                       f"scaled by batch and by {n_sparse} sparse + {len(cfg['skip'])} dense layers",
+                sparse_layer_s=best_sparse, dense_layer_s=best_dense)
+
+
+def run_reference_arm(args, cfg):
+    """The reference has no CPU (or Blackwell) implementation of this path; its arithmetic restated in
+    PyTorch eager on the host cores is what gets timed here."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    vals = []
+    for _ in range(args.warmup):
+        cpu_baseline(cfg, sample_requests=1)
+    cb = None
+    for _ in range(max(1, args.steps)):
+        cb = cpu_baseline(cfg, sample_requests=1)
+        vals.append(cb["value"])
+    v = float(np.median(vals))
+    cb["value"] = v
+    line = dict(metric=METRIC, value=v, unit="steps/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=1000.0 / v, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                data="synthetic", impl="reference", config=workload_config(cfg, args.gpus), cpu_baseline=cb,
+                e2e=dict(value=v, unit="steps/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+def workload_config(cfg, n):
+    return dict(workload="Qwen3-1.7B-shaped decode step: 28 layers (layer 0 dense, 1-27 sparse), 16 q heads, "
+                         "8 KV heads, head_dim 128, bf16, batch 64 per GPU at 8192 tokens, page_size 16, "
+                         "topk 30 + 1 BOS + 1 EOS",
+                global_batch=cfg["bs"] * n, sharding=f"requests x{n}, no hot-path collective",
+                l2="per-layer pools (2.1 GB K/V each, 60 GB per step working set) exceed L2; no flush needed",
+                flow="block_sparse_attention")
+
+
+# --------------------------------------------------------------------------- GPU arm
+def build_runtime(cfg, device, seed):
+    from vortex_torch import _cabi
+    from vortex_torch.runtime import GraphedDecodeStep, ServerArgs, VortexDecodeRuntime
+
+    P, H, bs = cfg["P"], cfg["Hkv"], cfg["bs"]
+    pages_per_req = cfg["ctx"] // P
+    num_pages = bs * pages_per_req
+    sa = ServerArgs(page_size=P, vortex_topk_val=cfg["K"], vortex_page_reserved_bos=cfg["bos"],
+                    vortex_page_reserved_eos=cfg["eos"], vortex_layers_skip=list(cfg["skip"]),
+                    vortex_max_seq_lens=cfg["ctx"])
+    rt = VortexDecodeRuntime(cfg["layers"], cfg["Hq"], H, cfg["D"], num_pages=num_pages, max_bs=bs,
+                             context_len=cfg["ctx"], server_args=sa, dtype=torch.bfloat16, device=device)
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(num_pages, generator=g)
+    slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1)
+    rt.model_runner.req_to_token_pool.req_to_token.copy_(slots.to(torch.int32))
+    torch.manual_seed(seed)
+    closing = (torch.arange(num_pages, device=device, dtype=torch.int64) * P + (P - 1))
+    for l in range(cfg["layers"]):
+        buf = rt.pool.buffers[l]
+        buf["k"].normal_()
+        buf["v"].normal_()
+        _cabi.cmean(buf["k"], buf["centroids"], closing, H, P)
+    step = GraphedDecodeStep(rt, bs)
+    step.seq_lens.fill_(cfg["ctx"])
+    step.req_indices.copy_(torch.arange(bs))
+    step.loc.copy_(slots[:, cfg["ctx"] - 1].to(torch.int64))
+    step.q.normal_()
+    step.new_k.normal_()
+    step.new_v.normal_()
+    torch.cuda.synchronize(device)
+    return rt, step, slots
+
+
+def verify_sample(rt, step, cfg, slots):
+    """Check request 0 of the last sparse layer and of the dense layer against the CPU oracle."""
+    from oracle import vortex_oracle as vo
+
+    P, H, G, D, K = cfg["P"], cfg["Hkv"], cfg["Hq"] // cfg["Hkv"], cfg["D"], cfg["K"]
+    pages = cfg["ctx"] // P
+    seq = np.asarray([cfg["ctx"]], dtype=np.int32)
+    r2t = slots[:1].numpy().astype(np.int32)
+    plan = vo.plan_decode(seq, r2t, np.zeros(1, dtype=np.int64), P, H, K, cfg["bos"], cfg["eos"], 64, 16)
+    rows = torch.as_tensor(plan["dense_kv_indices"], dtype=torch.long)
+    ok = True
+    for layer in (cfg["layers"] - 1, cfg["skip"][0] if cfg["skip"] else None):
+        if layer is None:
+            continue
+        buf = rt.pool.buffers[layer]
+        # compact copy of request 0's rows so the CPU side stays small
+        remap = {int(r): i for i, r in enumerate(rows.tolist())}
+        k = buf["k"][rows.to(rt.device)].cpu()
+        v = buf["v"][rows.to(rt.device)].cpu()
+        c = buf["centroids"][rows.to(rt.device)].cpu()
+        p2 = {kk: vv.copy() for kk, vv in plan.items()}
+        p2["dense_kv_indices"] = np.arange(len(rows), dtype=np.int32)
+        for s in range(H):
+            a, b = int(p2["sparse_kv_indptr"][s]), int(p2["sparse_kv_indptr"][s + 1])
+            p2["sparse_kv_indices"][a:b] = [remap.get(int(x), -1) for x in plan["sparse_kv_indices"][a:b]]
+        q = step.q[layer, 0].view(H, G, D).cpu()
+        got = step.out[layer, 0].view(H, G, D).float().cpu()
+        if layer in cfg["skip"]:
+            want = vo.decode_gqa(q, k, v, p2["dense_kv_indptr"], p2["dense_kv_indices"], p2["kv_last_page_len"])
+        else:
+            vo.forward_indexer(q, c, p2, K, cfg["bos"], cfg["eos"])
+            ns = int(p2["sparse_kv_indptr"][H])
+            if layer == cfg["layers"] - 1:  # the index buffers hold the last layer's selection
+                dev_sel = rt.backend.kv_indices_decode[1][:ns].cpu().numpy()
+                want_sel = rows.numpy()[p2["sparse_kv_indices"][:ns]]
+                ok = ok and bool(np.array_equal(dev_sel, want_sel))
+            want = vo.decode_gqa(q, k, v, p2["sparse_kv_indptr"], p2["sparse_kv_indices"], p2["kv_last_page_len"])
+        ok = ok and bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
+    return ok
+
+
+def time_kernels(rt, step, cfg, reps):
+    """CUDA-event duration of the indexer and decode launches, measured launch by launch (eager)."""
+    from vortex_torch import _cabi
+
+    dev = rt.device
+    b = rt.backend
+    eff_bs = cfg["bs"] * cfg["Hkv"]
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    t = dict(indexer=[], decode_sparse=[], decode_dense=[])
+    for _ in range(reps):
+        for l in range(cfg["layers"]):
+            cache = rt.pool.buffers[l]
+            qv = step.q[l].view(-1, rt.G, rt.D)
+            ov = step.out[l].view(-1, rt.G, rt.D)
+            if l in rt.skip:
+                e0, e1 = ev(), ev()
+                e0.record()
+                rt.attention(qv, l, ov, sparse=False)
+                e1.record()
+                t["decode_dense"].append((e0, e1))
+                continue
+            e0, e1, e2 = ev(), ev(), ev()
+            e0.record()
+            _cabi.indexer_fused(qv, cache["centroids"], b.kv_indptr_decode[0], b.kv_indptr_decode[1],
+                                b.kv_indices_decode[0], b.kv_indices_decode[1], eff_bs, cfg["K"], cfg["bos"],
+                                cfg["eos"], rt.ictx.max_num_pages_per_request)
+            e1.record()
+            rt.attention(qv, l, ov, sparse=True)
+            e2.record()
+            t["indexer"].append((e0, e1))
+            t["decode_sparse"].append((e1, e2))
+    torch.cuda.synchronize(dev)
+    return {k: (float(np.mean([a.elapsed_time(b_) for a, b_ in v])) * 1e-3 if v else None) for k, v in t.items()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (number is invalid as a bench)")
+    ap.add_argument("--batch", type=int, default=None, help="debug: smaller batch")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(CFG)
+    if args.layers:
+        cfg["layers"] = args.layers
+    if args.batch:
+        cfg["bs"] = args.batch
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+
+    rt, step, slots = build_runtime(cfg, device, seed=1234 + rank)
+    if not args.no_graph:
+        step.capture()
+    W = max(3, args.warmup)
+    for _ in range(W):
+        step.replay()
+    torch.cuda.synchronize(device)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---- device-resident timing
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step.replay()
+    e1.record()
+    barrier()
+    dev_s = e0.elapsed_time(e1) * 1e-3
+    # ---- end to end from pinned host buffers
+    h = step.host_buffers()
+    for n in ("seq_lens", "req_indices", "loc", "q", "new_k", "new_v"):
+        h[n].copy_(getattr(step, n).cpu())
+    for _ in range(3):
+        step.run_from_host()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step.run_from_host()
+    torch.cuda.synchronize(device)
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    if dist is not None:
+        tt = torch.tensor([dev_s, e2e_s], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dev_s, e2e_s = float(tt[0]), float(tt[1])
+
+    ok = verify_sample(rt, step, cfg, slots)
+    if dist is not None:
+        flags = [torch.zeros(1, device=device, dtype=torch.int32) for _ in range(world)]
+        dist.all_gather(flags, torch.tensor([int(ok)], device=device, dtype=torch.int32))
+        ok = all(int(f.item()) == 1 for f in flags)
+
+    kt = time_kernels(rt, step, cfg, reps=3)
+    peaks, peak_kind = measured_peaks()
+    ab = algorithmic_bytes(cfg)
+    peak = float(peaks["hbm_gbs"])
+
+    def roof(bytes_, secs):
+        if not secs:
+            return None
+        a = bytes_ / secs / 1e9
+        return dict(bound="hbm", achieved=a, peak=peak, unit="GB/s", frac=a / peak, peak_kind=f"of {peak_kind}")
+
+    if rank == 0:
+        n_sparse = cfg["layers"] - len(cfg["skip"])
+        launches_per_step = 1 + 2 * cfg["layers"] + 2 * n_sparse + len(cfg["skip"])
+        value = world * args.steps / dev_s
+        line = dict(
+            metric=METRIC, value=value, unit="steps/s", n_gpus=world, steps=args.steps, warmup=W,
+            ms_per_step=1000.0 * dev_s / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
+            dtype="bf16", data="synthetic", config=workload_config(cfg, world),
+            e2e=dict(value=world * args.steps / e2e_s, unit="steps/s", h2d_bytes_per_step=step.h2d_bytes,
+                     d2h_bytes_per_step=step.d2h_bytes),
+            gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
+            cuda_graph=not args.no_graph,
+            roofline=dict(kernel="decode_gqa_kernel (sparse layers)", traffic=None,
+                          **roof(ab["sparse_kv_per_layer"], kt["decode_sparse"])),
+            kernels=dict(indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),
+                         decode_sparse=roof(ab["sparse_kv_per_layer"], kt["decode_sparse"]),
+                         decode_dense=roof(ab["dense_kv_per_layer"], kt["decode_dense"]),
+                         us=dict((k, v * 1e6 if v else None) for k, v in kt.items())),
+            step_hbm=dict(algorithmic_bytes=ab["step"], achieved_gbs=ab["step"] * args.steps / dev_s / 1e9,
+                          frac_of_measured_peak=ab["step"] * args.steps / dev_s / 1e9 / peak,
+                          frac_of_nominal_8000=ab["step"] * args.steps / dev_s / 1e9 / 8000.0),
+        )
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(cfg)
+        elif not args.no_cpu_baseline:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
