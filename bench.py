@@ -249,38 +249,70 @@ def verify_sample(rt, step, cfg, slots):
 
 
 def time_kernels(rt, step, cfg, reps):
-    """CUDA-event duration of the indexer and decode launches, measured launch by launch (eager)."""
+    """Average device time per launch of each kernel kind, from CUDA events around graph replays.
+
+    For each kind (fused indexer, sparse decode, dense decode, KV write + centroid update) one CUDA
+    graph holds that kernel's launches of every layer of a step, back to back on each layer's own
+    pool; the graph is replayed ``reps`` times between two events on the launching stream.
+    """
     from vortex_torch import _cabi
+    from vortex_torch.cache import set_kv_buffer_launcher
 
     dev = rt.device
     b = rt.backend
     eff_bs = cfg["bs"] * cfg["Hkv"]
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    t = dict(indexer=[], decode_sparse=[], decode_dense=[])
-    for _ in range(reps):
-        for l in range(cfg["layers"]):
-            cache = rt.pool.buffers[l]
-            qv = step.q[l].view(-1, rt.G, rt.D)
-            ov = step.out[l].view(-1, rt.G, rt.D)
-            if l in rt.skip:
-                e0, e1 = ev(), ev()
-                e0.record()
-                rt.attention(qv, l, ov, sparse=False)
-                e1.record()
-                t["decode_dense"].append((e0, e1))
-                continue
-            e0, e1, e2 = ev(), ev(), ev()
-            e0.record()
+    sparse_layers = [l for l in range(cfg["layers"]) if l not in rt.skip]
+    dense_layers = [l for l in range(cfg["layers"]) if l in rt.skip]
+
+    def views(l):
+        return step.q[l].view(-1, rt.G, rt.D), step.out[l].view(-1, rt.G, rt.D), rt.pool.buffers[l]
+
+    def run_indexer():
+        for l in sparse_layers:
+            qv, _, cache = views(l)
             _cabi.indexer_fused(qv, cache["centroids"], b.kv_indptr_decode[0], b.kv_indptr_decode[1],
                                 b.kv_indices_decode[0], b.kv_indices_decode[1], eff_bs, cfg["K"], cfg["bos"],
                                 cfg["eos"], rt.ictx.max_num_pages_per_request)
-            e1.record()
-            rt.attention(qv, l, ov, sparse=True)
-            e2.record()
-            t["indexer"].append((e0, e1))
-            t["decode_sparse"].append((e1, e2))
-    torch.cuda.synchronize(dev)
-    return {k: (float(np.mean([a.elapsed_time(b_) for a, b_ in v])) * 1e-3 if v else None) for k, v in t.items()}
+
+    def run_decode(layers, sparse):
+        for l in layers:
+            qv, ov, _ = views(l)
+            rt.attention(qv, l, ov, sparse=sparse)
+
+    def run_cache():
+        for l in range(cfg["layers"]):
+            cache = rt.pool.buffers[l]
+            set_kv_buffer_launcher(cache["k"], cache["v"], step.new_k[l], step.new_v[l], step.loc, rt.P)
+            _cabi.cmean(cache["k"], cache["centroids"], step.loc, rt.H, rt.P)
+
+    kinds = dict(indexer=(run_indexer, len(sparse_layers)),
+                 decode_sparse=(lambda: run_decode(sparse_layers, True), len(sparse_layers)),
+                 decode_dense=(lambda: run_decode(dense_layers, False), len(dense_layers)),
+                 kv_write_cmean=(run_cache, 2 * cfg["layers"]))
+    out = {}
+    for name, (fn, n) in kinds.items():
+        if n == 0:
+            out[name] = None
+            continue
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        g.replay()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        out[name] = e0.elapsed_time(e1) * 1e-3 / (reps * n)
+    return out
 
 
 def main():
@@ -364,7 +396,7 @@ def main():
         dist.all_gather(flags, torch.tensor([int(ok)], device=device, dtype=torch.int32))
         ok = all(int(f.item()) == 1 for f in flags)
 
-    kt = time_kernels(rt, step, cfg, reps=3)
+    kt = time_kernels(rt, step, cfg, reps=5)
     peaks, peak_kind = measured_peaks()
     ab = algorithmic_bytes(cfg)
     peak = float(peaks["hbm_gbs"])

@@ -51,6 +51,7 @@ def test_runtime_step_matches_oracle(dtype, seq):
         ks.append(k); vs.append(v); cents.append(cent)
         qs.append(torch.randn(bs, H * G, D, generator=g).to(dtype)); nks.append(nk); nvs.append(nv)
     outs = [torch.empty(bs, H * G, D, dtype=dtype, device="cuda") for _ in range(L)]
+    rt.flow.gemv.output_buffer.fill_(-7.0)
     rt.step(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(),
             [q.cuda() for q in qs], [x.cuda() for x in nks], [x.cuda() for x in nvs], loc.cuda(), outs)
     torch.cuda.synchronize()
@@ -74,7 +75,8 @@ def test_runtime_step_matches_oracle(dtype, seq):
         got = outs[l].view(bs * H, G, D).cpu().float()
         assert bool(((got - want.float()).abs() <= tol * want.float().abs().clamp(min=1)).all())
     # the fused indexer path was taken: the GeMV never wrote its score buffer
-    assert rt.flow.gemv._fused_consumer is rt.flow.output_func
+    assert rt.flow.gemv._fused_consumer is rt.flow.output_func and not rt.flow.gemv._score_read_elsewhere
+    assert bool((rt.flow.gemv.output_buffer == -7.0).all())
 
 
 def test_user_flow_file_runs_unfused_when_scores_are_read(tmp_path):

@@ -96,6 +96,16 @@ def test_lazy_group_mean_is_invisible():
     assert lazy_group_mean_source(lazy) is q and lazy.shape == real.shape
     assert torch.equal(torch.Tensor(lazy * 1.0), torch.Tensor(real))           # any torch op sees the real mean
     assert torch.equal(torch.Tensor(materialize(lazy)), torch.Tensor(real))
+    calls = []
+    import vortex_torch.abs.tensor as vt
+    orig = vt.materialize
+    vt.materialize = lambda x: (calls.append(1), orig(x))[1]
+    try:  # shape / placement queries must not compute the mean
+        assert lazy.dim() == 3 and lazy.shape[1] == 1 and lazy.device == q.device and lazy.dtype == q.dtype
+        lazy.data_ptr(), lazy.size(0), lazy.is_contiguous()
+        assert calls == []
+    finally:
+        vt.materialize = orig
     assert lazy_group_mean_source(q.mean(dim=2, keepdim=True)) is None           # other reductions are untouched
     assert lazy_group_mean_source(q.mean(dim=1)) is None
 
@@ -110,6 +120,7 @@ def test_profile_pass_allocates_and_detects_fusion():
     assert rt.flow.gemv.output_buffer.shape == (32 * 3 * 8, 1, 1)
     assert rt.ictx._aux_total_bytes == 32 * 3 * 8 * 2 and rt.ictx._aux_total_flops == 128
     assert rt.flow.gemv._fused_consumer is rt.flow.output_func and rt.flow.gemv._x_is_group_mean
+    assert not rt.flow.gemv._score_read_elsewhere  # shape checks in the profile pass do not count as reads
     assert rt.ictx.missing() == [] and rt.cctx.missing() == []
     with pytest.raises(RuntimeError, match="already called"):
         rt.ictx.create(rt.backend, rt.model_runner)

@@ -1,10 +1,16 @@
 // Paged grouped-query decode attention over each segment's page list.
 //
 // One CTA (4 warps) per (request, head) segment; warps take the listed pages round-robin.
-// A (page, head) block of K or V is one contiguous run of page_size * D elements, so a warp
-// reads it with 16-byte loads, LPT lanes per token row (each lane owns 8 head dims).  Softmax
-// is the online (running max / running sum) form in fp32; partial results of the warps are
-// merged through shared memory.  The last listed page contributes kv_last_page_len tokens.
+// A (page, head) block of K or V is one contiguous run of page_size * D elements.  Every warp
+// runs its own asynchronous pipeline: K and V tiles of up to 16 token rows are copied
+// global -> shared with 16-byte cp.async (no register staging), three ring slots per warp, two
+// tiles in flight while one is consumed; only warp-level synchronisation in the main loop.
+// At the Qwen3 shapes a slot is 4 KB, a CTA holds 48 KB, four CTAs share an SM, so a batch of
+// 64 requests x 8 KV heads is resident in one wave with ~128 KB in flight per SM.
+// LPT lanes cover one token row (each lane owns 8 head dims); softmax is the online
+// (running max / running sum) form in fp32; warps are merged through shared memory at the end.
+// The last listed page contributes kv_last_page_len tokens; rows beyond it are zero-filled in
+// shared memory and masked.
 //
 // Data contract as produced by the block-table builder (reference: csrc/utils_sglang.cu:123-184,
 // indexer/context.py:117-121); in the reference the attention itself is a third-party
@@ -14,6 +20,8 @@
 namespace {
 
 constexpr int kWarps = 4;
+constexpr int kSlots = 3;        // ring slots per warp
+constexpr int kTileTokens = 16;  // token rows per tile
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct DecodeArgs {
@@ -35,14 +43,49 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 template <>
 __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 
-// LPT lanes per token row (D = 8 * LPT); UT token rows in flight per lane.
-template <typename T, int G, int LPT, int UT>
-__global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr, bool valid) {
+    const int src_bytes = valid ? 16 : 0;  // 0 => the 16 bytes are zero-filled, the source is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Eight elements of a shared-memory row widened to fp32.
+template <typename T>
+__device__ __forceinline__ void lds8(const T* p, float (&f)[8]);
+template <>
+__device__ __forceinline__ void lds8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    f[0] = vtx::bf16lo(r.x); f[1] = vtx::bf16hi(r.x);
+    f[2] = vtx::bf16lo(r.y); f[3] = vtx::bf16hi(r.y);
+    f[4] = vtx::bf16lo(r.z); f[5] = vtx::bf16hi(r.z);
+    f[6] = vtx::bf16lo(r.w); f[7] = vtx::bf16hi(r.w);
+}
+template <>
+__device__ __forceinline__ void lds8<float>(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+    f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// LPT lanes per token row (D = 8 * LPT).
+template <typename T, int G, int LPT>
+__global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt_kernel(DecodeArgs a) {
     constexpr int D = LPT * 8;
-    constexpr int TPW = 32 / LPT;  // token rows covered by one warp-wide load
-    __shared__ float sm_acc[kWarps][G][D];
-    __shared__ float sm_m[kWarps][G];
-    __shared__ float sm_l[kWarps][G];
+    constexpr int TPW = 32 / LPT;                 // token rows covered by one warp-wide access
+    constexpr int UT = kTileTokens / TPW;         // row steps per tile
+    constexpr int TILE_ELEMS = kTileTokens * D;
+    constexpr int CHUNKS = TILE_ELEMS * (int)sizeof(T) / 16;  // 16-byte chunks per tile
+    constexpr int CH_PER_ROW = D * (int)sizeof(T) / 16;
+    constexpr int CPL = CHUNKS / 32;              // chunks copied per lane per tile
+    static_assert(CHUNKS % 32 == 0, "tile must split evenly over a warp");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    T* ring = reinterpret_cast<T*>(smem_raw);
 
     const int s = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -50,6 +93,11 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
     const int beg = a.indptr[s];
     const int npages = a.indptr[s + 1] - beg;
     const int last_len = a.last_len[s];
+    const int P = a.P;
+    const int tiles_per_page = (P + kTileTokens - 1) / kTileTokens;
+
+    T* my_ring = ring + (size_t)warp * kSlots * TILE_ELEMS;
+    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
 
     float qf[G][8];
     {
@@ -63,7 +111,6 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
             for (int j = 0; j < 8; ++j) qf[g][j] *= a.scale_log2;
         }
     }
-
     float m[G], l[G], acc[G][8];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -73,33 +120,70 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
         for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
     }
 
+    // This warp's pages: warp, warp + kWarps, ...; items alternate K tile, V tile.
+    const int my_pages = npages > warp ? (npages - warp + kWarps - 1) / kWarps : 0;
+    const int n_items = my_pages * tiles_per_page * 2;
     const T* kc = reinterpret_cast<const T*>(a.k);
     const T* vc = reinterpret_cast<const T*>(a.v);
-    for (int pg = warp; pg < npages; pg += kWarps) {
-        const int64_t row = a.indices[beg + pg];
-        const int nvalid = (pg == npages - 1) ? last_len : a.P;
-        const T* kp = kc + row * a.P * D + sub * 8;
-        const T* vp = vc + row * a.P * D + sub * 8;
-        for (int t0 = 0; t0 < nvalid; t0 += UT * TPW) {
-            vtx::Vec8<T> kr[UT], vr[UT];
+
+    // Row ids of up to 32 of this warp's pages live in one register per lane.
+    int id_base = 0;
+    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kWarps * lane] : 0;
+
+    auto issue = [&](int item) {
+        // item -> (page ordinal, tile, K or V)
+        const int pair = item >> 1;
+        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
+        const int pg = warp + kWarps * po;
+        const int nvalid_page = (pg == npages - 1) ? last_len : P;
+        const int tok0 = tile * kTileTokens;
+        const T* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * D;
+        const uint32_t dst = my_ring_addr + (uint32_t)((item % kSlots) * TILE_ELEMS * sizeof(T));
 #pragma unroll
-            for (int u = 0; u < UT; ++u) {
-                const int t = t0 + u * TPW + tg;
-                if (t < nvalid) kr[u].load(kp + (int64_t)t * D);
-                else kr[u].zero();
-            }
+        for (int c = 0; c < CPL; ++c) {
+            const int ch = c * 32 + lane;
+            const int t = ch / CH_PER_ROW;
+            cp_async16(dst + ch * 16, reinterpret_cast<const unsigned char*>(src) + (size_t)ch * 16,
+                       tok0 + t < nvalid_page);
+        }
+    };
+
+    // prologue: two items in flight
 #pragma unroll
-            for (int u = 0; u < UT; ++u) {
-                const int t = t0 + u * TPW + tg;
-                if (t < nvalid) vr[u].load(vp + (int64_t)t * D);
-                else vr[u].zero();
+    for (int i = 0; i < kSlots - 1; ++i) {
+        if (i < n_items) issue(i);
+        cp_async_commit();
+    }
+
+    float sc[UT][G];
+    for (int item = 0; item < n_items; ++item) {
+        cp_async_wait<kSlots - 2>();  // item `item` has landed (this lane's part)
+        __syncwarp();                 // ... and every lane's part; also: all lanes are done with the slot refilled next
+        {
+            const int nxt = item + kSlots - 1;
+            if (nxt < n_items) {
+                const int po = (nxt >> 1) / tiles_per_page;
+                if (po - id_base >= 32) {  // refill the per-lane page ids (warp-uniform branch)
+                    id_base += 32;
+                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kWarps * (id_base + lane)] : 0;
+                }
+                issue(nxt);
             }
-            float sc[UT][G];
+            cp_async_commit();
+        }
+        const T* tile_ptr = my_ring + (size_t)(item % kSlots) * TILE_ELEMS + sub * 8;
+        const int pair = item >> 1;
+        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int pg = warp + kWarps * po;
+        const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kTileTokens;  // valid rows in this tile
+        if ((item & 1) == 0) {
+            // ---- K tile: scores, running max, probabilities
 #pragma unroll
             for (int u = 0; u < UT; ++u) {
                 float f[8];
-                kr[u].unpack(f);
-                const bool valid = (t0 + u * TPW + tg) < nvalid;
+                lds8<T>(tile_ptr + (u * TPW + tg) * D, f);
+                const bool valid = (u * TPW + tg) < nvalid;
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     float d = 0.f;
@@ -117,7 +201,8 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
                 for (int u = 1; u < UT; ++u) cmax = fmaxf(cmax, sc[u][g]);
 #pragma unroll
                 for (int w = LPT; w < 32; w <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, w));
-                const float mn = fmaxf(m[g], cmax);  // finite: token t0 of this chunk is valid
+                const float mn = fmaxf(m[g], cmax);
+                // a tile always holds at least one valid row, so mn is finite
                 const float alpha = exp2f(m[g] - mn);
                 m[g] = mn;
                 l[g] *= alpha;
@@ -130,10 +215,12 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
                     sc[u][g] = p;
                 }
             }
+        } else {
+            // ---- V tile: weighted accumulation (rows past the valid range are zero-filled, p = 0)
 #pragma unroll
             for (int u = 0; u < UT; ++u) {
                 float f[8];
-                vr[u].unpack(f);
+                lds8<T>(tile_ptr + (u * TPW + tg) * D, f);
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -142,8 +229,12 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
             }
         }
     }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its ring: reuse the space for the merge
 
-    // fold the token groups of the warp (they share m), then merge warps through shared memory
+    float* sm_acc = reinterpret_cast<float*>(smem_raw);           // [kWarps][G][D]
+    float* sm_m = sm_acc + kWarps * G * D;                        // [kWarps][G]
+    float* sm_l = sm_m + kWarps * G;                              // [kWarps][G]
 #pragma unroll
     for (int g = 0; g < G; ++g) {
 #pragma unroll
@@ -154,10 +245,10 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
         }
         if (tg == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) sm_acc[warp][g][sub * 8 + j] = acc[g][j];
+            for (int j = 0; j < 8; ++j) sm_acc[(warp * G + g) * D + sub * 8 + j] = acc[g][j];
             if (sub == 0) {
-                sm_m[warp][g] = m[g];
-                sm_l[warp][g] = l[g];
+                sm_m[warp * G + g] = m[g];
+                sm_l[warp * G + g] = l[g];
             }
         }
     }
@@ -165,38 +256,312 @@ __global__ void __launch_bounds__(kWarps * 32) decode_gqa_kernel(DecodeArgs a) {
     T* out = reinterpret_cast<T*>(a.out) + (int64_t)s * G * D;
     for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
         const int g = idx / D, d = idx % D;
-        float mx = sm_m[0][g];
+        float mx = sm_m[g];
 #pragma unroll
-        for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w][g]);
+        for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w * G + g]);
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
-            const float wm = sm_m[w][g];
+            const float wm = sm_m[w * G + g];
             const float wgt = (wm == -INFINITY) ? 0.f : exp2f(wm - mx);
-            num = fmaf(wgt, sm_acc[w][g][d], num);
-            den = fmaf(wgt, sm_l[w][g], den);
+            num = fmaf(wgt, sm_acc[(w * G + g) * D + d], num);
+            den = fmaf(wgt, sm_l[w * G + g], den);
         }
         store_out<T>(out + idx, den > 0.f ? num / den : 0.f);
     }
 }
 
-template <typename T, int G, int UT>
-int launch_decode_g(const DecodeArgs& a, int eff_bs, int head_dim, cudaStream_t st) {
-    switch (head_dim) {
-        case 64: decode_gqa_kernel<T, G, 8, UT><<<eff_bs, kWarps * 32, 0, st>>>(a); break;
-        case 128: decode_gqa_kernel<T, G, 16, UT><<<eff_bs, kWarps * 32, 0, st>>>(a); break;
-        default: return VTX_ERR_UNSUPPORTED;
+
+// ---------------------------------------------------------------------------------------------
+// bf16 path on the tensor cores (mma.sync m16n8k16, fp32 accumulate).
+//
+// The CUDA-core form above needs ~700 issue slots per 8 KB of K+V, which at one SM's share of HBM
+// bandwidth keeps the schedulers ~70 % busy at 25 % occupancy; the MMA form needs ~150.
+// Per 16-token tile and warp:
+//   S^T[head, token] = q . K^T     A = q (16 rows, rows >= G are zero, held in registers),
+//                                  B = K tile straight from shared memory via ldmatrix
+//   O^T[dim, head]  += V^T . P^T   A = V tile via ldmatrix.trans, B = P^T, which is exactly the
+//                                  accumulator layout of S^T (no data movement between the two)
+// Rows of a tile are 16-byte-chunk swizzled (chunk ^ (row & 7)) so ldmatrix is conflict-free.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// D = head dim (64 or 128); G <= 8 query heads per KV head.
+template <int G, int D>
+__global__ void __launch_bounds__(kWarps * 32, 4) decode_gqa_mma_kernel(DecodeArgs a) {
+    using T = __nv_bfloat16;
+    constexpr int KSTEPS = D / 16;                 // k-steps of QK^T == 16-dim tiles of the output
+    constexpr int ROWB = D * 2;                    // bytes per token row
+    constexpr int CH_PER_ROW = ROWB / 16;
+    constexpr int TILE_BYTES = kTileTokens * ROWB;
+    constexpr int CHUNKS = TILE_BYTES / 16;
+    constexpr int CPL = CHUNKS / 32;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+
+    const int s = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int beg = a.indptr[s];
+    const int npages = a.indptr[s + 1] - beg;
+    const int last_len = a.last_len[s];
+    const int P = a.P;
+    const int tiles_per_page = (P + kTileTokens - 1) / kTileTokens;
+
+    unsigned char* my_ring = smem_raw + (size_t)warp * kSlots * TILE_BYTES;
+    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
+
+    // q as the A operand: row gid (zero for gid >= G), 16 dims per k-step
+    uint32_t qa[KSTEPS][2];
+    {
+        const uint32_t* qs = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(a.q) +
+                                                               ((int64_t)s * G + gid) * D);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qa[ks][0] = gid < G ? qs[ks * 8 + tid] : 0u;
+            qa[ks][1] = gid < G ? qs[ks * 8 + 4 + tid] : 0u;
+        }
     }
+    float o[KSTEPS][4];  // O^T: [16 dims of tile mt] x [8 heads]
+#pragma unroll
+    for (int mt = 0; mt < KSTEPS; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // running max / partial sum of head `gid`
+    float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
+    uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
+
+    const int my_pages = npages > warp ? (npages - warp + kWarps - 1) / kWarps : 0;
+    const int n_items = my_pages * tiles_per_page * 2;
+    const unsigned char* kc = reinterpret_cast<const unsigned char*>(a.k);
+    const unsigned char* vc = reinterpret_cast<const unsigned char*>(a.v);
+    int id_base = 0;
+    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kWarps * lane] : 0;
+
+    auto issue = [&](int item) {
+        const int pair = item >> 1;
+        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
+        const int pg = warp + kWarps * po;
+        const int nvalid_page = (pg == npages - 1) ? last_len : P;
+        const int tok0 = tile * kTileTokens;
+        const unsigned char* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * ROWB;
+        const uint32_t dst = my_ring_addr + (uint32_t)((item % kSlots) * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+            const int ch = c * 32 + lane;
+            const int t = ch / CH_PER_ROW, cr = ch % CH_PER_ROW;
+            cp_async16(dst + t * ROWB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < nvalid_page);
+        }
+    };
+
+#pragma unroll
+    for (int i = 0; i < kSlots - 1; ++i) {
+        if (i < n_items) issue(i);
+        cp_async_commit();
+    }
+
+    // ldmatrix row address of this lane inside a tile: token row and which chunk of the pair
+    const int lm_t = ((lane >> 4) << 3) + (lane & 7);
+    const int lm_c = (lane >> 3) & 1;
+
+    for (int item = 0; item < n_items; ++item) {
+        cp_async_wait<kSlots - 2>();
+        __syncwarp();
+        {
+            const int nxt = item + kSlots - 1;
+            if (nxt < n_items) {
+                const int po = (nxt >> 1) / tiles_per_page;
+                if (po - id_base >= 32) {
+                    id_base += 32;
+                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kWarps * (id_base + lane)] : 0;
+                }
+                issue(nxt);
+            }
+            cp_async_commit();
+        }
+        const uint32_t tile_addr = my_ring_addr + (uint32_t)((item % kSlots) * TILE_BYTES) + lm_t * ROWB;
+        if ((item & 1) == 0) {
+            const int pair = item >> 1;
+            const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+            const int pg = warp + kWarps * po;
+            const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kTileTokens;
+            float st[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) st[j][i] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t kb[4];
+                ldmatrix_x4(kb, tile_addr + ((((ks << 1) + lm_c) ^ (lm_t & 7)) << 4));
+                mma_bf16(st[0], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
+                mma_bf16(st[1], qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
+            }
+            // this lane: head gid, tokens tid*2 + {0,1} (+8 for the second n-tile)
+            float sv[4];
+            sv[0] = (tid * 2 < nvalid) ? st[0][0] * a.scale_log2 : -INFINITY;
+            sv[1] = (tid * 2 + 1 < nvalid) ? st[0][1] * a.scale_log2 : -INFINITY;
+            sv[2] = (tid * 2 + 8 < nvalid) ? st[1][0] * a.scale_log2 : -INFINITY;
+            sv[3] = (tid * 2 + 9 < nvalid) ? st[1][1] * a.scale_log2 : -INFINITY;
+            float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float mn = fmaxf(m_run, tmax);
+            // mn stays -inf only while nothing valid was seen (tiles past the end of a short last page)
+            const float alpha = (mn == -INFINITY) ? 1.f : exp2f(m_run - mn);
+            const float base = (mn == -INFINITY) ? 0.f : mn;
+            m_run = mn;
+            const float p0 = exp2f(sv[0] - base), p1 = exp2f(sv[1] - base);
+            const float p2 = exp2f(sv[2] - base), p3 = exp2f(sv[3] - base);
+            l_run = l_run * alpha + (p0 + p1) + (p2 + p3);
+            pb0 = pack_bf16x2(p0, p1);
+            pb1 = pack_bf16x2(p2, p3);
+            // the O^T columns of this lane are heads tid*2 and tid*2+1
+            a0 = __shfl_sync(0xffffffffu, alpha, (tid * 2) << 2);
+            a1 = __shfl_sync(0xffffffffu, alpha, (tid * 2 + 1) << 2);
+        } else {
+#pragma unroll
+            for (int mt = 0; mt < KSTEPS; ++mt) {
+                uint32_t va[4];
+                ldmatrix_x4_trans(va, tile_addr + ((((mt << 1) + lm_c) ^ (lm_t & 7)) << 4));
+                o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
+                // A regs: (dims 0-7, tok 0-7), (dims 8-15, tok 0-7), (dims 0-7, tok 8-15), (dims 8-15, tok 8-15)
+                mma_bf16(o[mt], va[0], va[1], va[2], va[3], pb0, pb1);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    float* sm_acc = reinterpret_cast<float*>(smem_raw);  // [kWarps][G][D]
+    float* sm_m = sm_acc + kWarps * G * D;               // [kWarps][G]
+    float* sm_l = sm_m + kWarps * G;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (tid == 0 && gid < G) {
+        sm_m[warp * G + gid] = m_run;
+        sm_l[warp * G + gid] = l_run;
+    }
+#pragma unroll
+    for (int mt = 0; mt < KSTEPS; ++mt) {
+        const int h0 = tid * 2, d0 = mt * 16 + gid;
+        if (h0 < G) {
+            sm_acc[(warp * G + h0) * D + d0] = o[mt][0];
+            sm_acc[(warp * G + h0) * D + d0 + 8] = o[mt][2];
+        }
+        if (h0 + 1 < G) {
+            sm_acc[(warp * G + h0 + 1) * D + d0] = o[mt][1];
+            sm_acc[(warp * G + h0 + 1) * D + d0 + 8] = o[mt][3];
+        }
+    }
+    __syncthreads();
+    T* out = reinterpret_cast<T*>(a.out) + (int64_t)s * G * D;
+    for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+        const int g = idx / D, d = idx % D;
+        float mx = sm_m[g];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w * G + g]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float wm = sm_m[w * G + g];
+            const float wgt = (wm == -INFINITY) ? 0.f : exp2f(wm - mx);
+            num = fmaf(wgt, sm_acc[(w * G + g) * D + d], num);
+            den = fmaf(wgt, sm_l[w * G + g], den);
+        }
+        store_out<T>(out + idx, den > 0.f ? num / den : 0.f);
+    }
+}
+
+template <int G, int D>
+int launch_mma_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
+    const size_t ring = (size_t)kWarps * kSlots * kTileTokens * D * 2;
+    const size_t merge = (size_t)(kWarps * G * D + 2 * kWarps * G) * sizeof(float);
+    const size_t bytes = ring > merge ? ring : merge;
+    auto kern = decode_gqa_mma_kernel<G, D>;
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            vtx::note_cuda_error(e);
+            return VTX_ERR_CUDA;
+        }
+    }
+    kern<<<eff_bs, kWarps * 32, bytes, st>>>(a);
     return vtx::finish_launch();
 }
 
-template <typename T, int UT>
+template <int G>
+int launch_mma_g(const DecodeArgs& a, int eff_bs, int head_dim, cudaStream_t st) {
+    switch (head_dim) {
+        case 64: return launch_mma_cfg<G, 64>(a, eff_bs, st);
+        case 128: return launch_mma_cfg<G, 128>(a, eff_bs, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
+}
+
+int launch_mma(const DecodeArgs& a, int eff_bs, int group, int head_dim, cudaStream_t st) {
+    switch (group) {
+        case 1: return launch_mma_g<1>(a, eff_bs, head_dim, st);
+        case 2: return launch_mma_g<2>(a, eff_bs, head_dim, st);
+        case 4: return launch_mma_g<4>(a, eff_bs, head_dim, st);
+        case 8: return launch_mma_g<8>(a, eff_bs, head_dim, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
+}
+
+template <typename T, int G, int LPT>
+int launch_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
+    constexpr int D = LPT * 8;
+    const size_t ring = (size_t)kWarps * kSlots * kTileTokens * D * sizeof(T);
+    const size_t merge = (size_t)(kWarps * G * D + 2 * kWarps * G) * sizeof(float);
+    const size_t bytes = ring > merge ? ring : merge;
+    auto kern = decode_gqa_simt_kernel<T, G, LPT>;
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            vtx::note_cuda_error(e);
+            return VTX_ERR_CUDA;
+        }
+    }
+    kern<<<eff_bs, kWarps * 32, bytes, st>>>(a);
+    return vtx::finish_launch();
+}
+
+template <typename T, int G>
+int launch_decode_g(const DecodeArgs& a, int eff_bs, int head_dim, cudaStream_t st) {
+    switch (head_dim) {
+        case 64: return launch_cfg<T, G, 8>(a, eff_bs, st);
+        case 128: return launch_cfg<T, G, 16>(a, eff_bs, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
+}
+
+template <typename T>
 int launch_decode(const DecodeArgs& a, int eff_bs, int group, int head_dim, cudaStream_t st) {
     switch (group) {
-        case 1: return launch_decode_g<T, 1, UT>(a, eff_bs, head_dim, st);
-        case 2: return launch_decode_g<T, 2, UT>(a, eff_bs, head_dim, st);
-        case 4: return launch_decode_g<T, 4, UT>(a, eff_bs, head_dim, st);
-        case 8: return launch_decode_g<T, 8, UT>(a, eff_bs, head_dim, st);
+        case 1: return launch_decode_g<T, 1>(a, eff_bs, head_dim, st);
+        case 2: return launch_decode_g<T, 2>(a, eff_bs, head_dim, st);
+        case 4: return launch_decode_g<T, 4>(a, eff_bs, head_dim, st);
+        case 8: return launch_decode_g<T, 8>(a, eff_bs, head_dim, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
 }
@@ -222,7 +587,7 @@ extern "C" int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_
     a.P = page_size;
     a.scale_log2 = sm_scale * kLog2e;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == VTX_BF16) return launch_decode<__nv_bfloat16, 8>(a, eff_batch_size, group_size, head_dim, st);
-    if (dtype == VTX_F32) return launch_decode<float, 4>(a, eff_batch_size, group_size, head_dim, st);
+    if (dtype == VTX_BF16) return launch_mma(a, eff_batch_size, group_size, head_dim, st);
+    if (dtype == VTX_F32) return launch_decode<float>(a, eff_batch_size, group_size, head_dim, st);
     return VTX_ERR_INVALID_ARGUMENT;
 }

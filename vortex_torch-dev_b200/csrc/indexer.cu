@@ -1,26 +1,38 @@
 // Indexer kernels: grouped-query mean, centroid GeMV and top-k page selection.
 //
-// One CTA per (request, head) segment.  The fused kernel keeps the segment's scores in
-// shared memory as sortable keys, so they never travel to HBM; the stand-alone GeMV and
-// top-k kernels exist for flows that call the operators one by one and produce the same
-// bits.  Behaviour follows flow/algorithms.py:168-170, indexer/triton_kernels/mv_impl.py:53-62
-// and csrc/topk.cu:56-113 of the reference.
+// One CTA (4 warps) per (request, head) segment.  The fused kernel keeps the segment's scores in
+// shared memory as sortable keys, so they never travel to HBM; the stand-alone GeMV and top-k
+// kernels exist for flows that call the operators one by one and produce the same bits.
+// Behaviour follows flow/algorithms.py:168-170, indexer/triton_kernels/mv_impl.py:53-62 and
+// csrc/topk.cu:56-113 of the reference.
 //
 // Canonical score arithmetic (shared with the CPU checker, so selections are bit-exact):
 //   q_mean[d] = round_T( (q[0][d] + q[1][d] + ... in fp32, from +0.0) / G )
-//   product   = round_T( centroid[d] * q_mean[d] )          (fp32 multiply, then rounding to T)
-//   the D dims are cut in chunks of 8; LANES = min(32, pow2ceil(D/8)) partial sums; lane l adds
-//   the products of chunks l, l+LANES, ... one by one in ascending order into an fp32
-//   accumulator starting at +0.0 (no FMA); lanes are folded v[i] += v[i+w], w = LANES/2 .. 1;
+//   product   = round_T( centroid[d] * q_mean[d] )          (one rounding of the exact product)
+//   the D dims are cut in chunks of 8; L = min(32, pow2ceil(D/8)) partial sums; partial l adds the
+//   products of chunks l, l+L, ... one by one in ascending order into an fp32 accumulator
+//   starting at +0.0 (no FMA); partials are folded v[i] += v[i+w], w = L/2 .. 1;
 //   score = round_T(sum).
 // Selection order: score descending, ties by ascending candidate position (a stable
 // descending sort), -0.0 equal to +0.0.
+//
+// Data movement: centroid rows are gathered global -> shared with 16-byte cp.async into a ring
+// per warp (16 rows per slot, two slots in flight while one is scored), so no registers stage
+// the loads and the only block-wide barriers are before and after the gather.  Two threads
+// score one row: the thread of parity p owns the partial sums of parity p, which keeps every
+// fold level but the last inside a thread (one shuffle per row).  Rows are stored with their
+// 16-byte pieces swizzled (piece ^ 2*(row & 3)) so the 128-bit shared loads are conflict-free.
+// The sort is a bitonic network over registers (4..16 keys per thread): strides below the
+// per-thread block are register swaps, strides inside a warp are shuffles, and only the three
+// widest strides cross warps through shared memory.
 #include "vtx_common.cuh"
 
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
 constexpr int kMaxCandidates = 16384;
+constexpr int kRowsPerSlot = 16;
 
 // ---- sortable keys: high bits order the score, low bits make lower positions win ties ----
 template <typename T>
@@ -50,7 +62,8 @@ struct KeyOf<float> {
     static __device__ __forceinline__ int index(type k) { return (int)(0xffffffffu - (uint32_t)(k & 0xffffffffull)); }
 };
 
-// Descending bitonic sort of n (power of two) keys in shared memory by the whole CTA.
+// Descending bitonic sort of n (power of two) keys in shared memory by the whole CTA
+// (general fallback for segments with more than 2048 candidates).
 template <typename Key>
 __device__ void block_bitonic_desc(Key* keys, int n) {
     for (int k = 2; k <= n; k <<= 1) {
@@ -70,6 +83,100 @@ __device__ void block_bitonic_desc(Key* keys, int n) {
     }
 }
 
+// Descending bitonic sort of kThreads * EPT keys held EPT per thread, element e = thread * EPT + r.
+// xbuf: shared scratch of 2 * kThreads * EPT keys for the strides that cross warps.
+template <typename Key, int EPT>
+__device__ __forceinline__ void block_sort_desc_regs(Key (&v)[EPT], Key* xbuf) {
+    constexpr int N = kThreads * EPT;
+    const int t = threadIdx.x;
+    int buf = 0;
+#pragma unroll
+    for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j < EPT) {
+#pragma unroll
+                for (int r = 0; r < EPT; ++r) {
+                    if ((r & j) == 0) {
+                        const bool desc = (((t * EPT + r) & k) == 0);
+                        const Key x = v[r], y = v[r + j];
+                        const bool sw = (x < y) == desc;
+                        v[r] = sw ? y : x;
+                        v[r + j] = sw ? x : y;
+                    }
+                }
+            } else {
+                const int pt = j / EPT;                    // partner thread = t ^ pt
+                const bool lower = (t & pt) == 0;
+                const bool desc = (((t * EPT) & k) == 0);  // k > j >= EPT: bit k of e comes from t
+                const bool keep_max = lower == desc;
+                if (pt < 32) {
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) {
+                        const Key o = __shfl_xor_sync(0xffffffffu, v[r], pt);
+                        v[r] = keep_max ? (v[r] > o ? v[r] : o) : (v[r] < o ? v[r] : o);
+                    }
+                } else {
+                    Key* mine = xbuf + buf * N + t * EPT;
+                    const Key* theirs = xbuf + buf * N + (t ^ pt) * EPT;
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) mine[r] = v[r];
+                    __syncthreads();
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) {
+                        const Key o = theirs[r];
+                        v[r] = keep_max ? (v[r] > o ? v[r] : o) : (v[r] < o ? v[r] : o);
+                    }
+                    buf ^= 1;
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int EPT>
+__device__ __forceinline__ void select_regs(const typename KeyOf<T>::type* keys, const int32_t* ids, int c, int K,
+                                            int32_t* out, int32_t* out_pt, typename KeyOf<T>::type* xbuf) {
+    using Key = typename KeyOf<T>::type;
+    Key v[EPT];
+#pragma unroll
+    for (int r = 0; r < EPT; ++r) {
+        const int e = threadIdx.x * EPT + r;
+        v[r] = e < c ? keys[e] : (Key)0;  // real keys are never 0 for finite scores
+    }
+    block_sort_desc_regs<Key, EPT>(v, xbuf);
+#pragma unroll
+    for (int r = 0; r < EPT; ++r) {
+        const int e = threadIdx.x * EPT + r;
+        if (e < K) {
+            const int32_t row = ids[KeyOf<T>::index(v[r])];
+            out[e] = row;
+            if (out_pt) out_pt[e] = row;
+        }
+    }
+}
+
+// Sort the c keys of a segment (already in shared memory, visible to all threads) and emit the
+// first K row ids.  xbuf: shared scratch for the register sort (2 * max(512, min(pow2ceil(c), 2048))
+// keys), or null to force the shared-memory network.
+template <typename T>
+__device__ void select_and_store(typename KeyOf<T>::type* keys, const int32_t* ids, int c, int K, int32_t* out,
+                                 int32_t* out_pt, typename KeyOf<T>::type* xbuf) {
+    using Key = typename KeyOf<T>::type;
+    if (xbuf != nullptr && c <= kThreads * 4) return select_regs<T, 4>(keys, ids, c, K, out, out_pt, xbuf);
+    if (xbuf != nullptr && c <= kThreads * 8) return select_regs<T, 8>(keys, ids, c, K, out, out_pt, xbuf);
+    if (xbuf != nullptr && c <= kThreads * 16) return select_regs<T, 16>(keys, ids, c, K, out, out_pt, xbuf);
+    const int n = vtx::pow2_ceil(c);
+    for (int i = c + threadIdx.x; i < n; i += kThreads) keys[i] = (Key)0;
+    __syncthreads();
+    block_bitonic_desc<Key>(keys, n);
+    for (int j = threadIdx.x; j < K; j += kThreads) {
+        const int32_t row = ids[KeyOf<T>::index(keys[j])];
+        out[j] = row;
+        if (out_pt) out_pt[j] = row;
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ float load_score(const T* p);
 template <>
@@ -84,22 +191,6 @@ __device__ __forceinline__ void store_score<__nv_bfloat16>(__nv_bfloat16* p, flo
 template <>
 __device__ __forceinline__ void store_score<float>(float* p, float v) { *p = v; }
 
-// Sort the c keys of a segment and emit the first K row ids.
-template <typename T>
-__device__ void select_and_store(typename KeyOf<T>::type* keys, const int32_t* ids, int c, int K,
-                                 int32_t* out, int32_t* out_pt) {
-    using Key = typename KeyOf<T>::type;
-    const int n = vtx::pow2_ceil(c);
-    for (int i = c + threadIdx.x; i < n; i += kThreads) keys[i] = (Key)0;
-    __syncthreads();
-    block_bitonic_desc<Key>(keys, n);
-    for (int j = threadIdx.x; j < K; j += kThreads) {
-        const int32_t row = ids[KeyOf<T>::index(keys[j])];
-        out[j] = row;
-        if (out_pt) out_pt[j] = row;
-    }
-}
-
 struct IndexerArgs {
     const void* q;          // [eff_bs, G, D]
     const void* centroids;  // [rows, D]
@@ -113,13 +204,74 @@ struct IndexerArgs {
     int G, D, K, bos, eos, key_cap;
 };
 
+// ---- asynchronous row gather ----
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr, bool valid) {
+    const int src_bytes = valid ? 16 : 0;  // 0 => zero-fill, the source is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---- one chunk (8 dims) of products added one by one into acc ----
+// bf16: the packed multiply rounds each exact product once to bf16, as the canonical order asks.
+__device__ __forceinline__ void add_products(float& acc, const __nv_bfloat16* row_chunk, const __nv_bfloat16* q_chunk) {
+    const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
+    const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&rr[i]),
+                                         *reinterpret_cast<const __nv_bfloat162*>(&qq[i]));
+        const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p);
+        acc = __fadd_rn(acc, vtx::bf16lo(pw));
+        acc = __fadd_rn(acc, vtx::bf16hi(pw));
+    }
+}
+__device__ __forceinline__ void add_products(float& acc, const float* row_chunk, const float* q_chunk) {
+    const float4 r0 = *reinterpret_cast<const float4*>(row_chunk), r1 = *reinterpret_cast<const float4*>(row_chunk + 4);
+    const float4 q0 = *reinterpret_cast<const float4*>(q_chunk), q1 = *reinterpret_cast<const float4*>(q_chunk + 4);
+    acc = __fadd_rn(acc, __fmul_rn(r0.x, q0.x));
+    acc = __fadd_rn(acc, __fmul_rn(r0.y, q0.y));
+    acc = __fadd_rn(acc, __fmul_rn(r0.z, q0.z));
+    acc = __fadd_rn(acc, __fmul_rn(r0.w, q0.w));
+    acc = __fadd_rn(acc, __fmul_rn(r1.x, q1.x));
+    acc = __fadd_rn(acc, __fmul_rn(r1.y, q1.y));
+    acc = __fadd_rn(acc, __fmul_rn(r1.z, q1.z));
+    acc = __fadd_rn(acc, __fmul_rn(r1.w, q1.w));
+}
+
+template <typename T, int D>
+struct Geom {
+    static constexpr int nchunk = D / 8;  // canonical chunks of 8 dims
+    static constexpr int L = nchunk > 16 ? 32 : (nchunk > 8 ? 16 : (nchunk > 4 ? 8 : 4));
+    static constexpr int row_bytes = D * (int)sizeof(T);
+    static constexpr int pieces = row_bytes / 16;        // 16-byte pieces per row
+    static constexpr int ppc = 8 * (int)sizeof(T) / 16;  // pieces per canonical chunk (1 bf16, 2 fp32)
+    static constexpr int slot_bytes = kRowsPerSlot * row_bytes;
+    static constexpr int slots = slot_bytes * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    static constexpr size_t ring_bytes = (size_t)kWarps * slots * slot_bytes;
+    static_assert(pieces % 8 == 0, "row must be a multiple of 128 bytes");
+    static_assert(nchunk % 2 == 0, "two threads share a row by parity of the partial sums");
+    // the idle ring doubles as the sort's exchange buffer (2 x 2048 keys at most)
+    static_assert(ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
+};
+
 // MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
-template <typename T, int LANES, int CPL, int U, int MODE>
-__global__ void __launch_bounds__(kThreads) indexer_kernel(IndexerArgs a) {
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
     using Key = typename KeyOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    Key* keys = reinterpret_cast<Key*>(smem_raw);
-    int32_t* ids = reinterpret_cast<int32_t*>(smem_raw + (size_t)a.key_cap * sizeof(Key));
+    using Gm = Geom<T, D>;
+    constexpr int L = Gm::L, HALF = L / 2, SLOTS = Gm::slots;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    // layout: [ring][q_mean][keys][ids]
+    unsigned char* ring = smem_raw;
+    T* qbar = reinterpret_cast<T*>(smem_raw + Gm::ring_bytes);
+    Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + Gm::row_bytes);
+    int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
 
     const int s = blockIdx.x;
     const int beg = a.dense_indptr[s] + a.bos;
@@ -131,80 +283,97 @@ __global__ void __launch_bounds__(kThreads) indexer_kernel(IndexerArgs a) {
         for (int i = threadIdx.x; i < c; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
-
-    constexpr int NGRP = kThreads / LANES;
-    const int lane = threadIdx.x % LANES, grp = threadIdx.x / LANES;
-    const int nchunk = a.D / 8;
-
-    // grouped-query mean for the chunks this lane owns
-    float qm[CPL][8];
-    {
-        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * a.D;
+    // grouped-query mean, one canonical chunk per thread
+    for (int ch = threadIdx.x; ch < Gm::nchunk; ch += kThreads) {
+        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int g = 0; g < a.G; ++g) {
+            vtx::Vec8<T> v;
+            v.load_cached(qs + (int64_t)g * D);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+        }
         const float g_f = (float)a.G;
 #pragma unroll
-        for (int k = 0; k < CPL; ++k) {
-            const int ch = lane + k * LANES;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) qm[k][j] = 0.f;
-            if (ch < nchunk) {
-                for (int g = 0; g < a.G; ++g) {
-                    vtx::Vec8<T> v;
-                    v.load_cached(qs + (int64_t)g * a.D + ch * 8);
-                    float f[8];
-                    v.unpack(f);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) qm[k][j] = __fadd_rn(qm[k][j], f[j]);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) qm[k][j] = vtx::round_to<T>(__fdiv_rn(qm[k][j], g_f));
-            }
-        }
+        for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], g_f);
+        vtx::store8(qbar + ch * 8, acc);  // rounds once to T
     }
     __syncthreads();
 
-    const T* cent = reinterpret_cast<const T*>(a.centroids);
-    // Every thread runs the same number of iterations: the folds below shuffle across full warps.
-    for (int base = 0; base < c; base += NGRP * U) {
-        const int i0 = base + grp * U;
-        vtx::Vec8<T> v[U][CPL];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
+    unsigned char* my_ring = ring + (size_t)warp * SLOTS * Gm::slot_bytes;
+    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
+    const unsigned char* cent = reinterpret_cast<const unsigned char*>(a.centroids);
+    const int n_batches = (c + kRowsPerSlot - 1) / kRowsPerSlot;
+    const int my_batches = n_batches > warp ? (n_batches - warp + kWarps - 1) / kWarps : 0;
+    constexpr int pieces_per_slot = kRowsPerSlot * Gm::pieces;
+
+    auto issue = [&](int ord) {
+        const int row0 = (warp + ord * kWarps) * kRowsPerSlot;
+        const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * Gm::slot_bytes);
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = i0 + u;
-#pragma unroll
-            for (int k = 0; k < CPL; ++k) {
-                const int ch = lane + k * LANES;
-                if (i < c && ch < nchunk) v[u][k].load(cent + (int64_t)row_ids[i] * a.D + ch * 8);
-                else v[u][k].zero();
-            }
+        for (int pc = lane; pc < pieces_per_slot; pc += 32) {
+            const int r = pc / Gm::pieces, pr = pc - r * Gm::pieces;
+            const int i = row0 + r;
+            const bool valid = i < c;
+            const int64_t row = valid ? row_ids[i] : 0;
+            cp_async16(dst + r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4), cent + row * Gm::row_bytes + pr * 16,
+                       valid);
         }
+    };
+
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            float acc = 0.f;
+    for (int i = 0; i < SLOTS - 1; ++i) {
+        if (i < my_batches) issue(i);
+        cp_async_commit();
+    }
+    for (int ord = 0; ord < my_batches; ++ord) {
+        cp_async_wait<SLOTS - 2>();
+        __syncwarp();
+        if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
+        cp_async_commit();
+        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * Gm::slot_bytes + r_in * Gm::row_bytes;
+        const int sw = (r_in & 3) << 1;
+        float acc[HALF];
 #pragma unroll
-            for (int k = 0; k < CPL; ++k) {
-                float f[8];
-                v[u][k].unpack(f);
-                if (lane + k * LANES < nchunk) {
+        for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
+        // this thread owns partial sums 2*i + par; partial l takes chunks l, l + L, ...
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        acc = __fadd_rn(acc, vtx::round_to<T>(__fmul_rn(f[j], qm[k][j])));
+        for (int k = 0; k * L < Gm::nchunk; ++k) {
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) {
+                if (k * L + 2 * i < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
+                    const int ch = k * L + 2 * i + par;
+                    // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
+                    const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
+                    add_products(acc[i], src, qbar + ch * 8);
                 }
             }
+        }
 #pragma unroll
-            for (int w = LANES / 2; w > 0; w >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, w));
-            const int i = i0 + u;
-            if (lane == 0 && i < c) {
-                const float sc = vtx::round_to<T>(acc);
-                if (MODE == 0) keys[i] = KeyOf<T>::make(sc, i);
-                else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + i, sc);
-            }
+        for (int w = HALF / 2; w > 0; w >>= 1)
+#pragma unroll
+            for (int i = 0; i < w; ++i) acc[i] = __fadd_rn(acc[i], acc[i + w]);
+        const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
+        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;
+        if (par == 0 && i < c) {
+            const float sc = vtx::round_to<T>(total);
+            if (MODE == 0) keys[i] = KeyOf<T>::make(sc, i);
+            else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + i, sc);
         }
     }
+    cp_async_wait<0>();
     if (MODE == 0) {
-        __syncthreads();
+        __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
         const int o0 = a.sparse_indptr[s] + a.bos;
         select_and_store<T>(keys, ids, c, a.K, a.sparse_indices + o0,
-                            a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr);
+                            a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr,
+                            reinterpret_cast<Key*>(ring));
     }
 }
 
@@ -212,8 +381,11 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads) topk_kernel(const T* __restrict__ scores, IndexerArgs a) {
     using Key = typename KeyOf<T>::type;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    Key* keys = reinterpret_cast<Key*>(smem_raw);
-    int32_t* ids = reinterpret_cast<int32_t*>(smem_raw + (size_t)a.key_cap * sizeof(Key));
+    // layout: [scratch for the register sort][keys][ids]
+    Key* xbuf = reinterpret_cast<Key*>(smem_raw);
+    const int scratch_keys = 2 * (a.key_cap < 512 ? 512 : (a.key_cap < 2048 ? a.key_cap : 2048));
+    Key* keys = xbuf + scratch_keys;
+    int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
     const int s = blockIdx.x;
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
@@ -224,12 +396,7 @@ __global__ void __launch_bounds__(kThreads) topk_kernel(const T* __restrict__ sc
     }
     __syncthreads();
     const int o0 = a.sparse_indptr[s] + a.bos;
-    select_and_store<T>(keys, ids, c, a.K, a.sparse_indices + o0, nullptr);
-}
-
-template <typename T>
-size_t smem_bytes(int key_cap) {
-    return (size_t)key_cap * (sizeof(typename KeyOf<T>::type) + sizeof(int32_t));
+    select_and_store<T>(keys, ids, c, a.K, a.sparse_indices + o0, nullptr, xbuf);
 }
 
 template <typename Kern>
@@ -244,10 +411,14 @@ int set_smem(Kern kern, size_t bytes) {
     return VTX_OK;
 }
 
-template <typename T, int LANES, int CPL, int U, int MODE>
+template <typename T, int D, int MODE>
 int launch_indexer_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
-    const size_t bytes = MODE == 0 ? smem_bytes<T>(a.key_cap) : 0;
-    auto kern = indexer_kernel<T, LANES, CPL, U, MODE>;
+    using Gm = Geom<T, D>;
+    using Key = typename KeyOf<T>::type;
+    size_t bytes = Gm::ring_bytes + Gm::row_bytes;
+    if (MODE == 0) bytes += (size_t)a.key_cap * (sizeof(Key) + sizeof(int32_t));
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    auto kern = indexer_kernel<T, D, MODE>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
     kern<<<eff_bs, kThreads, bytes, st>>>(a);
@@ -257,13 +428,25 @@ int launch_indexer_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
 template <typename T, int MODE>
 int launch_indexer(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     switch (a.D) {
-        case 64: return launch_indexer_cfg<T, 8, 1, 8, MODE>(a, eff_bs, st);
-        case 128: return launch_indexer_cfg<T, 16, 1, 8, MODE>(a, eff_bs, st);
-        case 256: return launch_indexer_cfg<T, 32, 1, 8, MODE>(a, eff_bs, st);
-        case 512: return launch_indexer_cfg<T, 32, 2, 4, MODE>(a, eff_bs, st);
-        case 576: return launch_indexer_cfg<T, 32, 3, 4, MODE>(a, eff_bs, st);
+        case 64: return launch_indexer_cfg<T, 64, MODE>(a, eff_bs, st);
+        case 128: return launch_indexer_cfg<T, 128, MODE>(a, eff_bs, st);
+        case 256: return launch_indexer_cfg<T, 256, MODE>(a, eff_bs, st);
+        case 512: return launch_indexer_cfg<T, 512, MODE>(a, eff_bs, st);
+        case 576: return launch_indexer_cfg<T, 576, MODE>(a, eff_bs, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
+}
+
+template <typename T>
+int launch_topk(const void* scores, const IndexerArgs& a, int eff_bs, cudaStream_t st) {
+    using Key = typename KeyOf<T>::type;
+    const int scratch_keys = 2 * (a.key_cap < 512 ? 512 : (a.key_cap < 2048 ? a.key_cap : 2048));
+    const size_t bytes = (size_t)scratch_keys * sizeof(Key) + (size_t)a.key_cap * (sizeof(Key) + sizeof(int32_t));
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    int rc = set_smem(topk_kernel<T>, bytes);
+    if (rc != VTX_OK) return rc;
+    topk_kernel<T><<<eff_bs, kThreads, bytes, st>>>((const T*)scores, a);
+    return vtx::finish_launch();
 }
 
 int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int bos, int eos, int maxp,
@@ -274,6 +457,9 @@ int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int 
     if (maxp > kMaxCandidates) return VTX_ERR_UNSUPPORTED;
     return VTX_OK;
 }
+
+// Candidate capacity of one segment (sizes the key and row-id arrays in shared memory).
+int key_capacity(int max_pages) { return vtx::pow2_ceil(max_pages); }
 
 }  // namespace
 
@@ -297,7 +483,7 @@ extern "C" int vtx_gemv(const void* q_mean, const void* centroids, void* scores,
     a.K = topk_val;
     a.bos = page_reserved_bos;
     a.eos = page_reserved_eos;
-    a.key_cap = 0;  // GeMV mode keeps nothing in shared memory
+    a.key_cap = 0;  // GeMV mode keeps no keys in shared memory
     cudaStream_t st = (cudaStream_t)stream;
     return dtype == VTX_BF16 ? launch_indexer<__nv_bfloat16, 1>(a, eff_batch_size, st)
                              : launch_indexer<float, 1>(a, eff_batch_size, st);
@@ -320,20 +506,10 @@ extern "C" int vtx_topk(const void* scores, const int32_t* dense_kv_indptr, cons
     a.K = topk_val;
     a.bos = page_reserved_bos;
     a.eos = page_reserved_eos;
-    a.key_cap = vtx::pow2_ceil(max_num_pages_per_request);
+    a.key_cap = key_capacity(max_num_pages_per_request);
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == VTX_BF16) {
-        const size_t bytes = smem_bytes<__nv_bfloat16>(a.key_cap);
-        rc = set_smem(topk_kernel<__nv_bfloat16>, bytes);
-        if (rc != VTX_OK) return rc;
-        topk_kernel<__nv_bfloat16><<<eff_batch_size, kThreads, bytes, st>>>((const __nv_bfloat16*)scores, a);
-    } else {
-        const size_t bytes = smem_bytes<float>(a.key_cap);
-        rc = set_smem(topk_kernel<float>, bytes);
-        if (rc != VTX_OK) return rc;
-        topk_kernel<float><<<eff_batch_size, kThreads, bytes, st>>>((const float*)scores, a);
-    }
-    return vtx::finish_launch();
+    return dtype == VTX_BF16 ? launch_topk<__nv_bfloat16>(scores, a, eff_batch_size, st)
+                             : launch_topk<float>(scores, a, eff_batch_size, st);
 }
 
 extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int32_t* dense_kv_indptr,
@@ -362,7 +538,7 @@ extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int
     a.K = topk_val;
     a.bos = page_reserved_bos;
     a.eos = page_reserved_eos;
-    a.key_cap = vtx::pow2_ceil(max_num_pages_per_request);
+    a.key_cap = key_capacity(max_num_pages_per_request);
     cudaStream_t st = (cudaStream_t)stream;
     return dtype == VTX_BF16 ? launch_indexer<__nv_bfloat16, 0>(a, eff_batch_size, st)
                              : launch_indexer<float, 0>(a, eff_batch_size, st);

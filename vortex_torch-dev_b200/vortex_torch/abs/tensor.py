@@ -63,6 +63,22 @@ def _retag(result: Any, fmt: Optional["FORMAT"]) -> Any:
     return result
 
 
+def _metadata_functions():
+    """Tensor accessors that look at shape/placement only and never at the data."""
+    T = torch.Tensor
+    fns = {T.dim, T.size, T.stride, T.numel, T.nelement, T.ndimension, T.is_contiguous, T.data_ptr,
+           T.element_size, T.storage_offset, T.is_floating_point, T.is_complex, T.get_device}
+    for prop in ("shape", "device", "dtype", "ndim", "is_cuda", "is_cpu", "requires_grad", "layout", "is_sparse",
+                 "is_quantized", "is_meta", "names", "itemsize", "nbytes"):
+        getter = getattr(getattr(T, prop, None), "__get__", None)
+        if getter is not None:
+            fns.add(getter)
+    return fns
+
+
+_METADATA_FUNCS = _metadata_functions()
+
+
 def _is_group_mean_call(func, args, kwargs) -> bool:
     if func not in (torch.Tensor.mean, torch.mean) or not args:
         return False
@@ -125,6 +141,8 @@ class vTensor(torch.Tensor):
     def __torch_function__(cls, func, types, args=(), kwargs=None):
         kwargs = kwargs or {}
         if not any(issubclass(t, vTensor) for t in types):
+            return super().__torch_function__(func, types, args, kwargs)
+        if func in _METADATA_FUNCS:  # shape/device/dtype queries: no data is read, nothing to check or tag
             return super().__torch_function__(func, types, args, kwargs)
         tagged, plain, lazy = set(), False, False
         for t in _tensors_in((args, kwargs)):
