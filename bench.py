@@ -282,13 +282,13 @@ def time_kernels(rt, step, cfg, reps):
     def run_cache():
         for l in range(cfg["layers"]):
             cache = rt.pool.buffers[l]
-            set_kv_buffer_launcher(cache["k"], cache["v"], step.new_k[l], step.new_v[l], step.loc, rt.P)
-            _cabi.cmean(cache["k"], cache["centroids"], step.loc, rt.H, rt.P)
+            _cabi.set_kv_cmean(cache["k"], cache["v"], step.new_k[l], step.new_v[l], cache["centroids"], step.loc,
+                               rt.P)
 
     kinds = dict(indexer=(run_indexer, len(sparse_layers)),
                  decode_sparse=(lambda: run_decode(sparse_layers, True), len(sparse_layers)),
                  decode_dense=(lambda: run_decode(dense_layers, False), len(dense_layers)),
-                 kv_write_cmean=(run_cache, 2 * cfg["layers"]))
+                 kv_write_cmean=(run_cache, cfg["layers"]))
     out = {}
     for name, (fn, n) in kinds.items():
         if n == 0:
@@ -409,7 +409,7 @@ def main():
 
     if rank == 0:
         n_sparse = cfg["layers"] - len(cfg["skip"])
-        launches_per_step = 1 + 2 * cfg["layers"] + 2 * n_sparse + len(cfg["skip"])
+        launches_per_step = 1 + cfg["layers"] + 2 * n_sparse + len(cfg["skip"])
         value = world * args.steps / dev_s
         line = dict(
             metric=METRIC, value=value, unit="steps/s", n_gpus=world, steps=args.steps, warmup=W,

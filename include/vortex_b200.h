@@ -86,6 +86,18 @@ int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num
               int rows, int cols, int page_size, int dtype, void* stream);
 
 /*
+ * KV write fused with the page-completion mean of K: same results as vtx_set_kv followed by
+ * vtx_cmean(k_cache -> centroids) on the same loc, in one launch (the new row is averaged from
+ * registers).  Replaces the pair set_kv_buffer_launcher (cache/triton_kernels/set_kv.py:39-62) +
+ * reduce_pp Mean (cache/triton_kernels/reduce_impl.py:7-89) that the runtime issues back to back
+ * for flows whose forward_cache is `CMean(dim=1)(cache["k"], cache["centroids"])`
+ * (flow/algorithms.py:172-205).  centroids [num_pages*H, 1, D].
+ */
+int vtx_set_kv_cmean(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
+                     void* centroids, const int64_t* loc, int64_t nnz, int num_kv_heads,
+                     int head_dim, int page_size, int dtype, void* stream);
+
+/*
  * Centroid GeMV: score of every non-reserved candidate page of every segment that has
  * more than topk_val candidates, stored at the candidate's packed dense position.
  * Replaces `mv_bpr` (indexer/triton_kernels/mv_impl.py:6-81).

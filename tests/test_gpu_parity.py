@@ -85,6 +85,27 @@ def test_cmean_bit_exact(dtype, P, H, D):
                        out.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
 
 
+@pytest.mark.parametrize("dtype,P,H,D", [(torch.bfloat16, 16, 8, 128), (torch.float32, 16, 2, 128),
+                                         (torch.bfloat16, 64, 1, 576), (torch.bfloat16, 5, 3, 64)])
+def test_set_kv_cmean_fused_equals_separate(dtype, P, H, D):
+    pages, nnz = 30, 21
+    g = torch.Generator().manual_seed(4)
+    k = torch.randn(pages * H, P, D, generator=g).to(dtype)
+    v = torch.randn(pages * H, P, D, generator=g).to(dtype)
+    cent = torch.randn(pages * H, 1, D, generator=g).to(dtype)
+    pg = torch.randperm(pages, generator=g)[:nnz]
+    loc = pg * P + torch.where(torch.arange(nnz) % 2 == 0, torch.full((nnz,), P - 1), torch.randint(0, P - 1, (nnz,), generator=g))
+    nk = torch.randn(nnz, H, D, generator=g).to(dtype)
+    nv = torch.randn(nnz, H, D, generator=g).to(dtype)
+    k1, v1, c1 = k.cuda(), v.cuda(), cent.cuda()
+    _cabi.set_kv_cmean(k1, v1, nk.cuda(), nv.cuda(), c1, loc.cuda(), P)
+    vo.set_kv(k, v, nk, nv, loc, P)
+    vo.cmean(k, cent, loc, P, H)
+    assert torch.equal(k1.cpu(), k) and torch.equal(v1.cpu(), v)
+    it = torch.int16 if dtype == torch.bfloat16 else torch.int32
+    assert torch.equal(c1.cpu().view(it), cent.view(it))
+
+
 def test_cmean_prefill_shape():
     """Config 4b scaled down: every slot of a long request; only page-closing slots work."""
     P, H, D, pages = 16, 8, 128, 128

@@ -52,32 +52,105 @@ __global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* 
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            int r = 0;
-            for (; r + 8 <= rows; r += 8) {
+            for (int r = 0; r < rows; r += 8) {
                 vtx::Vec8<T> v[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) v[u].load(src + (int64_t)(r + u) * cols + c * 8);
+                for (int u = 0; u < 8; ++u) {
+                    if (r + u < rows) v[u].load(src + (int64_t)(r + u) * cols + c * 8);
+                    else v[u].zero();
+                }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    float f[8];
-                    v[u].unpack(f);
+                    if (r + u < rows) {
+                        float f[8];
+                        v[u].unpack(f);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                    }
                 }
-            }
-            for (; r < rows; ++r) {
-                vtx::Vec8<T> v;
-                v.load(src + (int64_t)r * cols + c * 8);
-                float f[8];
-                v.unpack(f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], denom);
             vtx::store8(out + pid * (int64_t)cols + c * 8, acc);
         }
     }
+}
+
+// KV write fused with the centroid update of the page the new token completes (if it does).
+// One group of LANES threads per (new token, head); each lane owns chunks of eight columns.
+// The mean adds the page's rows in ascending order with the new row (still in registers) last,
+// so the result has the same bits as set_kv_kernel followed by cmean_kernel.
+template <typename T, int LANES>
+__global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                          const T* __restrict__ new_k, const T* __restrict__ new_v,
+                                                          T* __restrict__ centroids, const int64_t* __restrict__ loc,
+                                                          int64_t nnz, int H, int D, int P) {
+    constexpr int GROUPS = 256 / LANES;
+    const int lane = threadIdx.x % LANES;
+    const int64_t items = nnz * H;
+    const int nchunk = D / 8;
+    const float denom = (float)P;
+    for (int64_t it = (int64_t)blockIdx.x * GROUPS + threadIdx.x / LANES; it < items;
+         it += (int64_t)gridDim.x * GROUPS) {
+        const int64_t t = loc[it / H];
+        const int h = (int)(it % H);
+        const int64_t pid = (t / P) * H + h;
+        const int tok = (int)(t % P);
+        T* kpage = k_cache + pid * (int64_t)P * D;
+        T* vpage = v_cache + pid * (int64_t)P * D;
+        const bool closes = tok == P - 1;
+        for (int c = lane; c < nchunk; c += LANES) {
+            vtx::Vec8<T> nk, nv;
+            nk.load_cached(new_k + it * D + c * 8);
+            nv.load_cached(new_v + it * D + c * 8);
+            float kf[8], vf[8];
+            nk.unpack(kf);
+            nv.unpack(vf);
+            vtx::store8(kpage + (int64_t)tok * D + c * 8, kf);  // values are already T-representable: exact copy
+            vtx::store8(vpage + (int64_t)tok * D + c * 8, vf);
+            if (!closes) continue;
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            // rows 0 .. P-2 come from the cache, eight loads in flight at a time (predicated tail)
+            for (int r = 0; r < P - 1; r += 8) {
+                vtx::Vec8<T> v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (r + u < P - 1) v[u].load(kpage + (int64_t)(r + u) * D + c * 8);
+                    else v[u].zero();
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (r + u < P - 1) {
+                        float f[8];
+                        v[u].unpack(f);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(__fadd_rn(acc[j], kf[j]), denom);
+            vtx::store8(centroids + pid * (int64_t)D + c * 8, acc);
+        }
+    }
+}
+
+template <typename T>
+int launch_set_kv_cmean(void* k, void* v, const void* nk, const void* nv, void* cent, const int64_t* loc,
+                        int64_t nnz, int H, int D, int P, cudaStream_t st) {
+    const int64_t items = nnz * H;
+    if (D <= 128) {
+        const int64_t blocks = (items + 15) / 16;
+        set_kv_cmean_kernel<T, 16><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
+            (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
+    } else {
+        const int64_t blocks = (items + 7) / 8;
+        set_kv_cmean_kernel<T, 32><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
+            (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
+    }
+    return vtx::finish_launch();
 }
 
 template <typename T>
@@ -126,5 +199,22 @@ extern "C" int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t n
     if (dtype == VTX_BF16)
         return launch_cmean<__nv_bfloat16>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
     if (dtype == VTX_F32) return launch_cmean<float>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
+    return VTX_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int vtx_set_kv_cmean(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
+                                void* centroids, const int64_t* loc, int64_t nnz, int num_kv_heads,
+                                int head_dim, int page_size, int dtype, void* stream) {
+    if (!k_cache || !v_cache || !new_k || !new_v || !centroids || !loc) return VTX_ERR_INVALID_ARGUMENT;
+    if (nnz < 0 || num_kv_heads < 1 || head_dim < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (head_dim % 8 != 0) return VTX_ERR_UNSUPPORTED;
+    if (nnz == 0) return VTX_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == VTX_BF16)
+        return launch_set_kv_cmean<__nv_bfloat16>(k_cache, v_cache, new_k, new_v, centroids, loc, nnz, num_kv_heads,
+                                                  head_dim, page_size, st);
+    if (dtype == VTX_F32)
+        return launch_set_kv_cmean<float>(k_cache, v_cache, new_k, new_v, centroids, loc, nnz, num_kv_heads,
+                                          head_dim, page_size, st);
     return VTX_ERR_INVALID_ARGUMENT;
 }

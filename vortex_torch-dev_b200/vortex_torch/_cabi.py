@@ -32,6 +32,7 @@ SIGNATURES = {
     "vtx_plan_decode": [_p, _p, _i64, _p] + [_p] * 10 + [_p] * 4 + [_i64] + [_i] * 8 + [_p],
     "vtx_set_kv": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _p],
     "vtx_cmean": [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _p],
+    "vtx_set_kv_cmean": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _p],
     "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
@@ -144,6 +145,16 @@ def cmean(x, out, loc, num_kv_heads, page_size) -> None:
     rc = lib.vtx_cmean(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
                        int(page_size), dtype_code(x.dtype), stream_of(x))
     check(rc, "vtx_cmean")
+
+
+def set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, page_size) -> None:
+    want(loc, torch.int64, "loc")
+    nnz, H, D = new_k.shape
+    if not (k_cache.dtype == v_cache.dtype == new_k.dtype == new_v.dtype == centroids.dtype):
+        raise TypeError("set_kv_cmean: caches, new tokens and centroids must share a dtype")
+    rc = lib.vtx_set_kv_cmean(ptr(k_cache), ptr(v_cache), ptr(new_k), ptr(new_v), ptr(centroids), ptr(loc), nnz, H,
+                              D, int(page_size), dtype_code(k_cache.dtype), stream_of(k_cache))
+    check(rc, "vtx_set_kv_cmean")
 
 
 def gemv(q_mean, centroids, scores, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos) -> None:

@@ -11,10 +11,28 @@ class Context(ContextBase):
     __slots__ = ContextBase.__slots__ + (
         "max_new_tokens_per_batch", "page_size", "total_num_pages", "head_dim", "head_num",
         "_aux_total_bytes", "_aux_total_flops",
+        # a KV write handed over by the runtime that the first cache operator may fuse with its own kernel
+        "_pending_kv",
     )
 
     def __init__(self) -> None:
-        self._reset_slots("Cache")
+        self._reset_slots("Cache", {"_pending_kv": None})
+
+    # ---- deferred KV write (fusion of set_kv with the flow's first cache operator) ----
+    def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int) -> None:
+        """Record a KV write instead of launching it.  The next cache operator either folds it into
+        its own kernel (``Mean(dim=1)`` over the same K cache and ``loc``) or launches it first;
+        the caller must call ``flush_kv_write`` after ``forward_cache`` in case no operator ran."""
+        self.flush_kv_write()
+        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size)
+
+    def flush_kv_write(self) -> None:
+        pend = self._pending_kv
+        if pend is not None:
+            self._pending_kv = None
+            from .set_kv import set_kv_buffer_launcher
+
+            set_kv_buffer_launcher(*pend)
 
     def create(self, parent: Any, model_runner: Any, *, overwrite: bool = False) -> "Context":
         """``parent`` is the KV pool (page_size, num_pages, head_num, head_dim)."""

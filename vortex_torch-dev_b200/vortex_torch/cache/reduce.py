@@ -54,6 +54,17 @@ class Reduce(vOp):
     def execute(self, x: torch.Tensor, output: Optional[torch.Tensor], loc: torch.Tensor,
                 ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}called before profile() (impl is None)"
+        pend = getattr(ctx, "_pending_kv", None)
+        if pend is not None:
+            k_cache, v_cache, new_k, new_v, ploc, P = pend
+            if (x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
+                    and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
+                    and new_k.shape[1] == ctx.head_num):
+                # the runtime's KV write and this mean touch the same page: one kernel does both
+                ctx._pending_kv = None
+                _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, output, loc, P)
+                return output
+            ctx.flush_kv_write()
         self.impl(x, output, loc, ctx.head_num, ctx.page_size)
         return output
 

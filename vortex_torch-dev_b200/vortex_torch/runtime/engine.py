@@ -152,8 +152,11 @@ class VortexDecodeRuntime:
         ``q`` ``[bs, H_q, D]``, ``new_k``/``new_v`` ``[bs, H_kv, D]``, ``loc`` ``[bs]`` int64, ``out`` like ``q``.
         """
         cache = self.pool.buffers[layer]
-        set_kv_buffer_launcher(cache["k"], cache["v"], new_k, new_v, loc, self.P)
+        # The KV write is handed to the cache context so that the flow's first cache operator can fold
+        # it into its own kernel; whatever is left is launched right after forward_cache.
+        self.cctx.defer_kv_write(cache["k"], cache["v"], new_k, new_v, loc, self.P)
         self.flow.forward_cache(cache, loc, ctx=self.cctx)
+        self.cctx.flush_kv_write()
         qv = q.view(-1, self.G, self.D)
         ov = out.view(-1, self.G, self.D)
         if layer in self.skip:
