@@ -325,6 +325,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="debug: smaller batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--pdl", action="store_true",
+                    help="chain the kernels of the graph by programmatic dependent launch (measured slower: 1.70 vs 1.62 ms)")
     args = ap.parse_args()
     cfg = dict(CFG)
     if args.layers:
@@ -350,7 +352,7 @@ def main():
 
     rt, step, slots = build_runtime(cfg, device, seed=1234 + rank)
     if not args.no_graph:
-        step.capture()
+        step.capture(programmatic_launch=args.pdl)
     W = max(3, args.warmup)
     for _ in range(W):
         step.replay()
@@ -418,7 +420,7 @@ def main():
             e2e=dict(value=world * args.steps / e2e_s, unit="steps/s", h2d_bytes_per_step=step.h2d_bytes,
                      d2h_bytes_per_step=step.d2h_bytes),
             gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
-            cuda_graph=not args.no_graph,
+            cuda_graph=not args.no_graph, programmatic_launch=bool(args.pdl and not args.no_graph),
             roofline=dict(kernel="decode_gqa_kernel (sparse layers)", traffic=None,
                           **roof(ab["sparse_kv_per_layer"], kt["decode_sparse"])),
             kernels=dict(indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),

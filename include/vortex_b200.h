@@ -39,6 +39,15 @@ const char* vtx_status_string(int status);
 const char* vtx_last_cuda_error(void);
 
 /*
+ * Switch programmatic dependent launch on (non-zero) or off (zero, the default) for every later
+ * launch of this library in the process.  When on, each kernel is launched with the programmatic
+ * stream-serialization attribute; each kernel waits for the complete preceding launch before it
+ * touches memory, so results are unchanged and only launch latency overlaps.  No counterpart in
+ * the reference (it launches every kernel with plain stream order).
+ */
+int vtx_set_programmatic_launch(int enable);
+
+/*
  * Block-table builder for one decode step.
  * Replaces `sglang_plan_decode` (csrc/register.h:15-36, csrc/utils_sglang.cu:313-460;
  * kernels :123-184, :188-254, :257-309) and, when the four trailing table pointers

@@ -146,3 +146,37 @@ def test_vortex_torch_C_shim_signatures():
     np.testing.assert_array_equal(sin_.cpu().numpy()[:ns], ref["sparse_kv_indices"])
     with pytest.raises(NotImplementedError):
         C.sglang_plan_prefill()
+
+
+def test_graphed_step_with_programmatic_launch_matches_eager():
+    """The CUDA-graph replay of a step, kernels chained by programmatic dependent launch, gives the
+    eager results bit for bit (and keeps doing so over repeated replays)."""
+    from vortex_torch.runtime import GraphedDecodeStep
+
+    seq, L, H, G, D, P, K = [2048, 1000, 4096, 300], 3, 8, 2, 128, 16, 30
+    prob = vo.make_paged_problem(17, seq, H, G, D, P)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16)
+    for l in range(L):
+        pl = vo.make_paged_problem(200 + l, seq, H, G, D, P)
+        for name in ("k", "v", "centroids"):
+            rt.pool.buffers[l][name].copy_(pl[name])
+    bs = len(seq)
+    step = GraphedDecodeStep(rt, bs)
+    step.seq_lens.copy_(torch.as_tensor(prob["seq_lens"]))
+    step.req_indices.copy_(torch.as_tensor(prob["req_indices"]))
+    step.loc.copy_(torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)]))
+    step.q.normal_(); step.new_k.normal_(); step.new_v.normal_()
+    step.replay()  # eager: no graph yet
+    torch.cuda.synchronize()
+    want_out, want_sel = step.out.clone(), rt.backend.kv_indices_decode[1].clone()
+    for pdl in (False, True):
+        step.graph = None
+        step.capture(programmatic_launch=pdl)
+        for _ in range(5):
+            step.out.zero_()
+            rt.backend.kv_indices_decode[1].fill_(-1)
+            step.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(step.out, want_out), f"graph replay differs (programmatic_launch={pdl})"
+        ns = int(rt.backend.kv_indptr_decode[1][bs * H].item())
+        assert torch.equal(rt.backend.kv_indices_decode[1][:ns], want_sel[:ns])

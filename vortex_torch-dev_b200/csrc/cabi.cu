@@ -3,8 +3,11 @@
 
 #include "vtx_common.cuh"
 
+#include <atomic>
+
 namespace {
 thread_local char g_last_error[256] = "";
+std::atomic<int> g_pdl{0};
 }
 
 namespace vtx {
@@ -13,6 +16,7 @@ void note_cuda_error(cudaError_t e) {
     strncpy(g_last_error, s ? s : "unknown CUDA error", sizeof(g_last_error) - 1);
     g_last_error[sizeof(g_last_error) - 1] = '\0';
 }
+bool programmatic_launch_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
 }  // namespace vtx
 
 extern "C" int vtx_version(void) { return 100; /* 0.1.0 */ }
@@ -28,3 +32,8 @@ extern "C" const char* vtx_status_string(int status) {
 }
 
 extern "C" const char* vtx_last_cuda_error(void) { return g_last_error; }
+
+extern "C" int vtx_set_programmatic_launch(int enable) {
+    g_pdl.store(enable ? 1 : 0, std::memory_order_relaxed);
+    return VTX_OK;
+}

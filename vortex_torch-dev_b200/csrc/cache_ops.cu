@@ -15,6 +15,8 @@ __global__ void __launch_bounds__(256) set_kv_kernel(uint4* __restrict__ k_cache
                                                     const uint4* __restrict__ new_v,
                                                     const int64_t* __restrict__ loc, int64_t nnz, int H,
                                                     int vec_per_row, int P) {
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int64_t total = nnz * H * vec_per_row;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
@@ -37,6 +39,8 @@ __global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* 
                                                    const int64_t* __restrict__ loc, int64_t nnz, int H,
                                                    int rows, int cols, int P) {
     constexpr int GROUPS = 256 / LANES;
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int lane = threadIdx.x % LANES;
     const int64_t items = nnz * H;
     const int nchunk = cols / 8;
@@ -86,6 +90,8 @@ __global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cac
                                                           T* __restrict__ centroids, const int64_t* __restrict__ loc,
                                                           int64_t nnz, int H, int D, int P) {
     constexpr int GROUPS = 256 / LANES;
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int lane = threadIdx.x % LANES;
     const int64_t items = nnz * H;
     const int nchunk = D / 8;
@@ -143,12 +149,12 @@ int launch_set_kv_cmean(void* k, void* v, const void* nk, const void* nv, void* 
     const int64_t items = nnz * H;
     if (D <= 128) {
         const int64_t blocks = (items + 15) / 16;
-        set_kv_cmean_kernel<T, 16><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
-            (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
+        return vtx::launch(set_kv_cmean_kernel<T, 16>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
+                           (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
     } else {
         const int64_t blocks = (items + 7) / 8;
-        set_kv_cmean_kernel<T, 32><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
-            (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
+        return vtx::launch(set_kv_cmean_kernel<T, 32>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
+                           (T*)k, (T*)v, (const T*)nk, (const T*)nv, (T*)cent, loc, nnz, H, D, P);
     }
     return vtx::finish_launch();
 }
@@ -159,12 +165,12 @@ int launch_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int 
     const int64_t items = nnz * H;
     if (cols <= 128) {
         const int64_t blocks = (items + 15) / 16;
-        cmean_kernel<T, 16><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
-            (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+        return vtx::launch(cmean_kernel<T, 16>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
+                           (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
     } else {
         const int64_t blocks = (items + 7) / 8;
-        cmean_kernel<T, 32><<<(unsigned)std::min<int64_t>(blocks, 1 << 20), 256, 0, st>>>(
-            (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+        return vtx::launch(cmean_kernel<T, 32>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
+                           (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
     }
     return vtx::finish_launch();
 }
@@ -183,10 +189,9 @@ extern "C" int vtx_set_kv(void* k_cache, void* v_cache, const void* new_k, const
     const int vec_per_row = head_dim * esize / 16;
     const int64_t total = nnz * num_kv_heads * vec_per_row;
     const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 1 << 20);
-    set_kv_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((uint4*)k_cache, (uint4*)v_cache,
-                                                            (const uint4*)new_k, (const uint4*)new_v, loc, nnz,
-                                                            num_kv_heads, vec_per_row, page_size);
-    return vtx::finish_launch();
+    return vtx::launch(set_kv_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (uint4*)k_cache,
+                       (uint4*)v_cache, (const uint4*)new_k, (const uint4*)new_v, loc, nnz, num_kv_heads,
+                       vec_per_row, page_size);
 }
 
 extern "C" int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads, int rows,

@@ -84,9 +84,11 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
     constexpr int CH_PER_ROW = D * (int)sizeof(T) / 16;
     constexpr int CPL = CHUNKS / 32;              // chunks copied per lane per tile
     static_assert(CHUNKS % 32 == 0, "tile must split evenly over a warp");
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     T* ring = reinterpret_cast<T*>(smem_raw);
 
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int s = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPT, tg = lane / LPT;
@@ -317,6 +319,8 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_gqa_mma_kernel(DecodeAr
     constexpr int CPL = CHUNKS / 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
 
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int s = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tid = lane & 3;
@@ -505,8 +509,7 @@ int launch_mma_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
             return VTX_ERR_CUDA;
         }
     }
-    kern<<<eff_bs, kWarps * 32, bytes, st>>>(a);
-    return vtx::finish_launch();
+    return vtx::launch(kern, dim3(eff_bs), dim3(kWarps * 32), bytes, st, a);
 }
 
 template <int G>
@@ -542,8 +545,7 @@ int launch_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
             return VTX_ERR_CUDA;
         }
     }
-    kern<<<eff_bs, kWarps * 32, bytes, st>>>(a);
-    return vtx::finish_launch();
+    return vtx::launch(kern, dim3(eff_bs), dim3(kWarps * 32), bytes, st, a);
 }
 
 template <typename T, int G>

@@ -273,6 +273,8 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
     Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + Gm::row_bytes);
     int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
 
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int s = blockIdx.x;
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
@@ -380,12 +382,14 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads) topk_kernel(const T* __restrict__ scores, IndexerArgs a) {
     using Key = typename KeyOf<T>::type;
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     // layout: [scratch for the register sort][keys][ids]
     Key* xbuf = reinterpret_cast<Key*>(smem_raw);
     const int scratch_keys = 2 * (a.key_cap < 512 ? 512 : (a.key_cap < 2048 ? a.key_cap : 2048));
     Key* keys = xbuf + scratch_keys;
     int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int s = blockIdx.x;
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
@@ -421,8 +425,7 @@ int launch_indexer_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     auto kern = indexer_kernel<T, D, MODE>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    kern<<<eff_bs, kThreads, bytes, st>>>(a);
-    return vtx::finish_launch();
+    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, a);
 }
 
 template <typename T, int MODE>
@@ -445,8 +448,7 @@ int launch_topk(const void* scores, const IndexerArgs& a, int eff_bs, cudaStream
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
     int rc = set_smem(topk_kernel<T>, bytes);
     if (rc != VTX_OK) return rc;
-    topk_kernel<T><<<eff_bs, kThreads, bytes, st>>>((const T*)scores, a);
-    return vtx::finish_launch();
+    return vtx::launch(topk_kernel<T>, dim3(eff_bs), dim3(kThreads), bytes, st, (const T*)scores, a);
 }
 
 int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int bos, int eos, int maxp,

@@ -61,6 +61,8 @@ __device__ __forceinline__ int chunks_of(int pages, int bos, int eos, int K, int
 
 __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     __shared__ int3 red[kPlanThreads / 32];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
     const int r = blockIdx.x, h = blockIdx.y, tx = threadIdx.x;
     const int budget = a.K + a.bos + a.eos;
 
@@ -191,6 +193,5 @@ extern "C" int vtx_plan_decode(const int32_t* cached_seq_lens, const int32_t* re
     a.eos = page_reserved_eos;
     a.max_chunk = max_chunk_size;
     dim3 grid(batch_size, num_kv_heads);
-    plan_decode_kernel<<<grid, kPlanThreads, 0, (cudaStream_t)stream>>>(a);
-    return vtx::finish_launch();
+    return vtx::launch(plan_decode_kernel, grid, dim3(kPlanThreads), 0, (cudaStream_t)stream, a);
 }

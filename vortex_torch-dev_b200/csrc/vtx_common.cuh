@@ -21,6 +21,36 @@ inline int finish_launch() {
     return VTX_OK;
 }
 
+// Programmatic dependent launch.  Every kernel of this library starts with pdl_wait() (all work of the
+// preceding launch on the stream is complete and visible once it returns) followed by pdl_trigger()
+// (the next launch may start placing its CTAs), so a launch never reads or writes anything before its
+// predecessor has finished; what overlaps is only the launch latency and CTA start-up of the next kernel
+// with the drain of the current one.  Both instructions are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool programmatic_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+inline int launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = programmatic_launch_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+    if (e != cudaSuccess) {
+        note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
+    return finish_launch();
+}
+
 __host__ __device__ inline int pow2_ceil(int n) {
     int p = 1;
     while (p < n) p <<= 1;

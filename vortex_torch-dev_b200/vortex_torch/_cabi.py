@@ -42,12 +42,20 @@ for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.argtypes = _args
     _fn.restype = _i
+lib.vtx_set_programmatic_launch.argtypes = [_i]
+lib.vtx_set_programmatic_launch.restype = _i
 lib.vtx_version.restype = _i
 lib.vtx_status_string.argtypes = [_i]
 lib.vtx_status_string.restype = C.c_char_p
 lib.vtx_last_cuda_error.restype = C.c_char_p
 
-EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error"])
+EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error",
+                                    "vtx_set_programmatic_launch"])
+
+
+def set_programmatic_launch(enable: bool) -> None:
+    """Overlap each kernel's launch latency with the drain of the previous one (results unchanged)."""
+    lib.vtx_set_programmatic_launch(1 if enable else 0)
 
 
 def version() -> int:

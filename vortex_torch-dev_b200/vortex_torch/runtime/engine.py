@@ -203,7 +203,17 @@ class GraphedDecodeStep:
     def _eager(self) -> None:
         self.rt.step(self.seq_lens, self.req_indices, self.q, self.new_k, self.new_v, self.loc, self.out)
 
-    def capture(self) -> None:
+    def capture(self, programmatic_launch: bool = False) -> None:
+        """Capture the step.  With ``programmatic_launch`` the kernels are chained by programmatic
+        dependent launch inside the graph (each still waits for its whole predecessor).  Off by
+        default: on the 84-kernel Qwen3-shaped step it measured 5 % slower than plain graph edges."""
+        _cabi.set_programmatic_launch(programmatic_launch)
+        try:
+            self._capture()
+        finally:
+            _cabi.set_programmatic_launch(False)
+
+    def _capture(self) -> None:
         side = torch.cuda.Stream(self.rt.device)
         side.wait_stream(torch.cuda.current_stream(self.rt.device))
         with torch.cuda.stream(side):
