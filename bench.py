@@ -344,6 +344,12 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    # Libraries (NCCL's version banner, for one) write to stdout; the JSON line must be the only thing
+    # there, so everything else goes to stderr until the line is printed.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -435,7 +441,8 @@ def main():
             line["cpu_baseline"] = cpu_baseline(cfg)
         elif not args.no_cpu_baseline:
             line["cpu_baseline"] = None
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
