@@ -155,6 +155,20 @@ int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void
                    const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
                    int head_dim, int page_size, float sm_scale, int dtype, void* stream);
 
+/*
+ * Block-table decode attention over a shared compressed latent (multi-head latent attention):
+ * keys are the full latent row, values its first value_dim dims.  No counterpart in the reference
+ * (it has no MLA path); the page table and sequence lengths are the block-table form its planner
+ * emits (csrc/utils_sglang.cu:949-1083), as written by vtx_plan_decode and vtx_indexer_fused.
+ * q [bs, num_heads, latent_dim]; latent_cache [rows, page_size, latent_dim]; out [bs, num_heads, value_dim];
+ * page_table [bs, page_table_stride] row ids; cache_seqlens [bs] token counts.
+ * Built for bf16, 16 heads, latent 576, values 512, page_size a multiple of 16.
+ */
+int vtx_decode_mla(const void* q, const void* latent_cache, void* out, const int32_t* page_table,
+                   int64_t page_table_stride, const int32_t* cache_seqlens, int batch_size,
+                   int num_heads, int latent_dim, int value_dim, int page_size, float sm_scale,
+                   int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

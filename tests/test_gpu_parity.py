@@ -226,3 +226,37 @@ def test_decode_is_invariant_to_page_order():
                          1.0 / math.sqrt(D))
         outs.append(o)
     assert close(outs[0], outs[1], 1e-2)
+
+
+# ------------------------------------------------------------------ MLA block-table decode
+@pytest.mark.parametrize("seq,K", [([4096, 1300, 64, 65, 1, 700], 32), ([16384, 8000], 32), ([100, 3000], 5)])
+def test_mla_block_table_decode(seq, K):
+    """Config-5 shapes: 16 heads over a 576-dim latent, page 64; plan (table form) -> fused indexer -> decode."""
+    H, G, D, P, bos, eos = 1, 16, 576, 64, 1, 1
+    prob = vo.make_paged_problem(31, seq, H, G, D, P, v_dim=8)
+    dp = DevicePlan(prob, P, H, K, bos, eos, tables=True)
+    ref = dp.oracle(prob)
+    vo.forward_indexer(prob["q"], prob["centroids"], ref, K, bos, eos)
+    d = to_dev(prob)
+    _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices,
+                        dp.sparse_indices, dp.S, K, bos, eos, dp.max_pages, sparse_page_table=dp.tables[2])
+    bs = len(seq)
+    for s in range(bs):  # the table rows hold the same selection as the packed list
+        n = int(ref["sparse_kv_indptr"][s + 1] - ref["sparse_kv_indptr"][s])
+        np.testing.assert_array_equal(dp.tables[2][s, :n].cpu().numpy(), ref["sparse_page_table"][s, :n])
+    scale = 1.0 / math.sqrt(192.0)
+    for table, lens, rt, rl in ((dp.tables[2], dp.tables[3], ref["sparse_page_table"], ref["sparse_cache_seqlens"]),
+                                (dp.tables[0], dp.tables[1], ref["dense_page_table"], ref["dense_cache_seqlens"])):
+        want = vo.decode_mla(prob["q"], prob["k"], rt, rl, 512, scale)
+        out = torch.empty(bs, G, 512, dtype=torch.bfloat16, device="cuda")
+        _cabi.decode_mla(d["q"], d["k"], out, table, lens, P, scale)
+        assert close(out, want, BF16_TOL), f"max err {(out.float().cpu() - want.float()).abs().max()}"
+
+
+def test_mla_rejects_other_shapes():
+    z = torch.zeros(1, 8, 576, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="not supported"):
+        _cabi.decode_mla(z, torch.zeros(1, 64, 576, dtype=torch.bfloat16, device="cuda"),
+                         torch.zeros(1, 8, 512, dtype=torch.bfloat16, device="cuda"),
+                         torch.zeros(1, 4, dtype=torch.int32, device="cuda"), torch.ones(1, dtype=torch.int32, device="cuda"),
+                         64, 0.1)

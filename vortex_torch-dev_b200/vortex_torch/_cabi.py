@@ -37,6 +37,7 @@ SIGNATURES = {
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -203,3 +204,15 @@ def decode_gqa(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len
                             ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_gqa")
+
+
+def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_scale) -> None:
+    """q [bs, heads, latent_dim], latent_cache [rows, P, latent_dim], out [bs, heads, value_dim]."""
+    want(page_table, torch.int32, "page_table")
+    want(cache_seqlens, torch.int32, "cache_seqlens")
+    if not (q.dtype == latent_cache.dtype == out.dtype):
+        raise TypeError("decode_mla: q, latent cache and out must share a dtype")
+    rc = lib.vtx_decode_mla(ptr(q), ptr(latent_cache), ptr(out), ptr(page_table), page_table.shape[1],
+                            ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
+                            float(sm_scale), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_decode_mla")
