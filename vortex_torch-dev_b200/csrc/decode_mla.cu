@@ -5,10 +5,12 @@
 // project has no such kernel; the block-table inputs are the ones its planner produces
 // (csrc/utils_sglang.cu:949-1083: page table [bs, stride] and per-request sequence lengths).
 //
-// One CTA (4 warps) per request.  The token list is cut in tiles of 16 tokens (18 KB); tiles stream
-// global -> shared through an 8-slot ring of 16-byte cp.async copies (~129 KB in flight per SM), rows
-// stored chunk-swizzled (chunk ^ (row & 7)) so ldmatrix is conflict-free.  Per tile, on mma.sync
-// m16n8k16 (the 16 heads are exactly one M tile):
+// One CTA per request: two groups of 4 warps, each group takes every other 16-token tile (18 KB) of the
+// token list and keeps its own running softmax state; the two states are merged once at the end.  Each
+// group streams its tiles global -> shared through its own 4-slot ring of 16-byte cp.async copies
+// (~110 KB in flight per SM) and synchronises on its own named barrier, so the groups overlap freely.
+// Rows are stored chunk-swizzled (chunk ^ (row & 7)) so ldmatrix is conflict-free.  Per tile, on
+// mma.sync m16n8k16 (the 16 heads are exactly one M tile):
 //   S^T[head, token] = q . K^T   the 576 dims are split over the warps (9 k-steps each, q fragments in
 //                                registers); partial sums meet in shared memory
 //   O^T[dim, head]  += V^T . P^T each warp owns 128 output dims; P^T is the accumulator layout of S^T
@@ -24,7 +26,8 @@ constexpr int kDv = 512;                 // leading dims: values
 constexpr int kTile = 16;                // tokens per tile
 constexpr int kRowB = kDl * 2;           // 1152 bytes
 constexpr int kTileB = kTile * kRowB;    // 18432 bytes
-constexpr int kStages = 8;
+constexpr int kGroups = 2;               // warp groups per CTA, alternating tiles
+constexpr int kStages = 4;               // ring slots per group
 constexpr int kKsteps = kDl / 16;        // 36
 constexpr int kKsPerWarp = kKsteps / kWarps;          // 9
 constexpr int kMtPerWarp = kDv / 16 / kWarps;         // 8 output tiles of 16 dims per warp
@@ -75,21 +78,29 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
+__device__ __forceinline__ void group_sync(int group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(kWarps * 32) : "memory");
+}
+
+__global__ void __launch_bounds__(kGroups * kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    // layout: [ring: kStages tiles][partial S^T: 2 buffers x kWarps x 16 tokens... see below]
-    float* s_part = reinterpret_cast<float*>(smem_raw + (size_t)kStages * kTileB);  // [2][kWarps][2 ntile][32 lanes][4]
+    // layout: [group 0 ring][group 1 ring][partial S^T: per group 2 buffers x kWarps x 2 n-tiles x 32 lanes x 4]
     vtx::pdl_wait();
     vtx::pdl_trigger();
 
     const int b = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = threadIdx.x / (kWarps * 32), gthread = threadIdx.x % (kWarps * 32);
+    const int warp = gthread >> 5, lane = threadIdx.x & 31;
+    float* s_part = reinterpret_cast<float*>(smem_raw + (size_t)kGroups * kStages * kTileB) +
+                    (size_t)group * (2 * kWarps * 2 * 32 * 4);
     const int gid = lane >> 2, tid = lane & 3;
     const int ntok = a.seqlens[b];
     const int n_tiles = (ntok + kTile - 1) / kTile;
     const int tiles_per_page = a.P / kTile;
     const int32_t* pt = a.page_table + (int64_t)b * a.pt_stride;
-    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const uint32_t ring_addr = (uint32_t)__cvta_generic_to_shared(smem_raw) + group * (kStages * kTileB);
+    // this group's tiles: group, group + kGroups, ...; `ord` counts them
+    const int my_tiles = n_tiles > group ? (n_tiles - group + kGroups - 1) / kGroups : 0;
 
     // q fragments (A operand, 16 heads x 16 dims per k-step) for this warp's 9 k-steps
     uint32_t qa[kKsPerWarp][4];
@@ -114,15 +125,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
             for (int i = 0; i < 4; ++i) o[mt][j][i] = 0.f;
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;  // heads gid and gid + 8
 
-    auto issue = [&](int tile) {
+    auto issue = [&](int ord) {
+        const int tile = group + ord * kGroups;
         const int page = tile / tiles_per_page, t_in = tile - page * tiles_per_page;
         const int64_t row = pt[page];
         const unsigned char* src = a.latent + ((row * a.P) + (int64_t)t_in * kTile) * kRowB;
-        const uint32_t dst = ring_addr + (uint32_t)((tile % kStages) * kTileB);
+        const uint32_t dst = ring_addr + (uint32_t)((ord % kStages) * kTileB);
         const int tok0 = tile * kTile;
 #pragma unroll
         for (int c = 0; c < kChunksPerTile / (kWarps * 32); ++c) {
-            const int ch = c * (kWarps * 32) + threadIdx.x;
+            const int ch = c * (kWarps * 32) + gthread;
             const int t = ch / kChunksPerRow, cr = ch - t * kChunksPerRow;
             cp_async16(dst + t * kRowB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < ntok);
         }
@@ -130,19 +142,20 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
 
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {
-        if (i < n_tiles) issue(i);
+        if (i < my_tiles) issue(i);
         cp_async_commit();
     }
     const int lm_t = ((lane >> 4) << 3) + (lane & 7);
     const int lm_c = (lane >> 3) & 1;
 
-    for (int tile = 0; tile < n_tiles; ++tile) {
+    for (int ord = 0; ord < my_tiles; ++ord) {
+        const int tile = group + ord * kGroups;
         cp_async_wait<kStages - 2>();
-        __syncthreads();  // tile landed for everyone; everyone is done with the slot refilled next
-        if (tile + kStages - 1 < n_tiles) issue(tile + kStages - 1);
+        group_sync(group);  // tile landed for the whole group; the group is done with the slot refilled next
+        if (ord + kStages - 1 < my_tiles) issue(ord + kStages - 1);
         cp_async_commit();
 
-        const uint32_t tile_addr = ring_addr + (uint32_t)((tile % kStages) * kTileB) + lm_t * kRowB;
+        const uint32_t tile_addr = ring_addr + (uint32_t)((ord % kStages) * kTileB) + lm_t * kRowB;
         // ---- partial S^T over this warp's dims
         float st[2][4];
 #pragma unroll
@@ -157,12 +170,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
             mma_bf16(st[0], qa[i][0], qa[i][1], qa[i][2], qa[i][3], kb[0], kb[1]);  // tokens 0-7
             mma_bf16(st[1], qa[i][0], qa[i][1], qa[i][2], qa[i][3], kb[2], kb[3]);  // tokens 8-15
         }
-        float* part = s_part + (size_t)(tile & 1) * (kWarps * 2 * 32 * 4);
+        float* part = s_part + (size_t)(ord & 1) * (kWarps * 2 * 32 * 4);
 #pragma unroll
         for (int j = 0; j < 2; ++j)
             *reinterpret_cast<float4*>(part + ((warp * 2 + j) * 32 + lane) * 4) =
                 make_float4(st[j][0], st[j][1], st[j][2], st[j][3]);
-        __syncthreads();
+        group_sync(group);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -231,12 +244,57 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_mla_kernel(MlaArgs a) {
     }
     cp_async_wait<0>();
 
-    // row sums over the 4 lanes of a head row, then normalise the columns this lane holds
+    // row sums over the 4 lanes of a head row
 #pragma unroll
     for (int w = 1; w <= 2; w <<= 1) {
         l_lo += __shfl_xor_sync(0xffffffffu, l_lo, w);
         l_hi += __shfl_xor_sync(0xffffffffu, l_hi, w);
     }
+    // ---- merge the two groups: group 1 parks its state in shared memory (the rings are idle now)
+    __syncthreads();
+    float* park = reinterpret_cast<float*>(smem_raw);  // [128 threads][68]: 64 accumulators + m_lo, m_hi, l_lo, l_hi
+    if (group == 1) {
+        float* mine = park + gthread * 68;
+#pragma unroll
+        for (int mt = 0; mt < kMtPerWarp; ++mt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                *reinterpret_cast<float4*>(mine + (mt * 2 + j) * 4) =
+                    make_float4(o[mt][j][0], o[mt][j][1], o[mt][j][2], o[mt][j][3]);
+        *reinterpret_cast<float4*>(mine + 64) = make_float4(m_lo, m_hi, l_lo, l_hi);
+    }
+    __syncthreads();
+    if (group == 1) return;
+    {
+        const float* other = park + gthread * 68;
+        const float4 st1 = *reinterpret_cast<const float4*>(other + 64);
+        const float M_lo = fmaxf(m_lo, st1.x), M_hi = fmaxf(m_hi, st1.y);
+        // a group that saw no tile has m = -inf and l = 0: its weight must be 0, not NaN
+        const float f0_lo = m_lo == -INFINITY ? 0.f : exp2f(m_lo - M_lo), f1_lo = st1.x == -INFINITY ? 0.f : exp2f(st1.x - M_lo);
+        const float f0_hi = m_hi == -INFINITY ? 0.f : exp2f(m_hi - M_hi), f1_hi = st1.y == -INFINITY ? 0.f : exp2f(st1.y - M_hi);
+        l_lo = l_lo * f0_lo + st1.z * f1_lo;
+        l_hi = l_hi * f0_hi + st1.w * f1_hi;
+        float w0[2][2], w1[2][2];  // weights of the columns this lane holds: heads 8j + tid*2 + {0,1}
+        w0[0][0] = __shfl_sync(0xffffffffu, f0_lo, (tid * 2) << 2);
+        w0[0][1] = __shfl_sync(0xffffffffu, f0_lo, (tid * 2 + 1) << 2);
+        w0[1][0] = __shfl_sync(0xffffffffu, f0_hi, (tid * 2) << 2);
+        w0[1][1] = __shfl_sync(0xffffffffu, f0_hi, (tid * 2 + 1) << 2);
+        w1[0][0] = __shfl_sync(0xffffffffu, f1_lo, (tid * 2) << 2);
+        w1[0][1] = __shfl_sync(0xffffffffu, f1_lo, (tid * 2 + 1) << 2);
+        w1[1][0] = __shfl_sync(0xffffffffu, f1_hi, (tid * 2) << 2);
+        w1[1][1] = __shfl_sync(0xffffffffu, f1_hi, (tid * 2 + 1) << 2);
+#pragma unroll
+        for (int mt = 0; mt < kMtPerWarp; ++mt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 v = *reinterpret_cast<const float4*>(other + (mt * 2 + j) * 4);
+                o[mt][j][0] = o[mt][j][0] * w0[j][0] + v.x * w1[j][0];
+                o[mt][j][1] = o[mt][j][1] * w0[j][1] + v.y * w1[j][1];
+                o[mt][j][2] = o[mt][j][2] * w0[j][0] + v.z * w1[j][0];
+                o[mt][j][3] = o[mt][j][3] * w0[j][1] + v.w * w1[j][1];
+            }
+    }
+    // normalise the columns this lane holds
     float inv[2][2];
     {
         const float i_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, i_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
@@ -281,11 +339,11 @@ extern "C" int vtx_decode_mla(const void* q, const void* latent_cache, void* out
     a.seqlens = cache_seqlens;
     a.P = page_size;
     a.scale_log2 = sm_scale * kLog2e;
-    const size_t bytes = (size_t)kStages * kTileB + (size_t)2 * kWarps * 2 * 32 * 4 * sizeof(float);
+    const size_t bytes = (size_t)kGroups * kStages * kTileB + (size_t)kGroups * 2 * kWarps * 2 * 32 * 4 * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(decode_mla_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess) {
         vtx::note_cuda_error(e);
         return VTX_ERR_CUDA;
     }
-    return vtx::launch(decode_mla_kernel, dim3(batch_size), dim3(kWarps * 32), bytes, (cudaStream_t)stream, a);
+    return vtx::launch(decode_mla_kernel, dim3(batch_size), dim3(kGroups * kWarps * 32), bytes, (cudaStream_t)stream, a);
 }
