@@ -9,20 +9,23 @@ CPU-baseline leg of the benchmark may import it; the product path never does.
 Parity status
 -------------
 * Integer planning (`plan_decode`), top-k ordering and the KV layout follow the
-  reference sources line by line (citations on each function) and are pinned
-  by hand-derived known-answer cases plus, on a GPU box, by the reference's own
-  CUDA kernels compiled into ``oracle/_ref`` (when that build is present).
+  reference sources line by line (citations on each function).  They are pinned
+  bit for bit by golden vectors recorded from the reference's own CUDA kernels
+  (`sglang_plan_decode`, `sglang_plan_decode_fa3`, `topk_output`, compiled for
+  sm_100 and run on a B200; tests/golden/ref_cuda_kernels.npz), by hand-derived
+  known-answer cases, and on a GPU box by running those reference kernels side
+  by side (tests/test_gpu_reference_crosscheck.py).
 * Floating-point order: the reference's GeMV/CMean reduction order is whatever
   Triton's layout produced and is pinned by no reference test.  The oracle
   fixes one canonical order (documented on `canonical_dot`), and the CUDA
   kernels implement exactly that order, so selections are bit-exact between the
-  two.  Against the reference's Triton kernels the agreement is within one
-  bf16 ulp of the score (checked by fixtures generated under the Triton
-  interpreter), not bit-exact: **parity unpinned** for the reduction order.
-* Paged attention and MLA decode are not in the reference tree at all (they
-  live in a third-party dependency, flashinfer-python 0.2.7.post1, called from
-  an un-vendored SGLang fork).  The oracle restates textbook softmax attention
-  over the listed pages: **parity unpinned**.
+  two.  Against the reference's Triton kernels (run under the Triton
+  interpreter, tests/golden/ref_triton_kernels.npz) the agreement is within one
+  bf16 ulp, not bit-exact: **parity unpinned** for the reduction order.
+* Paged attention and MLA decode are not in the reference tree at all (the
+  attention lives in a third-party dependency, flashinfer-python 0.2.7.post1,
+  called from an un-vendored SGLang fork; there is no MLA anywhere).  The oracle
+  restates textbook softmax attention over the listed pages: **parity unpinned**.
 
 All citations are paths inside the reference project.
 """
