@@ -397,6 +397,139 @@ def run_mla_workload(args):
     print(json.dumps(line))
 
 
+def run_ragged_workload(args):
+    """Side measurement (not the headline line): BASELINE config 3, one sparse layer of a ragged batch.
+
+    256 requests, context lengths uniform in [1024, 32768], 32 q heads / 8 KV heads / head_dim 128, bf16,
+    page 16, topk 64 + 1 + 1; requests are dealt to the ranks by total page count (strong scaling: the batch
+    is fixed, each rank holds only its own requests' pool).  No collective on the timed path; NCCL gathers
+    the selections of sampled requests for verification afterwards.
+    """
+    from oracle import vortex_oracle as vo
+    from vortex_torch import _cabi
+    from vortex_torch.runtime import balance_requests, gather_for_verification
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    nreq, Hq, H, D, P, K, bos, eos = 256, 32, 8, 128, 16, 64, 1, 1
+    G = Hq // H
+    g = torch.Generator().manual_seed(33)
+    seq_all = torch.randint(1024, 32769, (nreq,), generator=g).tolist()
+    pages_all = [(x + P - 1) // P for x in seq_all]
+    mine = balance_requests(pages_all, world)[rank]
+    seq = [seq_all[r] for r in mine]
+    n = [pages_all[r] for r in mine]
+    bs, total, maxp = len(mine), sum(n), max(n)
+    gl = torch.Generator().manual_seed(1000 + rank)
+    perm = torch.randperm(total, generator=gl)
+    r2t = torch.zeros(bs, maxp * P, dtype=torch.int32)
+    off = 0
+    for i in range(bs):
+        pg = perm[off:off + n[i]]
+        r2t[i, : n[i] * P] = (pg.view(-1, 1) * P + torch.arange(P).view(1, -1)).reshape(-1).to(torch.int32)
+        off += n[i]
+    i32 = dict(dtype=torch.int32, device=dev)
+    budget = K + bos + eos
+    S = bs * H
+    seq_d, r2t_d, ridx = torch.tensor(seq, **i32), r2t.to(dev), torch.arange(bs, device=dev)
+    dip, sip = torch.zeros(S + 1, **i32), torch.zeros(S + 1, **i32)
+    din, sin_ = torch.zeros(total * H, **i32), torch.zeros(S * budget, **i32)
+    last = torch.zeros(S, **i32)
+    w = [torch.zeros(total * H // 16 + S, **i32) for _ in range(3)] + [torch.zeros(1, **i32), torch.zeros(1, **i32)]
+    torch.manual_seed(1000 + rank)
+    k = torch.empty(total * H, P, D, dtype=torch.bfloat16, device=dev).normal_()
+    v = torch.empty(total * H, P, D, dtype=torch.bfloat16, device=dev).normal_()
+    cent = torch.zeros(total * H, 1, D, dtype=torch.bfloat16, device=dev)
+    _cabi.cmean(k, cent, torch.arange(total, device=dev, dtype=torch.int64) * P + (P - 1), H, P)
+    q = torch.randn(S, G, D, device=dev).bfloat16()
+    out = torch.empty_like(q)
+    scale = 1.0 / math.sqrt(D)
+
+    def layer():
+        _cabi.plan_decode(seq_d, r2t_d, ridx, dip, din, sip, sin_, last, *w, P, H, K, bos, eos, 64, 16)
+        _cabi.indexer_fused(q, cent, dip, sip, din, sin_, S, K, bos, eos, maxp)
+        _cabi.decode_gqa(q, k, v, out, sip, sin_, last, S, P, scale)
+
+    layer()
+    torch.cuda.synchronize(dev)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        layer()
+    for _ in range(max(3, args.warmup)):
+        gr.replay()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gr.replay()
+    e1.record()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    secs = e0.elapsed_time(e1) * 1e-3 / args.steps
+    if dist is not None:
+        tt = torch.tensor([secs], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        secs = float(tt[0])
+    # ---- verification of two sampled local requests against the CPU oracle, then gathered over NCCL
+    sel_local, ok = {}, True
+    sip_h, dip_h = sip.cpu().numpy(), dip.cpu().numpy()
+    for i in (0, bs // 2):
+        ni = n[i]
+        plan = vo.plan_decode([seq[i]], (np.arange(ni * P, dtype=np.int32)).reshape(1, -1), [0], P, H, K, bos, eos, 64, 16)
+        # oracle rows are page*H + h over a compact pool holding only this request, in logical order
+        kk = torch.stack([k[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
+        vv = torch.stack([v[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
+        cc = torch.stack([cent[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
+        qi = q[i * H:(i + 1) * H].cpu()
+        vo.forward_indexer(qi, cc, plan, K, bos, eos)
+        a, b = sip_h[i * H], sip_h[(i + 1) * H]
+        got_rows = sin_[a:b].cpu().numpy()
+        # translate device rows (physical page * H + h) to the compact numbering (logical page * H + h)
+        phys_to_log = {int(r2t[i, pg * P].item()) // P: pg for pg in range(ni)}
+        got = np.asarray([phys_to_log[int(r) // H] * H + int(r) % H for r in got_rows], dtype=np.int32)
+        ok = ok and bool(np.array_equal(got, plan["sparse_kv_indices"]))
+        want = vo.decode_gqa(qi, kk, vv, plan["sparse_kv_indptr"], plan["sparse_kv_indices"], plan["kv_last_page_len"])
+        gotv = out[i * H:(i + 1) * H].float().cpu()
+        ok = ok and bool(((gotv - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
+        sel_local[mine[i]] = torch.as_tensor(got.astype(np.int64), device=dev)
+    gathered = gather_for_verification(sel_local)
+    flags = torch.tensor([int(ok)], device=dev, dtype=torch.int32)
+    if dist is not None:
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    # ---- algorithmic bytes of the whole batch (all ranks)
+    cent_b = sum(H * max(0, p - bos - eos) * D * 2 for p in pages_all if p - bos - eos > K)
+    kv_b = 0
+    for s_len, p in zip(seq_all, pages_all):
+        toks = s_len if p <= budget else (budget - 1) * P + (s_len % P or P)
+        kv_b += H * toks * D * 2 * 2
+    peaks, kind = measured_peaks()
+    if rank == 0:
+        line = dict(workload="config 3: ragged batch, 256 requests ctx U[1024,32768], 32q/8kv heads, D128, page 16, "
+                             "topk 64+1+1, one sparse layer (plan + fused indexer + decode)",
+                    n_gpus=world, scaling="strong", requests_per_rank=[len(x) for x in balance_requests(pages_all, world)],
+                    us_per_layer=secs * 1e6, layers_per_s=1.0 / secs, algorithmic_bytes=cent_b + kv_b,
+                    achieved_gbs=(cent_b + kv_b) / secs / 1e9, frac_of_n_x_peak=(cent_b + kv_b) / secs / 1e9 / (world * peaks["hbm_gbs"]),
+                    peak_kind=f"of {kind}", parity_sample_ok=bool(int(flags.item())), verified_requests=sorted(gathered))
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -409,11 +542,14 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--pdl", action="store_true",
                     help="chain the kernels of the graph by programmatic dependent launch (measured slower: 1.70 vs 1.62 ms)")
-    ap.add_argument("--workload", default="c2", choices=["c2", "c5"],
+    ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"],
                     help="c2 = the headline decode step; c5 = side measurement of the MLA block-table decode")
     args = ap.parse_args()
     if args.workload == "c5":
         run_mla_workload(args)
+        return
+    if args.workload == "c3":
+        run_ragged_workload(args)
         return
     cfg = dict(CFG)
     if args.layers:

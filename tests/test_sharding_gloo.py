@@ -1,0 +1,67 @@
+"""The multi-rank path on CPU: two gloo ranks shard a ragged batch by request, each computes its shard
+(with the oracle standing in for the GPU kernels), results are gathered for verification and must equal
+the single-process result.  No collective is used anywhere but in that gather."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parent.parent
+SEQ = [1024, 5000, 333, 16, 2500, 700, 64, 4100]
+H, G, D, P, K = 2, 2, 64, 16, 8
+
+
+def _selection_for(requests):
+    """Oracle selection + attention output for a subset of requests, keyed by global request id."""
+    from oracle import vortex_oracle as vo
+
+    sel, out = {}, {}
+    for r in requests:
+        prob = vo.make_paged_problem(1000 + r, [SEQ[r]], H, G, D, P)   # a request's data depends on its id only
+        plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, 1, 1, 64, 16)
+        vo.forward_indexer(prob["q"], prob["centroids"], plan, K, 1, 1)
+        sel[r] = torch.as_tensor(plan["sparse_kv_indices"].astype(np.int64))
+        out[r] = vo.decode_gqa(prob["q"], prob["k"], prob["v"], plan["sparse_kv_indptr"], plan["sparse_kv_indices"],
+                               plan["kv_last_page_len"]).float()
+    return sel, out
+
+
+def _worker(rank, world, port, q):
+    for p in (str(ROOT), str(ROOT / "vortex_torch-dev_b200")):
+        sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vortex_torch.runtime import balance_requests, gather_for_verification
+
+    pages = [(s + P - 1) // P for s in SEQ]
+    parts = balance_requests(pages, world)            # every rank computes the same assignment
+    sel, out = _selection_for(parts[rank])
+    all_sel = gather_for_verification(sel)
+    all_out = gather_for_verification(out)
+    if rank == 0:
+        q.put((parts, {k: v.numpy() for k, v in all_sel.items()}, {k: v.numpy() for k, v in all_out.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharding_matches_single_process():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29000 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    parts, sel, out = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(parts[0] + parts[1]) == list(range(len(SEQ)))
+    want_sel, want_out = _selection_for(range(len(SEQ)))
+    assert sorted(sel) == list(range(len(SEQ)))
+    for r in range(len(SEQ)):
+        np.testing.assert_array_equal(sel[r], want_sel[r].numpy())
+        np.testing.assert_array_equal(out[r], want_out[r].numpy())

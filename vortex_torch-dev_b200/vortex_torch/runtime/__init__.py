@@ -8,7 +8,7 @@ reference's ``Context.create`` methods read, runs the profile pass, and drives o
 """
 from .engine import (AttentionBackendStub, GraphedDecodeStep, KVPool, ModelConfig, ModelRunnerStub, ReqToTokenPool, ServerArgs,
                      VortexDecodeRuntime)
-from .sharding import balance_requests
+from .sharding import balance_requests, gather_for_verification
 
 __all__ = ["ServerArgs", "ModelConfig", "ReqToTokenPool", "ModelRunnerStub", "KVPool", "AttentionBackendStub",
-           "VortexDecodeRuntime", "GraphedDecodeStep", "balance_requests"]
+           "VortexDecodeRuntime", "GraphedDecodeStep", "balance_requests", "gather_for_verification"]
