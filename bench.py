@@ -105,7 +105,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU baseline (oracle port)
-def cpu_baseline(cfg, sample_requests: int = 2, repeats: int = 1):
+def cpu_baseline(cfg, sample_requests: int = 16, repeats: int = 3):
     """Time the CPU port of the path on a bounded sample and scale it to one full step.
 
     Sample: ``sample_requests`` requests of the workload (all 8 KV heads each); one dense layer and
@@ -149,10 +149,10 @@ def run_reference_arm(args, cfg):
         return
     vals = []
     for _ in range(args.warmup):
-        cpu_baseline(cfg, sample_requests=1)
+        cpu_baseline(cfg, sample_requests=4, repeats=1)
     cb = None
-    for _ in range(max(1, args.steps)):
-        cb = cpu_baseline(cfg, sample_requests=1)
+    for _ in range(max(1, min(args.steps, 5))):
+        cb = cpu_baseline(cfg, sample_requests=8, repeats=1)
         vals.append(cb["value"])
     v = float(np.median(vals))
     cb["value"] = v
@@ -607,6 +607,8 @@ def main():
     h = step.host_buffers()
     for n in ("seq_lens", "req_indices", "loc", "q", "new_k", "new_v"):
         h[n].copy_(getattr(step, n).cpu())
+    if not args.no_graph:
+        step.capture_host_pipeline()
     for _ in range(3):
         step.run_from_host()
     barrier()
@@ -650,7 +652,10 @@ def main():
                      d2h_bytes_per_step=step.d2h_bytes),
             gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
             cuda_graph=not args.no_graph, programmatic_launch=bool(args.pdl and not args.no_graph),
-            roofline=dict(kernel="decode_gqa_kernel (sparse layers)", traffic=None,
+            # traffic: dram__bytes_read + dram__bytes_write of one sparse-layer launch from the ncu capture
+            # summarised in profiles/indexer_and_decode_gqa_c2_ncu.md (134.57 MB read + 7.0 MB written)
+            roofline=dict(kernel="decode_gqa_mma_kernel (27 sparse-layer launches per step)", traffic=141.6e6,
+                          algorithmic_bytes_per_launch=ab["sparse_kv_per_layer"],
                           **roof(ab["sparse_kv_per_layer"], kt["decode_sparse"])),
             kernels=dict(indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),
                          decode_sparse=roof(ab["sparse_kv_per_layer"], kt["decode_sparse"]),

@@ -180,3 +180,31 @@ def test_graphed_step_with_programmatic_launch_matches_eager():
         assert torch.equal(step.out, want_out), f"graph replay differs (programmatic_launch={pdl})"
         ns = int(rt.backend.kv_indptr_decode[1][bs * H].item())
         assert torch.equal(rt.backend.kv_indices_decode[1][:ns], want_sel[:ns])
+
+
+def test_host_pipeline_graph_matches_device_path():
+    """run_from_host through the overlapped copy/compute graph returns what the device-resident replay gives."""
+    from vortex_torch.runtime import GraphedDecodeStep
+
+    seq, L, H, G, D, P, K = [2048, 1000, 4096], 4, 8, 2, 128, 16, 30
+    prob = vo.make_paged_problem(19, seq, H, G, D, P)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16)
+    for l in range(L):
+        pl = vo.make_paged_problem(300 + l, seq, H, G, D, P)
+        for name in ("k", "v", "centroids"):
+            rt.pool.buffers[l][name].copy_(pl[name])
+    bs = len(seq)
+    step = GraphedDecodeStep(rt, bs)
+    h = step.host_buffers()
+    g = torch.Generator().manual_seed(0)
+    h["seq_lens"].copy_(torch.as_tensor(prob["seq_lens"]))
+    h["req_indices"].copy_(torch.as_tensor(prob["req_indices"]))
+    h["loc"].copy_(torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)]))
+    for n in ("q", "new_k", "new_v"):
+        h[n].copy_(torch.randn(h[n].shape, generator=g).bfloat16())
+    want = step.run_from_host().clone()      # plain copies + eager kernels
+    step.capture_host_pipeline()
+    for _ in range(3):
+        h["out"].zero_()
+        got = step.run_from_host()
+    assert torch.equal(got, want)

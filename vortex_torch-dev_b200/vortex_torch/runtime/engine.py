@@ -248,8 +248,55 @@ class GraphedDecodeStep:
     def d2h_bytes(self) -> int:
         return self.out.numel() * self.out.element_size()
 
+    def capture_host_pipeline(self) -> None:
+        """Capture the host-buffer step as one graph in which the copies overlap the kernels.
+
+        Three branches inside the graph: an input branch copies the step's pinned host inputs layer by
+        layer, the compute branch starts layer l as soon as its inputs have landed, and an output branch
+        copies layer l's attention output back while layer l+1 computes.  ``run_from_host`` replays it.
+        """
+        h = self.host_buffers()
+        dev = self.rt.device
+        self._eager()
+        torch.cuda.synchronize(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        L = self.rt.num_layers
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            main = torch.cuda.current_stream(dev)
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+            ev_in = [torch.cuda.Event() for _ in range(L + 1)]
+            with torch.cuda.stream(s_in):
+                for n in ("seq_lens", "req_indices", "loc"):
+                    getattr(self, n).copy_(h[n], non_blocking=True)
+                ev_in[L].record(s_in)
+                for l in range(L):
+                    self.q[l].copy_(h["q"][l], non_blocking=True)
+                    self.new_k[l].copy_(h["new_k"][l], non_blocking=True)
+                    self.new_v[l].copy_(h["new_v"][l], non_blocking=True)
+                    ev_in[l].record(s_in)
+            main.wait_event(ev_in[L])
+            self.rt.plan(self.seq_lens, self.req_indices)
+            for l in range(L):
+                main.wait_event(ev_in[l])
+                self.rt.layer(l, self.q[l], self.new_k[l], self.new_v[l], self.loc, self.out[l])
+                ev = torch.cuda.Event()
+                ev.record(main)
+                s_out.wait_event(ev)
+                with torch.cuda.stream(s_out):
+                    h["out"][l].copy_(self.out[l], non_blocking=True)
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+        self.graph_host = g
+
     def run_from_host(self, wait: bool = True):
         h = self.host_buffers()
+        if getattr(self, "graph_host", None) is not None:
+            self.graph_host.replay()
+            if wait:
+                torch.cuda.current_stream(self.rt.device).synchronize()
+            return h["out"]
         for n in ("seq_lens", "req_indices", "loc", "q", "new_k", "new_v"):
             getattr(self, n).copy_(h[n], non_blocking=True)
         self.replay()
