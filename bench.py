@@ -187,6 +187,8 @@ def build_runtime(cfg, device, seed):
                              context_len=cfg["ctx"], server_args=sa, dtype=torch.bfloat16, device=device)
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(num_pages, generator=g)
+    if os.environ.get("VTX_BENCH_IDENTITY_PAGES"):  # experiment: physical order = logical order
+        perm = torch.arange(num_pages)
     slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1)
     rt.model_runner.req_to_token_pool.req_to_token.copy_(slots.to(torch.int32))
     torch.manual_seed(seed)
@@ -285,7 +287,16 @@ def time_kernels(rt, step, cfg, reps):
             _cabi.set_kv_cmean(cache["k"], cache["v"], step.new_k[l], step.new_v[l], cache["centroids"], step.loc,
                                rt.P)
 
-    kinds = dict(indexer=(run_indexer, len(sparse_layers)),
+    def run_fused():
+        for l in sparse_layers:
+            qv, ov, cache = views(l)
+            _cabi.sparse_layer_fused(qv, cache["centroids"], cache["k"], cache["v"], ov, b.kv_indptr_decode[0],
+                                     b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
+                                     b.kv_last_page_len_decode, eff_bs, rt.P, cfg["K"], cfg["bos"], cfg["eos"],
+                                     rt.ictx.max_num_pages_per_request, rt.sm_scale)
+
+    kinds = dict(sparse_layer_fused=(run_fused, len(sparse_layers)),
+                 indexer=(run_indexer, len(sparse_layers)),
                  decode_sparse=(lambda: run_decode(sparse_layers, True), len(sparse_layers)),
                  decode_dense=(lambda: run_decode(dense_layers, False), len(dense_layers)),
                  kv_write_cmean=(run_cache, cfg["layers"]))
@@ -329,6 +340,8 @@ def run_mla_workload(args):
     num_pages = bs * pages_per_req
     g = torch.Generator().manual_seed(7)
     perm = torch.randperm(num_pages, generator=g)
+    if os.environ.get("VTX_BENCH_IDENTITY_PAGES"):  # experiment: physical order = logical order
+        perm = torch.arange(num_pages)
     slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1).to(torch.int32)
     i32 = dict(dtype=torch.int32, device=dev)
     r2t = slots.to(dev)
@@ -642,7 +655,7 @@ def main():
 
     if rank == 0:
         n_sparse = cfg["layers"] - len(cfg["skip"])
-        launches_per_step = 1 + cfg["layers"] + 2 * n_sparse + len(cfg["skip"])
+        launches_per_step = 1 + cfg["layers"] + n_sparse + len(cfg["skip"])
         value = world * args.steps / dev_s
         line = dict(
             metric=METRIC, value=value, unit="steps/s", n_gpus=world, steps=args.steps, warmup=W,
@@ -657,7 +670,9 @@ def main():
             roofline=dict(kernel="decode_gqa_mma_kernel (27 sparse-layer launches per step)", traffic=141.6e6,
                           algorithmic_bytes_per_launch=ab["sparse_kv_per_layer"],
                           **roof(ab["sparse_kv_per_layer"], kt["decode_sparse"])),
-            kernels=dict(indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),
+            kernels=dict(sparse_layer_fused=roof(ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
+                                                 kt["sparse_layer_fused"]),
+                         indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),
                          decode_sparse=roof(ab["sparse_kv_per_layer"], kt["decode_sparse"]),
                          decode_dense=roof(ab["dense_kv_per_layer"], kt["decode_dense"]),
                          us=dict((k, v * 1e6 if v else None) for k, v in kt.items())),

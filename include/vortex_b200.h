@@ -143,6 +143,20 @@ int vtx_indexer_fused(const void* q, const void* centroids, const int32_t* dense
                       int max_num_pages_per_request, int dtype, void* stream);
 
 /*
+ * One launch for a sparse layer: vtx_indexer_fused followed by vtx_decode_gqa on the sparse lists, run by
+ * the same CTA per segment (selection first, then attention over the selected pages; the selection is
+ * also written to sparse_kv_indices).  Same results as the two calls.  Replaces, per layer, the chain
+ * flow/algorithms.py:168-170 plus the paged-decode call the SGLang fork makes afterwards.  bf16 only.
+ */
+int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
+                           void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                           const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                           const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                           int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                           int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
+                           int dtype, void* stream);
+
+/*
  * Paged grouped-query decode attention over each segment's page list (sparse or dense).
  * Takes the place of the flashinfer paged-decode call the SGLang fork makes on
  * sparse_kv_indptr / sparse_kv_indices / kv_last_page_len (data contract:

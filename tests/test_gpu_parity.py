@@ -207,6 +207,30 @@ def test_decode_gqa_matches_oracle(case, sparse):
     assert close(out, want, tol), f"max err {(out.float().cpu() - want.float()).abs().max()}"
 
 
+@pytest.mark.parametrize("case", [c for c in DECODE_CASES if c[8] == torch.bfloat16],
+                         ids=lambda c: f"H{c[1]}G{c[2]}D{c[3]}P{c[4]}")
+def test_sparse_layer_fused_equals_indexer_then_decode(case):
+    """One launch (selection + attention) gives the selection of the oracle and the bits of the two-launch path."""
+    seq, H, G, D, P, K, bos, eos, dtype = case
+    prob, dp, ref, _ = _indexer_case(23, seq, H, G, D, P, K, bos, eos, dtype)
+    d = to_dev(prob)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    sel2 = dp.sparse_indices.clone()
+    out2 = torch.empty_like(d["q"])
+    _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel2, dp.S, K,
+                        bos, eos, dp.max_pages)
+    _cabi.decode_gqa(d["q"], d["k"], d["v"], out2, dp.sparse_indptr, sel2, dp.last_page_len, dp.S, P,
+                     1.0 / math.sqrt(D))
+    sel1 = dp.sparse_indices.clone()
+    out1 = torch.full_like(d["q"], float("nan"))
+    _cabi.sparse_layer_fused(d["q"], d["centroids"], d["k"], d["v"], out1, dp.dense_indptr, dp.sparse_indptr,
+                             dp.dense_indices, sel1, dp.last_page_len, dp.S, P, K, bos, eos, dp.max_pages,
+                             1.0 / math.sqrt(D))
+    np.testing.assert_array_equal(sel1.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+    assert torch.equal(sel1, sel2)
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+
+
 def test_decode_is_invariant_to_page_order():
     """Size-independent property: permuting the middle pages of a list changes nothing beyond fp32 re-association."""
     seq, H, G, D, P, K = [3000], 4, 2, 128, 16, 30

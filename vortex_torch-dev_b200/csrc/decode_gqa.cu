@@ -15,26 +15,20 @@
 // Data contract as produced by the block-table builder (reference: csrc/utils_sglang.cu:123-184,
 // indexer/context.py:117-121); in the reference the attention itself is a third-party
 // paged-decode call made with effective batch bs*H_kv, one KV head and group_size q heads.
+#include "decode_mma_body.cuh"
 #include "vtx_common.cuh"
 
 namespace {
+
+using vtxdec::DecodeArgs;
+using vtx::cp_async16;
+using vtx::cp_async_commit;
+using vtx::cp_async_wait;
 
 constexpr int kWarps = 4;
 constexpr int kSlots = 3;        // ring slots per warp
 constexpr int kTileTokens = 16;  // token rows per tile
 constexpr float kLog2e = 1.4426950408889634f;
-
-struct DecodeArgs {
-    const void* q;
-    const void* k;
-    const void* v;
-    void* out;
-    const int32_t* indptr;
-    const int32_t* indices;
-    const int32_t* last_len;
-    int P;
-    float scale_log2;
-};
 
 template <typename T>
 __device__ __forceinline__ void store_out(T* p, float v);
@@ -43,16 +37,6 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 template <>
 __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 
-__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr, bool valid) {
-    const int src_bytes = valid ? 16 : 0;  // 0 => the 16 bytes are zero-filled, the source is not read
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 
 // Eight elements of a shared-memory row widened to fp32.
 template <typename T>
@@ -285,222 +269,19 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
 //   O^T[dim, head]  += V^T . P^T   A = V tile via ldmatrix.trans, B = P^T, which is exactly the
 //                                  accumulator layout of S^T (no data movement between the two)
 // Rows of a tile are 16-byte-chunk swizzled (chunk ^ (row & 7)) so ldmatrix is conflict-free.
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // D = head dim (64 or 128); G <= 8 query heads per KV head.
 template <int G, int D>
 __global__ void __launch_bounds__(kWarps * 32, 4) decode_gqa_mma_kernel(DecodeArgs a) {
-    using T = __nv_bfloat16;
-    constexpr int KSTEPS = D / 16;                 // k-steps of QK^T == 16-dim tiles of the output
-    constexpr int ROWB = D * 2;                    // bytes per token row
-    constexpr int CH_PER_ROW = ROWB / 16;
-    constexpr int TILE_BYTES = kTileTokens * ROWB;
-    constexpr int CHUNKS = TILE_BYTES / 16;
-    constexpr int CPL = CHUNKS / 32;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    const int s = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int gid = lane >> 2, tid = lane & 3;
-    const int beg = a.indptr[s];
-    const int npages = a.indptr[s + 1] - beg;
-    const int last_len = a.last_len[s];
-    const int P = a.P;
-    const int tiles_per_page = (P + kTileTokens - 1) / kTileTokens;
-
-    unsigned char* my_ring = smem_raw + (size_t)warp * kSlots * TILE_BYTES;
-    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
-
-    // q as the A operand: row gid (zero for gid >= G), 16 dims per k-step
-    uint32_t qa[KSTEPS][2];
-    {
-        const uint32_t* qs = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(a.q) +
-                                                               ((int64_t)s * G + gid) * D);
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            qa[ks][0] = gid < G ? qs[ks * 8 + tid] : 0u;
-            qa[ks][1] = gid < G ? qs[ks * 8 + 4 + tid] : 0u;
-        }
-    }
-    float o[KSTEPS][4];  // O^T: [16 dims of tile mt] x [8 heads]
-#pragma unroll
-    for (int mt = 0; mt < KSTEPS; ++mt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;  // running max / partial sum of head `gid`
-    float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
-    uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
-
-    const int my_pages = npages > warp ? (npages - warp + kWarps - 1) / kWarps : 0;
-    const int n_items = my_pages * tiles_per_page * 2;
-    const unsigned char* kc = reinterpret_cast<const unsigned char*>(a.k);
-    const unsigned char* vc = reinterpret_cast<const unsigned char*>(a.v);
-    int id_base = 0;
-    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kWarps * lane] : 0;
-
-    auto issue = [&](int item) {
-        const int pair = item >> 1;
-        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
-        const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
-        const int pg = warp + kWarps * po;
-        const int nvalid_page = (pg == npages - 1) ? last_len : P;
-        const int tok0 = tile * kTileTokens;
-        const unsigned char* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * ROWB;
-        const uint32_t dst = my_ring_addr + (uint32_t)((item % kSlots) * TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < CPL; ++c) {
-            const int ch = c * 32 + lane;
-            const int t = ch / CH_PER_ROW, cr = ch % CH_PER_ROW;
-            cp_async16(dst + t * ROWB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < nvalid_page);
-        }
-    };
-
-#pragma unroll
-    for (int i = 0; i < kSlots - 1; ++i) {
-        if (i < n_items) issue(i);
-        cp_async_commit();
-    }
-
-    // ldmatrix row address of this lane inside a tile: token row and which chunk of the pair
-    const int lm_t = ((lane >> 4) << 3) + (lane & 7);
-    const int lm_c = (lane >> 3) & 1;
-
-    for (int item = 0; item < n_items; ++item) {
-        cp_async_wait<kSlots - 2>();
-        __syncwarp();
-        {
-            const int nxt = item + kSlots - 1;
-            if (nxt < n_items) {
-                const int po = (nxt >> 1) / tiles_per_page;
-                if (po - id_base >= 32) {
-                    id_base += 32;
-                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kWarps * (id_base + lane)] : 0;
-                }
-                issue(nxt);
-            }
-            cp_async_commit();
-        }
-        const uint32_t tile_addr = my_ring_addr + (uint32_t)((item % kSlots) * TILE_BYTES) + lm_t * ROWB;
-        if ((item & 1) == 0) {
-            const int pair = item >> 1;
-            const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
-            const int pg = warp + kWarps * po;
-            const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kTileTokens;
-            float st[2][4];
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) st[j][i] = 0.f;
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                uint32_t kb[4];
-                ldmatrix_x4(kb, tile_addr + ((((ks << 1) + lm_c) ^ (lm_t & 7)) << 4));
-                mma_bf16(st[0], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
-                mma_bf16(st[1], qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
-            }
-            // this lane: head gid, tokens tid*2 + {0,1} (+8 for the second n-tile)
-            float sv[4];
-            sv[0] = (tid * 2 < nvalid) ? st[0][0] * a.scale_log2 : -INFINITY;
-            sv[1] = (tid * 2 + 1 < nvalid) ? st[0][1] * a.scale_log2 : -INFINITY;
-            sv[2] = (tid * 2 + 8 < nvalid) ? st[1][0] * a.scale_log2 : -INFINITY;
-            sv[3] = (tid * 2 + 9 < nvalid) ? st[1][1] * a.scale_log2 : -INFINITY;
-            float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
-            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
-            const float mn = fmaxf(m_run, tmax);
-            // mn stays -inf only while nothing valid was seen (tiles past the end of a short last page)
-            const float alpha = (mn == -INFINITY) ? 1.f : exp2f(m_run - mn);
-            const float base = (mn == -INFINITY) ? 0.f : mn;
-            m_run = mn;
-            const float p0 = exp2f(sv[0] - base), p1 = exp2f(sv[1] - base);
-            const float p2 = exp2f(sv[2] - base), p3 = exp2f(sv[3] - base);
-            l_run = l_run * alpha + (p0 + p1) + (p2 + p3);
-            pb0 = pack_bf16x2(p0, p1);
-            pb1 = pack_bf16x2(p2, p3);
-            // the O^T columns of this lane are heads tid*2 and tid*2+1
-            a0 = __shfl_sync(0xffffffffu, alpha, (tid * 2) << 2);
-            a1 = __shfl_sync(0xffffffffu, alpha, (tid * 2 + 1) << 2);
-        } else {
-#pragma unroll
-            for (int mt = 0; mt < KSTEPS; ++mt) {
-                uint32_t va[4];
-                ldmatrix_x4_trans(va, tile_addr + ((((mt << 1) + lm_c) ^ (lm_t & 7)) << 4));
-                o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
-                // A regs: (dims 0-7, tok 0-7), (dims 8-15, tok 0-7), (dims 0-7, tok 8-15), (dims 8-15, tok 8-15)
-                mma_bf16(o[mt], va[0], va[1], va[2], va[3], pb0, pb1);
-            }
-        }
-    }
-    cp_async_wait<0>();
-    __syncthreads();
-
-    float* sm_acc = reinterpret_cast<float*>(smem_raw);  // [kWarps][G][D]
-    float* sm_m = sm_acc + kWarps * G * D;               // [kWarps][G]
-    float* sm_l = sm_m + kWarps * G;
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (tid == 0 && gid < G) {
-        sm_m[warp * G + gid] = m_run;
-        sm_l[warp * G + gid] = l_run;
-    }
-#pragma unroll
-    for (int mt = 0; mt < KSTEPS; ++mt) {
-        const int h0 = tid * 2, d0 = mt * 16 + gid;
-        if (h0 < G) {
-            sm_acc[(warp * G + h0) * D + d0] = o[mt][0];
-            sm_acc[(warp * G + h0) * D + d0 + 8] = o[mt][2];
-        }
-        if (h0 + 1 < G) {
-            sm_acc[(warp * G + h0 + 1) * D + d0] = o[mt][1];
-            sm_acc[(warp * G + h0 + 1) * D + d0 + 8] = o[mt][3];
-        }
-    }
-    __syncthreads();
-    T* out = reinterpret_cast<T*>(a.out) + (int64_t)s * G * D;
-    for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
-        const int g = idx / D, d = idx % D;
-        float mx = sm_m[g];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, sm_m[w * G + g]);
-        float num = 0.f, den = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            const float wm = sm_m[w * G + g];
-            const float wgt = (wm == -INFINITY) ? 0.f : exp2f(wm - mx);
-            num = fmaf(wgt, sm_acc[(w * G + g) * D + d], num);
-            den = fmaf(wgt, sm_l[w * G + g], den);
-        }
-        store_out<T>(out + idx, den > 0.f ? num / den : 0.f);
-    }
+    vtxdec::decode_mma_body<G, D>(a, smem_raw, blockIdx.x);
 }
 
 template <int G, int D>
 int launch_mma_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
-    const size_t ring = (size_t)kWarps * kSlots * kTileTokens * D * 2;
-    const size_t merge = (size_t)(kWarps * G * D + 2 * kWarps * G) * sizeof(float);
-    const size_t bytes = ring > merge ? ring : merge;
+    const size_t bytes = vtxdec::decode_mma_smem_bytes<G, D>();
     auto kern = decode_gqa_mma_kernel<G, D>;
     if (bytes > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);

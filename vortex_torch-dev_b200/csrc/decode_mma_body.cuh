@@ -1,0 +1,219 @@
+// Tensor-core body of the paged GQA decode (bf16), shared by the stand-alone decode kernel and the
+// fused sparse-layer kernel.  See decode_gqa.cu for the description of the algorithm.
+#pragma once
+
+#include "vtx_common.cuh"
+
+namespace vtxdec {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecSlots = 3;        // ring slots per warp
+constexpr int kDecTileTokens = 16;  // token rows per tile
+
+struct DecodeArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    const int32_t* indptr;
+    const int32_t* indices;
+    const int32_t* last_len;
+    int P;
+    float scale_log2;
+};
+
+template <int G, int D>
+constexpr size_t decode_mma_smem_bytes() {
+    constexpr size_t ring = (size_t)kDecWarps * kDecSlots * kDecTileTokens * D * 2;
+    constexpr size_t merge = (size_t)(kDecWarps * G * D + 2 * kDecWarps * G) * sizeof(float);
+    return ring > merge ? ring : merge;
+}
+
+// Body of the bf16 tensor-core decode for segment s; smem_raw: the CTA's dynamic shared memory
+// (decode_mma_smem_bytes<G, D>() bytes, 128-byte aligned).  Called by all kDecWarps * 32 threads.
+template <int G, int D>
+__device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned char* smem_raw, const int s) {
+    using T = __nv_bfloat16;
+    constexpr int KSTEPS = D / 16;                 // k-steps of QK^T == 16-dim tiles of the output
+    constexpr int ROWB = D * 2;                    // bytes per token row
+    constexpr int CH_PER_ROW = ROWB / 16;
+    constexpr int TILE_BYTES = kDecTileTokens * ROWB;
+    constexpr int CHUNKS = TILE_BYTES / 16;
+    constexpr int CPL = CHUNKS / 32;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int beg = a.indptr[s];
+    const int npages = a.indptr[s + 1] - beg;
+    const int last_len = a.last_len[s];
+    const int P = a.P;
+    const int tiles_per_page = (P + kDecTileTokens - 1) / kDecTileTokens;
+
+    unsigned char* my_ring = smem_raw + (size_t)warp * kDecSlots * TILE_BYTES;
+    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
+
+    // q as the A operand: row gid (zero for gid >= G), 16 dims per k-step
+    uint32_t qa[KSTEPS][2];
+    {
+        const uint32_t* qs = reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(a.q) +
+                                                               ((int64_t)s * G + gid) * D);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            qa[ks][0] = gid < G ? qs[ks * 8 + tid] : 0u;
+            qa[ks][1] = gid < G ? qs[ks * 8 + 4 + tid] : 0u;
+        }
+    }
+    float o[KSTEPS][4];  // O^T: [16 dims of tile mt] x [8 heads]
+#pragma unroll
+    for (int mt = 0; mt < KSTEPS; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;  // running max / partial sum of head `gid`
+    float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
+    uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
+
+    const int my_pages = npages > warp ? (npages - warp + kDecWarps - 1) / kDecWarps : 0;
+    const int n_items = my_pages * tiles_per_page * 2;
+    const unsigned char* kc = reinterpret_cast<const unsigned char*>(a.k);
+    const unsigned char* vc = reinterpret_cast<const unsigned char*>(a.v);
+    int id_base = 0;
+    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kDecWarps * lane] : 0;
+
+    auto issue = [&](int item) {
+        const int pair = item >> 1;
+        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
+        const int pg = warp + kDecWarps * po;
+        const int nvalid_page = (pg == npages - 1) ? last_len : P;
+        const int tok0 = tile * kDecTileTokens;
+        const unsigned char* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * ROWB;
+        const uint32_t dst = my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+            const int ch = c * 32 + lane;
+            const int t = ch / CH_PER_ROW, cr = ch % CH_PER_ROW;
+            vtx::cp_async16(dst + t * ROWB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < nvalid_page);
+        }
+    };
+
+#pragma unroll
+    for (int i = 0; i < kDecSlots - 1; ++i) {
+        if (i < n_items) issue(i);
+        vtx::cp_async_commit();
+    }
+
+    // ldmatrix row address of this lane inside a tile: token row and which chunk of the pair
+    const int lm_t = ((lane >> 4) << 3) + (lane & 7);
+    const int lm_c = (lane >> 3) & 1;
+
+    for (int item = 0; item < n_items; ++item) {
+        vtx::cp_async_wait<kDecSlots - 2>();
+        __syncwarp();
+        {
+            const int nxt = item + kDecSlots - 1;
+            if (nxt < n_items) {
+                const int po = (nxt >> 1) / tiles_per_page;
+                if (po - id_base >= 32) {
+                    id_base += 32;
+                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kDecWarps * (id_base + lane)] : 0;
+                }
+                issue(nxt);
+            }
+            vtx::cp_async_commit();
+        }
+        const uint32_t tile_addr = my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES) + lm_t * ROWB;
+        if ((item & 1) == 0) {
+            const int pair = item >> 1;
+            const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+            const int pg = warp + kDecWarps * po;
+            const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kDecTileTokens;
+            float st[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) st[j][i] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t kb[4];
+                vtx::ldmatrix_x4(kb, tile_addr + ((((ks << 1) + lm_c) ^ (lm_t & 7)) << 4));
+                vtx::mma_bf16(st[0], qa[ks][0], 0u, qa[ks][1], 0u, kb[0], kb[1]);
+                vtx::mma_bf16(st[1], qa[ks][0], 0u, qa[ks][1], 0u, kb[2], kb[3]);
+            }
+            // this lane: head gid, tokens tid*2 + {0,1} (+8 for the second n-tile)
+            float sv[4];
+            sv[0] = (tid * 2 < nvalid) ? st[0][0] * a.scale_log2 : -INFINITY;
+            sv[1] = (tid * 2 + 1 < nvalid) ? st[0][1] * a.scale_log2 : -INFINITY;
+            sv[2] = (tid * 2 + 8 < nvalid) ? st[1][0] * a.scale_log2 : -INFINITY;
+            sv[3] = (tid * 2 + 9 < nvalid) ? st[1][1] * a.scale_log2 : -INFINITY;
+            float tmax = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float mn = fmaxf(m_run, tmax);
+            // mn stays -inf only while nothing valid was seen (tiles past the end of a short last page)
+            const float alpha = (mn == -INFINITY) ? 1.f : exp2f(m_run - mn);
+            const float base = (mn == -INFINITY) ? 0.f : mn;
+            m_run = mn;
+            const float p0 = exp2f(sv[0] - base), p1 = exp2f(sv[1] - base);
+            const float p2 = exp2f(sv[2] - base), p3 = exp2f(sv[3] - base);
+            l_run = l_run * alpha + (p0 + p1) + (p2 + p3);
+            pb0 = vtx::pack_bf16x2(p0, p1);
+            pb1 = vtx::pack_bf16x2(p2, p3);
+            // the O^T columns of this lane are heads tid*2 and tid*2+1
+            a0 = __shfl_sync(0xffffffffu, alpha, (tid * 2) << 2);
+            a1 = __shfl_sync(0xffffffffu, alpha, (tid * 2 + 1) << 2);
+        } else {
+#pragma unroll
+            for (int mt = 0; mt < KSTEPS; ++mt) {
+                uint32_t va[4];
+                vtx::ldmatrix_x4_trans(va, tile_addr + ((((mt << 1) + lm_c) ^ (lm_t & 7)) << 4));
+                o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
+                // A regs: (dims 0-7, tok 0-7), (dims 8-15, tok 0-7), (dims 0-7, tok 8-15), (dims 8-15, tok 8-15)
+                vtx::mma_bf16(o[mt], va[0], va[1], va[2], va[3], pb0, pb1);
+            }
+        }
+    }
+    vtx::cp_async_wait<0>();
+    __syncthreads();
+
+    float* sm_acc = reinterpret_cast<float*>(smem_raw);  // [kDecWarps][G][D]
+    float* sm_m = sm_acc + kDecWarps * G * D;               // [kDecWarps][G]
+    float* sm_l = sm_m + kDecWarps * G;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (tid == 0 && gid < G) {
+        sm_m[warp * G + gid] = m_run;
+        sm_l[warp * G + gid] = l_run;
+    }
+#pragma unroll
+    for (int mt = 0; mt < KSTEPS; ++mt) {
+        const int h0 = tid * 2, d0 = mt * 16 + gid;
+        if (h0 < G) {
+            sm_acc[(warp * G + h0) * D + d0] = o[mt][0];
+            sm_acc[(warp * G + h0) * D + d0 + 8] = o[mt][2];
+        }
+        if (h0 + 1 < G) {
+            sm_acc[(warp * G + h0 + 1) * D + d0] = o[mt][1];
+            sm_acc[(warp * G + h0 + 1) * D + d0 + 8] = o[mt][3];
+        }
+    }
+    __syncthreads();
+    T* out = reinterpret_cast<T*>(a.out) + (int64_t)s * G * D;
+    for (int idx = threadIdx.x; idx < G * D; idx += kDecWarps * 32) {
+        const int g = idx / D, d = idx % D;
+        float mx = sm_m[g];
+#pragma unroll
+        for (int w = 1; w < kDecWarps; ++w) mx = fmaxf(mx, sm_m[w * G + g]);
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) {
+            const float wm = sm_m[w * G + g];
+            const float wgt = (wm == -INFINITY) ? 0.f : exp2f(wm - mx);
+            num = fmaf(wgt, sm_acc[(w * G + g) * D + d], num);
+            den = fmaf(wgt, sm_l[w * G + g], den);
+        }
+        out[idx] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+}
+
+
+}  // namespace vtxdec

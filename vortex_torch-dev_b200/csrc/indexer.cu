@@ -25,6 +25,7 @@
 // The sort is a bitonic network over registers (4..16 keys per thread): strides below the
 // per-thread block are register swaps, strides inside a warp are shuffles, and only the three
 // widest strides cross warps through shared memory.
+#include "decode_mma_body.cuh"
 #include "vtx_common.cuh"
 
 namespace {
@@ -262,20 +263,16 @@ struct Geom {
 
 // MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
 template <typename T, int D, int MODE>
-__global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
+__device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s) {
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
     constexpr int L = Gm::L, HALF = L / 2, SLOTS = Gm::slots;
-    extern __shared__ __align__(128) unsigned char smem_raw[];
     // layout: [ring][q_mean][keys][ids]
     unsigned char* ring = smem_raw;
     T* qbar = reinterpret_cast<T*>(smem_raw + Gm::ring_bytes);
     Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + Gm::row_bytes);
     int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
 
-    vtx::pdl_wait();
-    vtx::pdl_trigger();
-    const int s = blockIdx.x;
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
     if (c <= a.K) return;
@@ -344,6 +341,9 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
         float acc[HALF];
 #pragma unroll
         for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
+#ifdef VTX_EXP_NOSCORE
+        acc[0] = (float)*reinterpret_cast<const uint32_t*>(row_ptr + par * 16);
+#else
         // this thread owns partial sums 2*i + par; partial l takes chunks l, l + L, ...
 #pragma unroll
         for (int k = 0; k * L < Gm::nchunk; ++k) {
@@ -357,6 +357,7 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
                 }
             }
         }
+#endif
 #pragma unroll
         for (int w = HALF / 2; w > 0; w >>= 1)
 #pragma unroll
@@ -373,10 +374,36 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
     if (MODE == 0) {
         __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
         const int o0 = a.sparse_indptr[s] + a.bos;
+#ifndef VTX_EXP_NOSORT
         select_and_store<T>(keys, ids, c, a.K, a.sparse_indices + o0,
                             a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr,
                             reinterpret_cast<Key*>(ring));
+#else
+        if (threadIdx.x < a.K) a.sparse_indices[o0 + threadIdx.x] = ids[KeyOf<T>::index(keys[threadIdx.x])];
+#endif
     }
+}
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    indexer_body<T, D, MODE>(a, smem_raw, blockIdx.x);
+}
+
+// One launch per sparse layer: page selection, then attention over the selected pages, by the same CTA.
+// The decode phase of one segment overlaps the scan phase of its neighbours on the SM, so neither phase
+// pays its own launch and ramp-up; the selected rows still go to the sparse page list (the decode reads
+// them back after the block barrier).  bf16 only (the decode phase is the tensor-core body).
+template <int D, int G>
+__global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    indexer_body<__nv_bfloat16, D, 0>(ia, smem_raw, blockIdx.x);
+    __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
+    vtxdec::decode_mma_body<G, D>(da, smem_raw, blockIdx.x);
 }
 
 template <typename T>
@@ -449,6 +476,32 @@ int launch_topk(const void* scores, const IndexerArgs& a, int eff_bs, cudaStream
     int rc = set_smem(topk_kernel<T>, bytes);
     if (rc != VTX_OK) return rc;
     return vtx::launch(topk_kernel<T>, dim3(eff_bs), dim3(kThreads), bytes, st, (const T*)scores, a);
+}
+
+template <int D, int G>
+int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, int eff_bs, cudaStream_t st) {
+    using Gm = Geom<__nv_bfloat16, D>;
+    static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
+    size_t bytes = Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
+    const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
+    if (dec > bytes) bytes = dec;
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    auto kern = sparse_layer_kernel<D, G>;
+    int rc = set_smem(kern, bytes);
+    if (rc != VTX_OK) return rc;
+    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, ia, da);
+}
+
+template <int D>
+int launch_sparse_layer_d(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, int eff_bs, int group,
+                          cudaStream_t st) {
+    switch (group) {
+        case 1: return launch_sparse_layer_cfg<D, 1>(ia, da, eff_bs, st);
+        case 2: return launch_sparse_layer_cfg<D, 2>(ia, da, eff_bs, st);
+        case 4: return launch_sparse_layer_cfg<D, 4>(ia, da, eff_bs, st);
+        case 8: return launch_sparse_layer_cfg<D, 8>(ia, da, eff_bs, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
 }
 
 int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int bos, int eos, int maxp,
@@ -544,4 +597,51 @@ extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int
     cudaStream_t st = (cudaStream_t)stream;
     return dtype == VTX_BF16 ? launch_indexer<__nv_bfloat16, 0>(a, eff_batch_size, st)
                              : launch_indexer<float, 0>(a, eff_batch_size, st);
+}
+
+extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
+                                      void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                      const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                                      const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                      int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                                      int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
+                                      int dtype, void* stream) {
+    int rc = check_common(dense_kv_indptr, dense_kv_indices, eff_batch_size, topk_val, page_reserved_bos,
+                          page_reserved_eos, max_num_pages_per_request, dtype);
+    if (rc != VTX_OK) return rc;
+    if (!q || !centroids || !k_cache || !v_cache || !out || !sparse_kv_indptr || !sparse_kv_indices ||
+        !kv_last_page_len)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (group_size < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    if (eff_batch_size == 0) return VTX_OK;
+    IndexerArgs ia{};
+    ia.q = q;
+    ia.centroids = centroids;
+    ia.dense_indptr = dense_kv_indptr;
+    ia.sparse_indptr = sparse_kv_indptr;
+    ia.dense_indices = dense_kv_indices;
+    ia.sparse_indices = sparse_kv_indices;
+    ia.G = group_size;
+    ia.D = head_dim;
+    ia.K = topk_val;
+    ia.bos = page_reserved_bos;
+    ia.eos = page_reserved_eos;
+    ia.key_cap = key_capacity(max_num_pages_per_request);
+    vtxdec::DecodeArgs da;
+    da.q = q;
+    da.k = k_cache;
+    da.v = v_cache;
+    da.out = out;
+    da.indptr = sparse_kv_indptr;
+    da.indices = sparse_kv_indices;
+    da.last_len = kv_last_page_len;
+    da.P = page_size;
+    da.scale_log2 = sm_scale * 1.4426950408889634f;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (head_dim) {
+        case 64: return launch_sparse_layer_d<64>(ia, da, eff_batch_size, group_size, st);
+        case 128: return launch_sparse_layer_d<128>(ia, da, eff_batch_size, group_size, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
 }

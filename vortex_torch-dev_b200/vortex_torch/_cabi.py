@@ -36,6 +36,7 @@ SIGNATURES = {
     "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_sparse_layer_fused": [_p] * 10 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
@@ -216,3 +217,17 @@ def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_sc
                             ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_mla")
+
+
+def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
+                       sparse_kv_indices, kv_last_page_len, eff_bs, page_size, topk_val, bos, eos,
+                       max_pages_per_request, sm_scale) -> None:
+    """Page selection and attention over the selected pages in one launch (bf16)."""
+    if not (q.dtype == centroids.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
+        raise TypeError("sparse_layer_fused: q, centroids, caches and out must share a dtype")
+    rc = lib.vtx_sparse_layer_fused(ptr(q), ptr(centroids), ptr(k_cache), ptr(v_cache), ptr(out),
+                                    ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
+                                    ptr(sparse_kv_indices), ptr(kv_last_page_len), int(eff_bs), q.shape[1],
+                                    q.shape[2], int(page_size), int(topk_val), int(bos), int(eos),
+                                    int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_sparse_layer_fused")

@@ -29,10 +29,34 @@ class Context(ContextBase):
         "indexer_dtype", "topk_val", "page_reserved_bos", "page_reserved_eos",
         # profile-pass counters
         "_aux_total_bytes", "_aux_total_flops",
+        # a fused page selection that the runtime may fold into its attention launch (see defer_indexer)
+        "_defer_indexer", "_pending_indexer",
     )
 
     def __init__(self) -> None:
-        self._reset_slots("Indexer", {"batch_size": 0})
+        self._reset_slots("Indexer", {"batch_size": 0, "_defer_indexer": False, "_pending_indexer": None})
+
+    # ---- deferred page selection (fusion of the indexer with the attention that follows it) ----
+    def defer_indexer(self, enable: bool) -> None:
+        """When enabled, a fused ``q.mean -> GeMV -> topK`` chain is recorded instead of launched, so that
+        the caller's attention step can run selection and attention as one kernel.  The caller must call
+        ``take_pending_indexer`` or ``flush_indexer`` before anything reads the sparse page list."""
+        self.flush_indexer()
+        self._defer_indexer = bool(enable)
+
+    def take_pending_indexer(self):
+        pend, self._pending_indexer = self._pending_indexer, None
+        return pend
+
+    def flush_indexer(self) -> None:
+        pend = self.take_pending_indexer()
+        if pend is not None:
+            from .. import _cabi
+
+            q, y, o = pend
+            _cabi.indexer_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr, self.dense_kv_indices, o,
+                                self.batch_size * self.num_kv_heads, self.topk_val, self.page_reserved_bos,
+                                self.page_reserved_eos, self.max_num_pages_per_request)
 
     def set_batch_size(self, n: int) -> None:
         self.batch_size = n

@@ -49,10 +49,16 @@ class topK(vOp):
         if prod is not None and prod._pending is not None and x.data_ptr() == prod.output_buffer.data_ptr():
             q, y = prod._pending
             prod._pending = None
+            if getattr(ctx, "_defer_indexer", False):
+                ctx.flush_indexer()
+                ctx._pending_indexer = (q, y, o)  # the runtime's attention launch picks it up
+                return o
             _cabi.indexer_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
                                 o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
                                 ctx.max_num_pages_per_request)
             return o
+        if getattr(ctx, "_pending_indexer", None) is not None:
+            ctx.flush_indexer()
         self.impl(x, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o, eff_bs, ctx.topk_val,
                   ctx.page_reserved_bos, ctx.page_reserved_eos, ctx.max_num_pages_per_request)
         return o

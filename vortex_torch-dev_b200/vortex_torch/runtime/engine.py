@@ -101,6 +101,7 @@ class VortexDecodeRuntime:
         self.sm_scale = 1.0 / math.sqrt(head_dim) if sm_scale is None else sm_scale
         self.flow = flow or build_vflow(self.sa.vortex_module_name, None, self.sa.vortex_module_path)
         self.skip = set(self.sa.vortex_layers_skip) if self.sa.enable_vortex_sparsity else set(range(num_layers))
+        self.fuse_attention = True  # run the flow's page selection and the attention as one kernel when possible
 
         self.model_runner = ModelRunnerStub(self.sa, context_len, max_bs, self.device)
         longest = context_len if self.sa.vortex_max_seq_lens < 0 else self.sa.vortex_max_seq_lens
@@ -141,6 +142,21 @@ class VortexDecodeRuntime:
         which = 1 if sparse else 0
         eff_bs = self.ictx.batch_size * self.H
         cache = self.pool.buffers[layer]
+        pend = self.ictx.take_pending_indexer()
+        if pend is not None:
+            pq, py, po = pend
+            if (sparse and self.dtype == torch.bfloat16 and self.D in (64, 128) and self.G in (1, 2, 4, 8)
+                    and pq.data_ptr() == q.data_ptr() and pq.shape[1] == self.G
+                    and po.data_ptr() == b.kv_indices_decode[1].data_ptr()):
+                # selection and attention of this layer in one launch
+                _cabi.sparse_layer_fused(q, py, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
+                                         b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
+                                         b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
+                                         self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
+                                         self.ictx.max_num_pages_per_request, self.sm_scale)
+                return out
+            self.ictx._pending_indexer = pend
+            self.ictx.flush_indexer()
         _cabi.decode_gqa(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which], b.kv_indices_decode[which],
                          b.kv_last_page_len_decode, eff_bs, self.P, self.sm_scale)
         return out
@@ -163,8 +179,12 @@ class VortexDecodeRuntime:
             return self.attention(qv, layer, ov, sparse=False)
         qt = as_vtensor(qv, FORMAT.BATCHED)
         qt._vtx_allow_lazy_mean = True
-        self.flow.forward_indexer(qt, self.backend.kv_indices_decode[1].view(-1, 1, 1), cache, ctx=self.ictx)
-        return self.attention(qv, layer, ov, sparse=True)
+        self.ictx.defer_indexer(self.fuse_attention)
+        try:
+            self.flow.forward_indexer(qt, self.backend.kv_indices_decode[1].view(-1, 1, 1), cache, ctx=self.ictx)
+            return self.attention(qv, layer, ov, sparse=True)
+        finally:
+            self.ictx.defer_indexer(False)
 
     def step(self, cached_seq_lens: torch.Tensor, req_indices: torch.Tensor, q: Sequence[torch.Tensor],
              new_k: Sequence[torch.Tensor], new_v: Sequence[torch.Tensor], loc: torch.Tensor,
