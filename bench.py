@@ -293,7 +293,8 @@ def time_kernels(rt, step, cfg, reps):
             _cabi.sparse_layer_fused(qv, cache["centroids"], cache["k"], cache["v"], ov, b.kv_indptr_decode[0],
                                      b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
                                      b.kv_last_page_len_decode, eff_bs, rt.P, cfg["K"], cfg["bos"], cfg["eos"],
-                                     rt.ictx.max_num_pages_per_request, rt.sm_scale)
+                                     rt.ictx.max_num_pages_per_request, rt.sm_scale, step.new_k[l], step.new_v[l],
+                                     step.loc)
 
     kinds = dict(sparse_layer_fused=(run_fused, len(sparse_layers)),
                  indexer=(run_indexer, len(sparse_layers)),
@@ -655,7 +656,7 @@ def main():
 
     if rank == 0:
         n_sparse = cfg["layers"] - len(cfg["skip"])
-        launches_per_step = 1 + cfg["layers"] + n_sparse + len(cfg["skip"])
+        launches_per_step = 1 + n_sparse + 2 * len(cfg["skip"])
         value = world * args.steps / dev_s
         line = dict(
             metric=METRIC, value=value, unit="steps/s", n_gpus=world, steps=args.steps, warmup=W,

@@ -143,13 +143,17 @@ int vtx_indexer_fused(const void* q, const void* centroids, const int32_t* dense
                       int max_num_pages_per_request, int dtype, void* stream);
 
 /*
- * One launch for a sparse layer: vtx_indexer_fused followed by vtx_decode_gqa on the sparse lists, run by
- * the same CTA per segment (selection first, then attention over the selected pages; the selection is
- * also written to sparse_kv_indices).  Same results as the two calls.  Replaces, per layer, the chain
- * flow/algorithms.py:168-170 plus the paged-decode call the SGLang fork makes afterwards.  bf16 only.
+ * One launch for a sparse layer: [vtx_set_kv_cmean,] vtx_indexer_fused and vtx_decode_gqa on the sparse
+ * lists, run by the same CTA per segment (new-token write, selection, then attention over the selected
+ * pages; the selection is also written to sparse_kv_indices).  Same results as the separate calls.
+ * Replaces, per layer, set_kv_buffer_launcher + CMean (flow/algorithms.py:172-205), the indexer chain
+ * (flow/algorithms.py:168-170) and the paged-decode call the SGLang fork makes afterwards.
+ * new_k, new_v [bs, num_kv_heads, D] and loc [bs] are all null (no write) or all set; with them set,
+ * k_cache, v_cache and centroids are written and page_reserved_eos must be >= 1.  bf16 only.
  */
 int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
-                           void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                           void* out, const void* new_k, const void* new_v, const int64_t* loc,
+                           int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
                            const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
                            const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
                            int head_dim, int page_size, int topk_val, int page_reserved_bos,

@@ -231,6 +231,38 @@ def test_sparse_layer_fused_equals_indexer_then_decode(case):
     assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
 
 
+@pytest.mark.parametrize("seq", [[2048, 1024, 4096, 512], [2047, 1000, 33, 4096]])
+def test_sparse_layer_fused_with_token_append(seq):
+    """The one-launch layer that also writes the new token equals set_kv_cmean + indexer + decode."""
+    H, G, D, P, K, bos, eos = 8, 2, 128, 16, 30, 1, 1
+    prob, dp, ref, _ = _indexer_case(29, seq, H, G, D, P, K, bos, eos, torch.bfloat16)
+    bs = len(seq)
+    loc = torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)], dtype=torch.int64)
+    g = torch.Generator().manual_seed(5)
+    nk = torch.randn(bs, H, D, generator=g).bfloat16().cuda()
+    nv = torch.randn(bs, H, D, generator=g).bfloat16().cuda()
+    res = []
+    for fused in (False, True):
+        d = to_dev(prob)
+        k, v, c = d["k"].clone(), d["v"].clone(), d["centroids"].clone()
+        sel = dp.sparse_indices.clone()
+        out = torch.full_like(d["q"], float("nan"))
+        if fused:
+            _cabi.sparse_layer_fused(d["q"], c, k, v, out, dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel,
+                                     dp.last_page_len, dp.S, P, K, bos, eos, dp.max_pages, 1.0 / math.sqrt(D),
+                                     nk, nv, loc.cuda())
+        else:
+            _cabi.set_kv_cmean(k, v, nk, nv, c, loc.cuda(), P)
+            _cabi.indexer_fused(d["q"], c, dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel, dp.S, K, bos, eos,
+                                dp.max_pages)
+            _cabi.decode_gqa(d["q"], k, v, out, dp.sparse_indptr, sel, dp.last_page_len, dp.S, P, 1.0 / math.sqrt(D))
+        res.append((k, v, c, sel, out))
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a.view(torch.int16) if a.dtype == torch.bfloat16 else a,
+                           b.view(torch.int16) if b.dtype == torch.bfloat16 else b)
+    assert not torch.isnan(res[1][4].float()).any()
+
+
 def test_decode_is_invariant_to_page_order():
     """Size-independent property: permuting the middle pages of a list changes nothing beyond fp32 re-association."""
     seq, H, G, D, P, K = [3000], 4, 2, 128, 16, 30

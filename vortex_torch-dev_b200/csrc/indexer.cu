@@ -261,9 +261,75 @@ struct Geom {
     static_assert(ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
 };
 
+// New-token write for one segment, optional part of the fused sparse-layer kernel (all pointers null
+// when unused).  Same arithmetic as set_kv_cmean_kernel in cache_ops.cu.
+struct AppendArgs {
+    __nv_bfloat16* k_cache;
+    __nv_bfloat16* v_cache;
+    __nv_bfloat16* centroids;
+    const __nv_bfloat16* new_k;  // [bs, H, D]
+    const __nv_bfloat16* new_v;
+    const int64_t* loc;          // [bs]
+    int H, P;
+};
+
+// Executed by one warp: lanes 0 .. D/8-1 each own 8 head dims of segment s = request * H + head.
+// Writes the new token's K and V rows and, if the token closes its page, the page's mean of K
+// (rows 0 .. P-2 from the cache in ascending order, the new row last, one division, one rounding).
+template <int D>
+__device__ __forceinline__ void append_token(const AppendArgs& ap, const int s, const int lane) {
+    constexpr int NCH = D / 8;
+    if (lane >= NCH) return;
+    const int r = s / ap.H, h = s - r * ap.H;
+    const int64_t t = ap.loc[r];
+    const int64_t pid = (t / ap.P) * ap.H + h;
+    const int tok = (int)(t % ap.P);
+    __nv_bfloat16* kpage = ap.k_cache + pid * (int64_t)ap.P * D;
+    __nv_bfloat16* vpage = ap.v_cache + pid * (int64_t)ap.P * D;
+    vtx::Vec8<__nv_bfloat16> nk, nv;
+    nk.load_cached(ap.new_k + (int64_t)s * D + lane * 8);
+    nv.load_cached(ap.new_v + (int64_t)s * D + lane * 8);
+    *reinterpret_cast<uint4*>(kpage + (int64_t)tok * D + lane * 8) = nk.raw;
+    *reinterpret_cast<uint4*>(vpage + (int64_t)tok * D + lane * 8) = nv.raw;
+    if (tok != ap.P - 1) return;
+    float acc[8], kf[8];
+    nk.unpack(kf);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
+        vtx::Vec8<__nv_bfloat16> v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
+            else v[u].zero();
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u < ap.P - 1) {
+                float f[8];
+                v[u].unpack(f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+            }
+        }
+    }
+    const float denom = (float)ap.P;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(__fadd_rn(acc[j], kf[j]), denom);
+    vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, acc);
+}
+
 // MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
-template <typename T, int D, int MODE>
-__device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s) {
+// `side_work(warp, lane)` is called once by every thread, at a point where this CTA's first gather
+// batches are already in flight (or right away for segments that need no selection); the fused layer
+// kernel uses it for the new-token write of one warp.
+struct NoSideWork {
+    __device__ __forceinline__ void operator()(int, int) const {}
+};
+
+template <typename T, int D, int MODE, typename SideWork = NoSideWork>
+__device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s,
+                                             SideWork side_work = SideWork()) {
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
     constexpr int L = Gm::L, HALF = L / 2, SLOTS = Gm::slots;
@@ -275,10 +341,12 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
 
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
-    if (c <= a.K) return;
+    if (c <= a.K || (MODE == 0 && c > a.key_cap)) {  // nothing to select / more candidates than shared memory holds
+        side_work(threadIdx.x >> 5, threadIdx.x & 31);
+        return;
+    }
     const int32_t* row_ids = a.dense_indices + beg;
     if (MODE == 0) {
-        if (c > a.key_cap) return;  // more candidates than the caller sized shared memory for
         for (int i = threadIdx.x; i < c; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
@@ -331,6 +399,7 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         if (i < my_batches) issue(i);
         cp_async_commit();
     }
+    side_work(warp, lane);
     for (int ord = 0; ord < my_batches; ++ord) {
         cp_async_wait<SLOTS - 2>();
         __syncwarp();
@@ -396,12 +465,19 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
 // The decode phase of one segment overlaps the scan phase of its neighbours on the SM, so neither phase
 // pays its own launch and ramp-up; the selected rows still go to the sparse page list (the decode reads
 // them back after the block barrier).  bf16 only (the decode phase is the tensor-core body).
-template <int D, int G>
-__global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da) {
+// With APPEND the CTA first writes its segment's new token (and the centroid of the page it closes):
+// the page is the segment's last one, which is never a candidate (eos >= 1), and the decode phase reads
+// it only after two block barriers, so the write needs no kernel of its own.
+template <int D, int G, bool APPEND>
+__global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
+                                                                  AppendArgs ap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<__nv_bfloat16, D, 0>(ia, smem_raw, blockIdx.x);
+    const int seg = blockIdx.x;
+    indexer_body<__nv_bfloat16, D, 0>(ia, smem_raw, seg, [&](int warp, int lane) {
+        if (APPEND && warp == kWarps - 1) append_token<D>(ap, seg, lane);
+    });
     __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
     vtxdec::decode_mma_body<G, D>(da, smem_raw, blockIdx.x);
 }
@@ -479,27 +555,28 @@ int launch_topk(const void* scores, const IndexerArgs& a, int eff_bs, cudaStream
 }
 
 template <int D, int G>
-int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, int eff_bs, cudaStream_t st) {
+int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
+                            cudaStream_t st) {
     using Gm = Geom<__nv_bfloat16, D>;
     static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
     size_t bytes = Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
     const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
     if (dec > bytes) bytes = dec;
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
-    auto kern = sparse_layer_kernel<D, G>;
+    auto kern = ap.loc ? sparse_layer_kernel<D, G, true> : sparse_layer_kernel<D, G, false>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, ia, da);
+    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, ia, da, ap);
 }
 
 template <int D>
-int launch_sparse_layer_d(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, int eff_bs, int group,
-                          cudaStream_t st) {
+int launch_sparse_layer_d(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
+                          int group, cudaStream_t st) {
     switch (group) {
-        case 1: return launch_sparse_layer_cfg<D, 1>(ia, da, eff_bs, st);
-        case 2: return launch_sparse_layer_cfg<D, 2>(ia, da, eff_bs, st);
-        case 4: return launch_sparse_layer_cfg<D, 4>(ia, da, eff_bs, st);
-        case 8: return launch_sparse_layer_cfg<D, 8>(ia, da, eff_bs, st);
+        case 1: return launch_sparse_layer_cfg<D, 1>(ia, da, ap, eff_bs, st);
+        case 2: return launch_sparse_layer_cfg<D, 2>(ia, da, ap, eff_bs, st);
+        case 4: return launch_sparse_layer_cfg<D, 4>(ia, da, ap, eff_bs, st);
+        case 8: return launch_sparse_layer_cfg<D, 8>(ia, da, ap, eff_bs, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
 }
@@ -600,7 +677,8 @@ extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int
 }
 
 extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
-                                      void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                      void* out, const void* new_k, const void* new_v, const int64_t* loc,
+                                      int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
                                       const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
                                       const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
                                       int head_dim, int page_size, int topk_val, int page_reserved_bos,
@@ -613,8 +691,23 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
         !kv_last_page_len)
         return VTX_ERR_INVALID_ARGUMENT;
     if (group_size < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    const int appends = (new_k != nullptr) + (new_v != nullptr) + (loc != nullptr);
+    if (appends != 0 && appends != 3) return VTX_ERR_INVALID_ARGUMENT;
+    if (appends == 3 && (num_kv_heads < 1 || eff_batch_size % num_kv_heads != 0 || page_reserved_eos < 1))
+        return VTX_ERR_INVALID_ARGUMENT;  // the written page must be a reserved (never scanned) one
     if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
     if (eff_batch_size == 0) return VTX_OK;
+    AppendArgs ap{};
+    if (appends == 3) {
+        ap.k_cache = (__nv_bfloat16*)const_cast<void*>(k_cache);
+        ap.v_cache = (__nv_bfloat16*)const_cast<void*>(v_cache);
+        ap.centroids = (__nv_bfloat16*)const_cast<void*>(centroids);
+        ap.new_k = (const __nv_bfloat16*)new_k;
+        ap.new_v = (const __nv_bfloat16*)new_v;
+        ap.loc = loc;
+        ap.H = num_kv_heads;
+        ap.P = page_size;
+    }
     IndexerArgs ia{};
     ia.q = q;
     ia.centroids = centroids;
@@ -640,8 +733,8 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
     da.scale_log2 = sm_scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)stream;
     switch (head_dim) {
-        case 64: return launch_sparse_layer_d<64>(ia, da, eff_batch_size, group_size, st);
-        case 128: return launch_sparse_layer_d<128>(ia, da, eff_batch_size, group_size, st);
+        case 64: return launch_sparse_layer_d<64>(ia, da, ap, eff_batch_size, group_size, st);
+        case 128: return launch_sparse_layer_d<128>(ia, da, ap, eff_batch_size, group_size, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
 }

@@ -36,7 +36,7 @@ SIGNATURES = {
     "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
-    "vtx_sparse_layer_fused": [_p] * 10 + [_i] * 8 + [_f, _i, _p],
+    "vtx_sparse_layer_fused": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
@@ -221,12 +221,20 @@ def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_sc
 
 def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
                        sparse_kv_indices, kv_last_page_len, eff_bs, page_size, topk_val, bos, eos,
-                       max_pages_per_request, sm_scale) -> None:
-    """Page selection and attention over the selected pages in one launch (bf16)."""
+                       max_pages_per_request, sm_scale, new_k=None, new_v=None, loc=None) -> None:
+    """Page selection and attention over the selected pages in one launch (bf16); with ``new_k``,
+    ``new_v`` ``[bs, H, D]`` and ``loc`` ``[bs]`` the launch also writes the new token and the centroid
+    of the page it closes."""
     if not (q.dtype == centroids.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("sparse_layer_fused: q, centroids, caches and out must share a dtype")
+    H = 0
+    if new_k is not None:
+        want(loc, torch.int64, "loc")
+        H = new_k.shape[1]
+        if new_k.dtype != q.dtype or new_v.dtype != q.dtype:
+            raise TypeError("sparse_layer_fused: new_k/new_v must have q's dtype")
     rc = lib.vtx_sparse_layer_fused(ptr(q), ptr(centroids), ptr(k_cache), ptr(v_cache), ptr(out),
-                                    ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
+                                    ptr(new_k), ptr(new_v), ptr(loc), H, ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
                                     ptr(sparse_kv_indices), ptr(kv_last_page_len), int(eff_bs), q.shape[1],
                                     q.shape[2], int(page_size), int(topk_val), int(bos), int(eos),
                                     int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))

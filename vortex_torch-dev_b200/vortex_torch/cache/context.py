@@ -13,10 +13,36 @@ class Context(ContextBase):
         "_aux_total_bytes", "_aux_total_flops",
         # a KV write handed over by the runtime that the first cache operator may fuse with its own kernel
         "_pending_kv",
+        # a fused KV write + page mean that the runtime may fold into its attention launch (see defer_append)
+        "_defer_append", "_pending_append",
     )
 
     def __init__(self) -> None:
-        self._reset_slots("Cache", {"_pending_kv": None})
+        self._reset_slots("Cache", {"_pending_kv": None, "_defer_append": False, "_pending_append": None})
+
+    # ---- deferred append (KV write + page mean folded into the layer's attention kernel) ----
+    def defer_append(self, enable: bool) -> None:
+        """When enabled, a KV write that a ``Mean(dim=1)`` over the same K cache absorbed is recorded
+        instead of launched; the runtime's attention step takes it (``take_pending_append``) or it is
+        issued by ``flush_append`` / ``_deferred.flush_all`` before anything could read its results."""
+        from .. import _deferred
+
+        self.flush_append()
+        self._defer_append = bool(enable)
+        if enable:
+            _deferred.register(self.flush_append)
+
+    def take_pending_append(self):
+        pend, self._pending_append = self._pending_append, None
+        return pend
+
+    def flush_append(self) -> None:
+        pend = self.take_pending_append()
+        if pend is not None:
+            from .. import _cabi
+
+            k_cache, v_cache, new_k, new_v, centroids, loc, P = pend
+            _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, P)
 
     # ---- deferred KV write (fusion of set_kv with the flow's first cache operator) ----
     def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int) -> None:
@@ -27,6 +53,7 @@ class Context(ContextBase):
         self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size)
 
     def flush_kv_write(self) -> None:
+        self.flush_append()
         pend = self._pending_kv
         if pend is not None:
             self._pending_kv = None

@@ -54,6 +54,8 @@ class Reduce(vOp):
     def execute(self, x: torch.Tensor, output: Optional[torch.Tensor], loc: torch.Tensor,
                 ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}called before profile() (impl is None)"
+        if getattr(ctx, "_pending_append", None) is not None:
+            ctx.flush_append()
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
             k_cache, v_cache, new_k, new_v, ploc, P = pend
@@ -62,6 +64,10 @@ class Reduce(vOp):
                     and new_k.shape[1] == ctx.head_num):
                 # the runtime's KV write and this mean touch the same page: one kernel does both
                 ctx._pending_kv = None
+                if getattr(ctx, "_defer_append", False):
+                    ctx.flush_append()
+                    ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, loc, P)
+                    return output
                 _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, output, loc, P)
                 return output
             ctx.flush_kv_write()

@@ -51,8 +51,9 @@ class Context(ContextBase):
     def flush_indexer(self) -> None:
         pend = self.take_pending_indexer()
         if pend is not None:
-            from .. import _cabi
+            from .. import _cabi, _deferred
 
+            _deferred.flush_all()
             q, y, o = pend
             _cabi.indexer_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr, self.dense_kv_indices, o,
                                 self.batch_size * self.num_kv_heads, self.topk_val, self.page_reserved_bos,

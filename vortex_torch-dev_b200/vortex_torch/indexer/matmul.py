@@ -14,7 +14,7 @@ from typing import Optional
 
 import torch
 
-from .. import _cabi
+from .. import _cabi, _deferred
 from ..abs import FORMAT, as_vtensor, vOp, vTensor
 from ..abs.tensor import lazy_group_mean_source, materialize
 from .context import Context
@@ -67,6 +67,7 @@ class GeMV(vOp):
             self._pending = (src if src is not None else x, y)
             return self.output_buffer
         x = materialize(x)
+        _deferred.flush_all()  # eager launch: anything recorded earlier must reach the GPU first
         eff_bs = ctx.batch_size * ctx.num_kv_heads
         self.impl(x, y, self.output_buffer, ctx.dense_kv_indptr, ctx.dense_kv_indices, eff_bs, ctx.topk_val,
                   ctx.page_reserved_bos, ctx.page_reserved_eos)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .. import _cabi
+from .. import _cabi, _deferred
 from ..abs import FORMAT, vOp, vTensor
 from .context import Context
 
@@ -53,10 +53,12 @@ class topK(vOp):
                 ctx.flush_indexer()
                 ctx._pending_indexer = (q, y, o)  # the runtime's attention launch picks it up
                 return o
+            _deferred.flush_all()
             _cabi.indexer_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
                                 o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
                                 ctx.max_num_pages_per_request)
             return o
+        _deferred.flush_all()  # eager launch: anything recorded earlier must reach the GPU first
         if getattr(ctx, "_pending_indexer", None) is not None:
             ctx.flush_indexer()
         self.impl(x, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o, eff_bs, ctx.topk_val,

@@ -148,15 +148,26 @@ class VortexDecodeRuntime:
             if (sparse and self.dtype == torch.bfloat16 and self.D in (64, 128) and self.G in (1, 2, 4, 8)
                     and pq.data_ptr() == q.data_ptr() and pq.shape[1] == self.G
                     and po.data_ptr() == b.kv_indices_decode[1].data_ptr()):
-                # selection and attention of this layer in one launch
+                # new-token write (if it is still pending), selection and attention of this layer in one launch
+                app = self.cctx.take_pending_append()
+                nk = nv = loc = None
+                if app is not None:
+                    ak, av, nk, nv, ac, loc, aP = app
+                    if not (ak.data_ptr() == cache["k"].data_ptr() and av.data_ptr() == cache["v"].data_ptr()
+                            and ac.data_ptr() == py.data_ptr() and aP == self.P and nk.shape[0] == self.ictx.batch_size
+                            and nk.shape[1] == self.H and self.ictx.page_reserved_eos >= 1):
+                        self.cctx._pending_append = app
+                        self.cctx.flush_append()
+                        nk = nv = loc = None
                 _cabi.sparse_layer_fused(q, py, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
                                          b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
                                          b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
                                          self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
-                                         self.ictx.max_num_pages_per_request, self.sm_scale)
+                                         self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc)
                 return out
             self.ictx._pending_indexer = pend
             self.ictx.flush_indexer()
+        self.cctx.flush_append()
         _cabi.decode_gqa(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which], b.kv_indices_decode[which],
                          b.kv_last_page_len_decode, eff_bs, self.P, self.sm_scale)
         return out
@@ -170,9 +181,12 @@ class VortexDecodeRuntime:
         cache = self.pool.buffers[layer]
         # The KV write is handed to the cache context so that the flow's first cache operator can fold
         # it into its own kernel; whatever is left is launched right after forward_cache.
+        self.cctx.defer_append(self.fuse_attention and layer not in self.skip)
         self.cctx.defer_kv_write(cache["k"], cache["v"], new_k, new_v, loc, self.P)
         self.flow.forward_cache(cache, loc, ctx=self.cctx)
+        pend_append = self.cctx.take_pending_append()  # keep a recorded append across the flush below
         self.cctx.flush_kv_write()
+        self.cctx._pending_append = pend_append
         qv = q.view(-1, self.G, self.D)
         ov = out.view(-1, self.G, self.D)
         if layer in self.skip:
@@ -185,6 +199,7 @@ class VortexDecodeRuntime:
             return self.attention(qv, layer, ov, sparse=True)
         finally:
             self.ictx.defer_indexer(False)
+            self.cctx.defer_append(False)
 
     def step(self, cached_seq_lens: torch.Tensor, req_indices: torch.Tensor, q: Sequence[torch.Tensor],
              new_k: Sequence[torch.Tensor], new_v: Sequence[torch.Tensor], loc: torch.Tensor,
