@@ -71,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
@@ -547,15 +547,15 @@ def run_ragged_workload(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (number is invalid as a bench)")
     ap.add_argument("--batch", type=int, default=None, help="debug: smaller batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--pdl", action="store_true",
-                    help="chain the kernels of the graph by programmatic dependent launch (measured slower: 1.70 vs 1.62 ms)")
+    ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
+                    help="programmatic dependent launch inside the step graph: 0 off, 1 on, 2 on + early prologue")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"],
                     help="c2 = the headline decode step; c5 = side measurement of the MLA block-table decode")
     args = ap.parse_args()
@@ -622,7 +622,7 @@ def main():
     for n in ("seq_lens", "req_indices", "loc", "q", "new_k", "new_v"):
         h[n].copy_(getattr(step, n).cpu())
     if not args.no_graph:
-        step.capture_host_pipeline()
+        step.capture_host_pipeline(programmatic_launch=args.pdl)
     for _ in range(3):
         step.run_from_host()
     barrier()
@@ -665,7 +665,7 @@ def main():
             e2e=dict(value=world * args.steps / e2e_s, unit="steps/s", h2d_bytes_per_step=step.h2d_bytes,
                      d2h_bytes_per_step=step.d2h_bytes),
             gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
-            cuda_graph=not args.no_graph, programmatic_launch=bool(args.pdl and not args.no_graph),
+            cuda_graph=not args.no_graph, programmatic_launch=int(args.pdl if not args.no_graph else 0),
             # traffic: dram__bytes_read + dram__bytes_write of one sparse-layer launch from the ncu capture
             # summarised in profiles/indexer_and_decode_gqa_c2_ncu.md (134.57 MB read + 7.0 MB written)
             roofline=dict(kernel="decode_gqa_mma_kernel (27 sparse-layer launches per step)", traffic=141.6e6,

@@ -39,11 +39,16 @@ const char* vtx_status_string(int status);
 const char* vtx_last_cuda_error(void);
 
 /*
- * Switch programmatic dependent launch on (non-zero) or off (zero, the default) for every later
- * launch of this library in the process.  When on, each kernel is launched with the programmatic
- * stream-serialization attribute; each kernel waits for the complete preceding launch before it
- * touches memory, so results are unchanged and only launch latency overlaps.  No counterpart in
- * the reference (it launches every kernel with plain stream order).
+ * Programmatic dependent launch for every later launch of this library in the process.
+ *   0  off (the default): plain stream order.
+ *   1  each kernel is launched with the programmatic stream-serialization attribute and waits for the
+ *      complete preceding launch before it touches memory: results unchanged, launch latency overlaps.
+ *   2  as 1, and vtx_sparse_layer_fused additionally stages its row ids and starts its first centroid
+ *      gathers BEFORE that wait.  Those reads touch only vtx_plan_decode's outputs and centroid rows of
+ *      non-reserved pages, so the caller must guarantee that the plan launch of the step has completed
+ *      when such a kernel starts: use mode 2 only for a launch that follows, on the same stream, at least
+ *      one other launch of this library issued after vtx_plan_decode.
+ * No counterpart in the reference (it launches every kernel with plain stream order).
  */
 int vtx_set_programmatic_launch(int enable);
 

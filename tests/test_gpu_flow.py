@@ -169,7 +169,7 @@ def test_graphed_step_with_programmatic_launch_matches_eager():
     step.replay()  # eager: no graph yet
     torch.cuda.synchronize()
     want_out, want_sel = step.out.clone(), rt.backend.kv_indices_decode[1].clone()
-    for pdl in (False, True):
+    for pdl in (0, 1, 2):
         step.graph = None
         step.capture(programmatic_launch=pdl)
         for _ in range(5):
@@ -203,8 +203,9 @@ def test_host_pipeline_graph_matches_device_path():
     for n in ("q", "new_k", "new_v"):
         h[n].copy_(torch.randn(h[n].shape, generator=g).bfloat16())
     want = step.run_from_host().clone()      # plain copies + eager kernels
-    step.capture_host_pipeline()
-    for _ in range(3):
-        h["out"].zero_()
-        got = step.run_from_host()
-    assert torch.equal(got, want)
+    for pdl in (0, 2):
+        step.capture_host_pipeline(programmatic_launch=pdl)
+        for _ in range(3):
+            h["out"].zero_()
+            got = step.run_from_host()
+        assert torch.equal(got, want), f"host pipeline differs (programmatic_launch={pdl})"

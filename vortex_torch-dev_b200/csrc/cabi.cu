@@ -17,6 +17,7 @@ void note_cuda_error(cudaError_t e) {
     g_last_error[sizeof(g_last_error) - 1] = '\0';
 }
 bool programmatic_launch_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
+int programmatic_launch_mode() { return g_pdl.load(std::memory_order_relaxed); }
 }  // namespace vtx
 
 extern "C" int vtx_version(void) { return 100; /* 0.1.0 */ }
@@ -34,6 +35,6 @@ extern "C" const char* vtx_status_string(int status) {
 extern "C" const char* vtx_last_cuda_error(void) { return g_last_error; }
 
 extern "C" int vtx_set_programmatic_launch(int enable) {
-    g_pdl.store(enable ? 1 : 0, std::memory_order_relaxed);
+    g_pdl.store(enable < 0 ? 0 : (enable > 2 ? 2 : enable), std::memory_order_relaxed);
     return VTX_OK;
 }

@@ -350,26 +350,7 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         for (int i = threadIdx.x; i < c; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
-    // grouped-query mean, one canonical chunk per thread
-    for (int ch = threadIdx.x; ch < Gm::nchunk; ch += kThreads) {
-        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
-        float acc[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int g = 0; g < a.G; ++g) {
-            vtx::Vec8<T> v;
-            v.load_cached(qs + (int64_t)g * D);
-            float f[8];
-            v.unpack(f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
-        }
-        const float g_f = (float)a.G;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], g_f);
-        vtx::store8(qbar + ch * 8, acc);  // rounds once to T
-    }
-    __syncthreads();
+    __syncthreads();  // row ids are staged
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
@@ -400,6 +381,26 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         cp_async_commit();
     }
     side_work(warp, lane);
+    // grouped-query mean, one canonical chunk per thread
+    for (int ch = threadIdx.x; ch < Gm::nchunk; ch += kThreads) {
+        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int g = 0; g < a.G; ++g) {
+            vtx::Vec8<T> v;
+            v.load_cached(qs + (int64_t)g * D);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+        }
+        const float g_f = (float)a.G;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], g_f);
+        vtx::store8(qbar + ch * 8, acc);  // rounds once to T
+    }
+    __syncthreads();  // q_mean is staged
     for (int ord = 0; ord < my_batches; ++ord) {
         cp_async_wait<SLOTS - 2>();
         __syncwarp();
@@ -468,14 +469,19 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
 // With APPEND the CTA first writes its segment's new token (and the centroid of the page it closes):
 // the page is the segment's last one, which is never a candidate (eos >= 1), and the decode phase reads
 // it only after two block barriers, so the write needs no kernel of its own.
-template <int D, int G, bool APPEND>
+// With EARLY (programmatic launch mode 2) the CTA stages its row ids and starts its first centroid
+// gathers before it waits for the preceding launch: those reads touch only the planner's outputs and
+// this layer's centroid rows of non-reserved pages, which no launch between the planner and this one
+// writes.  Everything else (q, the token write, the sparse list, the output) comes after the wait.
+template <int D, int G, bool APPEND, bool EARLY>
 __global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
                                                                   AppendArgs ap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    vtx::pdl_wait();
+    if (!EARLY) vtx::pdl_wait();
     vtx::pdl_trigger();
     const int seg = blockIdx.x;
     indexer_body<__nv_bfloat16, D, 0>(ia, smem_raw, seg, [&](int warp, int lane) {
+        if (EARLY) vtx::pdl_wait();
         if (APPEND && warp == kWarps - 1) append_token<D>(ap, seg, lane);
     });
     __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
@@ -563,7 +569,9 @@ int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da,
     const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
     if (dec > bytes) bytes = dec;
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
-    auto kern = ap.loc ? sparse_layer_kernel<D, G, true> : sparse_layer_kernel<D, G, false>;
+    const bool early = vtx::programmatic_launch_mode() == 2;
+    auto kern = ap.loc ? (early ? sparse_layer_kernel<D, G, true, true> : sparse_layer_kernel<D, G, true, false>)
+                       : (early ? sparse_layer_kernel<D, G, false, true> : sparse_layer_kernel<D, G, false, false>);
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
     return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, ia, da, ap);

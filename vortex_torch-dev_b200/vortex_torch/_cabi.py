@@ -55,9 +55,10 @@ EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_l
                                     "vtx_set_programmatic_launch"])
 
 
-def set_programmatic_launch(enable: bool) -> None:
-    """Overlap each kernel's launch latency with the drain of the previous one (results unchanged)."""
-    lib.vtx_set_programmatic_launch(1 if enable else 0)
+def set_programmatic_launch(mode) -> None:
+    """0/False off, 1/True on, 2 on with the fused layer kernel's read-only prologue ahead of its wait
+    (see the header for the condition under which 2 is safe).  Results are unchanged in every mode."""
+    lib.vtx_set_programmatic_launch(int(mode))
 
 
 def version() -> int:

@@ -102,6 +102,8 @@ class VortexDecodeRuntime:
         self.flow = flow or build_vflow(self.sa.vortex_module_name, None, self.sa.vortex_module_path)
         self.skip = set(self.sa.vortex_layers_skip) if self.sa.enable_vortex_sparsity else set(range(num_layers))
         self.fuse_attention = True  # run the flow's page selection and the attention as one kernel when possible
+        self.pdl_mode = 0           # programmatic dependent launch: 0 off, 1 on, 2 on + early prologue
+        self._launches_since_plan = 0
 
         self.model_runner = ModelRunnerStub(self.sa, context_len, max_bs, self.device)
         longest = context_len if self.sa.vortex_max_seq_lens < 0 else self.sa.vortex_max_seq_lens
@@ -134,6 +136,8 @@ class VortexDecodeRuntime:
 
     # ------------------------------------------------------------------ one decode step
     def plan(self, cached_seq_lens: torch.Tensor, req_indices: torch.Tensor) -> None:
+        self._launches_since_plan = 0
+        _cabi.set_programmatic_launch(min(self.pdl_mode, 1))
         utils_sglang.plan_decode(cached_seq_lens, self.model_runner.req_to_token_pool.req_to_token, req_indices,
                                  self.ictx)
 
@@ -159,17 +163,27 @@ class VortexDecodeRuntime:
                         self.cctx._pending_append = app
                         self.cctx.flush_append()
                         nk = nv = loc = None
-                _cabi.sparse_layer_fused(q, py, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
-                                         b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
-                                         b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
-                                         self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
-                                         self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc)
+                # the early prologue reads the planner's outputs: allowed once another launch separates us from it
+                early = self.pdl_mode == 2 and self._launches_since_plan >= 1
+                if early:
+                    _cabi.set_programmatic_launch(2)
+                try:
+                    _cabi.sparse_layer_fused(q, py, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
+                                             b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
+                                             b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
+                                             self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
+                                             self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc)
+                finally:
+                    if early:
+                        _cabi.set_programmatic_launch(1)
+                self._launches_since_plan += 1
                 return out
             self.ictx._pending_indexer = pend
             self.ictx.flush_indexer()
         self.cctx.flush_append()
         _cabi.decode_gqa(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which], b.kv_indices_decode[which],
                          b.kv_last_page_len_decode, eff_bs, self.P, self.sm_scale)
+        self._launches_since_plan += 1
         return out
 
     def layer(self, layer: int, q: torch.Tensor, new_k: torch.Tensor, new_v: torch.Tensor, loc: torch.Tensor,
@@ -238,15 +252,16 @@ class GraphedDecodeStep:
     def _eager(self) -> None:
         self.rt.step(self.seq_lens, self.req_indices, self.q, self.new_k, self.new_v, self.loc, self.out)
 
-    def capture(self, programmatic_launch: bool = False) -> None:
-        """Capture the step.  With ``programmatic_launch`` the kernels are chained by programmatic
-        dependent launch inside the graph (each still waits for its whole predecessor).  Off by
-        default: on the 84-kernel Qwen3-shaped step it measured 5 % slower than plain graph edges."""
-        _cabi.set_programmatic_launch(programmatic_launch)
+    def capture(self, programmatic_launch=0) -> None:
+        """Capture the step.  ``programmatic_launch``: 0 plain graph edges, 1 kernels chained by
+        programmatic dependent launch (each waits for its whole predecessor), 2 additionally lets the
+        fused layer kernels run their read-only prologue ahead of that wait."""
+        self.rt.pdl_mode = int(programmatic_launch)
         try:
             self._capture()
         finally:
-            _cabi.set_programmatic_launch(False)
+            self.rt.pdl_mode = 0
+            _cabi.set_programmatic_launch(0)
 
     def _capture(self) -> None:
         side = torch.cuda.Stream(self.rt.device)
@@ -283,7 +298,7 @@ class GraphedDecodeStep:
     def d2h_bytes(self) -> int:
         return self.out.numel() * self.out.element_size()
 
-    def capture_host_pipeline(self) -> None:
+    def capture_host_pipeline(self, programmatic_launch=0) -> None:
         """Capture the host-buffer step as one graph in which the copies overlap the kernels.
 
         Three branches inside the graph: an input branch copies the step's pinned host inputs layer by
@@ -294,6 +309,14 @@ class GraphedDecodeStep:
         dev = self.rt.device
         self._eager()
         torch.cuda.synchronize(dev)
+        self.rt.pdl_mode = int(programmatic_launch)
+        try:
+            self._capture_host_pipeline(h, dev)
+        finally:
+            self.rt.pdl_mode = 0
+            _cabi.set_programmatic_launch(0)
+
+    def _capture_host_pipeline(self, h, dev) -> None:
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         L = self.rt.num_layers
         g = torch.cuda.CUDAGraph()
