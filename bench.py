@@ -666,11 +666,11 @@ def main():
                      d2h_bytes_per_step=step.d2h_bytes),
             gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
             cuda_graph=not args.no_graph, programmatic_launch=int(args.pdl if not args.no_graph else 0),
-            # traffic: dram__bytes_read + dram__bytes_write of one sparse-layer launch from the ncu capture
-            # summarised in profiles/indexer_and_decode_gqa_c2_ncu.md (134.57 MB read + 7.0 MB written)
-            roofline=dict(kernel="decode_gqa_mma_kernel (27 sparse-layer launches per step)", traffic=141.6e6,
-                          algorithmic_bytes_per_launch=ab["sparse_kv_per_layer"],
-                          **roof(ab["sparse_kv_per_layer"], kt["decode_sparse"])),
+            # traffic: dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
+            # profiles/sparse_layer_kernel_c2_ncu.md (204.9 MB read + 7.4 MB written)
+            roofline=dict(kernel="sparse_layer_kernel (token write + indexer + decode, 27 launches per step)",
+                          traffic=212.3e6, algorithmic_bytes_per_launch=ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
+                          **roof(ab["centroids_per_layer"] + ab["sparse_kv_per_layer"], kt["sparse_layer_fused"])),
             kernels=dict(sparse_layer_fused=roof(ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
                                                  kt["sparse_layer_fused"]),
                          indexer_fused=roof(ab["centroids_per_layer"], kt["indexer"]),
