@@ -1,0 +1,91 @@
+"""BASELINE's full sizes on the GPU, checked through size-independent properties (and against the oracle
+where the oracle's vectorised forms finish in seconds)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import vortex_oracle as vo
+from vortex_torch import _cabi
+
+pytestmark = pytest.mark.gpu
+
+
+def test_config4a_page_completion_512_requests():
+    """512 requests each finish one 16-token page; centroid [8, 128] written at a random row: bit-exact."""
+    P, H, D, pages = 16, 8, 128, 4096
+    g = torch.Generator().manual_seed(41)
+    k = torch.randn(pages * H, P, D, generator=g).bfloat16()
+    pg = torch.randperm(pages, generator=g)[:512]
+    loc = pg * P + (P - 1)
+    out = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16, device="cuda")
+    _cabi.cmean(k.cuda(), out, loc.cuda(), H, P)
+    rows = (pg.view(-1, 1) * H + torch.arange(H).view(1, -1)).reshape(-1)
+    want = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16)
+    want[rows, 0] = vo.cmean_pages(k, rows)
+    assert torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
+
+
+def test_config4b_prefill_32768_tokens():
+    """Prefill of one 32768-token request: 2048 page centroids x 8 heads from every token slot: bit-exact."""
+    P, H, D, pages = 16, 8, 128, 2048
+    g = torch.Generator().manual_seed(42)
+    k = torch.randn(pages * H, P, D, generator=g).bfloat16()
+    perm = torch.randperm(pages, generator=g)
+    loc = (perm.view(-1, 1) * P + torch.arange(P).view(1, -1)).reshape(-1)  # all 32768 slots, page order shuffled
+    out = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16, device="cuda")
+    _cabi.cmean(k.cuda(), out, loc.cuda(), H, P)
+    rows = torch.arange(pages * H)
+    assert torch.equal(out.cpu()[:, 0].view(torch.int16), vo.cmean_pages(k, rows).view(torch.int16))
+
+
+def test_config2_layer_properties_at_full_batch():
+    """bs64 x 8192 tokens, one layer: the one-launch layer equals the separate kernels bit for bit, is
+    idempotent, and its selection is a sorted prefix under the (score desc, position asc) order."""
+    from _util import DevicePlan
+
+    bs, H, G, D, P, K, bos, eos, ctx = 64, 8, 2, 128, 16, 30, 1, 1, 8192
+    pages_per_req = ctx // P
+    num_pages = bs * pages_per_req
+    g = torch.Generator().manual_seed(43)
+    perm = torch.randperm(num_pages, generator=g)
+    slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1).to(torch.int32)
+    prob = dict(seq_lens=np.full(bs, ctx, dtype=np.int32), req_to_token=slots.numpy(),
+                req_indices=np.arange(bs, dtype=np.int64))
+    dp = DevicePlan(prob, P, H, K, bos, eos)
+    torch.manual_seed(43)
+    k = torch.empty(num_pages * H, P, D, dtype=torch.bfloat16, device="cuda").normal_()
+    v = torch.empty(num_pages * H, P, D, dtype=torch.bfloat16, device="cuda").normal_()
+    cent = torch.zeros(num_pages * H, 1, D, dtype=torch.bfloat16, device="cuda")
+    _cabi.cmean(k, cent, torch.arange(num_pages, device="cuda", dtype=torch.int64) * P + (P - 1), H, P)
+    q = torch.randn(bs * H, G, D, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(D)
+    sel_a, out_a = dp.sparse_indices.clone(), torch.empty_like(q)
+    _cabi.indexer_fused(q, cent, dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel_a, dp.S, K, bos, eos, dp.max_pages)
+    _cabi.decode_gqa(q, k, v, out_a, dp.sparse_indptr, sel_a, dp.last_page_len, dp.S, P, scale)
+    for _ in range(2):  # twice: idempotent
+        sel_b, out_b = dp.sparse_indices.clone(), torch.empty_like(q)
+        _cabi.sparse_layer_fused(q, cent, k, v, out_b, dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel_b,
+                                 dp.last_page_len, dp.S, P, K, bos, eos, dp.max_pages, scale)
+        assert torch.equal(sel_a, sel_b) and torch.equal(out_a.view(torch.int16), out_b.view(torch.int16))
+    # sorted-prefix property from the stand-alone GeMV scores
+    qm = q.float().mean(1, keepdim=True).bfloat16()
+    scores = torch.zeros(num_pages * H, dtype=torch.bfloat16, device="cuda")
+    _cabi.gemv(qm, cent, scores, dp.dense_indptr, dp.dense_indices, dp.S, K, bos, eos)
+    sc = scores.float().view(dp.S, pages_per_req)[:, bos:pages_per_req - eos]          # [S, 510] by position
+    rows = dp.dense_indices.view(dp.S, pages_per_req)[:, bos:pages_per_req - eos].long()
+    chosen = sel_a.view(dp.S, K + bos + eos)[:, bos:bos + K].long()
+    pos = torch.argsort(rows, dim=1)
+    chosen_pos = torch.gather(pos, 1, torch.searchsorted(torch.gather(rows, 1, pos), chosen))
+    chosen_sc = torch.gather(sc, 1, chosen_pos)
+    # descending scores, ties by ascending position
+    assert bool((chosen_sc[:, :-1] >= chosen_sc[:, 1:]).all())
+    tie = chosen_sc[:, :-1] == chosen_sc[:, 1:]
+    assert bool((chosen_pos[:, :-1][tie] < chosen_pos[:, 1:][tie]).all())
+    # nothing left out beats the last selected one
+    mask = torch.ones_like(sc, dtype=torch.bool)
+    mask.scatter_(1, chosen_pos, False)
+    rest_max = torch.where(mask, sc, torch.full_like(sc, -float("inf"))).max(dim=1).values
+    assert bool((rest_max <= chosen_sc[:, -1]).all())
+    assert torch.isfinite(out_a.float()).all()
