@@ -179,6 +179,22 @@ int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_cache, void
                    int head_dim, int page_size, float sm_scale, int dtype, void* stream);
 
 /*
+ * vtx_decode_gqa with the page list of every segment cut into num_splits parts (one CTA per part, a
+ * second kernel merges the parts): for batches too small to fill the GPU with one CTA per segment.
+ * workspace: caller-owned device scratch of at least vtx_decode_gqa_splitkv_workspace_bytes(...) bytes,
+ * fully overwritten by each call.  Same data contract and results (up to fp32 re-association) as
+ * vtx_decode_gqa; bf16 only.  The split count plays the role of flashinfer's split-KV planning inside
+ * the reference's third-party decode call.
+ */
+int64_t vtx_decode_gqa_splitkv_workspace_bytes(int eff_batch_size, int group_size, int head_dim,
+                                               int num_splits);
+int vtx_decode_gqa_splitkv(const void* q, const void* k_cache, const void* v_cache, void* out,
+                           const int32_t* kv_indptr, const int32_t* kv_indices,
+                           const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                           int head_dim, int page_size, float sm_scale, int num_splits, void* workspace,
+                           int64_t workspace_bytes, int dtype, void* stream);
+
+/*
  * Block-table decode attention over a shared compressed latent (multi-head latent attention):
  * keys are the full latent row, values its first value_dim dims.  No counterpart in the reference
  * (it has no MLA path); the page table and sequence lengths are the block-table form its planner

@@ -263,6 +263,28 @@ def test_sparse_layer_fused_with_token_append(seq):
     assert not torch.isnan(res[1][4].float()).any()
 
 
+@pytest.mark.parametrize("case", [c for c in DECODE_CASES if c[8] == torch.bfloat16],
+                         ids=lambda c: f"H{c[1]}G{c[2]}D{c[3]}P{c[4]}")
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_decode_gqa_splitkv_matches_oracle(case, splits):
+    """Split page lists (also with more splits than pages) merged through the caller's workspace."""
+    seq, H, G, D, P, K, bos, eos, dtype = case
+    prob, dp, ref, _ = _indexer_case(21, seq, H, G, D, P, K, bos, eos, dtype)
+    d = to_dev(prob)
+    ws = torch.full((_cabi.splitkv_workspace_bytes(dp.S, G, D, splits) // 4,), float("nan"), device="cuda")
+    for key in ("sparse", "dense"):
+        indptr, indices = ref[f"{key}_kv_indptr"], ref[f"{key}_kv_indices"]
+        want = vo.decode_gqa(prob["q"], prob["k"], prob["v"], indptr, indices, ref["kv_last_page_len"])
+        out = torch.empty_like(d["q"])
+        _cabi.decode_gqa_splitkv(d["q"], d["k"], d["v"], out, torch.as_tensor(indptr).cuda(),
+                                 torch.as_tensor(indices).cuda(), dp.last_page_len, dp.S, P, 1.0 / math.sqrt(D),
+                                 splits, ws)
+        assert close(out, want, BF16_TOL), f"max err {(out.float().cpu() - want.float()).abs().max()}"
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        _cabi.decode_gqa_splitkv(d["q"], d["k"], d["v"], out, dp.sparse_indptr, dp.sparse_indices, dp.last_page_len,
+                                 dp.S, P, 1.0, splits, ws[:8])
+
+
 def test_decode_is_invariant_to_page_order():
     """Size-independent property: permuting the middle pages of a list changes nothing beyond fp32 re-association."""
     seq, H, G, D, P, K = [3000], 4, 2, 128, 16, 30

@@ -279,6 +279,73 @@ __global__ void __launch_bounds__(kWarps * 32, 4) decode_gqa_mma_kernel(DecodeAr
     vtxdec::decode_mma_body<G, D>(a, smem_raw, blockIdx.x);
 }
 
+// ---- split-KV: the page list of a segment is cut into num_splits parts, one CTA each; the parts'
+// states go to a caller-provided workspace and a second kernel merges them.  For batches that do not
+// fill the GPU with one CTA per segment (few requests, long dense lists).
+template <int G, int D>
+__global__ void __launch_bounds__(kWarps * 32, 4) decode_gqa_split_kernel(DecodeArgs a, float* workspace,
+                                                                         int num_splits) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    const int s = blockIdx.x, sp = blockIdx.y;
+    const int npages = a.indptr[s + 1] - a.indptr[s];
+    const int chunk = (npages + num_splits - 1) / num_splits;
+    const int lo = min(sp * chunk, npages);
+    const int cnt = min(chunk, npages - lo);
+    vtxdec::decode_mma_body<G, D>(a, smem_raw, s, lo, cnt,
+                                  workspace + ((size_t)s * num_splits + sp) * G * (D + 2));
+}
+
+template <int G, int D>
+__global__ void __launch_bounds__(128) decode_gqa_merge_kernel(const float* __restrict__ workspace,
+                                                              __nv_bfloat16* __restrict__ out, int num_splits) {
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    const int s = blockIdx.x;
+    const float* ws = workspace + (size_t)s * num_splits * G * (D + 2);
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+        const int g = idx / D, d = idx % D;
+        float mx = -INFINITY;
+        for (int sp = 0; sp < num_splits; ++sp) mx = fmaxf(mx, ws[(sp * G + g) * (D + 2) + D]);
+        float num = 0.f, den = 0.f;
+        for (int sp = 0; sp < num_splits; ++sp) {
+            const float* p = ws + (sp * G + g) * (D + 2);
+            const float w = p[D] == -INFINITY ? 0.f : exp2f(p[D] - mx);
+            num = fmaf(w, p[d], num);
+            den = fmaf(w, p[D + 1], den);
+        }
+        out[(size_t)s * G * D + idx] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+}
+
+template <int G, int D>
+int launch_split_cfg(const DecodeArgs& a, int eff_bs, int num_splits, float* workspace, cudaStream_t st) {
+    const size_t bytes = vtxdec::decode_mma_smem_bytes<G, D>();
+    auto kern = decode_gqa_split_kernel<G, D>;
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            vtx::note_cuda_error(e);
+            return VTX_ERR_CUDA;
+        }
+    }
+    int rc = vtx::launch(kern, dim3(eff_bs, num_splits), dim3(kWarps * 32), bytes, st, a, workspace, num_splits);
+    if (rc != VTX_OK) return rc;
+    return vtx::launch(decode_gqa_merge_kernel<G, D>, dim3(eff_bs), dim3(128), 0, st, (const float*)workspace,
+                       (__nv_bfloat16*)a.out, num_splits);
+}
+
+int launch_split(const DecodeArgs& a, int eff_bs, int group, int head_dim, int num_splits, float* workspace,
+                 cudaStream_t st) {
+#define VTX_SPLIT_CASE(G_, D_) \
+    if (group == G_ && head_dim == D_) return launch_split_cfg<G_, D_>(a, eff_bs, num_splits, workspace, st);
+    VTX_SPLIT_CASE(1, 64) VTX_SPLIT_CASE(2, 64) VTX_SPLIT_CASE(4, 64) VTX_SPLIT_CASE(8, 64)
+    VTX_SPLIT_CASE(1, 128) VTX_SPLIT_CASE(2, 128) VTX_SPLIT_CASE(4, 128) VTX_SPLIT_CASE(8, 128)
+#undef VTX_SPLIT_CASE
+    return VTX_ERR_UNSUPPORTED;
+}
+
 template <int G, int D>
 int launch_mma_cfg(const DecodeArgs& a, int eff_bs, cudaStream_t st) {
     const size_t bytes = vtxdec::decode_mma_smem_bytes<G, D>();
@@ -373,4 +440,38 @@ extern "C" int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_
     if (dtype == VTX_BF16) return launch_mma(a, eff_batch_size, group_size, head_dim, st);
     if (dtype == VTX_F32) return launch_decode<float>(a, eff_batch_size, group_size, head_dim, st);
     return VTX_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int64_t vtx_decode_gqa_splitkv_workspace_bytes(int eff_batch_size, int group_size, int head_dim,
+                                                          int num_splits) {
+    if (eff_batch_size < 0 || group_size < 1 || head_dim < 1 || num_splits < 1) return -1;
+    return (int64_t)eff_batch_size * num_splits * group_size * (head_dim + 2) * (int64_t)sizeof(float);
+}
+
+extern "C" int vtx_decode_gqa_splitkv(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int32_t* kv_indptr, const int32_t* kv_indices,
+                                      const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                      int head_dim, int page_size, float sm_scale, int num_splits, void* workspace,
+                                      int64_t workspace_bytes, int dtype, void* stream) {
+    if (!q || !k_cache || !v_cache || !out || !kv_indptr || !kv_indices || !kv_last_page_len || !workspace)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (eff_batch_size < 0 || group_size < 1 || head_dim < 1 || page_size < 1 || num_splits < 1 || num_splits > 65535)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    if (workspace_bytes < vtx_decode_gqa_splitkv_workspace_bytes(eff_batch_size, group_size, head_dim, num_splits))
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (eff_batch_size == 0) return VTX_OK;
+    DecodeArgs a;
+    a.q = q;
+    a.k = k_cache;
+    a.v = v_cache;
+    a.out = out;
+    a.indptr = kv_indptr;
+    a.indices = kv_indices;
+    a.last_len = kv_last_page_len;
+    a.P = page_size;
+    a.scale_log2 = sm_scale * kLog2e;
+    return launch_split(a, eff_batch_size, group_size, head_dim, num_splits, (float*)workspace,
+                        (cudaStream_t)stream);
 }

@@ -31,8 +31,13 @@ constexpr size_t decode_mma_smem_bytes() {
 
 // Body of the bf16 tensor-core decode for segment s; smem_raw: the CTA's dynamic shared memory
 // (decode_mma_smem_bytes<G, D>() bytes, 128-byte aligned).  Called by all kDecWarps * 32 threads.
+// pg_lo / pg_cnt: the part of the segment's page list this CTA attends to (whole list: 0 / -1).
+// partial: null -> the normalised result goes to a.out; else the CTA's un-normalised state goes to
+// partial[g * (D + 2) + {0..D-1: sum of p*V, D: running max (log2 domain), D+1: sum of p}] (split-KV).
 template <int G, int D>
-__device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned char* smem_raw, const int s) {
+__device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned char* smem_raw, const int s,
+                                                const int pg_lo = 0, const int pg_cnt = -1,
+                                                float* partial = nullptr) {
     using T = __nv_bfloat16;
     constexpr int KSTEPS = D / 16;                 // k-steps of QK^T == 16-dim tiles of the output
     constexpr int ROWB = D * 2;                    // bytes per token row
@@ -72,19 +77,20 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
     float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
     uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
 
-    const int my_pages = npages > warp ? (npages - warp + kDecWarps - 1) / kDecWarps : 0;
+    const int np_local = pg_cnt < 0 ? npages : pg_cnt;
+    const int my_pages = np_local > warp ? (np_local - warp + kDecWarps - 1) / kDecWarps : 0;
     const int n_items = my_pages * tiles_per_page * 2;
     const unsigned char* kc = reinterpret_cast<const unsigned char*>(a.k);
     const unsigned char* vc = reinterpret_cast<const unsigned char*>(a.v);
     int id_base = 0;
-    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kDecWarps * lane] : 0;
+    int id_reg = (lane < my_pages) ? a.indices[beg + pg_lo + warp + kDecWarps * lane] : 0;
 
     auto issue = [&](int item) {
         const int pair = item >> 1;
         const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
         const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
         const int pg = warp + kDecWarps * po;
-        const int nvalid_page = (pg == npages - 1) ? last_len : P;
+        const int nvalid_page = (pg_lo + pg == npages - 1) ? last_len : P;
         const int tok0 = tile * kDecTileTokens;
         const unsigned char* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * ROWB;
         const uint32_t dst = my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES);
@@ -115,7 +121,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
                 const int po = (nxt >> 1) / tiles_per_page;
                 if (po - id_base >= 32) {
                     id_base += 32;
-                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kDecWarps * (id_base + lane)] : 0;
+                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + pg_lo + warp + kDecWarps * (id_base + lane)] : 0;
                 }
                 issue(nxt);
             }
@@ -126,7 +132,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
             const int pair = item >> 1;
             const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
             const int pg = warp + kDecWarps * po;
-            const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kDecTileTokens;
+            const int nvalid = ((pg_lo + pg == npages - 1) ? last_len : P) - tile * kDecTileTokens;
             float st[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -211,7 +217,15 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
             num = fmaf(wgt, sm_acc[(w * G + g) * D + d], num);
             den = fmaf(wgt, sm_l[w * G + g], den);
         }
-        out[idx] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        if (partial == nullptr) {
+            out[idx] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+        } else {
+            partial[g * (D + 2) + d] = num;
+            if (d == 0) {
+                partial[g * (D + 2) + D] = mx;
+                partial[g * (D + 2) + D + 1] = den;
+            }
+        }
     }
 }
 

@@ -38,12 +38,15 @@ SIGNATURES = {
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_sparse_layer_fused": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_decode_gqa_splitkv": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p, _i64, _i, _p],
     "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.argtypes = _args
     _fn.restype = _i
+lib.vtx_decode_gqa_splitkv_workspace_bytes.argtypes = [_i, _i, _i, _i]
+lib.vtx_decode_gqa_splitkv_workspace_bytes.restype = _i64
 lib.vtx_set_programmatic_launch.argtypes = [_i]
 lib.vtx_set_programmatic_launch.restype = _i
 lib.vtx_version.restype = _i
@@ -52,7 +55,7 @@ lib.vtx_status_string.restype = C.c_char_p
 lib.vtx_last_cuda_error.restype = C.c_char_p
 
 EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error",
-                                    "vtx_set_programmatic_launch"])
+                                    "vtx_set_programmatic_launch", "vtx_decode_gqa_splitkv_workspace_bytes"])
 
 
 def set_programmatic_launch(mode) -> None:
@@ -240,3 +243,20 @@ def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, spa
                                     q.shape[2], int(page_size), int(topk_val), int(bos), int(eos),
                                     int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_sparse_layer_fused")
+
+
+def splitkv_workspace_bytes(eff_bs: int, group: int, head_dim: int, num_splits: int) -> int:
+    return int(lib.vtx_decode_gqa_splitkv_workspace_bytes(int(eff_bs), int(group), int(head_dim), int(num_splits)))
+
+
+def decode_gqa_splitkv(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len, eff_bs, page_size,
+                       sm_scale, num_splits, workspace) -> None:
+    """Split-KV form of `decode_gqa`; ``workspace`` is a device tensor of at least
+    ``splitkv_workspace_bytes(...)`` bytes that the call overwrites."""
+    if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
+        raise TypeError("decode_gqa_splitkv: q, caches and out must share a dtype")
+    rc = lib.vtx_decode_gqa_splitkv(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(kv_indptr), ptr(kv_indices),
+                                    ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size),
+                                    float(sm_scale), int(num_splits), ptr(workspace),
+                                    workspace.numel() * workspace.element_size(), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_decode_gqa_splitkv")

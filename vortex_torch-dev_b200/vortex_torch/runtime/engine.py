@@ -113,6 +113,15 @@ class VortexDecodeRuntime:
                                             self.device)
         self.pool = KVPool(num_layers, num_pages, num_kv_heads, head_dim, self.P,
                            self.flow.get_cache_meta_info(self.P, head_dim), dtype, self.device)
+        # Batches that cannot fill the GPU with one CTA per segment get their page lists split (bf16 only).
+        segs = max_bs * num_kv_heads
+        self.num_splits = 1
+        if dtype == torch.bfloat16 and head_dim in (64, 128) and self.G in (1, 2, 4, 8) and self.device.type == "cuda":
+            self.num_splits = max(1, min(8, 592 // max(1, segs)))
+        self.split_workspace = None
+        if self.num_splits > 1:
+            nbytes = _cabi.splitkv_workspace_bytes(segs, self.G, head_dim, self.num_splits)
+            self.split_workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=self.device)
         self.ictx = IndexerContext().create(self.backend, self.model_runner)
         self.cctx = CacheContext().create(self.pool, self.model_runner)
         self._profile(max_bs)
@@ -181,8 +190,13 @@ class VortexDecodeRuntime:
             self.ictx._pending_indexer = pend
             self.ictx.flush_indexer()
         self.cctx.flush_append()
-        _cabi.decode_gqa(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which], b.kv_indices_decode[which],
-                         b.kv_last_page_len_decode, eff_bs, self.P, self.sm_scale)
+        if self.num_splits > 1:
+            _cabi.decode_gqa_splitkv(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which],
+                                     b.kv_indices_decode[which], b.kv_last_page_len_decode, eff_bs, self.P,
+                                     self.sm_scale, self.num_splits, self.split_workspace)
+        else:
+            _cabi.decode_gqa(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which], b.kv_indices_decode[which],
+                             b.kv_last_page_len_decode, eff_bs, self.P, self.sm_scale)
         self._launches_since_plan += 1
         return out
 
