@@ -25,6 +25,7 @@ extern "C" {
 #define VTX_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, bad enum */
 #define VTX_ERR_UNSUPPORTED 2      /* shape outside what the kernels are built for */
 #define VTX_ERR_CUDA 3             /* the CUDA runtime reported an error at launch */
+#define VTX_ERR_SCRATCH_LIMIT 4    /* the call needs more scratch than the library's built-in buffer holds */
 
 #define VTX_BF16 0
 #define VTX_F32 1
@@ -193,6 +194,29 @@ int vtx_decode_gqa_splitkv(const void* q, const void* k_cache, const void* v_cac
                            const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
                            int head_dim, int page_size, float sm_scale, int num_splits, void* workspace,
                            int64_t workspace_bytes, int dtype, void* stream);
+
+/*
+ * vtx_decode_gqa_splitkv for callers that must not allocate device memory.  (No counterpart in the
+ * reference.)  Some hosts of this library cannot call cudaMalloc when they reach the attention step: a
+ * serving engine that handed the whole device to its own memory pool at start-up has nothing left to
+ * ask the driver for, and a latency-critical decode loop cannot afford the device-wide synchronisation an
+ * allocation implies.  This variant takes no workspace: the split states go to a fixed array of
+ * VTX_NOALLOC_SCRATCH_BYTES that is part of the library image (each GPU that loads the library holds it
+ * until the process exits).  Inputs and outputs are still the caller's.
+ *   - A call whose states need more than that - eff_batch_size * num_splits * group_size * (head_dim + 2)
+ *     * 4 bytes - is refused with VTX_ERR_SCRATCH_LIMIT; lower num_splits or use vtx_decode_gqa_splitkv.
+ *   - The first call on each device looks up the array's device address (with that device current); make
+ *     that first call before any stream capture begins.  No call allocates or frees anything.
+ *   - All calls on a device share the array.  Every call overwrites all of the states it reads, so
+ *     nothing needs clearing between calls, but two calls whose kernels overlap on the GPU (different
+ *     streams) would overwrite each other's states: serialise them.
+ */
+#define VTX_NOALLOC_SCRATCH_BYTES (8 * 1024 * 1024)
+int vtx_decode_gqa_splitkv_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                   const int32_t* kv_indptr, const int32_t* kv_indices,
+                                   const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                   int head_dim, int page_size, float sm_scale, int num_splits,
+                                   int dtype, void* stream);
 
 /*
  * Block-table decode attention over a shared compressed latent (multi-head latent attention):

@@ -28,6 +28,9 @@ extern "C" const char* vtx_status_string(int status) {
         case VTX_ERR_INVALID_ARGUMENT: return "invalid argument (null pointer, negative size or bad enum)";
         case VTX_ERR_UNSUPPORTED: return "shape or size not supported by the sm_100a kernels";
         case VTX_ERR_CUDA: return "CUDA runtime error at launch (see vtx_last_cuda_error)";
+        case VTX_ERR_SCRATCH_LIMIT:
+            return "the call needs more scratch than the library's built-in buffer holds "
+                   "(VTX_NOALLOC_SCRATCH_BYTES): use fewer splits or the variant with a caller workspace";
         default: return "unknown status";
     }
 }

@@ -15,6 +15,8 @@
 // Data contract as produced by the block-table builder (reference: csrc/utils_sglang.cu:123-184,
 // indexer/context.py:117-121); in the reference the attention itself is a third-party
 // paged-decode call made with effective batch bs*H_kv, one KV head and group_size q heads.
+#include <mutex>
+
 #include "decode_mma_body.cuh"
 #include "vtx_common.cuh"
 
@@ -440,6 +442,72 @@ extern "C" int vtx_decode_gqa(const void* q, const void* k_cache, const void* v_
     if (dtype == VTX_BF16) return launch_mma(a, eff_batch_size, group_size, head_dim, st);
     if (dtype == VTX_F32) return launch_decode<float>(a, eff_batch_size, group_size, head_dim, st);
     return VTX_ERR_INVALID_ARGUMENT;
+}
+
+// ---- split-KV decode for callers that cannot allocate device memory ----
+// The parts' states live in this array, which is part of the library image: every GPU that loads the
+// library carries these 8 MB until the process exits.  All calls on a device share it.
+static __device__ __align__(256) float g_splitkv_static_scratch[VTX_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+namespace {
+// In host code the array's name is only a handle for the runtime; the device address has to be asked for,
+// once per device, with that device current.
+std::mutex g_static_scratch_mu;
+float* g_static_scratch_addr[64] = {};
+
+int static_scratch_address(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        vtx::note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
+    if (dev < 0 || dev >= 64) return VTX_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_splitkv_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            vtx::note_cuda_error(e);
+            return VTX_ERR_CUDA;
+        }
+        g_static_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_scratch_addr[dev];
+    return VTX_OK;
+}
+}  // namespace
+
+extern "C" int vtx_decode_gqa_splitkv_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                              const int32_t* kv_indptr, const int32_t* kv_indices,
+                                              const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                              int head_dim, int page_size, float sm_scale, int num_splits,
+                                              int dtype, void* stream) {
+    if (!q || !k_cache || !v_cache || !out || !kv_indptr || !kv_indices || !kv_last_page_len)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (eff_batch_size < 0 || group_size < 1 || head_dim < 1 || page_size < 1 || num_splits < 1 || num_splits > 65535)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    const int64_t need = (int64_t)eff_batch_size * num_splits * group_size * (head_dim + 2) * (int64_t)sizeof(float);
+    if (need > (int64_t)VTX_NOALLOC_SCRATCH_BYTES) return VTX_ERR_SCRATCH_LIMIT;
+    if (eff_batch_size == 0) return VTX_OK;
+    float* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != VTX_OK) return rc;
+    DecodeArgs a;
+    a.q = q;
+    a.k = k_cache;
+    a.v = v_cache;
+    a.out = out;
+    a.indptr = kv_indptr;
+    a.indices = kv_indices;
+    a.last_len = kv_last_page_len;
+    a.P = page_size;
+    a.scale_log2 = sm_scale * kLog2e;
+    // every part writes its whole state (parts without pages write the neutral one), so nothing in the
+    // shared array has to be cleared between calls
+    return launch_split(a, eff_batch_size, group_size, head_dim, num_splits, scratch, (cudaStream_t)stream);
 }
 
 extern "C" int64_t vtx_decode_gqa_splitkv_workspace_bytes(int eff_batch_size, int group_size, int head_dim,

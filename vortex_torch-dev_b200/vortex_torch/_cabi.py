@@ -39,6 +39,7 @@ SIGNATURES = {
     "vtx_sparse_layer_fused": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_gqa_splitkv": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p, _i64, _i, _p],
+    "vtx_decode_gqa_splitkv_noalloc": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _p],
     "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
 for _name, _args in SIGNATURES.items():
