@@ -328,7 +328,7 @@ def time_kernels(rt, step, cfg, reps):
 
 
 def run_mla_workload(args):
-    """Side measurement (not the headline line): BASELINE config 5, MLA block-table sparse decode.
+    """Side measurement (not the headline line): the MLA block-table sparse decode configuration.
 
     bs128, 16 heads, 576-dim latent (values = first 512), page 64, 16384 tokens, topk 32 + 1 + 1.
     Four distinct 2.4 GB latent pools are cycled so that consecutive launches never share L2 lines.
@@ -412,7 +412,7 @@ def run_mla_workload(args):
 
 
 def run_ragged_workload(args):
-    """Side measurement (not the headline line): BASELINE config 3, one sparse layer of a ragged batch.
+    """Side measurement (not the headline line): the ragged-batch configuration, one sparse layer.
 
     256 requests, context lengths uniform in [1024, 32768], 32 q heads / 8 KV heads / head_dim 128, bf16,
     page 16, topk 64 + 1 + 1; requests are dealt to the ranks by total page count (strong scaling: the batch

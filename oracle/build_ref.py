@@ -19,7 +19,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 MODULE = "vortex_torch_C_ref"
-REFERENCE = Path(os.environ.get("VORTEX_REFERENCE_DIR", "/root/reference"))
+REFERENCE = Path(os.environ.get("VORTEX_REFERENCE_DIR", str(Path.home() / "reference")))
 SOURCES = ["csrc/register.cc", "csrc/topk.cu", "csrc/utils_sglang.cu"]
 
 

@@ -15,7 +15,7 @@ import sys
 import types
 
 os.environ["TRITON_INTERPRET"] = "1"
-REF = os.environ.get("VORTEX_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("VORTEX_REFERENCE_DIR", os.path.join(os.path.expanduser("~"), "reference"))
 sys.path.insert(0, REF)
 stub = types.ModuleType("vortex_torch_C")
 for n in ["sglang_plan_decode", "sglang_plan_prefill", "sglang_plan_decode_fa3", "sglang_plan_prefill_fa3",

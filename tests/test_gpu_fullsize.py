@@ -1,4 +1,4 @@
-"""BASELINE's full sizes on the GPU, checked through size-independent properties (and against the oracle
+"""The benchmark configurations' full sizes on the GPU, checked through size-independent properties (and against the oracle
 where the oracle's vectorised forms finish in seconds)."""
 import math
 

@@ -113,7 +113,7 @@ def test_canonical_dot_close_to_exact_and_order_sensitive_cases():
 
 
 def test_config1_cpu_plumbing_matches_plain_torch():
-    """BASELINE config 1: one request, 16 q heads, 8 KV heads, D=128, fp32, 256 pages, top-30 + 1 + 1."""
+    """The CPU-plumbing configuration: one request, 16 q heads, 8 KV heads, D=128, fp32, 256 pages, top-30 + 1 + 1."""
     P, H, G, D, K, bos, eos = 16, 8, 2, 128, 30, 1, 1
     prob = vo.make_paged_problem(0, [4096], H, G, D, P, dtype=torch.float32, permute=True)
     plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64)
