@@ -149,6 +149,22 @@ int vtx_indexer_fused(const void* q, const void* centroids, const int32_t* dense
                       int max_num_pages_per_request, int dtype, void* stream);
 
 /*
+ * Fused indexer of the gqa_block_sparse_attention flow (flow/algorithms.py:238-352): per query head the
+ * dot of q with each candidate page's centroid (GeMM: fp32 products and sum, bf16 result,
+ * indexer/triton_kernels/matmul_impl.py:6-113), a softmax of softmax_scale * score over the segment's
+ * candidates (softmax_impl.py:6-105, bf16 result), the maximum over the group's heads
+ * (reduce_impl.py:58-75) and the top-k selection (csrc/topk.cu), one CTA per segment, nothing but the
+ * selection leaves the SM.  q [eff_bs, group, D]; other arguments as vtx_indexer_fused.  bf16 only.
+ */
+int vtx_indexer_gqa_softmax_fused(const void* q, const void* centroids, const int32_t* dense_kv_indptr,
+                                  const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                                  int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                                  int64_t page_table_stride, int eff_batch_size, int group_size,
+                                  int head_dim, int topk_val, int page_reserved_bos,
+                                  int page_reserved_eos, int max_num_pages_per_request,
+                                  float softmax_scale, int dtype, void* stream);
+
+/*
  * One launch for a sparse layer: [vtx_set_kv_cmean,] vtx_indexer_fused and vtx_decode_gqa on the sparse
  * lists, run by the same CTA per segment (new-token write, selection, then attention over the selected
  * pages; the selection is also written to sparse_kv_indices).  Same results as the separate calls.

@@ -454,3 +454,85 @@ def make_paged_problem(seed: int, seq_lens, num_kv_heads: int, group: int, head_
         cent[fr, 0] = cmean_pages(k, fr)
     return dict(seq_lens=seq, req_to_token=r2t, req_indices=np.arange(bs, dtype=np.int64),
                 k=k, v=v, q=q, centroids=cent, perm=perm)
+
+
+# --------------------------------------------------------------------------- #
+# indexer of the gqa_block_sparse_attention flow
+# --------------------------------------------------------------------------- #
+def exp_canonical(x: np.ndarray) -> np.ndarray:
+    """exp(x) for x <= 0 as a fixed sequence of fp32 operations (so CPU and GPU agree bit for bit).
+
+    k = rint(x * log2(e)); r = x - k*ln2_hi - k*ln2_lo; degree-6 Taylor polynomial by Horner with separate
+    multiplies and adds; result = p * 2^k.  Inputs below -87 give 0.  About 2 ulp from the true value.
+    """
+    f = np.float32
+    x = np.asarray(x, dtype=f)
+    k = np.rint(x * f(1.44269504)).astype(f)
+    r = x - k * f(0.693145751953125)
+    r = r - k * f(1.42860677e-6)
+    p = f(1.0 / 720.0)
+    for c in (1.0 / 120.0, 1.0 / 24.0, 1.0 / 6.0, 0.5, 1.0, 1.0):
+        p = p * r + f(c)
+    scale = ((np.clip(k, -126, 127).astype(np.int32) + 127) << 23).view(f)
+    return np.where(x < f(-87.0), f(0.0), p * scale).astype(f)
+
+
+def canonical_sum128(v: np.ndarray) -> np.float32:
+    """Sum of a vector in the order the kernels use: 128 partial sums (element i goes to partial i % 128,
+    added in ascending i from +0.0), then folded in halves v[j] += v[j + w], w = 64 .. 1."""
+    f = np.float32
+    n = len(v)
+    pad = (-n) % 128
+    a = np.concatenate([np.asarray(v, dtype=f), np.zeros(pad, dtype=f)]).reshape(-1, 128)
+    part = np.zeros(128, dtype=f)
+    for row in a:
+        part = part + row
+    w = 64
+    while w >= 1:
+        part = part[:w] + part[w:2 * w]
+        w //= 2
+    return part[0]
+
+
+def gqa_softmax_scores(q, centroids, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos, scale: float,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Aggregated page scores of the ``gqa_block_sparse_attention`` flow (flow/algorithms.py:238-352):
+    ``GeMM(q, centroids)`` -> ``Softmax(dim=0, scale)`` over the candidate pages -> ``Max(dim=2)`` over the
+    query heads of the group, every operator output rounded to bf16 as in the reference
+    (indexer/triton_kernels/matmul_impl.py:81-88 fp32 products and sum, bf16 out;
+    softmax_impl.py:33-73 scaled softmax over candidates of segments with more than topk_val of them,
+    bf16 out; reduce_impl.py:58-75 max over the last axis).  Reduction orders and exp are the canonical
+    ones of this file (`canonical_dot`, `exp_canonical`, `canonical_sum128`).
+    """
+    assert q.dtype == torch.bfloat16, "this flow's operators are bf16 in the reference"
+    total = int(dense_indptr[eff_bs])
+    if out is None:
+        out = torch.zeros(total, dtype=torch.bfloat16)
+    G = q.shape[1]
+    cf = centroids.view(centroids.shape[0], -1)
+    sc32 = np.float32(scale)
+    for s in range(eff_bs):
+        a = int(dense_indptr[s]) + bos
+        b = int(dense_indptr[s + 1]) - eos
+        if b - a <= topk_val:
+            continue
+        rows = cf[torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)].to(torch.float32)
+        probs = []
+        for g in range(G):
+            dot = bf16_rne(canonical_dot(rows, q[s, g].to(torch.float32), bf16_products=False)).numpy()
+            t = dot.astype(np.float32) * sc32
+            e = exp_canonical(t - t.max())
+            l = canonical_sum128(e)
+            probs.append(bf16_rne(torch.from_numpy((e / l).astype(np.float32))))
+        out.view(-1)[a:b] = torch.stack(probs).max(dim=0).values.to(torch.bfloat16)
+    return out
+
+
+def forward_indexer_gqa(q, centroids, plan, topk_val, bos, eos, scale: float = 0.09):
+    """``GeMM -> Softmax -> Max -> topK`` of the gqa_block_sparse_attention flow; completes ``plan`` in place."""
+    eff_bs = q.shape[0]
+    scores = gqa_softmax_scores(q, centroids, plan["dense_kv_indptr"], plan["dense_kv_indices"], eff_bs, topk_val,
+                                bos, eos, scale)
+    topk_select(scores, plan["dense_kv_indptr"], plan["sparse_kv_indptr"], plan["dense_kv_indices"],
+                plan["sparse_kv_indices"], eff_bs, topk_val, bos, eos)
+    return scores

@@ -163,6 +163,23 @@ def test_indexer_fused_and_split_match_oracle(case):
     np.testing.assert_array_equal(sparse_split.cpu().numpy()[:ns], ref["sparse_kv_indices"])
 
 
+@pytest.mark.parametrize("seq,H,G,D,P,K", [([2048, 1000, 600], 8, 2, 128, 16, 30), ([1024, 5000, 333, 17], 4, 4, 128, 16, 64),
+                                           ([700, 130], 2, 8, 64, 8, 5), ([8192], 2, 1, 128, 16, 30)])
+def test_indexer_gqa_softmax_fused_matches_oracle(seq, H, G, D, P, K):
+    """gqa_block_sparse_attention indexer (GeMM -> Softmax -> Max -> topK): selection bit-exact."""
+    bos, eos = 1, 1
+    prob = vo.make_paged_problem(13, seq, H, G, D, P)
+    dp = DevicePlan(prob, P, H, K, bos, eos)
+    ref = dp.oracle(prob)
+    vo.forward_indexer_gqa(prob["q"], prob["centroids"], ref, K, bos, eos, scale=0.09)
+    d = to_dev(prob)
+    sel = dp.sparse_indices.clone()
+    _cabi.indexer_gqa_softmax_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel,
+                                    dp.S, K, bos, eos, dp.max_pages, 0.09)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(sel.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+
+
 def test_topk_heavy_ties():
     """Scores drawn from four values: selection must follow candidate order inside each tie class."""
     H, K, bos, eos, P = 2, 30, 1, 1, 16

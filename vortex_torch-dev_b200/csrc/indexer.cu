@@ -203,6 +203,7 @@ struct IndexerArgs {
     int32_t* sparse_pt;
     int64_t pt_stride;
     int G, D, K, bos, eos, key_cap;
+    float scale;  // MODE 2: softmax scale
 };
 
 // ---- asynchronous row gather ----
@@ -243,6 +244,38 @@ __device__ __forceinline__ void add_products(float& acc, const float* row_chunk,
     acc = __fadd_rn(acc, __fmul_rn(r1.y, q1.y));
     acc = __fadd_rn(acc, __fmul_rn(r1.z, q1.z));
     acc = __fadd_rn(acc, __fmul_rn(r1.w, q1.w));
+}
+
+// bf16 row chunk times fp32 query chunk, products kept in fp32 (the GeMM operator's arithmetic).
+__device__ __forceinline__ void add_products_f32(float& acc, const __nv_bfloat16* row_chunk, const float* q_chunk) {
+    const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
+    const float4 q0 = *reinterpret_cast<const float4*>(q_chunk), q1 = *reinterpret_cast<const float4*>(q_chunk + 4);
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.x), q0.x));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.x), q0.y));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.y), q0.z));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.y), q0.w));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.z), q1.x));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.z), q1.y));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.w), q1.z));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.w), q1.w));
+}
+
+// exp(x) for x <= 0 as a fixed sequence of fp32 operations, identical on CPU and GPU:
+// k = rint(x * log2 e); r = x - k*ln2_hi - k*ln2_lo; degree-6 Taylor polynomial (Horner, separate
+// multiply and add); result = p * 2^k; inputs below -87 give 0.
+__device__ __forceinline__ float exp_canonical(float x) {
+    if (x < -87.0f) return 0.f;
+    const float k = rintf(__fmul_rn(x, 1.44269504f));
+    float r = __fsub_rn(x, __fmul_rn(k, 0.693145751953125f));
+    r = __fsub_rn(r, __fmul_rn(k, 1.42860677e-6f));
+    float p = (float)(1.0 / 720.0);
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 120.0));
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 24.0));
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 6.0));
+    p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+    return __fmul_rn(p, __int_as_float(((int)k + 127) << 23));
 }
 
 template <typename T, int D>
@@ -327,26 +360,33 @@ struct NoSideWork {
     __device__ __forceinline__ void operator()(int, int) const {}
 };
 
-template <typename T, int D, int MODE, typename SideWork = NoSideWork>
+// MODE 2 (bf16 only, GQ = query heads per KV head): the gqa_block_sparse_attention scores, i.e.
+// per query head the fp32-product dot with the page's row rounded to bf16, a softmax of scale * score over
+// the segment's candidates (canonical exp and sum) rounded to bf16, and the maximum over the heads.
+template <typename T, int D, int MODE, typename SideWork = NoSideWork, int GQ = 1>
 __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s,
                                              SideWork side_work = SideWork()) {
+    constexpr int NQ = MODE == 2 ? GQ : 1;                          // score accumulators per row
+    constexpr int QBYTES = MODE == 2 ? GQ * D * 4 : D * (int)sizeof(T);  // staged query: fp32 heads / mean in T
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
     constexpr int L = Gm::L, HALF = L / 2, SLOTS = Gm::slots;
     // layout: [ring][q_mean][keys][ids]
     unsigned char* ring = smem_raw;
     T* qbar = reinterpret_cast<T*>(smem_raw + Gm::ring_bytes);
-    Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + Gm::row_bytes);
+    Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + QBYTES);
     int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
+    __nv_bfloat16* sbuf = reinterpret_cast<__nv_bfloat16*>(ids + a.key_cap);  // MODE 2: [candidate][head] scores
+    float* qf32 = reinterpret_cast<float*>(qbar);                               // MODE 2: [head][D]
 
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;
-    if (c <= a.K || (MODE == 0 && c > a.key_cap)) {  // nothing to select / more candidates than shared memory holds
+    if (c <= a.K || (MODE != 1 && c > a.key_cap)) {  // nothing to select / more candidates than shared memory holds
         side_work(threadIdx.x >> 5, threadIdx.x & 31);
         return;
     }
     const int32_t* row_ids = a.dense_indices + beg;
-    if (MODE == 0) {
+    if (MODE != 1) {
         for (int i = threadIdx.x; i < c; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
@@ -381,8 +421,19 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         cp_async_commit();
     }
     side_work(warp, lane);
+    if (MODE == 2) {  // the group's query heads, widened to fp32
+        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
+        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
+            vtx::Vec8<T> v;
+            v.load_cached(qs + ch * 8);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qf32[ch * 8 + j] = f[j];
+        }
+    }
     // grouped-query mean, one canonical chunk per thread
-    for (int ch = threadIdx.x; ch < Gm::nchunk; ch += kThreads) {
+    for (int ch = threadIdx.x; MODE != 2 && ch < Gm::nchunk; ch += kThreads) {
         const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
         float acc[8];
 #pragma unroll
@@ -408,49 +459,102 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         cp_async_commit();
         const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * Gm::slot_bytes + r_in * Gm::row_bytes;
         const int sw = (r_in & 3) << 1;
-        float acc[HALF];
+        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;
 #pragma unroll
-        for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
-#ifdef VTX_EXP_NOSCORE
-        acc[0] = (float)*reinterpret_cast<const uint32_t*>(row_ptr + par * 16);
-#else
-        // this thread owns partial sums 2*i + par; partial l takes chunks l, l + L, ...
+        for (int g = 0; g < NQ; ++g) {
+            float acc[HALF];
 #pragma unroll
-        for (int k = 0; k * L < Gm::nchunk; ++k) {
+            for (int ii = 0; ii < HALF; ++ii) acc[ii] = 0.f;
+            // this thread owns partial sums 2*ii + par; partial l takes chunks l, l + L, ...
 #pragma unroll
-            for (int i = 0; i < HALF; ++i) {
-                if (k * L + 2 * i < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
-                    const int ch = k * L + 2 * i + par;
-                    // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
-                    const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
-                    add_products(acc[i], src, qbar + ch * 8);
+            for (int k = 0; k * L < Gm::nchunk; ++k) {
+#pragma unroll
+                for (int ii = 0; ii < HALF; ++ii) {
+                    if (k * L + 2 * ii < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
+                        const int ch = k * L + 2 * ii + par;
+                        // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
+                        const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
+                        if constexpr (MODE == 2)
+                            add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             qf32 + g * D + ch * 8);
+                        else
+                            add_products(acc[ii], src, qbar + ch * 8);
+                    }
                 }
             }
-        }
-#endif
 #pragma unroll
-        for (int w = HALF / 2; w > 0; w >>= 1)
+            for (int w = HALF / 2; w > 0; w >>= 1)
 #pragma unroll
-            for (int i = 0; i < w; ++i) acc[i] = __fadd_rn(acc[i], acc[i + w]);
-        const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
-        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;
-        if (par == 0 && i < c) {
-            const float sc = vtx::round_to<T>(total);
-            if (MODE == 0) keys[i] = KeyOf<T>::make(sc, i);
-            else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + i, sc);
+                for (int ii = 0; ii < w; ++ii) acc[ii] = __fadd_rn(acc[ii], acc[ii + w]);
+            const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
+            if (par == 0 && i < c) {
+                const float sc = vtx::round_to<T>(total);
+                if (MODE == 0) keys[i] = KeyOf<T>::make(sc, i);
+                else if (MODE == 2) sbuf[i * NQ + g] = __float2bfloat16_rn(sc);
+                else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + i, sc);
+            }
         }
     }
     cp_async_wait<0>();
-    if (MODE == 0) {
+    if constexpr (MODE == 2) {
+        __syncthreads();  // all head scores written; the rings are idle and lend their space to the reductions
+        float* red = reinterpret_cast<float*>(ring);  // [NQ][kThreads]
+        float mx[NQ], l[NQ];
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) mx[g] = -INFINITY;
+        for (int i = threadIdx.x; i < c; i += kThreads)
+#pragma unroll
+            for (int g = 0; g < NQ; ++g)
+                mx[g] = fmaxf(mx[g], __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale));
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) red[g * kThreads + threadIdx.x] = mx[g];
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) {
+            float m = red[g * kThreads];
+            for (int t = 1; t < kThreads; ++t) m = fmaxf(m, red[g * kThreads + t]);
+            mx[g] = m;
+        }
+        __syncthreads();
+        // sum of exp: partial t takes candidates t, t + 128, ... in ascending order, then halves are folded
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) l[g] = 0.f;
+        for (int i = threadIdx.x; i < c; i += kThreads)
+#pragma unroll
+            for (int g = 0; g < NQ; ++g) {
+                const float t = __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale);
+                l[g] = __fadd_rn(l[g], exp_canonical(__fsub_rn(t, mx[g])));
+            }
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) red[g * kThreads + threadIdx.x] = l[g];
+        __syncthreads();
+        for (int w = kThreads / 2; w > 0; w >>= 1) {
+            if (threadIdx.x < w)
+#pragma unroll
+                for (int g = 0; g < NQ; ++g)
+                    red[g * kThreads + threadIdx.x] =
+                        __fadd_rn(red[g * kThreads + threadIdx.x], red[g * kThreads + threadIdx.x + w]);
+            __syncthreads();
+        }
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) l[g] = red[g * kThreads];
+        for (int i = threadIdx.x; i < c; i += kThreads) {
+            float best = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < NQ; ++g) {
+                const float t = __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale);
+                const float pr = __fdiv_rn(exp_canonical(__fsub_rn(t, mx[g])), l[g]);
+                best = fmaxf(best, vtx::round_to<T>(pr));
+            }
+            keys[i] = KeyOf<T>::make(best, i);
+        }
+    }
+    if (MODE != 1) {
         __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
         const int o0 = a.sparse_indptr[s] + a.bos;
-#ifndef VTX_EXP_NOSORT
         select_and_store<T>(keys, ids, c, a.K, a.sparse_indices + o0,
                             a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr,
                             reinterpret_cast<Key*>(ring));
-#else
-        if (threadIdx.x < a.K) a.sparse_indices[o0 + threadIdx.x] = ids[KeyOf<T>::index(keys[threadIdx.x])];
-#endif
     }
 }
 
@@ -460,6 +564,15 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
     vtx::pdl_wait();
     vtx::pdl_trigger();
     indexer_body<T, D, MODE>(a, smem_raw, blockIdx.x);
+}
+
+// gqa_block_sparse_attention indexer: GeMM -> Softmax over pages -> Max over heads -> top-k, one launch.
+template <int D, int GQ>
+__global__ void __launch_bounds__(kThreads, 4) indexer_gqa_kernel(IndexerArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    indexer_body<__nv_bfloat16, D, 2, NoSideWork, GQ>(a, smem_raw, blockIdx.x);
 }
 
 // One launch per sparse layer: page selection, then attention over the selected pages, by the same CTA.
@@ -558,6 +671,27 @@ int launch_topk(const void* scores, const IndexerArgs& a, int eff_bs, cudaStream
     int rc = set_smem(topk_kernel<T>, bytes);
     if (rc != VTX_OK) return rc;
     return vtx::launch(topk_kernel<T>, dim3(eff_bs), dim3(kThreads), bytes, st, (const T*)scores, a);
+}
+
+template <int D, int GQ>
+int launch_indexer_gqa_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
+    using Gm = Geom<__nv_bfloat16, D>;
+    const size_t bytes = Gm::ring_bytes + (size_t)GQ * D * 4 +
+                         (size_t)a.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + GQ * sizeof(__nv_bfloat16));
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    auto kern = indexer_gqa_kernel<D, GQ>;
+    int rc = set_smem(kern, bytes);
+    if (rc != VTX_OK) return rc;
+    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, a);
+}
+
+int launch_indexer_gqa(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
+#define VTX_GQA_CASE(D_, G_) \
+    if (a.D == D_ && a.G == G_) return launch_indexer_gqa_cfg<D_, G_>(a, eff_bs, st);
+    VTX_GQA_CASE(64, 1) VTX_GQA_CASE(64, 2) VTX_GQA_CASE(64, 4) VTX_GQA_CASE(64, 8)
+    VTX_GQA_CASE(128, 1) VTX_GQA_CASE(128, 2) VTX_GQA_CASE(128, 4) VTX_GQA_CASE(128, 8)
+#undef VTX_GQA_CASE
+    return VTX_ERR_UNSUPPORTED;
 }
 
 template <int D, int G>
@@ -745,4 +879,37 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
         case 128: return launch_sparse_layer_d<128>(ia, da, ap, eff_batch_size, group_size, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
+}
+
+extern "C" int vtx_indexer_gqa_softmax_fused(const void* q, const void* centroids, const int32_t* dense_kv_indptr,
+                                             const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                                             int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                                             int64_t page_table_stride, int eff_batch_size, int group_size,
+                                             int head_dim, int topk_val, int page_reserved_bos,
+                                             int page_reserved_eos, int max_num_pages_per_request,
+                                             float softmax_scale, int dtype, void* stream) {
+    int rc = check_common(dense_kv_indptr, dense_kv_indices, eff_batch_size, topk_val, page_reserved_bos,
+                          page_reserved_eos, max_num_pages_per_request, dtype);
+    if (rc != VTX_OK) return rc;
+    if (!q || !centroids || !sparse_kv_indptr || !sparse_kv_indices) return VTX_ERR_INVALID_ARGUMENT;
+    if (group_size < 1 || (sparse_page_table && page_table_stride < 1)) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    if (eff_batch_size == 0) return VTX_OK;
+    IndexerArgs a{};
+    a.q = q;
+    a.centroids = centroids;
+    a.dense_indptr = dense_kv_indptr;
+    a.sparse_indptr = sparse_kv_indptr;
+    a.dense_indices = dense_kv_indices;
+    a.sparse_indices = sparse_kv_indices;
+    a.sparse_pt = sparse_page_table;
+    a.pt_stride = page_table_stride;
+    a.G = group_size;
+    a.D = head_dim;
+    a.K = topk_val;
+    a.bos = page_reserved_bos;
+    a.eos = page_reserved_eos;
+    a.key_cap = key_capacity(max_num_pages_per_request);
+    a.scale = softmax_scale;
+    return launch_indexer_gqa(a, eff_batch_size, (cudaStream_t)stream);
 }

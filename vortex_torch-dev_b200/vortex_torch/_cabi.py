@@ -36,6 +36,7 @@ SIGNATURES = {
     "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_indexer_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_indexer_gqa_softmax_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "vtx_sparse_layer_fused": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_gqa_splitkv": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p, _i64, _i, _p],
@@ -261,3 +262,18 @@ def decode_gqa_splitkv(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_
                                     float(sm_scale), int(num_splits), ptr(workspace),
                                     workspace.numel() * workspace.element_size(), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_gqa_splitkv")
+
+
+def indexer_gqa_softmax_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                              eff_bs, topk_val, bos, eos, max_pages_per_request, softmax_scale,
+                              sparse_page_table=None) -> None:
+    """GeMM -> Softmax(scale) over pages -> Max over heads -> topK of the gqa_block_sparse_attention flow."""
+    if q.dtype != centroids.dtype:
+        raise TypeError("indexer_gqa_softmax_fused: q and centroids must share a dtype")
+    stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    rc = lib.vtx_indexer_gqa_softmax_fused(ptr(q), ptr(centroids), ptr(dense_kv_indptr), ptr(sparse_kv_indptr),
+                                           ptr(dense_kv_indices), ptr(sparse_kv_indices), ptr(sparse_page_table),
+                                           stride, int(eff_bs), q.shape[1], q.shape[2], int(topk_val), int(bos),
+                                           int(eos), int(max_pages_per_request), float(softmax_scale),
+                                           dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_indexer_gqa_softmax_fused")
