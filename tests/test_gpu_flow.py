@@ -209,3 +209,35 @@ def test_host_pipeline_graph_matches_device_path():
             h["out"].zero_()
             got = step.run_from_host()
         assert torch.equal(got, want), f"host pipeline differs (programmatic_launch={pdl})"
+
+
+def test_gqa_block_sparse_flow_through_runtime():
+    """The shipped gqa_block_sparse_attention flow (GeMM -> Softmax -> Max -> topK; CMean) run by the
+    runtime: selections bit-exact with the oracle's restatement of that flow, attention within tolerance."""
+    from vortex_torch.flow import build_vflow
+
+    seq, L, H, G, D, P, K, bos, eos = [2048, 1000, 4096, 300], 2, 8, 2, 128, 16, 30, 1, 1
+    prob = vo.make_paged_problem(37, seq, H, G, D, P)
+    flow = build_vflow("gqa_block_sparse_attention")
+    rt = _runtime(prob, seq, L, H, G, D, P, K, bos, eos, torch.bfloat16, flow=flow)
+    assert flow.output_func._gqa_chain is not None
+    for l in range(L):
+        for name in ("k", "v", "centroids"):
+            rt.pool.buffers[l][name].copy_(prob[name])
+    bs = len(seq)
+    loc = torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)], dtype=torch.int64)
+    nk = torch.stack([prob["k"][(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)]).cuda()
+    nv = torch.stack([prob["v"][(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)]).cuda()
+    q = prob["q"].view(bs, H * G, D).cuda()
+    outs = [torch.empty_like(q) for _ in range(L)]
+    rt.step(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(), [q] * L, [nk] * L,
+            [nv] * L, loc.cuda(), outs)
+    torch.cuda.synchronize()
+    plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)
+    vo.forward_indexer_gqa(prob["q"], prob["centroids"], plan, K, bos, eos, scale=0.09)
+    ns = int(plan["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], plan["sparse_kv_indices"])
+    want = vo.decode_gqa(prob["q"], prob["k"], prob["v"], plan["sparse_kv_indptr"], plan["sparse_kv_indices"],
+                         plan["kv_last_page_len"])
+    got = outs[1].view(bs * H, G, D).float().cpu()
+    assert bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())

@@ -146,3 +146,26 @@ def test_balance_requests():
         loads = [sum(pages[i] for i in p) for p in parts]
         assert max(loads) - min(loads) <= max(pages)
     assert balance_requests(pages, 2) == balance_requests(pages, 2)
+
+
+def test_gqa_chain_is_recognised_and_unchained_use_fails():
+    from vortex_torch.abs import FORMAT, as_vtensor
+    from vortex_torch.indexer import Context, GeMM, Max, Softmax
+    from vortex_torch.runtime import ServerArgs, VortexDecodeRuntime
+
+    rt = VortexDecodeRuntime(2, 8, 2, 128, num_pages=32, max_bs=2, context_len=256, device="cpu",
+                             server_args=ServerArgs(vortex_module_name="gqa_block_sparse_attention"))
+    f = rt.flow
+    assert f.output_func._gqa_chain == (f.gemm, f.softmax, f.max_op)
+    assert f.gemm.output_buffer.shape == (rt.ictx.max_num_pages, 1, 4) and f.max_op.output_buffer.shape[1:] == (1, 1)
+    # a GeMM whose result does not end in the fused chain has nothing to run
+    ctx = Context()
+    ctx.max_num_pages = 8
+    g = GeMM()
+    g.profile(as_vtensor(torch.zeros(1, 2, 16), FORMAT.BATCHED), as_vtensor(torch.zeros(4, 1, 16), FORMAT.PAGED), ctx)
+    with pytest.raises(NotImplementedError, match="no stand-alone sm_100a kernel"):
+        g.execute(torch.zeros(1, 2, 16), torch.zeros(4, 1, 16), ctx)
+    with pytest.raises(NotImplementedError):
+        Softmax(dim=0, scale=0.5).execute(torch.zeros(1, 1, 1), ctx)
+    with pytest.raises(NotImplementedError):
+        Max(dim=2).execute(torch.zeros(1, 1, 1), ctx)

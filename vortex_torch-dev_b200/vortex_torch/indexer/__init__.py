@@ -1,19 +1,19 @@
 """Indexer-side operators: score pages against the query and pick the sparse page set.
 
 Export list of the reference's ``indexer/__init__.py:49-71``.  Built on sm_100a: ``GeMV``,
-``topK``, ``Context``/``get_ctx`` and ``utils_sglang``; the other names are placeholders that
-raise ``NotImplementedError`` when used.
+``topK``, ``Context``/``get_ctx``, ``utils_sglang`` and - as links of one fused kernel - ``GeMM``,
+``Softmax`` and ``Max(dim=2)``; the other names are placeholders that raise ``NotImplementedError``
+when used.
 """
 from ._unbuilt import unbuilt as _unbuilt
 from .context import Context, get_ctx
-from .matmul import GeMV
+from .matmul import GeMM, GeMV
 from .output_func import topK
+from .reduce import L2Norm, Max, Mean, Min, Sum
+from .scan import Normalize, Softmax
 from . import utils_sglang
 
 _W = "indexer"
-GeMM = _unbuilt("GeMM", _W)
-Max, Mean, Min, L2Norm, Sum = (_unbuilt(n, _W) for n in ("Max", "Mean", "Min", "L2Norm", "Sum"))
-Softmax, Normalize = _unbuilt("Softmax", _W), _unbuilt("Normalize", _W)
 Transpose = _unbuilt("Transpose", _W)
 Maximum, Minimum, Multiply, Add = (_unbuilt(n, _W) for n in ("Maximum", "Minimum", "Multiply", "Add"))
 Relu, Sigmoid, Silu, Add_Mul, Abs = (_unbuilt(n, _W) for n in ("Relu", "Sigmoid", "Silu", "Add_Mul", "Abs"))

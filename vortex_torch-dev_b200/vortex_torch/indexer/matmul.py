@@ -18,6 +18,7 @@ from .. import _cabi, _deferred
 from ..abs import FORMAT, as_vtensor, vOp, vTensor
 from ..abs.tensor import lazy_group_mean_source, materialize
 from .context import Context
+from ._chain import ChainedOp, tag
 
 
 class GeMV(vOp):
@@ -71,4 +72,39 @@ class GeMV(vOp):
         eff_bs = ctx.batch_size * ctx.num_kv_heads
         self.impl(x, y, self.output_buffer, ctx.dense_kv_indptr, ctx.dense_kv_indices, eff_bs, ctx.topk_val,
                   ctx.page_reserved_bos, ctx.page_reserved_eos)
+        return self.output_buffer
+
+
+class GeMM(vOp, ChainedOp):
+    """``GeMM()(x, y, ctx=ctx)`` computes ``O[s] = Y[s] X^T`` per page (reference: ``indexer/matmul.py:194-399``
+    over ``mm_bpr``): ``x`` BATCHED ``[S, G, D]``, ``y`` PAGED ``[num_pages*H, C, D]`` -> RAGGED
+    ``[max_num_pages, C, G]`` (fp32 products and sum, rounded once to the input dtype).
+
+    On sm_100a it exists as the head of the fused chain ``GeMM -> Softmax -> Max -> topK`` (``C == 1``).
+    """
+
+    def __init__(self):
+        super().__init__()
+        self.output_buffer: Optional[torch.Tensor] = None
+        self.output_format: Optional[FORMAT] = None
+        self._pending = None
+
+    def profile(self, x: vTensor, y: vTensor, ctx: Context) -> vTensor:
+        p = self._prefix()
+        assert isinstance(x, vTensor) and isinstance(y, vTensor), f"{p}profile expects vTensor inputs"
+        assert x.dim() == 3 and y.dim() == 3, f"{p}expected 3D inputs; got x.ndim={x.dim()}, y.ndim={y.dim()}"
+        assert x.shape[2] == y.shape[2], f"{p}last dimension mismatch: {x.shape[2]} vs {y.shape[2]}"
+        key = (x._format, y._format)
+        assert key == (FORMAT.BATCHED, FORMAT.PAGED), f"{p}no implementation for (x_fmt, y_fmt) = {key}"
+        self.output_format = FORMAT.RAGGED
+        self.output_buffer = torch.empty((ctx.max_num_pages, y.shape[1], x.shape[1]), device=x.device, dtype=x.dtype)
+        ctx.add_aux_memory(self.output_buffer)
+        ctx.add_aux_flops(x.shape[1] * y.shape[1] * y.shape[2])
+        out = as_vtensor(self.output_buffer, self.output_format)
+        tag(out, [("gemm", self)], self)
+        return out
+
+    def execute(self, x: torch.Tensor, y: torch.Tensor, ctx: Context) -> torch.Tensor:
+        self._require_fused("GeMM")
+        self._pending = (materialize(x), y)
         return self.output_buffer

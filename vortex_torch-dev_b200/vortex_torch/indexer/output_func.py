@@ -12,6 +12,7 @@ import torch
 
 from .. import _cabi, _deferred
 from ..abs import FORMAT, vOp, vTensor
+from ._chain import chain_of
 from .context import Context
 
 
@@ -22,6 +23,7 @@ class topK(vOp):
         super().__init__()
         self.impl = None
         self._fused_producer = None
+        self._gqa_chain = None
 
     def profile(self, x: vTensor, o: vTensor, ctx: Context) -> None:
         p = self._prefix()
@@ -36,6 +38,15 @@ class topK(vOp):
         assert x.device == o.device, (
             f"{p}x and o must be on the same device (x.device={x.device}, o.device={o.device})")
         self.impl = _cabi.topk
+        # GeMM -> Softmax(dim=0) -> Max(dim=2) -> topK: one fused kernel owned by this operator
+        names = [n for n, _ in chain_of(x)]
+        if names == ["gemm", "softmax", "max"]:
+            gemm, softmax, mx = (op for _, op in chain_of(x))
+            if gemm.output_buffer.shape[1] == 1 and mx.dim == 2:
+                self._gqa_chain = (gemm, softmax, mx)
+                for op in self._gqa_chain:
+                    op._fused_into = self
+                return
         # Fuse with the producing GeMV when its scores are read by this operator only.
         producer = getattr(x, "_vtx_producer", None)
         if producer is not None and getattr(producer, "_fused_consumer", None) is None:
@@ -45,6 +56,17 @@ class topK(vOp):
     def execute(self, x: torch.Tensor, o: torch.Tensor, ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}execute called before profile() (impl is None)"
         eff_bs = ctx.batch_size * ctx.num_kv_heads
+        if self._gqa_chain is not None:
+            gemm, softmax, mx = self._gqa_chain
+            for op in self._gqa_chain:
+                op._require_fused(type(op).__name__)
+            q, y = gemm._pending
+            gemm._pending = None
+            _deferred.flush_all()
+            _cabi.indexer_gqa_softmax_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
+                                            o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
+                                            ctx.max_num_pages_per_request, softmax.scale)
+            return o
         prod = self._fused_producer
         if prod is not None and prod._pending is not None and x.data_ptr() == prod.output_buffer.data_ptr():
             q, y = prod._pending
