@@ -101,6 +101,14 @@ int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num
               int rows, int cols, int page_size, int dtype, void* stream);
 
 /*
+ * Page-completion reduction over the token axis with a choice of operator: op 0 mean (= vtx_cmean),
+ * 1 maximum, 2 minimum - the cache-side `Mean/Max/Min(dim=1)` ops.  Replaces `reduce_pp` with
+ * REDUCE_TYPE 0/1/2, DIM=1 (cache/triton_kernels/reduce_impl.py:7-89).  Arguments as vtx_cmean.
+ */
+int vtx_creduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads,
+                int rows, int cols, int page_size, int op, int dtype, void* stream);
+
+/*
  * KV write fused with the page-completion mean of K: same results as vtx_set_kv followed by
  * vtx_cmean(k_cache -> centroids) on the same loc, in one launch (the new row is averaged from
  * registers).  Replaces the pair set_kv_buffer_launcher (cache/triton_kernels/set_kv.py:39-62) +
@@ -163,6 +171,21 @@ int vtx_indexer_gqa_softmax_fused(const void* q, const void* centroids, const in
                                   int head_dim, int topk_val, int page_reserved_bos,
                                   int page_reserved_eos, int max_num_pages_per_request,
                                   float softmax_scale, int dtype, void* stream);
+
+/*
+ * Fused indexer of the gqa_quest_sparse_attention flow (flow/algorithms.py:356-496): per query head
+ * sum over the head dim of max(q*page_max, q*page_min) with bf16 products (Multiply x2 and Maximum,
+ * indexer/triton_kernels/elementwise_binary_impl.py:167-307; Sum(dim=2) and Max(dim=1),
+ * reduce_impl.py:8-120), then the top-k selection, one CTA per segment.
+ * cache_max, cache_min [num_pages*H, 1, D]; other arguments as vtx_indexer_fused.  bf16 only.
+ */
+int vtx_indexer_quest_fused(const void* q, const void* cache_max, const void* cache_min,
+                            const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                            const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                            int32_t* sparse_page_table, int64_t page_table_stride, int eff_batch_size,
+                            int group_size, int head_dim, int topk_val, int page_reserved_bos,
+                            int page_reserved_eos, int max_num_pages_per_request, int dtype,
+                            void* stream);
 
 /*
  * One launch for a sparse layer: [vtx_set_kv_cmean,] vtx_indexer_fused and vtx_decode_gqa on the sparse

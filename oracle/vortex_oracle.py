@@ -536,3 +536,78 @@ def forward_indexer_gqa(q, centroids, plan, topk_val, bos, eos, scale: float = 0
     topk_select(scores, plan["dense_kv_indptr"], plan["sparse_kv_indptr"], plan["dense_kv_indices"],
                 plan["sparse_kv_indices"], eff_bs, topk_val, bos, eos)
     return scores
+
+
+# --------------------------------------------------------------------------- #
+# gqa_quest_sparse_attention flow: min/max envelopes and their indexer
+# --------------------------------------------------------------------------- #
+def cminmax(x: torch.Tensor, out: torch.Tensor, loc: torch.Tensor, page_size: int, num_kv_heads: int,
+            op: str) -> None:
+    """Page-completion ``Max(dim=1)`` / ``Min(dim=1)`` cache ops (cache/triton_kernels/reduce_impl.py:21-47,
+    REDUCE_TYPE 1 / 2): same trigger and addressing as `cmean`; the reduction is exact in any order."""
+    for t in loc.tolist():
+        if (t + 1) % page_size != 0:
+            continue
+        for h in range(num_kv_heads):
+            pid = (t // page_size) * num_kv_heads + h
+            blk = x[pid].to(torch.float32)
+            red = blk.max(dim=0).values if op == "max" else blk.min(dim=0).values
+            out[pid, 0] = red.to(out.dtype)
+
+
+def canonical_rowsum(vals: torch.Tensor) -> torch.Tensor:
+    """Sum of every row of ``vals`` [R, D] (fp32) in the order of `canonical_dot` (chunks of 8, L partial
+    sums taking chunks l, l+L, ..., folded in halves)."""
+    R, D = vals.shape
+    L = canonical_lanes(D)
+    nch = D // 8
+    v = vals.view(R, nch, 8)
+    lane = torch.zeros(R, L, dtype=torch.float32)
+    for c0 in range(0, nch, L):
+        n = min(L, nch - c0)
+        for j in range(8):
+            lane[:, :n] = lane[:, :n] + v[:, c0:c0 + n, j]
+    w = L // 2
+    while w >= 1:
+        lane = lane[:, :w] + lane[:, w:2 * w]
+        w //= 2
+    return lane[:, 0]
+
+
+def quest_scores(q, cache_max, cache_min, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Aggregated page scores of the ``gqa_quest_sparse_attention`` flow (flow/algorithms.py:356-496):
+    ``Multiply(q, max)`` and ``Multiply(q, min)`` (bf16 products, elementwise_binary_impl.py:167-260),
+    ``Maximum`` of the two, ``Sum(dim=2)`` over the head dim (fp32 sum, bf16 result, reduce_impl.py:58-75),
+    ``Max(dim=1)`` over the query heads.  The fp32 sum uses the canonical order of `canonical_rowsum`."""
+    assert q.dtype == torch.bfloat16
+    total = int(dense_indptr[eff_bs])
+    if out is None:
+        out = torch.zeros(total, dtype=torch.bfloat16)
+    G = q.shape[1]
+    mx = cache_max.view(cache_max.shape[0], -1)
+    mn = cache_min.view(cache_min.shape[0], -1)
+    for s in range(eff_bs):
+        a = int(dense_indptr[s]) + bos
+        b = int(dense_indptr[s + 1]) - eos
+        if b - a <= topk_val:
+            continue
+        rows = torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)
+        hi, lo = mx[rows].to(torch.float32), mn[rows].to(torch.float32)
+        per_head = []
+        for g in range(G):
+            qg = q[s, g].to(torch.float32).unsqueeze(0)
+            u = torch.maximum(bf16_rne(hi * qg), bf16_rne(lo * qg))
+            per_head.append(bf16_rne(canonical_rowsum(u)))
+        out.view(-1)[a:b] = torch.stack(per_head).max(dim=0).values.to(torch.bfloat16)
+    return out
+
+
+def forward_indexer_quest(q, cache_max, cache_min, plan, topk_val, bos, eos):
+    """Indexer of the gqa_quest_sparse_attention flow; completes ``plan['sparse_kv_indices']`` in place."""
+    eff_bs = q.shape[0]
+    scores = quest_scores(q, cache_max, cache_min, plan["dense_kv_indptr"], plan["dense_kv_indices"], eff_bs,
+                          topk_val, bos, eos)
+    topk_select(scores, plan["dense_kv_indptr"], plan["sparse_kv_indptr"], plan["dense_kv_indices"],
+                plan["sparse_kv_indices"], eff_bs, topk_val, bos, eos)
+    return scores

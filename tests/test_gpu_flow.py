@@ -241,3 +241,42 @@ def test_gqa_block_sparse_flow_through_runtime():
                          plan["kv_last_page_len"])
     got = outs[1].view(bs * H, G, D).float().cpu()
     assert bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
+
+
+def test_gqa_quest_flow_through_runtime():
+    """The shipped gqa_quest_sparse_attention flow (CMax/CMin caches; Multiply x2 -> Maximum -> Sum -> Max ->
+    topK) run by the runtime: envelopes of the page the step closes exact, selections bit-exact with the oracle."""
+    from vortex_torch.flow import build_vflow
+
+    seq, L, H, G, D, P, K, bos, eos = [2048, 1000, 4096, 300], 2, 8, 2, 128, 16, 30, 1, 1
+    prob = vo.make_paged_problem(38, seq, H, G, D, P)
+    kf = prob["k"].float()
+    cmax, cmin = kf.max(1, keepdim=True).values.bfloat16(), kf.min(1, keepdim=True).values.bfloat16()
+    flow = build_vflow("gqa_quest_sparse_attention")
+    rt = _runtime(prob, seq, L, H, G, D, P, K, bos, eos, torch.bfloat16, flow=flow)
+    assert flow.output_func._quest_chain is not None
+    bs = len(seq)
+    loc = torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)], dtype=torch.int64)
+    closing_rows = torch.cat([(loc[r] // P) * H + torch.arange(H) for r in range(bs) if seq[r] % P == 0])
+    for l in range(L):
+        rt.pool.buffers[l]["k"].copy_(prob["k"]); rt.pool.buffers[l]["v"].copy_(prob["v"])
+        c0, c1 = cmax.clone(), cmin.clone()
+        c0[closing_rows] = 0; c1[closing_rows] = 0      # must be produced by forward_cache during the step
+        rt.pool.buffers[l]["max"].copy_(c0); rt.pool.buffers[l]["min"].copy_(c1)
+    nk = torch.stack([prob["k"][(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)]).cuda()
+    nv = torch.stack([prob["v"][(loc[r] // P) * H + torch.arange(H), loc[r] % P] for r in range(bs)]).cuda()
+    q = prob["q"].view(bs, H * G, D).cuda()
+    outs = [torch.empty_like(q) for _ in range(L)]
+    rt.step(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(), [q] * L, [nk] * L,
+            [nv] * L, loc.cuda(), outs)
+    torch.cuda.synchronize()
+    assert torch.equal(rt.pool.buffers[1]["max"].cpu()[closing_rows], cmax[closing_rows])
+    assert torch.equal(rt.pool.buffers[1]["min"].cpu()[closing_rows], cmin[closing_rows])
+    plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)
+    vo.forward_indexer_quest(prob["q"], cmax, cmin, plan, K, bos, eos)
+    ns = int(plan["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], plan["sparse_kv_indices"])
+    want = vo.decode_gqa(prob["q"], prob["k"], prob["v"], plan["sparse_kv_indptr"], plan["sparse_kv_indices"],
+                         plan["kv_last_page_len"])
+    got = outs[1].view(bs * H, G, D).float().cpu()
+    assert bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())

@@ -180,6 +180,42 @@ def test_indexer_gqa_softmax_fused_matches_oracle(seq, H, G, D, P, K):
     np.testing.assert_array_equal(sel.cpu().numpy()[:ns], ref["sparse_kv_indices"])
 
 
+def _envelopes(prob):
+    k = prob["k"].float()
+    return k.max(dim=1, keepdim=True).values.bfloat16(), k.min(dim=1, keepdim=True).values.bfloat16()
+
+
+@pytest.mark.parametrize("seq,H,G,D,P,K", [([2048, 1000, 600], 8, 2, 128, 16, 30), ([1024, 5000, 333, 17], 4, 4, 128, 16, 64),
+                                           ([700, 130], 2, 8, 64, 8, 5)])
+def test_indexer_quest_fused_matches_oracle(seq, H, G, D, P, K):
+    """gqa_quest_sparse_attention indexer (Multiply x2 -> Maximum -> Sum -> Max -> topK): selection bit-exact."""
+    bos, eos = 1, 1
+    prob = vo.make_paged_problem(14, seq, H, G, D, P)
+    cmax, cmin = _envelopes(prob)
+    dp = DevicePlan(prob, P, H, K, bos, eos)
+    ref = dp.oracle(prob)
+    vo.forward_indexer_quest(prob["q"], cmax, cmin, ref, K, bos, eos)
+    sel = dp.sparse_indices.clone()
+    _cabi.indexer_quest_fused(prob["q"].cuda(), cmax.cuda(), cmin.cuda(), dp.dense_indptr, dp.sparse_indptr,
+                              dp.dense_indices, sel, dp.S, K, bos, eos, dp.max_pages)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(sel.cpu().numpy()[:ns], ref["sparse_kv_indices"])
+
+
+@pytest.mark.parametrize("op", ["max", "min"])
+@pytest.mark.parametrize("dtype,P,H,D", [(torch.bfloat16, 16, 8, 128), (torch.float32, 12, 3, 64)])
+def test_cminmax_exact(op, dtype, P, H, D):
+    pages = 40
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(pages * H, P, D, generator=g).to(dtype)
+    out = torch.zeros(pages * H, 1, D, dtype=dtype)
+    loc = torch.cat([torch.randperm(pages, generator=g)[:15] * P + (P - 1), torch.randperm(pages, generator=g)[:7] * P])
+    od = out.cuda()
+    _cabi.creduce(x.cuda(), od, loc.cuda(), H, P, 1 if op == "max" else 2)
+    vo.cminmax(x, out, loc, P, H, op)
+    assert torch.equal(od.cpu(), out)
+
+
 def test_topk_heavy_ties():
     """Scores drawn from four values: selection must follow candidate order inside each tie class."""
     H, K, bos, eos, P = 2, 30, 1, 1, 16

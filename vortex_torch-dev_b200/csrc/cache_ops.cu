@@ -32,12 +32,12 @@ __global__ void __launch_bounds__(256) set_kv_kernel(uint4* __restrict__ k_cache
 }
 
 // A group of LANES threads owns one (new token, head) item; each lane owns chunks of eight
-// columns and adds the page's rows in ascending order into fp32 accumulators that start at
-// +0.0, divides once by the row count and rounds once to T.
-template <typename T, int LANES>
-__global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* __restrict__ out,
-                                                   const int64_t* __restrict__ loc, int64_t nnz, int H,
-                                                   int rows, int cols, int P) {
+// columns and reduces the page's rows in ascending order.  OP 0: mean (fp32 accumulators that start at
+// +0.0, one division by the row count, one rounding to T); OP 1 / 2: maximum / minimum (exact).
+template <typename T, int LANES, int OP>
+__global__ void __launch_bounds__(256) creduce_kernel(const T* __restrict__ x, T* __restrict__ out,
+                                                     const int64_t* __restrict__ loc, int64_t nnz, int H,
+                                                     int rows, int cols, int P) {
     constexpr int GROUPS = 256 / LANES;
     vtx::pdl_wait();
     vtx::pdl_trigger();
@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* 
         for (int c = lane; c < nchunk; c += LANES) {
             float acc[8];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            for (int j = 0; j < 8; ++j) acc[j] = OP == 0 ? 0.f : (OP == 1 ? -INFINITY : INFINITY);
             for (int r = 0; r < rows; r += 8) {
                 vtx::Vec8<T> v[8];
 #pragma unroll
@@ -69,12 +69,15 @@ __global__ void __launch_bounds__(256) cmean_kernel(const T* __restrict__ x, T* 
                         float f[8];
                         v[u].unpack(f);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                        for (int j = 0; j < 8; ++j)
+                            acc[j] = OP == 0 ? __fadd_rn(acc[j], f[j]) : (OP == 1 ? fmaxf(acc[j], f[j]) : fminf(acc[j], f[j]));
                     }
                 }
             }
+            if (OP == 0) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], denom);
+                for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], denom);
+            }
             vtx::store8(out + pid * (int64_t)cols + c * 8, acc);
         }
     }
@@ -159,20 +162,29 @@ int launch_set_kv_cmean(void* k, void* v, const void* nk, const void* nv, void* 
     return vtx::finish_launch();
 }
 
-template <typename T>
-int launch_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int H, int rows, int cols, int P,
-                 cudaStream_t st) {
+template <typename T, int OP>
+int launch_creduce_op(const void* x, void* out, const int64_t* loc, int64_t nnz, int H, int rows, int cols, int P,
+                      cudaStream_t st) {
     const int64_t items = nnz * H;
     if (cols <= 128) {
         const int64_t blocks = (items + 15) / 16;
-        return vtx::launch(cmean_kernel<T, 16>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
-                           (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
-    } else {
-        const int64_t blocks = (items + 7) / 8;
-        return vtx::launch(cmean_kernel<T, 32>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
-                           (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+        return vtx::launch(creduce_kernel<T, 16, OP>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0,
+                           st, (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
     }
-    return vtx::finish_launch();
+    const int64_t blocks = (items + 7) / 8;
+    return vtx::launch(creduce_kernel<T, 32, OP>, dim3((unsigned)std::min<int64_t>(blocks, 1 << 20)), dim3(256), 0, st,
+                       (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+}
+
+template <typename T>
+int launch_creduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int H, int rows, int cols, int P,
+                   int op, cudaStream_t st) {
+    switch (op) {
+        case 0: return launch_creduce_op<T, 0>(x, out, loc, nnz, H, rows, cols, P, st);
+        case 1: return launch_creduce_op<T, 1>(x, out, loc, nnz, H, rows, cols, P, st);
+        case 2: return launch_creduce_op<T, 2>(x, out, loc, nnz, H, rows, cols, P, st);
+        default: return VTX_ERR_INVALID_ARGUMENT;
+    }
 }
 
 }  // namespace
@@ -194,17 +206,23 @@ extern "C" int vtx_set_kv(void* k_cache, void* v_cache, const void* new_k, const
                        vec_per_row, page_size);
 }
 
-extern "C" int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads, int rows,
-                         int cols, int page_size, int dtype, void* stream) {
+extern "C" int vtx_creduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads, int rows,
+                           int cols, int page_size, int op, int dtype, void* stream) {
     if (!x || !out || !loc) return VTX_ERR_INVALID_ARGUMENT;
     if (nnz < 0 || num_kv_heads < 1 || rows < 1 || cols < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (op < 0 || op > 2) return VTX_ERR_INVALID_ARGUMENT;
     if (cols % 8 != 0) return VTX_ERR_UNSUPPORTED;
     if (nnz == 0) return VTX_OK;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == VTX_BF16)
-        return launch_cmean<__nv_bfloat16>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
-    if (dtype == VTX_F32) return launch_cmean<float>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, st);
+        return launch_creduce<__nv_bfloat16>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, op, st);
+    if (dtype == VTX_F32) return launch_creduce<float>(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, op, st);
     return VTX_ERR_INVALID_ARGUMENT;
+}
+
+extern "C" int vtx_cmean(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads, int rows,
+                         int cols, int page_size, int dtype, void* stream) {
+    return vtx_creduce(x, out, loc, nnz, num_kv_heads, rows, cols, page_size, 0, dtype, stream);
 }
 
 extern "C" int vtx_set_kv_cmean(void* k_cache, void* v_cache, const void* new_k, const void* new_v,

@@ -195,6 +195,7 @@ __device__ __forceinline__ void store_score<float>(float* p, float v) { *p = v; 
 struct IndexerArgs {
     const void* q;          // [eff_bs, G, D]
     const void* centroids;  // [rows, D]
+    const void* centroids2; // MODE 3: second summary cache (per-page minimum); centroids is the maximum
     void* scores;           // packed, GEMV mode only
     const int32_t* dense_indptr;
     const int32_t* sparse_indptr;
@@ -258,6 +259,24 @@ __device__ __forceinline__ void add_products_f32(float& acc, const __nv_bfloat16
     acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.z), q1.y));
     acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.w), q1.z));
     acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.w), q1.w));
+}
+
+// Quest upper bound for one chunk: max(round_bf16(q*hi), round_bf16(q*lo)) per dim, added one by one.
+__device__ __forceinline__ void add_quest_bounds(float& acc, const __nv_bfloat16* hi_chunk, const __nv_bfloat16* lo_chunk,
+                                                 const __nv_bfloat16* q_chunk) {
+    const uint4 h = *reinterpret_cast<const uint4*>(hi_chunk);
+    const uint4 l = *reinterpret_cast<const uint4*>(lo_chunk);
+    const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
+    const uint32_t hh[4] = {h.x, h.y, h.z, h.w}, ll[4] = {l.x, l.y, l.z, l.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 qv = *reinterpret_cast<const __nv_bfloat162*>(&qq[i]);
+        const __nv_bfloat162 u = __hmax2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&hh[i]), qv),
+                                         __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ll[i]), qv));
+        const uint32_t uw = *reinterpret_cast<const uint32_t*>(&u);
+        acc = __fadd_rn(acc, vtx::bf16lo(uw));
+        acc = __fadd_rn(acc, vtx::bf16hi(uw));
+    }
 }
 
 // exp(x) for x <= 0 as a fixed sequence of fp32 operations, identical on CPU and GPU:
@@ -366,14 +385,20 @@ struct NoSideWork {
 template <typename T, int D, int MODE, typename SideWork = NoSideWork, int GQ = 1>
 __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s,
                                              SideWork side_work = SideWork()) {
-    constexpr int NQ = MODE == 2 ? GQ : 1;                          // score accumulators per row
-    constexpr int QBYTES = MODE == 2 ? GQ * D * 4 : D * (int)sizeof(T);  // staged query: fp32 heads / mean in T
+    // MODE 3 (bf16 only): the gqa_quest_sparse_attention scores from two summary caches (per-page max and min):
+    // per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
+    constexpr int NQ = MODE >= 2 ? GQ : 1;                          // score accumulators per row
+    constexpr int NSRC = MODE == 3 ? 2 : 1;                         // summary rows gathered per page
+    constexpr int QBYTES = MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : D * (int)sizeof(T));
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
-    constexpr int L = Gm::L, HALF = L / 2, SLOTS = Gm::slots;
+    constexpr int L = Gm::L, HALF = L / 2;
+    constexpr int SLOT_B = NSRC * Gm::slot_bytes;
+    constexpr int SLOTS = SLOT_B * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
     // layout: [ring][q_mean][keys][ids]
     unsigned char* ring = smem_raw;
-    T* qbar = reinterpret_cast<T*>(smem_raw + Gm::ring_bytes);
+    T* qbar = reinterpret_cast<T*>(smem_raw + RING_B);
     Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + QBYTES);
     int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
     __nv_bfloat16* sbuf = reinterpret_cast<__nv_bfloat16*>(ids + a.key_cap);  // MODE 2: [candidate][head] scores
@@ -394,24 +419,26 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
-    unsigned char* my_ring = ring + (size_t)warp * SLOTS * Gm::slot_bytes;
+    unsigned char* my_ring = ring + (size_t)warp * SLOTS * SLOT_B;
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
     const unsigned char* cent = reinterpret_cast<const unsigned char*>(a.centroids);
+    const unsigned char* cent2 = reinterpret_cast<const unsigned char*>(a.centroids2);
     const int n_batches = (c + kRowsPerSlot - 1) / kRowsPerSlot;
     const int my_batches = n_batches > warp ? (n_batches - warp + kWarps - 1) / kWarps : 0;
     constexpr int pieces_per_slot = kRowsPerSlot * Gm::pieces;
 
     auto issue = [&](int ord) {
         const int row0 = (warp + ord * kWarps) * kRowsPerSlot;
-        const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * Gm::slot_bytes);
+        const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * SLOT_B);
 #pragma unroll
         for (int pc = lane; pc < pieces_per_slot; pc += 32) {
             const int r = pc / Gm::pieces, pr = pc - r * Gm::pieces;
             const int i = row0 + r;
             const bool valid = i < c;
             const int64_t row = valid ? row_ids[i] : 0;
-            cp_async16(dst + r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4), cent + row * Gm::row_bytes + pr * 16,
-                       valid);
+            const uint32_t off = r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4);
+            cp_async16(dst + off, cent + row * Gm::row_bytes + pr * 16, valid);
+            if (NSRC == 2) cp_async16(dst + Gm::slot_bytes + off, cent2 + row * Gm::row_bytes + pr * 16, valid);
         }
     };
 
@@ -421,6 +448,10 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         cp_async_commit();
     }
     side_work(warp, lane);
+    if (MODE == 3) {  // the group's query heads as they are
+        const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
+        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
+    }
     if (MODE == 2) {  // the group's query heads, widened to fp32
         const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
         for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
@@ -433,7 +464,7 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         }
     }
     // grouped-query mean, one canonical chunk per thread
-    for (int ch = threadIdx.x; MODE != 2 && ch < Gm::nchunk; ch += kThreads) {
+    for (int ch = threadIdx.x; MODE < 2 && ch < Gm::nchunk; ch += kThreads) {
         const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
         float acc[8];
 #pragma unroll
@@ -457,9 +488,10 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
         __syncwarp();
         if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
         cp_async_commit();
-        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * Gm::slot_bytes + r_in * Gm::row_bytes;
+        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
         const int sw = (r_in & 3) << 1;
         const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;
+        float best = -INFINITY;  // MODE 3: running maximum over the heads
 #pragma unroll
         for (int g = 0; g < NQ; ++g) {
             float acc[HALF];
@@ -474,7 +506,12 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
                         const int ch = k * L + 2 * ii + par;
                         // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
                         const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
-                        if constexpr (MODE == 2)
+                        if constexpr (MODE == 3)
+                            add_quest_bounds(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             reinterpret_cast<const __nv_bfloat16*>(
+                                                 reinterpret_cast<const unsigned char*>(src) + Gm::slot_bytes),
+                                             reinterpret_cast<const __nv_bfloat16*>(qbar) + g * D + ch * 8);
+                        else if constexpr (MODE == 2)
                             add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
                                              qf32 + g * D + ch * 8);
                         else
@@ -491,9 +528,11 @@ __device__ __forceinline__ void indexer_body(const IndexerArgs& a, unsigned char
                 const float sc = vtx::round_to<T>(total);
                 if (MODE == 0) keys[i] = KeyOf<T>::make(sc, i);
                 else if (MODE == 2) sbuf[i * NQ + g] = __float2bfloat16_rn(sc);
+                else if (MODE == 3) best = fmaxf(best, sc);
                 else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + i, sc);
             }
         }
+        if (MODE == 3 && par == 0 && i < c) keys[i] = KeyOf<T>::make(best, i);
     }
     cp_async_wait<0>();
     if constexpr (MODE == 2) {
@@ -573,6 +612,15 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_gqa_kernel(IndexerArgs a)
     vtx::pdl_wait();
     vtx::pdl_trigger();
     indexer_body<__nv_bfloat16, D, 2, NoSideWork, GQ>(a, smem_raw, blockIdx.x);
+}
+
+// gqa_quest_sparse_attention indexer: envelope bound per head -> Max over heads -> top-k, one launch.
+template <int D, int GQ>
+__global__ void __launch_bounds__(kThreads, 2) indexer_quest_kernel(IndexerArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    indexer_body<__nv_bfloat16, D, 3, NoSideWork, GQ>(a, smem_raw, blockIdx.x);
 }
 
 // One launch per sparse layer: page selection, then attention over the selected pages, by the same CTA.
@@ -691,6 +739,29 @@ int launch_indexer_gqa(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     VTX_GQA_CASE(64, 1) VTX_GQA_CASE(64, 2) VTX_GQA_CASE(64, 4) VTX_GQA_CASE(64, 8)
     VTX_GQA_CASE(128, 1) VTX_GQA_CASE(128, 2) VTX_GQA_CASE(128, 4) VTX_GQA_CASE(128, 8)
 #undef VTX_GQA_CASE
+    return VTX_ERR_UNSUPPORTED;
+}
+
+template <int D, int GQ>
+int launch_indexer_quest_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
+    using Gm = Geom<__nv_bfloat16, D>;
+    constexpr int slot_b = 2 * Gm::slot_bytes;
+    constexpr int slots = slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    const size_t bytes = (size_t)kWarps * slots * slot_b + (size_t)GQ * D * 2 +
+                         (size_t)a.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    auto kern = indexer_quest_kernel<D, GQ>;
+    int rc = set_smem(kern, bytes);
+    if (rc != VTX_OK) return rc;
+    return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, a);
+}
+
+int launch_indexer_quest(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
+#define VTX_QUEST_CASE(D_, G_) \
+    if (a.D == D_ && a.G == G_) return launch_indexer_quest_cfg<D_, G_>(a, eff_bs, st);
+    VTX_QUEST_CASE(64, 1) VTX_QUEST_CASE(64, 2) VTX_QUEST_CASE(64, 4) VTX_QUEST_CASE(64, 8)
+    VTX_QUEST_CASE(128, 1) VTX_QUEST_CASE(128, 2) VTX_QUEST_CASE(128, 4) VTX_QUEST_CASE(128, 8)
+#undef VTX_QUEST_CASE
     return VTX_ERR_UNSUPPORTED;
 }
 
@@ -912,4 +983,37 @@ extern "C" int vtx_indexer_gqa_softmax_fused(const void* q, const void* centroid
     a.key_cap = key_capacity(max_num_pages_per_request);
     a.scale = softmax_scale;
     return launch_indexer_gqa(a, eff_batch_size, (cudaStream_t)stream);
+}
+
+extern "C" int vtx_indexer_quest_fused(const void* q, const void* cache_max, const void* cache_min,
+                                       const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                       const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                                       int32_t* sparse_page_table, int64_t page_table_stride, int eff_batch_size,
+                                       int group_size, int head_dim, int topk_val, int page_reserved_bos,
+                                       int page_reserved_eos, int max_num_pages_per_request, int dtype,
+                                       void* stream) {
+    int rc = check_common(dense_kv_indptr, dense_kv_indices, eff_batch_size, topk_val, page_reserved_bos,
+                          page_reserved_eos, max_num_pages_per_request, dtype);
+    if (rc != VTX_OK) return rc;
+    if (!q || !cache_max || !cache_min || !sparse_kv_indptr || !sparse_kv_indices) return VTX_ERR_INVALID_ARGUMENT;
+    if (group_size < 1 || (sparse_page_table && page_table_stride < 1)) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    if (eff_batch_size == 0) return VTX_OK;
+    IndexerArgs a{};
+    a.q = q;
+    a.centroids = cache_max;
+    a.centroids2 = cache_min;
+    a.dense_indptr = dense_kv_indptr;
+    a.sparse_indptr = sparse_kv_indptr;
+    a.dense_indices = dense_kv_indices;
+    a.sparse_indices = sparse_kv_indices;
+    a.sparse_pt = sparse_page_table;
+    a.pt_stride = page_table_stride;
+    a.G = group_size;
+    a.D = head_dim;
+    a.K = topk_val;
+    a.bos = page_reserved_bos;
+    a.eos = page_reserved_eos;
+    a.key_cap = key_capacity(max_num_pages_per_request);
+    return launch_indexer_quest(a, eff_batch_size, (cudaStream_t)stream);
 }

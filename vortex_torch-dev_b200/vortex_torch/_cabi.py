@@ -32,6 +32,8 @@ SIGNATURES = {
     "vtx_plan_decode": [_p, _p, _i64, _p] + [_p] * 10 + [_p] * 4 + [_i64] + [_i] * 8 + [_p],
     "vtx_set_kv": [_p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _p],
     "vtx_cmean": [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _p],
+    "vtx_creduce": [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_indexer_quest_fused": [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_set_kv_cmean": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _p],
     "vtx_gemv": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
     "vtx_topk": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p],
@@ -277,3 +279,28 @@ def indexer_gqa_softmax_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, d
                                            int(eos), int(max_pages_per_request), float(softmax_scale),
                                            dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_indexer_gqa_softmax_fused")
+
+
+def creduce(x, out, loc, num_kv_heads, page_size, op: int) -> None:
+    """Page-completion reduction over rows: op 0 mean, 1 max, 2 min."""
+    want(loc, torch.int64, "loc")
+    if out.dtype != x.dtype:
+        raise TypeError("creduce: x and out must share a dtype")
+    rc = lib.vtx_creduce(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
+                         int(page_size), int(op), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_creduce")
+
+
+def indexer_quest_fused(q, cache_max, cache_min, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
+                        sparse_kv_indices, eff_bs, topk_val, bos, eos, max_pages_per_request,
+                        sparse_page_table=None) -> None:
+    """Multiply x2 -> Maximum -> Sum(dim=2) -> Max(dim=1) -> topK of the gqa_quest_sparse_attention flow."""
+    if not (q.dtype == cache_max.dtype == cache_min.dtype):
+        raise TypeError("indexer_quest_fused: q and the two caches must share a dtype")
+    stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    rc = lib.vtx_indexer_quest_fused(ptr(q), ptr(cache_max), ptr(cache_min), ptr(dense_kv_indptr),
+                                     ptr(sparse_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indices),
+                                     ptr(sparse_page_table), stride, int(eff_bs), q.shape[1], q.shape[2],
+                                     int(topk_val), int(bos), int(eos), int(max_pages_per_request),
+                                     dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_indexer_quest_fused")

@@ -38,10 +38,10 @@ class Reduce(vOp):
         assert isinstance(output, vTensor), f"{p}output must be vTensor, got {type(output)}"
         assert output.dim() == 3, f"{p}output must be 3D, got ndim={output.dim()} shape={tuple(output.shape)}"
         if (x._format, output._format) != (FORMAT.PAGED, FORMAT.PAGED) or self.dim != 1 \
-                or self.reduce_type != ReduceType.Mean:
+                or self.reduce_type not in (ReduceType.Mean, ReduceType.Max, ReduceType.Min):
             raise NotImplementedError(
-                f"{p}only Mean(dim=1) PAGED->PAGED has an sm_100a kernel; got {self.reduce_type}, dim={self.dim}, "
-                f"({x._format}, {output._format})")
+                f"{p}only Mean/Max/Min(dim=1) PAGED->PAGED have sm_100a kernels; got {self.reduce_type}, "
+                f"dim={self.dim}, ({x._format}, {output._format})")
         assert output.shape[1] == 1, f"{p}profile(dim=1): expected output.shape[1] == 1, got {tuple(output.shape)}"
         assert output.shape[2] == x.shape[2], (
             f"{p}profile(dim=1): expected output.shape[2] == x.shape[2], got {output.shape[2]} vs {x.shape[2]}")
@@ -59,7 +59,8 @@ class Reduce(vOp):
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
             k_cache, v_cache, new_k, new_v, ploc, P = pend
-            if (x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
+            if (self.reduce_type == ReduceType.Mean
+                    and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
                     and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
                     and new_k.shape[1] == ctx.head_num):
                 # the runtime's KV write and this mean touch the same page: one kernel does both
@@ -71,7 +72,10 @@ class Reduce(vOp):
                 _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, output, loc, P)
                 return output
             ctx.flush_kv_write()
-        self.impl(x, output, loc, ctx.head_num, ctx.page_size)
+        if self.reduce_type == ReduceType.Mean:
+            self.impl(x, output, loc, ctx.head_num, ctx.page_size)
+        else:
+            _cabi.creduce(x, output, loc, ctx.head_num, ctx.page_size, 1 if self.reduce_type == ReduceType.Max else 2)
         return output
 
 
@@ -79,3 +83,15 @@ class Mean(Reduce):
     def __init__(self, dim: int = 1):
         super().__init__(dim)
         self.reduce_type = ReduceType.Mean
+
+
+class Max(Reduce):
+    def __init__(self, dim: int = 1):
+        super().__init__(dim)
+        self.reduce_type = ReduceType.Max
+
+
+class Min(Reduce):
+    def __init__(self, dim: int = 1):
+        super().__init__(dim)
+        self.reduce_type = ReduceType.Min

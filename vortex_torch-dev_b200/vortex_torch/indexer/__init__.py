@@ -7,6 +7,7 @@ when used.
 """
 from ._unbuilt import unbuilt as _unbuilt
 from .context import Context, get_ctx
+from .elementwise_binary import Add, Maximum, Minimum, Multiply
 from .matmul import GeMM, GeMV
 from .output_func import topK
 from .reduce import L2Norm, Max, Mean, Min, Sum
@@ -15,7 +16,6 @@ from . import utils_sglang
 
 _W = "indexer"
 Transpose = _unbuilt("Transpose", _W)
-Maximum, Minimum, Multiply, Add = (_unbuilt(n, _W) for n in ("Maximum", "Minimum", "Multiply", "Add"))
 Relu, Sigmoid, Silu, Add_Mul, Abs = (_unbuilt(n, _W) for n in ("Relu", "Sigmoid", "Silu", "Add_Mul", "Abs"))
 Save, Load = _unbuilt("Save", _W), _unbuilt("Load", _W)
 

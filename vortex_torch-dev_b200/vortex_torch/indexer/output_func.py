@@ -24,6 +24,7 @@ class topK(vOp):
         self.impl = None
         self._fused_producer = None
         self._gqa_chain = None
+        self._quest_chain = None
 
     def profile(self, x: vTensor, o: vTensor, ctx: Context) -> None:
         p = self._prefix()
@@ -39,12 +40,24 @@ class topK(vOp):
             f"{p}x and o must be on the same device (x.device={x.device}, o.device={o.device})")
         self.impl = _cabi.topk
         # GeMM -> Softmax(dim=0) -> Max(dim=2) -> topK: one fused kernel owned by this operator
-        names = [n for n, _ in chain_of(x)]
+        names = [l[0] for l in chain_of(x)]
         if names == ["gemm", "softmax", "max"]:
-            gemm, softmax, mx = (op for _, op in chain_of(x))
+            gemm, softmax, mx = (l[1] for l in chain_of(x))
             if gemm.output_buffer.shape[1] == 1 and mx.dim == 2:
                 self._gqa_chain = (gemm, softmax, mx)
                 for op in self._gqa_chain:
+                    op._fused_into = self
+                return
+        # Multiply(q, max) / Multiply(q, min) -> Maximum -> Sum(dim=2) -> Max(dim=1) -> topK: one fused kernel
+        links = chain_of(x)
+        if [l[0] for l in links] == ["maximum", "sum", "max"]:
+            maximum, sum_op, mx = links[0][1], links[1][1], links[2][1]
+            srcs = links[0][2]
+            if (len(srcs) == 2 and all(len(c) == 1 and c[0][0] == "multiply" for c in srcs)
+                    and sum_op.dim == 2 and mx.dim == 1 and all(c[0][1]._y_rows == 1 for c in srcs)):
+                mul_a, mul_b = srcs[0][0][1], srcs[1][0][1]
+                self._quest_chain = (mul_a, mul_b, maximum, sum_op, mx)
+                for op in self._quest_chain:
                     op._fused_into = self
                 return
         # Fuse with the producing GeMV when its scores are read by this operator only.
@@ -56,6 +69,19 @@ class topK(vOp):
     def execute(self, x: torch.Tensor, o: torch.Tensor, ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}execute called before profile() (impl is None)"
         eff_bs = ctx.batch_size * ctx.num_kv_heads
+        if self._quest_chain is not None:
+            for op in self._quest_chain:
+                op._require_fused(type(op).__name__)
+            mul_a, mul_b = self._quest_chain[0], self._quest_chain[1]
+            (qa, ya), (qb, yb) = mul_a._pending, mul_b._pending
+            mul_a._pending = mul_b._pending = None
+            if qa.data_ptr() != qb.data_ptr():
+                raise NotImplementedError("topK: the two Multiply operators of the quest chain must share their query")
+            _deferred.flush_all()
+            _cabi.indexer_quest_fused(qa, ya, yb, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o,
+                                      eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
+                                      ctx.max_num_pages_per_request)
+            return o
         if self._gqa_chain is not None:
             gemm, softmax, mx = self._gqa_chain
             for op in self._gqa_chain:

@@ -2,7 +2,8 @@
 
 ``Max(dim=2)(x, ctx=ctx)`` reduces the last axis of every page block, ``[S_pack, r, c] -> [S_pack, r, 1]``.
 On sm_100a ``Max(dim=2)`` exists as a link of the fused chain ``GeMM -> Softmax -> Max -> topK``; the other
-reductions are placeholders.
+reductions are placeholders, except ``Sum(dim=2)`` and ``Max(dim=1)`` which are links of the quest
+indexer's fused chain.
 """
 from __future__ import annotations
 
@@ -43,4 +44,21 @@ class Max(vOp, ChainedOp):
         return self.output_buffer
 
 
-Mean, Min, L2Norm, Sum = (unbuilt(n, "indexer") for n in ("Mean", "Min", "L2Norm", "Sum"))
+class Sum(Max):
+    """``Sum(dim=2)``: fp32 sum over the last axis, rounded once (a link of the quest indexer's fused chain)."""
+
+    def __init__(self, dim: int = 1):
+        super().__init__(dim)
+        self.reduce_type = ReduceType.Sum
+
+    def profile(self, x: vTensor, ctx: Context) -> vTensor:
+        out = super().profile(x, ctx)
+        out._vtx_chain[-1] = ("sum", self)
+        return out
+
+    def execute(self, x: torch.Tensor, ctx: Context) -> torch.Tensor:
+        self._require_fused("Sum")
+        return self.output_buffer
+
+
+Mean, Min, L2Norm = (unbuilt(n, "indexer") for n in ("Mean", "Min", "L2Norm"))
