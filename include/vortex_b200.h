@@ -271,6 +271,48 @@ int vtx_decode_mla(const void* q, const void* latent_cache, void* out, const int
                    int num_heads, int latent_dim, int value_dim, int page_size, float sm_scale,
                    int dtype, void* stream);
 
+/*
+ * Prefill planner.  Replaces `sglang_plan_prefill` (csrc/register.h, csrc/utils_sglang.cu:462-621).
+ * cached_seq_lens, input_seq_lens [bs] i32; outputs dense_kv_indptr, qo_indptr_paged [bs*H + 1],
+ * qo_indptr_ragged [bs + 1], dense_kv_indices (packed row ids), kv_last_page_len [bs*H],
+ * batch_table [sum of input lengths] u16 (token -> request).  One launch, no batch limit up to 65536.
+ */
+int vtx_plan_prefill(const int32_t* cached_seq_lens, const int32_t* input_seq_lens,
+                     const int32_t* req_to_token, int64_t req_to_token_stride,
+                     const int64_t* req_indices, int32_t* dense_kv_indptr, int32_t* dense_kv_indices,
+                     int32_t* qo_indptr_ragged, int32_t* qo_indptr_paged, int32_t* kv_last_page_len,
+                     uint16_t* batch_table, int batch_size, int page_size, int num_kv_heads,
+                     void* stream);
+
+/*
+ * Prefill planner, block-table form.  Replaces `sglang_plan_prefill_fa3` (csrc/utils_sglang.cu:797-869).
+ * cached_seq_lens [bs*H] (per segment), cu_seqlens_q [bs*H + 1]; outputs page_table [bs*H, stride] and
+ * batch_table u16.
+ */
+int vtx_plan_prefill_fa3(const int32_t* cached_seq_lens, const int32_t* cu_seqlens_q,
+                         const int32_t* req_to_token, int64_t req_to_token_stride,
+                         const int64_t* req_indices, int32_t* page_table, int64_t page_table_stride,
+                         uint16_t* batch_table, int batch_size, int page_size, int num_kv_heads,
+                         void* stream);
+
+/*
+ * Token-major [N, H*G, D] -> per-request head-major [N*H, G, D] shuffle of bf16 rows (q before the
+ * prefill attention).  Replaces `Chunkwise_NH2HN_Transpose` (csrc/utils_sglang.cu:623-695); the caller
+ * owns x_out.  indptr [bs + 1] token offsets per request, batch_table [N] u16.
+ */
+int vtx_chunkwise_nh2hn(const void* x, void* x_out, const int32_t* indptr, const uint16_t* batch_table,
+                        int64_t num_tokens, int num_kv_heads, int group_size, int head_dim,
+                        void* stream);
+
+/*
+ * The inverse shuffle for the attention output x (bf16) and, when y / y_out are non-null, the fp32
+ * log-sum-exp [N*H, G] -> [N, H*G].  Replaces `Chunkwise_HN2NH_Transpose` (csrc/utils_sglang.cu:698-793)
+ * and, with y null, `Chunkwise_HN2NH_Transpose_FA3` (:872-946).
+ */
+int vtx_chunkwise_hn2nh(const void* x, void* x_out, const float* y, float* y_out, const int32_t* indptr,
+                        const uint16_t* batch_table, int64_t num_tokens, int num_kv_heads,
+                        int group_size, int head_dim, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -611,3 +611,91 @@ def forward_indexer_quest(q, cache_max, cache_min, plan, topk_val, bos, eos):
     topk_select(scores, plan["dense_kv_indptr"], plan["sparse_kv_indptr"], plan["dense_kv_indices"],
                 plan["sparse_kv_indices"], eff_bs, topk_val, bos, eos)
     return scores
+
+
+# --------------------------------------------------------------------------- #
+# prefill side: planners and chunk-wise transposes
+# --------------------------------------------------------------------------- #
+def plan_prefill(cached_seq_lens, input_seq_lens, req_to_token, req_indices, page_size: int, num_kv_heads: int):
+    """Prefill planner (csrc/utils_sglang.cu:462-551): indptr of cached pages and of new query tokens in
+    ragged (per request) and paged (per request and head) form, dense page list, last-page lengths and the
+    token -> request table."""
+    cached = np.asarray(cached_seq_lens, dtype=np.int64)
+    inp = np.asarray(input_seq_lens, dtype=np.int64)
+    r2t = np.asarray(req_to_token, dtype=np.int64)
+    ridx = np.asarray(req_indices, dtype=np.int64)
+    bs, H, P = len(cached), num_kv_heads, page_size
+    n = (cached + P - 1) // P
+    cn = np.concatenate([[0], np.cumsum(n)])
+    ci = np.concatenate([[0], np.cumsum(inp)])
+    kv_indptr = np.zeros(bs * H + 1, dtype=np.int32)
+    qo_paged = np.zeros(bs * H + 1, dtype=np.int32)
+    for r in range(bs):
+        for j in range(H + 1):
+            kv_indptr[r * H + j] = H * cn[r] + j * n[r]
+            qo_paged[r * H + j] = H * ci[r] + j * inp[r]
+    kv_indices = np.full(int(kv_indptr[-1]), NEG_FILL, dtype=np.int32)
+    last = np.zeros(bs * H, dtype=np.int32)
+    table = np.zeros(int(ci[-1]), dtype=np.uint16)
+    for r in range(bs):
+        toks = r2t[ridx[r]]
+        ll = int(cached[r] % P)
+        for h in range(H):
+            s = r * H + h
+            last[s] = P if ll == 0 else ll
+            kv_indices[kv_indptr[s]:kv_indptr[s] + n[r]] = (toks[np.arange(n[r]) * P] // P) * H + h
+        table[ci[r]:ci[r + 1]] = r
+    return dict(dense_kv_indptr=kv_indptr, dense_kv_indices=kv_indices, qo_indptr_ragged=ci.astype(np.int32),
+                qo_indptr_paged=qo_paged, kv_last_page_len=last, batch_table=table)
+
+
+def plan_prefill_fa3(cached_seq_lens_per_seg, cu_seqlens_q, req_to_token, req_indices, page_size: int,
+                     num_kv_heads: int, page_table_stride: int, num_tokens: int):
+    """Block-table prefill planner (csrc/utils_sglang.cu:797-834): per-segment page table rows and the
+    token -> request table located at ``cu_seqlens_q[r*H] / H``."""
+    cached = np.asarray(cached_seq_lens_per_seg, dtype=np.int64)
+    cu = np.asarray(cu_seqlens_q, dtype=np.int64)
+    r2t = np.asarray(req_to_token, dtype=np.int64)
+    ridx = np.asarray(req_indices, dtype=np.int64)
+    H, P = num_kv_heads, page_size
+    bs = len(ridx)
+    pt = np.full((bs * H, page_table_stride), NEG_FILL, dtype=np.int32)
+    table = np.zeros(num_tokens, dtype=np.uint16)
+    for r in range(bs):
+        toks = r2t[ridx[r]]
+        for h in range(H):
+            s = r * H + h
+            npg = int((cached[s] + P - 1) // P)
+            pt[s, :npg] = (toks[np.arange(npg) * P] // P) * H + h
+        q_len = int(cu[r * H + 1] - cu[r * H])
+        o = int(cu[r * H] // H)
+        table[o:o + q_len] = r
+    return dict(page_table=pt, batch_table=table)
+
+
+def chunkwise_nh2hn(x: torch.Tensor, indptr, num_kv_heads: int) -> torch.Tensor:
+    """[N, H*G, D] token-major -> [N*H, G, D] with every request's tokens regrouped head-major
+    (csrc/utils_sglang.cu:623-663)."""
+    N, HG, D = x.shape
+    H = num_kv_heads
+    G = HG // H
+    out = torch.empty(N * H, G, D, dtype=x.dtype)
+    xv = x.view(N, H, G, D)
+    for b in range(len(indptr) - 1):
+        o, e = int(indptr[b]), int(indptr[b + 1])
+        out[o * H:e * H] = xv[o:e].permute(1, 0, 2, 3).reshape((e - o) * H, G, D)
+    return out
+
+
+def chunkwise_hn2nh(x: torch.Tensor, indptr, num_kv_heads: int) -> torch.Tensor:
+    """Inverse of `chunkwise_nh2hn` for a tensor [N*H, G, ...] -> [N, H*G, ...] (csrc/utils_sglang.cu:698-751)."""
+    H = num_kv_heads
+    N = x.shape[0] // H
+    G = x.shape[1]
+    tail = tuple(x.shape[2:])
+    out = torch.empty((N, H * G) + tail, dtype=x.dtype)
+    for b in range(len(indptr) - 1):
+        o, e = int(indptr[b]), int(indptr[b + 1])
+        blk = x[o * H:e * H].reshape((H, e - o, G) + tail)
+        out[o:e] = blk.transpose(0, 1).reshape((e - o, H * G) + tail)
+    return out

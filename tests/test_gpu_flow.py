@@ -144,8 +144,6 @@ def test_vortex_torch_C_shim_signatures():
     C.topk_output(scores.cuda(), dip, sip, din, sin_, S, K, bos, eos, 64)
     ns = int(ref["sparse_kv_indptr"][-1])
     np.testing.assert_array_equal(sin_.cpu().numpy()[:ns], ref["sparse_kv_indices"])
-    with pytest.raises(NotImplementedError):
-        C.sglang_plan_prefill()
 
 
 def test_graphed_step_with_programmatic_launch_matches_eager():

@@ -43,6 +43,10 @@ SIGNATURES = {
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_gqa_splitkv": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p, _i64, _i, _p],
     "vtx_decode_gqa_splitkv_noalloc": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _p],
+    "vtx_plan_prefill": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _p],
+    "vtx_plan_prefill_fa3": [_p, _p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _p],
+    "vtx_chunkwise_nh2hn": [_p, _p, _p, _p, _i64, _i, _i, _i, _p],
+    "vtx_chunkwise_hn2nh": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
 }
 for _name, _args in SIGNATURES.items():
@@ -304,3 +308,61 @@ def indexer_quest_fused(q, cache_max, cache_min, dense_kv_indptr, sparse_kv_indp
                                      int(topk_val), int(bos), int(eos), int(max_pages_per_request),
                                      dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_indexer_quest_fused")
+
+
+def plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_lens, qo_indptr_ragged,
+                 qo_indptr_paged, kv_last_page_len, req_to_token, req_indices, batch_table, page_size,
+                 num_kv_heads) -> None:
+    for n, t in (("cached_seq_lens", cached_seq_lens), ("dense_kv_indptr", dense_kv_indptr),
+                 ("dense_kv_indices", dense_kv_indices), ("input_seq_lens", input_seq_lens),
+                 ("qo_indptr_ragged", qo_indptr_ragged), ("qo_indptr_paged", qo_indptr_paged),
+                 ("kv_last_page_len", kv_last_page_len), ("req_to_token", req_to_token)):
+        want(t, torch.int32, n)
+    want(req_indices, torch.int64, "req_indices")
+    want(batch_table, torch.uint16, "batch_table")
+    rc = lib.vtx_plan_prefill(ptr(cached_seq_lens), ptr(input_seq_lens), ptr(req_to_token), req_to_token.shape[1],
+                              ptr(req_indices), ptr(dense_kv_indptr), ptr(dense_kv_indices), ptr(qo_indptr_ragged),
+                              ptr(qo_indptr_paged), ptr(kv_last_page_len), ptr(batch_table),
+                              cached_seq_lens.shape[0], int(page_size), int(num_kv_heads), stream_of(cached_seq_lens))
+    check(rc, "vtx_plan_prefill")
+
+
+def plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, page_table, batch_table, page_size,
+                     num_kv_heads) -> None:
+    for n, t in (("cached_seq_lens", cached_seq_lens), ("cu_seqlens_q", cu_seqlens_q), ("req_to_token", req_to_token),
+                 ("page_table", page_table)):
+        want(t, torch.int32, n)
+    want(req_indices, torch.int64, "req_indices")
+    want(batch_table, torch.uint16, "batch_table")
+    rc = lib.vtx_plan_prefill_fa3(ptr(cached_seq_lens), ptr(cu_seqlens_q), ptr(req_to_token), req_to_token.shape[1],
+                                  ptr(req_indices), ptr(page_table), page_table.shape[1], ptr(batch_table),
+                                  req_indices.shape[0], int(page_size), int(num_kv_heads), stream_of(req_indices))
+    check(rc, "vtx_plan_prefill_fa3")
+
+
+def chunkwise_nh2hn(x, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim):
+    want(x, torch.bfloat16, "x")
+    want(indptr, torch.int32, "indptr")
+    want(batch_table, torch.uint16, "batch_table")
+    n, G = x.shape[0], num_qo_heads // num_kv_heads
+    out = torch.empty((n * num_kv_heads, G, head_dim), dtype=x.dtype, device=x.device)
+    rc = lib.vtx_chunkwise_nh2hn(ptr(x), ptr(out), ptr(indptr), ptr(batch_table), n, int(num_kv_heads), G,
+                                 int(head_dim), stream_of(x))
+    check(rc, "vtx_chunkwise_nh2hn")
+    return out
+
+
+def chunkwise_hn2nh(x, y, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim):
+    want(x, torch.bfloat16, "x")
+    want(indptr, torch.int32, "indptr")
+    want(batch_table, torch.uint16, "batch_table")
+    n, G = x.shape[0] // num_kv_heads, x.shape[1]
+    x_out = torch.empty((n, num_qo_heads, head_dim), dtype=x.dtype, device=x.device)
+    y_out = None
+    if y is not None:
+        want(y, torch.float32, "y")
+        y_out = torch.empty((n, num_qo_heads), dtype=y.dtype, device=y.device)
+    rc = lib.vtx_chunkwise_hn2nh(ptr(x), ptr(x_out), ptr(y), ptr(y_out), ptr(indptr), ptr(batch_table), n,
+                                 int(num_kv_heads), G, int(head_dim), stream_of(x))
+    check(rc, "vtx_chunkwise_hn2nh")
+    return x_out, y_out

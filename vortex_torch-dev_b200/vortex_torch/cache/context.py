@@ -45,12 +45,18 @@ class Context(ContextBase):
             _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, P)
 
     # ---- deferred KV write (fusion of set_kv with the flow's first cache operator) ----
-    def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int) -> None:
+    def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int,
+                       single_token_pages: bool = False) -> None:
         """Record a KV write instead of launching it.  The next cache operator either folds it into
         its own kernel (``Mean(dim=1)`` over the same K cache and ``loc``) or launches it first;
-        the caller must call ``flush_kv_write`` after ``forward_cache`` in case no operator ran."""
+        the caller must call ``flush_kv_write`` after ``forward_cache`` in case no operator ran.
+
+        ``single_token_pages``: the caller guarantees that no two slots of ``loc`` fall into the same
+        page (a decode step: one new token per request).  Only then may the write be folded into the
+        mean, which reads the page's other rows from the cache; a prefill, where one launch writes many
+        rows of a page, must leave it False."""
         self.flush_kv_write()
-        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size)
+        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size, bool(single_token_pages))
 
     def flush_kv_write(self) -> None:
         self.flush_append()
@@ -59,7 +65,7 @@ class Context(ContextBase):
             self._pending_kv = None
             from .set_kv import set_kv_buffer_launcher
 
-            set_kv_buffer_launcher(*pend)
+            set_kv_buffer_launcher(*pend[:6])
 
     def create(self, parent: Any, model_runner: Any, *, overwrite: bool = False) -> "Context":
         """``parent`` is the KV pool (page_size, num_pages, head_num, head_dim)."""

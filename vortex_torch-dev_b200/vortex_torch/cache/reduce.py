@@ -58,8 +58,8 @@ class Reduce(vOp):
             ctx.flush_append()
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
-            k_cache, v_cache, new_k, new_v, ploc, P = pend
-            if (self.reduce_type == ReduceType.Mean
+            k_cache, v_cache, new_k, new_v, ploc, P, single = pend
+            if (single and self.reduce_type == ReduceType.Mean
                     and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
                     and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
                     and new_k.shape[1] == ctx.head_num):

@@ -2,8 +2,8 @@
 
 Same call signatures as the reference's ``indexer/utils_sglang.py:15-44`` (``plan_decode``) and
 ``:135-171`` (``plan_decode_fa3``, the block-table form); both run as one kernel launch through
-the C ABI.  The prefill-side helpers of the reference module are not part of the decode path
-and raise ``NotImplementedError``.
+the C ABI.  The prefill-side helpers (``:47-187``: planners and chunk-wise transposes) keep their
+signatures as well.
 """
 from __future__ import annotations
 
@@ -37,21 +37,30 @@ def plan_decode_fa3(cached_seq_lens: torch.Tensor, req_to_token: torch.Tensor, r
     ctx.set_batch_size(cached_seq_lens.shape[0])
 
 
-def _prefill_only(name: str):
-    def _raise(*_a, **_k):
-        raise NotImplementedError(
-            f"vortex_torch.indexer.utils_sglang.{name}: prefill-side helper, not built in the sm_100a "
-            f"decode-path library")
-
-    _raise.__name__ = name
-    return _raise
+def plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_lens, qo_indptr_ragged,
+                 qo_indptr_paged, kv_last_page_len, req_to_token, req_indices, batch_table, page_size: int,
+                 num_kv_heads: int) -> None:
+    _cabi.plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_lens, qo_indptr_ragged,
+                       qo_indptr_paged, kv_last_page_len, req_to_token, req_indices, batch_table, page_size,
+                       num_kv_heads)
 
 
-plan_prefill = _prefill_only("plan_prefill")
-plan_prefill_fa3 = _prefill_only("plan_prefill_fa3")
-chunkwise_nh2hn_transpose = _prefill_only("chunkwise_nh2hn_transpose")
-chunkwise_hn2nh_transpose = _prefill_only("chunkwise_hn2nh_transpose")
-chunkwise_hn2nh_transpose_fa3 = _prefill_only("chunkwise_hn2nh_transpose_fa3")
+def plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, page_table, batch_table,
+                     page_size: int, num_kv_heads: int) -> None:
+    _cabi.plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, page_table, batch_table,
+                           page_size, num_kv_heads)
+
+
+def chunkwise_nh2hn_transpose(x, indptr, batch_table, num_qo_heads: int, num_kv_heads: int, head_dim: int):
+    return _cabi.chunkwise_nh2hn(x, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)
+
+
+def chunkwise_hn2nh_transpose(x, y, indptr, batch_table, num_qo_heads: int, num_kv_heads: int, head_dim: int):
+    return _cabi.chunkwise_hn2nh(x, y, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)
+
+
+def chunkwise_hn2nh_transpose_fa3(x, indptr, batch_table, num_qo_heads: int, num_kv_heads: int, head_dim: int):
+    return _cabi.chunkwise_hn2nh(x, None, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)[0]
 
 
 def indices_to_page_table(page_table: torch.Tensor, ctx: Context) -> None:

@@ -210,7 +210,7 @@ class VortexDecodeRuntime:
         # The KV write is handed to the cache context so that the flow's first cache operator can fold
         # it into its own kernel; whatever is left is launched right after forward_cache.
         self.cctx.defer_append(self.fuse_attention and layer not in self.skip)
-        self.cctx.defer_kv_write(cache["k"], cache["v"], new_k, new_v, loc, self.P)
+        self.cctx.defer_kv_write(cache["k"], cache["v"], new_k, new_v, loc, self.P, single_token_pages=True)
         self.flow.forward_cache(cache, loc, ctx=self.cctx)
         pend_append = self.cctx.take_pending_append()  # keep a recorded append across the flush below
         self.cctx.flush_kv_write()

@@ -2,8 +2,8 @@
 
 Same function names and positional signatures (``csrc/register.h:15-133``; for ``topk_output`` the
 order of the definition, ``csrc/topk.cu:117-128``, which is what the Python callers use), taking
-torch tensors and forwarding to the C ABI of ``libvortex_b200.so``.  The five prefill-side
-functions are not part of the decode path and raise ``NotImplementedError``.
+torch tensors and forwarding to the C ABI of ``libvortex_b200.so``.  The three transposes allocate and
+return their outputs, as the reference's do.
 """
 from __future__ import annotations
 
@@ -39,17 +39,27 @@ def topk_output(x, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_k
                topk_val, reserved_bos, reserved_eos, max_num_pages)
 
 
-def _prefill_only(name):
-    def _raise(*_a, **_k):
-        raise NotImplementedError(f"vortex_torch_C.{name}: prefill-side function, not built in the sm_100a "
-                                  f"decode-path library")
+def sglang_plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_lens, qo_indptr_ragged,
+                        qo_indptr_paged, kv_last_page_len, req_to_token, req_indices, batch_table, page_size,
+                        num_kv_heads):
+    _cabi.plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_lens, qo_indptr_ragged,
+                       qo_indptr_paged, kv_last_page_len, req_to_token, req_indices, batch_table, page_size,
+                       num_kv_heads)
 
-    _raise.__name__ = name
-    return _raise
+
+def sglang_plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, page_table, batch_table,
+                            page_size, num_kv_heads):
+    _cabi.plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, page_table, batch_table,
+                           page_size, num_kv_heads)
 
 
-sglang_plan_prefill = _prefill_only("sglang_plan_prefill")
-sglang_plan_prefill_fa3 = _prefill_only("sglang_plan_prefill_fa3")
-Chunkwise_NH2HN_Transpose = _prefill_only("Chunkwise_NH2HN_Transpose")
-Chunkwise_HN2NH_Transpose = _prefill_only("Chunkwise_HN2NH_Transpose")
-Chunkwise_HN2NH_Transpose_FA3 = _prefill_only("Chunkwise_HN2NH_Transpose_FA3")
+def Chunkwise_NH2HN_Transpose(x, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim):
+    return _cabi.chunkwise_nh2hn(x, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)
+
+
+def Chunkwise_HN2NH_Transpose(x, y, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim):
+    return _cabi.chunkwise_hn2nh(x, y, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)
+
+
+def Chunkwise_HN2NH_Transpose_FA3(x, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim):
+    return _cabi.chunkwise_hn2nh(x, None, indptr, batch_table, num_qo_heads, num_kv_heads, head_dim)[0]
