@@ -173,7 +173,7 @@ def workload_config(cfg, n):
 
 
 # --------------------------------------------------------------------------- GPU arm
-def build_runtime(cfg, device, seed):
+def build_runtime(cfg, device, seed, flow_name="block_sparse_attention"):
     from vortex_torch import _cabi
     from vortex_torch.runtime import GraphedDecodeStep, ServerArgs, VortexDecodeRuntime
 
@@ -182,7 +182,7 @@ def build_runtime(cfg, device, seed):
     num_pages = bs * pages_per_req
     sa = ServerArgs(page_size=P, vortex_topk_val=cfg["K"], vortex_page_reserved_bos=cfg["bos"],
                     vortex_page_reserved_eos=cfg["eos"], vortex_layers_skip=list(cfg["skip"]),
-                    vortex_max_seq_lens=cfg["ctx"])
+                    vortex_max_seq_lens=cfg["ctx"], vortex_module_name=flow_name)
     rt = VortexDecodeRuntime(cfg["layers"], cfg["Hq"], H, cfg["D"], num_pages=num_pages, max_bs=bs,
                              context_len=cfg["ctx"], server_args=sa, dtype=torch.bfloat16, device=device)
     g = torch.Generator().manual_seed(seed)
@@ -197,7 +197,11 @@ def build_runtime(cfg, device, seed):
         buf = rt.pool.buffers[l]
         buf["k"].normal_()
         buf["v"].normal_()
-        _cabi.cmean(buf["k"], buf["centroids"], closing, H, P)
+        if "centroids" in buf:
+            _cabi.cmean(buf["k"], buf["centroids"], closing, H, P)
+        if "max" in buf:
+            _cabi.creduce(buf["k"], buf["max"], closing, H, P, 1)
+            _cabi.creduce(buf["k"], buf["min"], closing, H, P, 2)
     step = GraphedDecodeStep(rt, bs)
     step.seq_lens.fill_(cfg["ctx"])
     step.req_indices.copy_(torch.arange(bs))
@@ -336,7 +340,7 @@ def run_mla_workload(args):
     from vortex_torch import _cabi
 
     dev = torch.device("cuda", 0)
-    bs, Hq, Dl, Dv, P, ctx, K, bos, eos, L = 128, 16, 576, 512, 64, 16384, 32, 1, 1, 4
+    bs, Hq, Dl, Dv, P, ctx, K, bos, eos, L = 128, 16, 576, 512, 64, 16384, 32, 1, 1, (args.layers or 4)
     pages_per_req = ctx // P
     num_pages = bs * pages_per_req
     g = torch.Generator().manual_seed(7)
@@ -544,6 +548,31 @@ def run_ragged_workload(args):
         dist.destroy_process_group()
 
 
+def side_flow_measurement(args, cfg, rt, step):
+    """Side measurement (not the headline line): the same decode step with another shipped flow choosing
+    the pages.  Prints steps/s of the graphed step; parity of these flows is covered by the tests."""
+    dev = rt.device
+    step.capture(programmatic_launch=min(args.pdl, 1))
+    for _ in range(max(3, args.warmup)):
+        step.replay()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step.replay()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    secs = e0.elapsed_time(e1) * 1e-3 / args.steps
+    peaks, kind = measured_peaks()
+    ab = algorithmic_bytes(cfg)
+    n_sparse = cfg["layers"] - len(cfg["skip"])
+    extra = ab["centroids_per_layer"] * n_sparse if args.flow == "gqa_quest_sparse_attention" else 0  # two summary rows
+    total = ab["step"] + extra
+    print(json.dumps(dict(flow=args.flow, workload=workload_config(cfg, 1)["workload"], steps_per_s=1.0 / secs,
+                          ms_per_step=secs * 1e3, algorithmic_bytes=total, achieved_gbs=total / secs / 1e9,
+                          frac=total / secs / 1e9 / peaks["hbm_gbs"], peak_kind=f"of {kind}")))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -556,6 +585,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch inside the step graph: 0 off, 1 on, 2 on + early prologue")
+    ap.add_argument("--flow", default="block_sparse_attention",
+                    choices=["block_sparse_attention", "gqa_block_sparse_attention", "gqa_quest_sparse_attention"],
+                    help="which shipped flow selects the pages (the headline line uses the default)")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"],
                     help="c2 = the headline decode step; c5 = side measurement of the MLA block-table decode")
     args = ap.parse_args()
@@ -593,7 +625,10 @@ def main():
 
         dist.init_process_group("nccl", device_id=device)
 
-    rt, step, slots = build_runtime(cfg, device, seed=1234 + rank)
+    rt, step, slots = build_runtime(cfg, device, seed=1234 + rank, flow_name=args.flow)
+    if args.flow != "block_sparse_attention":
+        side_flow_measurement(args, cfg, rt, step)
+        return
     if not args.no_graph:
         step.capture(programmatic_launch=args.pdl)
     W = max(3, args.warmup)
