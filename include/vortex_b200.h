@@ -264,12 +264,22 @@ int vtx_decode_gqa_splitkv_noalloc(const void* q, const void* k_cache, const voi
  * emits (csrc/utils_sglang.cu:949-1083), as written by vtx_plan_decode and vtx_indexer_fused.
  * q [bs, num_heads, latent_dim]; latent_cache [rows, page_size, latent_dim]; out [bs, num_heads, value_dim];
  * page_table [bs, page_table_stride] row ids; cache_seqlens [bs] token counts.
- * Built for bf16, 16 heads, latent 576, values 512, page_size a multiple of 16.
+ * num_cache_pages = rows of latent_cache (bounds what the TMA tensor map may address).
+ * Built for bf16, 16 heads, latent 576, values 512.  Two forms: tcgen05 tensor cores fed by TMA
+ * (page_size a power of two >= 16; the default) and warp-level mma.sync fed by cp.async (page_size a
+ * multiple of 16).  vtx_set_mla_path picks: 0 = tcgen05 where the page size allows (default),
+ * 1 = always mma.sync.  Returns the previous setting.
+ * Every wait inside the tcgen05 kernel is bounded; one that gives up sets a bit in a device word that
+ * stays set.  vtx_mla_fault_word returns that word's device address (or NULL); vtx_mla_fault_read
+ * copies it to *host_bits with a synchronous cudaMemcpy (so it waits for the device).
  */
-int vtx_decode_mla(const void* q, const void* latent_cache, void* out, const int32_t* page_table,
-                   int64_t page_table_stride, const int32_t* cache_seqlens, int batch_size,
-                   int num_heads, int latent_dim, int value_dim, int page_size, float sm_scale,
-                   int dtype, void* stream);
+int vtx_decode_mla(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
+                   const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
+                   int batch_size, int num_heads, int latent_dim, int value_dim, int page_size,
+                   float sm_scale, int dtype, void* stream);
+int vtx_set_mla_path(int path);
+void* vtx_mla_fault_word(void);
+int vtx_mla_fault_read(uint32_t* host_bits);
 
 /*
  * Prefill planner.  Replaces `sglang_plan_prefill` (csrc/register.h, csrc/utils_sglang.cu:462-621).

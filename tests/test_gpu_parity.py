@@ -384,6 +384,43 @@ def test_mla_block_table_decode(seq, K):
         assert close(out, want, BF16_TOL), f"max err {(out.float().cpu() - want.float()).abs().max()}"
 
 
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("P", [16, 32, 64, 128, 256])
+def test_mla_page_sizes_both_forms(P, path):
+    """tcgen05 (path 0) and mma.sync (path 1) forms on every page size, ragged lengths incl. empty and
+    one-token requests, full and partial last tiles; the cache rows past a request's end hold NaN."""
+    g = torch.Generator().manual_seed(100 + P)
+    seq = [0, 1, 127, 128, 129, 1000, 2048, 3 * P, 3 * P + 1, 5000]
+    bs = len(seq)
+    pages = [(n + P - 1) // P for n in seq]
+    total = sum(pages) + 3
+    perm = torch.randperm(total, generator=g).to(torch.int32)
+    stride = max(pages) + 2
+    table = torch.full((bs, stride), -1, dtype=torch.int32)
+    cache = torch.randn(total, P, 576, generator=g).to(torch.bfloat16)
+    at = 0
+    for b, n in enumerate(seq):
+        table[b, :pages[b]] = perm[at:at + pages[b]]
+        at += pages[b]
+        if n % P:  # poison the unwritten tail of the last page
+            cache[int(table[b, pages[b] - 1]), n % P:] = float("nan")
+    cache[perm[at:]] = float("nan")  # pages no request owns
+    q = torch.randn(bs, 16, 576, generator=g).to(torch.bfloat16)
+    lens = torch.tensor(seq, dtype=torch.int32)
+    scale = 1.0 / math.sqrt(192.0)
+    want = vo.decode_mla(q, cache, table.clamp(min=0).numpy(), lens.numpy(), 512, scale)
+    out = torch.full((bs, 16, 512), 7.0, dtype=torch.bfloat16, device="cuda")
+    old = _cabi.set_mla_path(path)
+    try:
+        _cabi.decode_mla(q.cuda(), cache.cuda(), out, table.clamp(min=0).cuda(), lens.cuda(), P, scale)
+        torch.cuda.synchronize()
+    finally:
+        _cabi.set_mla_path(old)
+    assert _cabi.mla_fault_bits() == 0
+    assert not torch.isnan(out.float()).any()
+    assert close(out, want, BF16_TOL), f"max err {(out.float().cpu() - want.float()).abs().max()}"
+
+
 def test_mla_rejects_other_shapes():
     z = torch.zeros(1, 8, 576, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="not supported"):

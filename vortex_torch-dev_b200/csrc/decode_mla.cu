@@ -318,18 +318,50 @@ __global__ void __launch_bounds__(kGroups * kWarps * 32, 1) decode_mla_kernel(Ml
     }
 }
 
+int g_mla_path = 0;  // 0: tcgen05 form where supported, 1: always the mma.sync form
+
 }  // namespace
 
-extern "C" int vtx_decode_mla(const void* q, const void* latent_cache, void* out, const int32_t* page_table,
-                              int64_t page_table_stride, const int32_t* cache_seqlens, int batch_size,
-                              int num_heads, int latent_dim, int value_dim, int page_size, float sm_scale,
-                              int dtype, void* stream) {
+namespace vtx {
+bool mla_tc_supported(int page_size);
+int launch_decode_mla_tc(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
+                         const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
+                         int batch_size, int page_size, float sm_scale, cudaStream_t stream);
+void* mla_fault_word();
+}  // namespace vtx
+
+extern "C" int vtx_set_mla_path(int path) {
+    const int old = g_mla_path;
+    g_mla_path = path == 1 ? 1 : 0;
+    return old;
+}
+
+extern "C" void* vtx_mla_fault_word(void) { return vtx::mla_fault_word(); }
+
+extern "C" int vtx_mla_fault_read(uint32_t* host_bits) {
+    void* w = vtx::mla_fault_word();
+    if (!host_bits || !w) return VTX_ERR_INVALID_ARGUMENT;
+    cudaError_t e = cudaMemcpy(host_bits, w, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        vtx::note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
+    return VTX_OK;
+}
+
+extern "C" int vtx_decode_mla(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
+                              const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
+                              int batch_size, int num_heads, int latent_dim, int value_dim, int page_size,
+                              float sm_scale, int dtype, void* stream) {
     if (!q || !latent_cache || !out || !page_table || !cache_seqlens) return VTX_ERR_INVALID_ARGUMENT;
-    if (batch_size < 0 || page_table_stride < 1 || page_size < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (batch_size < 0 || page_table_stride < 1 || page_size < 1 || num_cache_pages < 1) return VTX_ERR_INVALID_ARGUMENT;
     if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
     if (dtype != VTX_BF16 || num_heads != kHeads || latent_dim != kDl || value_dim != kDv || page_size % kTile != 0)
         return VTX_ERR_UNSUPPORTED;
     if (batch_size == 0) return VTX_OK;
+    if (g_mla_path == 0 && vtx::mla_tc_supported(page_size))
+        return vtx::launch_decode_mla_tc(q, latent_cache, num_cache_pages, out, page_table, page_table_stride,
+                                         cache_seqlens, batch_size, page_size, sm_scale, (cudaStream_t)stream);
     MlaArgs a;
     a.q = (const __nv_bfloat16*)q;
     a.latent = (const unsigned char*)latent_cache;

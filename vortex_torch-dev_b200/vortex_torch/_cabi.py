@@ -47,7 +47,9 @@ SIGNATURES = {
     "vtx_plan_prefill_fa3": [_p, _p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _p],
     "vtx_chunkwise_nh2hn": [_p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_chunkwise_hn2nh": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _p],
-    "vtx_decode_mla": [_p, _p, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_decode_mla": [_p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_set_mla_path": [_i],
+    "vtx_mla_fault_read": [_p],
 }
 for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
@@ -55,6 +57,8 @@ for _name, _args in SIGNATURES.items():
     _fn.restype = _i
 lib.vtx_decode_gqa_splitkv_workspace_bytes.argtypes = [_i, _i, _i, _i]
 lib.vtx_decode_gqa_splitkv_workspace_bytes.restype = _i64
+lib.vtx_mla_fault_word.argtypes = []
+lib.vtx_mla_fault_word.restype = _p
 lib.vtx_set_programmatic_launch.argtypes = [_i]
 lib.vtx_set_programmatic_launch.restype = _i
 lib.vtx_version.restype = _i
@@ -63,7 +67,8 @@ lib.vtx_status_string.restype = C.c_char_p
 lib.vtx_last_cuda_error.restype = C.c_char_p
 
 EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error",
-                                    "vtx_set_programmatic_launch", "vtx_decode_gqa_splitkv_workspace_bytes"])
+                                    "vtx_set_programmatic_launch", "vtx_decode_gqa_splitkv_workspace_bytes",
+                                    "vtx_mla_fault_word"])
 
 
 def set_programmatic_launch(mode) -> None:
@@ -225,10 +230,22 @@ def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_sc
     want(cache_seqlens, torch.int32, "cache_seqlens")
     if not (q.dtype == latent_cache.dtype == out.dtype):
         raise TypeError("decode_mla: q, latent cache and out must share a dtype")
-    rc = lib.vtx_decode_mla(ptr(q), ptr(latent_cache), ptr(out), ptr(page_table), page_table.shape[1],
-                            ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
+    rc = lib.vtx_decode_mla(ptr(q), ptr(latent_cache), latent_cache.shape[0], ptr(out), ptr(page_table),
+                            page_table.shape[1], ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_mla")
+
+
+def set_mla_path(path: int) -> int:
+    """0: tcgen05 form of the MLA decode where the page size allows (default); 1: mma.sync form."""
+    return lib.vtx_set_mla_path(int(path))
+
+
+def mla_fault_bits() -> int:
+    """The sticky fault word of the tcgen05 MLA kernel (0 = no bounded wait ever gave up).  Synchronises."""
+    host = C.c_uint32(0xFFFFFFFF)
+    check(lib.vtx_mla_fault_read(C.byref(host)), "vtx_mla_fault_read")
+    return int(host.value)
 
 
 def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
