@@ -39,7 +39,7 @@ constexpr int kQuadSlots = 5;             // a tile holds 2
 constexpr int kRopeSlots = 4;
 constexpr int kQB = kHeads * kDl * 2;     // 18 KB: 9 blocks of 16 heads x 64 dims
 constexpr int kPB = kHeads * kTile * 2;   // 2 KB: 16 heads x 64 tokens
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;            // warps: 0 TMA, 1 QK issue, 2-5 softmax, 6 PV issue
 constexpr int kSoftmaxThreads = 128;
 constexpr uint32_t kTmemCols = 256;
 constexpr int kAcc = 4;  // partial S^T accumulators per buffer: k-step j of every block adds into accumulator j
@@ -60,7 +60,8 @@ enum Bar {
     kFullRope = kEmptyQuad + kQuadSlots,
     kEmptyRope = kFullRope + kRopeSlots,
     kSFull = kEmptyRope + kRopeSlots,  // 2
-    kPFull = kSFull + 2,
+    kSFree = kSFull + 2,               // 2
+    kPFull = kSFree + 2,
     kODone,
     kFixed,
     kQReady,
@@ -97,6 +98,18 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// non-blocking test (try_wait may suspend the thread for a while before it answers)
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -159,6 +172,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+// the same load without the wait: the registers are valid only after tmem_wait_ld()
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, float (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+          "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+// Wait for the loads in flight; naming the registers as in/out operands keeps every use of them below the wait.
+__device__ __forceinline__ void tmem_wait_ld(float (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+f"(v[0]), "+f"(v[1]), "+f"(v[2]), "+f"(v[3]), "+f"(v[4]), "+f"(v[5]), "+f"(v[6]), "+f"(v[7]),
+                   "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]), "+f"(v[15])
+                 :
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float (&v)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
@@ -209,6 +239,13 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// 2^x on the special-function unit (2^-inf = 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ int float_key(float x) {  // order-preserving map to signed int
     const int i = __float_as_int(x);
     return i ^ ((i >> 31) & 0x7fffffff);
@@ -242,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
         for (int i = 0; i < kQuadSlots; ++i) { mbar_init(bar(kFullQuad + i), 1); mbar_init(bar(kEmptyQuad + i), 1); }
         for (int i = 0; i < kRopeSlots; ++i) { mbar_init(bar(kFullRope + i), 1); mbar_init(bar(kEmptyRope + i), 1); }
         mbar_init(bar(kSFull), 1); mbar_init(bar(kSFull + 1), 1);
+        mbar_init(bar(kSFree), kSoftmaxThreads); mbar_init(bar(kSFree + 1), kSoftmaxThreads);
         mbar_init(bar(kPFull), kSoftmaxThreads);
         mbar_init(bar(kODone), 1);
         mbar_init(bar(kFixed), kSoftmaxThreads);
@@ -319,10 +357,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                     if (clock64() - t0 > 200000000ll) { atomicOr(&g_mla_fault, kFaultDrain); break; }
             }
         }
-    } else if (warp == 1) {
-        // ================================================= MMA issuer.  The whole warp walks the loop and waits;
-        // one elected lane issues (the elect.sync form lets the descriptors live in uniform registers, which
-        // more than halves the cost of an issue compared with a lane-0 branch).
+    } else if (warp == 1 || warp == 6) {
+        // ================================================= MMA issuers: warp 1 the S^T products, warp 6 the PV
+        // products.  Two warps, so that PV(i) never queues behind a wait for the next tile's data and S^T(i + 1)
+        // never behind the softmax of tile i.  The whole warp walks the loop and waits; one elected lane issues
+        // (the elect.sync form lets the descriptors live in uniform registers, which more than halves the cost
+        // of an issue compared with a lane-0 branch).
         if (n_tiles > 0) {
             bool ok = true;
             auto wait_all = [&](int which, uint32_t parity, unsigned code) {
@@ -330,45 +370,55 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 ok = __all_sync(0xffffffffu, ok) != 0;
                 return ok;
             };
-            wait_all(kQReady, 0, kFaultQ);
+            if (warp == 1) wait_all(kQReady, 0, kFaultQ);
             // descriptors: constant high part + (byte address >> 4)
             const uint64_t dk = smem_desc(0, 0, 1024), dmn = smem_desc(0, kBlockB, 1024);
             const uint64_t qd = dk + ((base + kOffQ) >> 4), pd = dk + ((base + kOffP) >> 4);
             auto is_partial = [&](int i) { return last_partial && i == n_tiles - 1; };
-            auto qk = [&](int i) {  // S^T of tile i into buffer i & 1: k-step j of every block adds into accumulator j
-                if (is_partial(i) && !wait_all(kFixed, 0, kFaultFixed)) return;
-                const uint32_t sd = tmem + kColS + (i & 1) * kAcc * 16;
-                for (int u = 0; u < 2; ++u) {
-                    const int idx = 2 * i + u, slot = idx % kQuadSlots;
-                    if (!wait_all(kFullQuad + slot, (idx / kQuadSlots) & 1, kFaultFull)) return;
-                    tc_fence_after();
-                    if (elect_one()) {
-                        const uint64_t ad = dk + ((base + kOffQuads + slot * kQuadB) >> 4);
+            // S^T of tile i into buffer i & 1 is issued in three parts as their data lands: quad 0, quad 1 (16
+            // k-steps each) and the rope block (4 k-steps, then the commits that release the rope slot and
+            // publish S^T); k-step j of every block adds into accumulator j.  A last tile that is not full is
+            // ready, as a whole, once the softmax warps have zeroed its tail.
+            auto part_wait = [&](int i, int part) {
+                if (is_partial(i)) return wait_all(kFixed, 0, kFaultFixed);
+                if (part == 2) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
+                return wait_all(kFullQuad + (2 * i + part) % kQuadSlots, ((2 * i + part) / kQuadSlots) & 1, kFaultFull);
+            };
+            auto part_issue = [&](int i, int part) {
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint32_t sd = tmem + kColS + (i & 1) * kAcc * 16;
+                    if (part < 2) {
+                        const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + part) % kQuadSlots) * kQuadB) >> 4);
 #pragma unroll
                         for (int blk = 0; blk < 4; ++blk)
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
                                 umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
-                                     qd + (((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, (u | blk) != 0 ? 1u : 0u);
-                    }
-                    __syncwarp();
-                }
-                const int rslot = i % kRopeSlots;
-                if (!wait_all(kFullRope + rslot, (i / kRopeSlots) & 1, kFaultFull)) return;
-                tc_fence_after();
-                if (elect_one()) {
-                    const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
+                                     qd + (uint64_t)(((4 * part + blk) * 2048 + j * 32) >> 4), kIdescQK,
+                                     (part | blk) != 0 ? 1u : 0u);
+                    } else {
+                        const int rslot = i % kRopeSlots;
+                        const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) umma(sd + j * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, 1u);
-                    umma_commit(bar(kEmptyRope + rslot));
-                    umma_commit(bar(kSFull + (i & 1)));
+                        for (int j = 0; j < 4; ++j)
+                            umma(sd + j * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, 1u);
+                        umma_commit(bar(kEmptyRope + rslot));
+                        umma_commit(bar(kSFull + (i & 1)));
+                    }
                 }
                 __syncwarp();
             };
-            qk(0);
-            for (int i = 0; i < n_tiles && ok; ++i) {
-                if (i + 1 < n_tiles) qk(i + 1);  // runs under the softmax of tile i
-                if (!ok || !wait_all(kPFull, i & 1, kFaultP)) break;
+            if (warp == 1) {
+                for (int i = 0; i < n_tiles && ok; ++i) {
+                    // S^T buffer i & 1 was last read by the softmax of tile i - 2
+                    if (i >= 2 && !wait_all(kSFree + (i & 1), ((i - 2) >> 1) & 1, kFaultS)) break;
+                    for (int part = 0; part < 3 && ok; ++part)
+                        if (part_wait(i, part)) part_issue(i, part);
+                }
+            }
+            for (int i = 0; i < n_tiles && ok && warp == 6; ++i) {
+                if (!wait_all(kPFull, i & 1, kFaultP)) break;
                 tc_fence_after();
                 const int slot0 = (2 * i) % kQuadSlots, slot1 = (2 * i + 1) % kQuadSlots;
                 if (elect_one()) {
@@ -452,14 +502,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 mbar_wait(bar(kSFull + buf), (i >> 1) & 1, abort_flag, kFaultS);
                 tc_fence_after();
                 float s[kHeads];
-                tmem_ld16(tlane + kColS + buf * kAcc * 16, s);
+                {
+                    float part[kAcc][kHeads];  // the four partial sums, one round trip to TMEM
 #pragma unroll
-                for (int acc = 1; acc < kAcc; ++acc) {
-                    float part[kHeads];
-                    tmem_ld16(tlane + kColS + (buf * kAcc + acc) * 16, part);
+                    for (int acc = 0; acc < kAcc; ++acc) tmem_ld16_nowait(tlane + kColS + (buf * kAcc + acc) * 16, part[acc]);
 #pragma unroll
-                    for (int h = 0; h < kHeads; ++h) s[h] += part[h];
+                    for (int acc = 0; acc < kAcc; ++acc) tmem_wait_ld(part[acc]);
+#pragma unroll
+                    for (int h = 0; h < kHeads; ++h) s[h] = (part[0][h] + part[1][h]) + (part[2][h] + part[3][h]);
                 }
+                tc_fence_before();
+                mbar_arrive(bar(kSFree + buf));
                 const bool valid = tlive && i * kTile + trow < ntok;
                 int key[kHeads];
 #pragma unroll
@@ -490,16 +543,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const int h = 4 * h4 + k;
-                        const float mn = fmaxf(m[h], tm[k]);
-                        alpha[h] = exp2f(m[h] - mn);
-                        moved |= mn != m[h];
+                        alpha[h] = fmaxf(m[h], tm[k]);  // the new maximum for now
+                        moved |= alpha[h] != m[h];
+                    }
+                }
+                if (moved) {  // same decision in every thread: they all hold the same maxima
+#pragma unroll
+                    for (int h = 0; h < kHeads; ++h) {
+                        const float mn = alpha[h];
+                        alpha[h] = ex2(m[h] - mn);
+                        l[h] *= alpha[h];
                         m[h] = mn;
                     }
                 }
 #pragma unroll
                 for (int h = 0; h < kHeads; ++h) {
-                    s[h] = exp2f(s[h] - m[h]);
-                    l[h] = l[h] * alpha[h] + s[h];
+                    s[h] = ex2(s[h] - m[h]);
+                    l[h] += s[h];
                 }
                 if (i > 0) {
                     // the previous PV product must be complete before P^T is overwritten or O^T rescaled
