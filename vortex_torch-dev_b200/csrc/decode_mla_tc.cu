@@ -13,7 +13,9 @@
 // fetched once, by three TMA copies through a 3-d view of the cache [64 dims][tokens][9 blocks]: two
 // "quads" of four value blocks (32 KB, two 128-dim groups of the PV product each) and the rope block.
 // Few large copies matter: a copy costs the issuing thread ~0.2 us, and nine 8 KB copies per tile capped
-// the kernel at two thirds of the HBM rate that three copies reach.  The rings hold 2.5 tiles.
+// the kernel at two thirds of the HBM rate that three copies reach.  The quad ring holds 3 tiles: with
+// less, a copy could only be issued about one tile time before its data is needed, which is less than an
+// HBM round trip under load.
 // Accumulators live in TMEM: S^T twice, as four partial sums of 16 columns each (an M = 64 product puts
 // rows 16w..16w+15 in lanes 32w..32w+15), and O^T (64 columns, lane = dim).
 //
@@ -35,8 +37,8 @@ constexpr int kTile = 64;                 // tokens per tile
 constexpr int kBlockDims = 64;            // dims per block: one 128-byte swizzle row
 constexpr int kBlockB = kTile * 128;      // 8 KB: 64 tokens x 64 dims
 constexpr int kQuadB = 4 * kBlockB;       // 32 KB: 256 dims of the values
-constexpr int kQuadSlots = 5;             // a tile holds 2
-constexpr int kRopeSlots = 4;
+constexpr int kQuadSlots = 6;             // a tile holds 2
+constexpr int kRopeSlots = 1;             // read first by the S^T product, so it is free again a tile ahead of its next use
 constexpr int kQB = kHeads * kDl * 2;     // 18 KB: 9 blocks of 16 heads x 64 dims
 constexpr int kPB = kHeads * kTile * 2;   // 2 KB: 16 heads x 64 tokens
 constexpr int kThreads = 224;            // warps: 0 TMA, 1 QK issue, 2-5 softmax, 6 PV issue
@@ -69,6 +71,7 @@ enum Bar {
 };
 constexpr int kOffMisc = kOffBars + kNumBars * 8;       // tmem base (u32), abort flag (int)
 constexpr int kSmemBytes = kOffMisc + 16 + 1024;        // + slack for the manual 1024-byte alignment
+static_assert(kSmemBytes <= 227 * 1024, "over the shared memory of one CTA");
 
 __device__ unsigned int g_mla_fault = 0;  // sticky: a bounded wait gave up (bit = which barrier kind)
 
@@ -294,8 +297,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     const uint32_t tmem = *tmem_slot;
 
     if (warp == 0) {
-        // ================================================= TMA producer.  Three units per tile: quad 0 (blocks 0-3),
-        // quad 1 (blocks 4-7), rope (block 8).  Pages of 64 tokens or more: one copy per unit from an elected
+        // ================================================= TMA producer.  Three units per tile: rope (block 8), quad 0
+        // (blocks 0-3), quad 1 (blocks 4-7).  Pages of 64 tokens or more: one copy per unit from an elected
         // lane.  Smaller pages: a unit is (blocks x boxes) copies of [64 dims x page] spread over the lanes.
         const int nb = kTile / a.box_tok;
         const bool big_pages = nb == 1;
@@ -316,8 +319,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             const int nload = left >= kTile ? nb : (left + a.box_tok - 1) / a.box_tok;
             const uint32_t block_bytes = (uint32_t)nload * a.box_tok * 128u;
             for (int u = 0; u < 3 && ok; ++u) {
-                const bool rope = u == 2;
-                const int idx = rope ? i : 2 * i + u, nslots = rope ? kRopeSlots : kQuadSlots;
+                const bool rope = u == 0;
+                const int idx = rope ? i : 2 * i + u - 1, nslots = rope ? kRopeSlots : kQuadSlots;
                 const int slot = idx % nslots, use = idx / nslots;
                 const int full = (rope ? kFullRope : kFullQuad) + slot, empty = (rope ? kEmptyRope : kEmptyQuad) + slot;
                 if (use > 0) ok = mbar_wait(bar(empty), (use - 1) & 1, abort_flag, kFaultEmpty);
@@ -326,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 armed |= 1u << full;
                 armed_parity = (armed_parity & ~(1u << full)) | ((unsigned)(use & 1) << full);
                 const uint32_t dst = base + (rope ? kOffRope + slot * kBlockB : kOffQuads + slot * kQuadB);
-                const int nblk = rope ? 1 : 4, blk0 = rope ? 8 : 4 * u;
+                const int nblk = rope ? 1 : 4, blk0 = rope ? 8 : 4 * (u - 1);
                 if (big_pages) {
                     if (elect_one()) {
                         mbar_arrive_expect_tx(bar(full), block_bytes * nblk);
@@ -375,36 +378,36 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             const uint64_t dk = smem_desc(0, 0, 1024), dmn = smem_desc(0, kBlockB, 1024);
             const uint64_t qd = dk + ((base + kOffQ) >> 4), pd = dk + ((base + kOffP) >> 4);
             auto is_partial = [&](int i) { return last_partial && i == n_tiles - 1; };
-            // S^T of tile i into buffer i & 1 is issued in three parts as their data lands: quad 0, quad 1 (16
-            // k-steps each) and the rope block (4 k-steps, then the commits that release the rope slot and
-            // publish S^T); k-step j of every block adds into accumulator j.  A last tile that is not full is
+            // S^T of tile i into buffer i & 1 is issued in three parts as their data lands: the rope block (4
+            // k-steps, then the commit that releases the rope slot), quad 0 and quad 1 (16 k-steps each, then
+            // the commit that publishes S^T); k-step j of every block goes into accumulator j.  A last tile that is not full is
             // ready, as a whole, once the softmax warps have zeroed its tail.
             auto part_wait = [&](int i, int part) {
                 if (is_partial(i)) return wait_all(kFixed, 0, kFaultFixed);
-                if (part == 2) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
-                return wait_all(kFullQuad + (2 * i + part) % kQuadSlots, ((2 * i + part) / kQuadSlots) & 1, kFaultFull);
+                if (part == 0) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
+                return wait_all(kFullQuad + (2 * i + part - 1) % kQuadSlots, ((2 * i + part - 1) / kQuadSlots) & 1, kFaultFull);
             };
             auto part_issue = [&](int i, int part) {
                 tc_fence_after();
                 if (elect_one()) {
                     const uint32_t sd = tmem + kColS + (i & 1) * kAcc * 16;
-                    if (part < 2) {
-                        const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + part) % kQuadSlots) * kQuadB) >> 4);
+                    if (part > 0) {
+                        const int u = part - 1;
+                        const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + u) % kQuadSlots) * kQuadB) >> 4);
 #pragma unroll
                         for (int blk = 0; blk < 4; ++blk)
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
                                 umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
-                                     qd + (uint64_t)(((4 * part + blk) * 2048 + j * 32) >> 4), kIdescQK,
-                                     (part | blk) != 0 ? 1u : 0u);
+                                     qd + (uint64_t)(((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, 1u);
+                        if (part == 2) umma_commit(bar(kSFull + (i & 1)));
                     } else {
                         const int rslot = i % kRopeSlots;
                         const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            umma(sd + j * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, 1u);
+                            umma(sd + j * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, 0u);
                         umma_commit(bar(kEmptyRope + rslot));
-                        umma_commit(bar(kSFull + (i & 1)));
                     }
                 }
                 __syncwarp();
@@ -425,15 +428,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                     // 128-dim group g: blocks 2g, 2g+1 = the lower or upper half of quad g / 2
                     const uint32_t ga[4] = {base + kOffQuads + slot0 * kQuadB, base + kOffQuads + slot0 * kQuadB + 2 * kBlockB,
                                             base + kOffQuads + slot1 * kQuadB, base + kOffQuads + slot1 * kQuadB + 2 * kBlockB};
-                    // the four 128-dim groups are independent accumulators: interleave them
+                    // quad by quad, so that the first one is released half a product earlier
 #pragma unroll
-                    for (int t = 0; t < kTile / 16; ++t)
+                    for (int qd2 = 0; qd2 < 2; ++qd2) {
 #pragma unroll
-                        for (int g = 0; g < 4; ++g)
-                            umma(tmem + kColO + g * 16, dmn + ((ga[g] + t * 2048) >> 4),
-                                 pd + ((t * 32) >> 4), kIdescPV, (i | t) != 0 ? 1u : 0u);
-                    umma_commit(bar(kEmptyQuad + slot0));
-                    umma_commit(bar(kEmptyQuad + slot1));
+                        for (int t = 0; t < kTile / 16; ++t)
+#pragma unroll
+                            for (int g = 2 * qd2; g < 2 * qd2 + 2; ++g)
+                                umma(tmem + kColO + g * 16, dmn + ((ga[g] + t * 2048) >> 4),
+                                     pd + ((t * 32) >> 4), kIdescPV, (i | t) != 0 ? 1u : 0u);
+                        umma_commit(bar(kEmptyQuad + (qd2 == 0 ? slot0 : slot1)));
+                    }
                     umma_commit(bar(kODone));
                 }
                 __syncwarp();
