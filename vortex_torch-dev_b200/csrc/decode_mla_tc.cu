@@ -45,7 +45,8 @@ constexpr int kThreads = 224;            // warps: 0 TMA, 1 QK issue, 2-5 softma
 constexpr int kSoftmaxThreads = 128;
 constexpr uint32_t kTmemCols = 256;
 constexpr int kAcc = 4;  // partial S^T accumulators per buffer: k-step j of every block adds into accumulator j
-constexpr uint32_t kColS = 0, kColO = 2 * kAcc * 16;
+constexpr int kSBufs = 3;  // S^T buffers: the rope part of tile i + 1 is issued before the quads of tile i
+constexpr uint32_t kColS = 0, kColO = kSBufs * kAcc * 16;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
@@ -61,9 +62,9 @@ enum Bar {
     kEmptyQuad = kFullQuad + kQuadSlots,
     kFullRope = kEmptyQuad + kQuadSlots,
     kEmptyRope = kFullRope + kRopeSlots,
-    kSFull = kEmptyRope + kRopeSlots,  // 2
-    kSFree = kSFull + 2,               // 2
-    kPFull = kSFree + 2,
+    kSFull = kEmptyRope + kRopeSlots,  // kSBufs
+    kSFree = kSFull + kSBufs,          // kSBufs
+    kPFull = kSFree + kSBufs,
     kODone,
     kFixed,
     kQReady,
@@ -281,8 +282,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     if (threadIdx.x == 0) {
         for (int i = 0; i < kQuadSlots; ++i) { mbar_init(bar(kFullQuad + i), 1); mbar_init(bar(kEmptyQuad + i), 1); }
         for (int i = 0; i < kRopeSlots; ++i) { mbar_init(bar(kFullRope + i), 1); mbar_init(bar(kEmptyRope + i), 1); }
-        mbar_init(bar(kSFull), 1); mbar_init(bar(kSFull + 1), 1);
-        mbar_init(bar(kSFree), kSoftmaxThreads); mbar_init(bar(kSFree + 1), kSoftmaxThreads);
+        for (int i = 0; i < kSBufs; ++i) { mbar_init(bar(kSFull + i), 1); mbar_init(bar(kSFree + i), kSoftmaxThreads); }
         mbar_init(bar(kPFull), kSoftmaxThreads);
         mbar_init(bar(kODone), 1);
         mbar_init(bar(kFixed), kSoftmaxThreads);
@@ -378,10 +378,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             const uint64_t dk = smem_desc(0, 0, 1024), dmn = smem_desc(0, kBlockB, 1024);
             const uint64_t qd = dk + ((base + kOffQ) >> 4), pd = dk + ((base + kOffP) >> 4);
             auto is_partial = [&](int i) { return last_partial && i == n_tiles - 1; };
-            // S^T of tile i into buffer i & 1 is issued in three parts as their data lands: the rope block (4
+            // S^T of tile i into buffer i % 3 is issued in three parts as their data lands: the rope block (4
             // k-steps, then the commit that releases the rope slot), quad 0 and quad 1 (16 k-steps each, then
-            // the commit that publishes S^T); k-step j of every block goes into accumulator j.  A last tile that is not full is
-            // ready, as a whole, once the softmax warps have zeroed its tail.
+            // the commit that publishes S^T); k-step j of every block goes into accumulator j.  The rope part
+            // of tile i + 1 follows the quads of tile i, so that the single rope slot is free again more than a
+            // tile time before its next block is needed.  A last tile that is not full is ready, as a whole, once the softmax
+            // warps have zeroed its tail; its rope part is not taken ahead.
             auto part_wait = [&](int i, int part) {
                 if (is_partial(i)) return wait_all(kFixed, 0, kFaultFixed);
                 if (part == 0) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
@@ -390,7 +392,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             auto part_issue = [&](int i, int part) {
                 tc_fence_after();
                 if (elect_one()) {
-                    const uint32_t sd = tmem + kColS + (i & 1) * kAcc * 16;
+                    const uint32_t sd = tmem + kColS + (i % kSBufs) * kAcc * 16;
                     if (part > 0) {
                         const int u = part - 1;
                         const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + u) % kQuadSlots) * kQuadB) >> 4);
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                             for (int j = 0; j < 4; ++j)
                                 umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
                                      qd + (uint64_t)(((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, 1u);
-                        if (part == 2) umma_commit(bar(kSFull + (i & 1)));
+                        if (part == 2) umma_commit(bar(kSFull + i % kSBufs));
                     } else {
                         const int rslot = i % kRopeSlots;
                         const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
@@ -413,11 +415,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 __syncwarp();
             };
             if (warp == 1) {
+                auto rope_part = [&](int i) {
+                    // S^T buffer i % 3 was last read by the softmax of tile i - 3
+                    if (i >= kSBufs && !wait_all(kSFree + i % kSBufs, ((i - kSBufs) / kSBufs) & 1, kFaultS)) return;
+                    if (part_wait(i, 0)) part_issue(i, 0);
+                };
+                rope_part(0);
                 for (int i = 0; i < n_tiles && ok; ++i) {
-                    // S^T buffer i & 1 was last read by the softmax of tile i - 2
-                    if (i >= 2 && !wait_all(kSFree + (i & 1), ((i - 2) >> 1) & 1, kFaultS)) break;
-                    for (int part = 0; part < 3 && ok; ++part)
+                    if (i > 0 && is_partial(i)) rope_part(i);
+                    for (int part = 1; part < 3 && ok; ++part)
                         if (part_wait(i, part)) part_issue(i, part);
+                    if (ok && i + 1 < n_tiles && !is_partial(i + 1)) rope_part(i + 1);
                 }
             }
             for (int i = 0; i < n_tiles && ok && warp == 6; ++i) {
@@ -502,9 +510,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             float* wmax = reinterpret_cast<float*>(gbase + kOffWmax);
 
             for (int i = 0; i < n_tiles; ++i) {
-                const int buf = i & 1;
+                const int buf = i % kSBufs;
                 if (last_partial && i + 1 == n_tiles - 1) zero_tail(i + 1);
-                mbar_wait(bar(kSFull + buf), (i >> 1) & 1, abort_flag, kFaultS);
+                mbar_wait(bar(kSFull + buf), (i / kSBufs) & 1, abort_flag, kFaultS);
                 tc_fence_after();
                 float s[kHeads];
                 {
@@ -526,7 +534,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                     key[h] = __reduce_max_sync(0xffffffffu, float_key(s[h]));
                 }
                 if (lane == 0) {
-                    float4* w = reinterpret_cast<float4*>(wmax + (buf * 4 + q4) * 16);
+                    float4* w = reinterpret_cast<float4*>(wmax + ((i & 1) * 4 + q4) * 16);
 #pragma unroll
                     for (int h4 = 0; h4 < 4; ++h4)
                         w[h4] = make_float4(key_float(key[4 * h4]), key_float(key[4 * h4 + 1]),
@@ -538,10 +546,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 bool moved = false;
 #pragma unroll
                 for (int h4 = 0; h4 < 4; ++h4) {
-                    float4 t = *reinterpret_cast<const float4*>(wmax + (buf * 4 + 0) * 16 + 4 * h4);
+                    float4 t = *reinterpret_cast<const float4*>(wmax + ((i & 1) * 4 + 0) * 16 + 4 * h4);
 #pragma unroll
                     for (int w = 1; w < 4; ++w) {
-                        const float4 u = *reinterpret_cast<const float4*>(wmax + (buf * 4 + w) * 16 + 4 * h4);
+                        const float4 u = *reinterpret_cast<const float4*>(wmax + ((i & 1) * 4 + w) * 16 + 4 * h4);
                         t.x = fmaxf(t.x, u.x); t.y = fmaxf(t.y, u.y); t.z = fmaxf(t.z, u.z); t.w = fmaxf(t.w, u.w);
                     }
                     const float tm[4] = {t.x, t.y, t.z, t.w};
