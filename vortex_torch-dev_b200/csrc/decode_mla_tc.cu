@@ -19,7 +19,8 @@
 // Accumulators live in TMEM: S^T twice, as four partial sums of 16 columns each (an M = 64 product puts
 // rows 16w..16w+15 in lanes 32w..32w+15), and O^T (64 columns, lane = dim).
 //
-// Warp roles: warp 0 issues the TMA copies, warp 1 issues every MMA from one elected lane, warps 2-5 do
+// Warp roles: warps 0 and 7 issue the TMA copies (quads, rope), warps 1 and 6 the MMAs (S^T, PV) from one
+// elected lane each, warps 2-5 do
 // the online softmax in fp32: S^T out of TMEM, per-head maxima over the tile, P^T as bf16 into shared
 // memory, O^T rescaled in TMEM only when a maximum moved, and the final normalisation.
 // All hand-offs are mbarriers; every wait is bounded and, when it gives up, raises a fault word that the
@@ -41,7 +42,7 @@ constexpr int kQuadSlots = 6;             // a tile holds 2
 constexpr int kRopeSlots = 1;             // read first by the S^T product, so it is free again a tile ahead of its next use
 constexpr int kQB = kHeads * kDl * 2;     // 18 KB: 9 blocks of 16 heads x 64 dims
 constexpr int kPB = kHeads * kTile * 2;   // 2 KB: 16 heads x 64 tokens
-constexpr int kThreads = 224;            // warps: 0 TMA, 1 QK issue, 2-5 softmax, 6 PV issue
+constexpr int kThreads = 256;            // warps: 0 TMA quads, 1 S^T issue, 2-5 softmax, 6 PV issue, 7 TMA rope
 constexpr int kSoftmaxThreads = 128;
 constexpr uint32_t kTmemCols = 256;
 constexpr int kAcc = 4;  // partial S^T accumulators per buffer: k-step j of every block adds into accumulator j
@@ -135,6 +136,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     }
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned code) {
+    if (mbar_test(bar, parity)) return true;  // a try_wait costs ~140 cycles even when the phase is already complete
     if (mbar_try(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, abort_flag, code);
 }
@@ -296,9 +298,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // ================================================= TMA producer.  Three units per tile: rope (block 8), quad 0
-        // (blocks 0-3), quad 1 (blocks 4-7).  Pages of 64 tokens or more: one copy per unit from an elected
+    if (warp == 0 || warp == 7) {
+        // ================================================= TMA producers.  Three units per tile: rope (block 8), quad 0
+        // (blocks 0-3), quad 1 (blocks 4-7).  Warp 0 streams the quads, warp 7 the rope blocks: two queues, so
+        // that a wait for the single rope slot never holds back the quads behind it.  Pages of 64 tokens or more: one copy per unit from an elected
         // lane.  Smaller pages: a unit is (blocks x boxes) copies of [64 dims x page] spread over the lanes.
         const int nb = kTile / a.box_tok;
         const bool big_pages = nb == 1;
@@ -318,7 +321,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             const int left = ntok - i * kTile;
             const int nload = left >= kTile ? nb : (left + a.box_tok - 1) / a.box_tok;
             const uint32_t block_bytes = (uint32_t)nload * a.box_tok * 128u;
-            for (int u = 0; u < 3 && ok; ++u) {
+            for (int u = (warp == 7 ? 0 : 1); u < (warp == 7 ? 1 : 3) && ok; ++u) {
                 const bool rope = u == 0;
                 const int idx = rope ? i : 2 * i + u - 1, nslots = rope ? kRopeSlots : kQuadSlots;
                 const int slot = idx % nslots, use = idx / nslots;
@@ -389,20 +392,22 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 if (part == 0) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
                 return wait_all(kFullQuad + (2 * i + part - 1) % kQuadSlots, ((2 * i + part - 1) / kQuadSlots) & 1, kFaultFull);
             };
-            auto part_issue = [&](int i, int part) {
+            auto part_issue = [&](int i, int part) {  // part 0: the rope block; part 1: both quads
                 tc_fence_after();
                 if (elect_one()) {
                     const uint32_t sd = tmem + kColS + (i % kSBufs) * kAcc * 16;
                     if (part > 0) {
-                        const int u = part - 1;
-                        const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + u) % kQuadSlots) * kQuadB) >> 4);
 #pragma unroll
-                        for (int blk = 0; blk < 4; ++blk)
+                        for (int u = 0; u < 2; ++u) {
+                            const uint64_t ad = dk + ((base + kOffQuads + ((2 * i + u) % kQuadSlots) * kQuadB) >> 4);
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
-                                     qd + (uint64_t)(((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, 1u);
-                        if (part == 2) umma_commit(bar(kSFull + i % kSBufs));
+                            for (int blk = 0; blk < 4; ++blk)
+#pragma unroll
+                                for (int j = 0; j < 4; ++j)
+                                    umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
+                                         qd + (((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, 1u);
+                        }
+                        umma_commit(bar(kSFull + i % kSBufs));
                     } else {
                         const int rslot = i % kRopeSlots;
                         const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
@@ -423,8 +428,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 rope_part(0);
                 for (int i = 0; i < n_tiles && ok; ++i) {
                     if (i > 0 && is_partial(i)) rope_part(i);
-                    for (int part = 1; part < 3 && ok; ++part)
-                        if (part_wait(i, part)) part_issue(i, part);
+                    // one issue block for both quads: every wait / fence / elect / commit round costs the issuing
+                    // warp some hundreds of cycles, about as much as the 32 products themselves
+                    if (part_wait(i, 1) && part_wait(i, 2)) part_issue(i, 1);
                     if (ok && i + 1 < n_tiles && !is_partial(i + 1)) rope_part(i + 1);
                 }
             }
