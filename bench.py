@@ -339,6 +339,7 @@ def run_mla_workload(args):
     """
     from vortex_torch import _cabi
 
+    _cabi.set_mla_path(args.mla_path)
     dev = torch.device("cuda", 0)
     bs, Hq, Dl, Dv, P, ctx, K, bos, eos, L = 128, 16, 576, 512, 64, 16384, 32, 1, 1, (args.layers or 4)
     pages_per_req = ctx // P
@@ -411,6 +412,8 @@ def run_mla_workload(args):
                                 tflops=flops / res["decode_mla"] / 1e12),
                 layer=dict(bytes=cent_b + kv_b, us=(res["indexer"] + res["decode_mla"]) * 1e6,
                            frac=(cent_b + kv_b) / (res["indexer"] + res["decode_mla"]) / 1e9 / peaks["hbm_gbs"]),
+                mla_form="mma.sync + cp.async" if args.mla_path else "tcgen05 + TMA",
+                mla_fault_bits=_cabi.mla_fault_bits(),
                 peak_kind=f"of {kind}")
     print(json.dumps(line))
 
@@ -588,6 +591,8 @@ def main():
     ap.add_argument("--flow", default="block_sparse_attention",
                     choices=["block_sparse_attention", "gqa_block_sparse_attention", "gqa_quest_sparse_attention"],
                     help="which shipped flow selects the pages (the headline line uses the default)")
+    ap.add_argument("--mla-path", type=int, default=0, choices=[0, 1],
+                    help="c5 workload: 0 = tcgen05 + TMA form of the MLA decode (default), 1 = mma.sync + cp.async form")
     ap.add_argument("--workload", default="c2", choices=["c2", "c3", "c5"],
                     help="c2 = the headline decode step; c5 = side measurement of the MLA block-table decode")
     args = ap.parse_args()
