@@ -40,6 +40,7 @@ constexpr int kBlockB = kTile * 128;      // 8 KB: 64 tokens x 64 dims
 constexpr int kQuadB = 4 * kBlockB;       // 32 KB: 256 dims of the values
 constexpr int kQuadSlots = 6;             // a tile holds 2
 constexpr int kRopeSlots = 1;             // read first by the S^T product, so it is free again a tile ahead of its next use
+constexpr int kRopeAhead = 3;             // tiles whose rope block is pulled into L2 ahead of its copy
 constexpr int kQB = kHeads * kDl * 2;     // 18 KB: 9 blocks of 16 heads x 64 dims
 constexpr int kPB = kHeads * kTile * 2;   // 2 KB: 16 heads x 64 tokens
 constexpr int kThreads = 256;            // warps: 0 TMA quads, 1 S^T issue, 2-5 softmax, 6 PV issue, 7 TMA rope
@@ -157,6 +158,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
+}
+
+// the same box fetched into L2 only (no shared-memory slot involved)
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
@@ -314,10 +321,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
             return a.page_table[(int64_t)b * a.pt_stride + page] * a.P + (tok - page * a.P);
         };
         // this lane's box of the tile: the only box (big pages) or box lane % nb
+        // The single rope slot makes "rope part of S^T(i) done -> slot free -> copy of block i + 1 -> rope part of
+        // S^T(i + 1)" a chain with one memory round trip per tile.  Pulling the rope blocks of the next tiles
+        // into L2 ahead of time (8 KB per tile) shortens that round trip from an HBM access to an L2 hit.
+        auto prefetch_rope = [&](int tile) {
+            if (warp != 7 || tile >= n_tiles) return;
+            const int yp = box_row(tile, big_pages ? 0 : lane % nb);
+            if (yp >= 0 && (big_pages ? lane == 0 : lane < nb)) tma_prefetch_2d(&block_map, 8 * kBlockDims, yp);
+            __syncwarp();
+        };
+        for (int t = 1; t <= kRopeAhead; ++t) prefetch_rope(t);
         int y_next = n_tiles > 0 ? box_row(0, big_pages ? 0 : lane % nb) : -1;
         for (int i = 0; i < n_tiles && ok; ++i) {
             const int y = y_next;
             if (i + 1 < n_tiles) y_next = box_row(i + 1, big_pages ? 0 : lane % nb);
+            prefetch_rope(i + 1 + kRopeAhead);
             const int left = ntok - i * kTile;
             const int nload = left >= kTile ? nb : (left + a.box_tok - 1) / a.box_tok;
             const uint32_t block_bytes = (uint32_t)nload * a.box_tok * 128u;
