@@ -45,8 +45,9 @@ constexpr int kQB = kHeads * kDl * 2;     // 18 KB: 9 blocks of 16 heads x 64 di
 constexpr int kPB = kHeads * kTile * 2;   // 2 KB: 16 heads x 64 tokens
 constexpr int kThreads = 256;            // warps: 0 TMA quads, 1 S^T issue, 2-5 softmax, 6 PV issue, 7 TMA rope
 constexpr int kSoftmaxThreads = 128;
-constexpr uint32_t kTmemCols = 256;
-constexpr int kAcc = 4;  // partial S^T accumulators per buffer: k-step j of every block adds into accumulator j
+constexpr uint32_t kTmemCols = 512;
+constexpr int kAcc = 5;  // partial S^T accumulators per buffer: k-step j of every value block adds into accumulator j,
+                         // the rope block (issued by the other MMA warp) into accumulator 4
 constexpr int kSBufs = 3;  // S^T buffers: the rope part of tile i + 1 is issued before the quads of tile i
 constexpr uint32_t kColS = 0, kColO = kSBufs * kAcc * 16;
 constexpr float kLog2e = 1.4426950408889634f;
@@ -291,7 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     if (threadIdx.x == 0) {
         for (int i = 0; i < kQuadSlots; ++i) { mbar_init(bar(kFullQuad + i), 1); mbar_init(bar(kEmptyQuad + i), 1); }
         for (int i = 0; i < kRopeSlots; ++i) { mbar_init(bar(kFullRope + i), 1); mbar_init(bar(kEmptyRope + i), 1); }
-        for (int i = 0; i < kSBufs; ++i) { mbar_init(bar(kSFull + i), 1); mbar_init(bar(kSFree + i), kSoftmaxThreads); }
+        for (int i = 0; i < kSBufs; ++i) { mbar_init(bar(kSFull + i), 2); mbar_init(bar(kSFree + i), kSoftmaxThreads); }
         mbar_init(bar(kPFull), kSoftmaxThreads);
         mbar_init(bar(kODone), 1);
         mbar_init(bar(kFixed), kSoftmaxThreads);
@@ -394,21 +395,24 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 ok = __all_sync(0xffffffffu, ok) != 0;
                 return ok;
             };
-            if (warp == 1) wait_all(kQReady, 0, kFaultQ);
+            wait_all(kQReady, 0, kFaultQ);  // both issuers read q
             // descriptors: constant high part + (byte address >> 4)
             const uint64_t dk = smem_desc(0, 0, 1024), dmn = smem_desc(0, kBlockB, 1024);
             const uint64_t qd = dk + ((base + kOffQ) >> 4), pd = dk + ((base + kOffP) >> 4);
             auto is_partial = [&](int i) { return last_partial && i == n_tiles - 1; };
-            // S^T of tile i into buffer i % 3 is issued in three parts as their data lands: the rope block (4
-            // k-steps, then the commit that releases the rope slot), quad 0 and quad 1 (16 k-steps each, then
-            // the commit that publishes S^T); k-step j of every block goes into accumulator j.  The rope part
-            // of tile i + 1 follows the quads of tile i, so that the single rope slot is free again more than a
-            // tile time before its next block is needed.  A last tile that is not full is ready, as a whole, once the softmax
-            // warps have zeroed its tail; its rope part is not taken ahead.
+            // S^T of tile i goes into buffer i % 3 in two parts, each by its own warp: the two quads (32 k-steps;
+            // k-step j of every block into accumulator j) from warp 1, the rope block (4 k-steps into accumulator
+            // 4, then the commit that releases the rope slot) from warp 6 between its PV products.  Each part
+            // ends with a commit on the buffer's "full" barrier, which expects both.  A last tile that is not
+            // full is ready, as a whole, once the softmax warps have zeroed its tail.
             auto part_wait = [&](int i, int part) {
                 if (is_partial(i)) return wait_all(kFixed, 0, kFaultFixed);
                 if (part == 0) return wait_all(kFullRope + i % kRopeSlots, (i / kRopeSlots) & 1, kFaultFull);
                 return wait_all(kFullQuad + (2 * i + part - 1) % kQuadSlots, ((2 * i + part - 1) / kQuadSlots) & 1, kFaultFull);
+            };
+            // S^T buffer i % 3 was last read by the softmax of tile i - 3
+            auto sbuf_free = [&](int i) {
+                return i < kSBufs || wait_all(kSFree + i % kSBufs, ((i - kSBufs) / kSBufs) & 1, kFaultS);
             };
             auto part_issue = [&](int i, int part) {  // part 0: the rope block; part 1: both quads
                 tc_fence_after();
@@ -423,37 +427,35 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
 #pragma unroll
                                 for (int j = 0; j < 4; ++j)
                                     umma(sd + j * 16, ad + ((blk * kBlockB + j * 32) >> 4),
-                                         qd + (((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, 1u);
+                                         qd + (((4 * u + blk) * 2048 + j * 32) >> 4), kIdescQK, (u | blk) != 0 ? 1u : 0u);
                         }
-                        umma_commit(bar(kSFull + i % kSBufs));
                     } else {
                         const int rslot = i % kRopeSlots;
                         const uint64_t ad = dk + ((base + kOffRope + rslot * kBlockB) >> 4);
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            umma(sd + j * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, 0u);
+                            umma(sd + 4 * 16, ad + ((j * 32) >> 4), qd + ((8 * 2048 + j * 32) >> 4), kIdescQK, j != 0 ? 1u : 0u);
                         umma_commit(bar(kEmptyRope + rslot));
                     }
+                    umma_commit(bar(kSFull + i % kSBufs));  // one of the two arrivals that publish S^T
                 }
                 __syncwarp();
             };
             if (warp == 1) {
-                auto rope_part = [&](int i) {
-                    // S^T buffer i % 3 was last read by the softmax of tile i - 3
-                    if (i >= kSBufs && !wait_all(kSFree + i % kSBufs, ((i - kSBufs) / kSBufs) & 1, kFaultS)) return;
-                    if (part_wait(i, 0)) part_issue(i, 0);
-                };
-                rope_part(0);
-                for (int i = 0; i < n_tiles && ok; ++i) {
-                    if (i > 0 && is_partial(i)) rope_part(i);
-                    // one issue block for both quads: every wait / fence / elect / commit round costs the issuing
-                    // warp some hundreds of cycles, about as much as the 32 products themselves
-                    if (part_wait(i, 1) && part_wait(i, 2)) part_issue(i, 1);
-                    if (ok && i + 1 < n_tiles && !is_partial(i + 1)) rope_part(i + 1);
-                }
+                // one issue block for both quads of a tile: every wait / fence / elect / commit round costs the
+                // issuing warp some hundreds of cycles, about as much as the 32 products themselves
+                for (int i = 0; i < n_tiles && ok; ++i)
+                    if (sbuf_free(i) && part_wait(i, 1) && part_wait(i, 2)) part_issue(i, 1);
             }
+            auto rope_part = [&](int i) {
+                if (sbuf_free(i) && part_wait(i, 0)) part_issue(i, 0);
+            };
+            if (warp == 6) rope_part(0);
             for (int i = 0; i < n_tiles && ok && warp == 6; ++i) {
-                if (!wait_all(kPFull, i & 1, kFaultP)) break;
+                // the next tile's rope part first: its block has been in flight for a tile time, and the sooner
+                // it is consumed the sooner the single rope slot takes the block after it
+                if (i + 1 < n_tiles) rope_part(i + 1);
+                if (!ok || !wait_all(kPFull, i & 1, kFaultP)) break;
                 tc_fence_after();
                 const int slot0 = (2 * i) % kQuadSlots, slot1 = (2 * i + 1) % kQuadSlots;
                 if (elect_one()) {
@@ -540,13 +542,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
                 tc_fence_after();
                 float s[kHeads];
                 {
-                    float part[kAcc][kHeads];  // the four partial sums, one round trip to TMEM
+                    float part[kAcc][kHeads];  // the five partial sums, one round trip to TMEM
 #pragma unroll
                     for (int acc = 0; acc < kAcc; ++acc) tmem_ld16_nowait(tlane + kColS + (buf * kAcc + acc) * 16, part[acc]);
 #pragma unroll
                     for (int acc = 0; acc < kAcc; ++acc) tmem_wait_ld(part[acc]);
 #pragma unroll
-                    for (int h = 0; h < kHeads; ++h) s[h] = (part[0][h] + part[1][h]) + (part[2][h] + part[3][h]);
+                    for (int h = 0; h < kHeads; ++h) s[h] = ((part[0][h] + part[1][h]) + (part[2][h] + part[3][h])) + part[4][h];
                 }
                 tc_fence_before();
                 mbar_arrive(bar(kSFree + buf));
