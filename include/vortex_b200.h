@@ -206,6 +206,21 @@ int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_c
                            int dtype, void* stream);
 
 /*
+ * The same single launch for the gqa_block_sparse_attention flow: page scores are those of
+ * vtx_indexer_gqa_softmax_fused (GeMM -> Softmax(scale = softmax_scale) -> Max over the group's heads,
+ * flow/algorithms.py:281-309) on the same centroid cache; token write and attention as above.
+ */
+int vtx_sparse_layer_fused_gqa_softmax(const void* q, const void* centroids, const void* k_cache,
+                                       const void* v_cache, void* out, const void* new_k, const void* new_v,
+                                       const int64_t* loc, int num_kv_heads, const int32_t* dense_kv_indptr,
+                                       const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                                       int32_t* sparse_kv_indices, const int32_t* kv_last_page_len,
+                                       int eff_batch_size, int group_size, int head_dim, int page_size,
+                                       int topk_val, int page_reserved_bos, int page_reserved_eos,
+                                       int max_num_pages_per_request, float sm_scale, float softmax_scale,
+                                       int dtype, void* stream);
+
+/*
  * Paged grouped-query decode attention over each segment's page list (sparse or dense).
  * Takes the place of the flashinfer paged-decode call the SGLang fork makes on
  * sparse_kv_indptr / sparse_kv_indices / kv_last_page_len (data contract:

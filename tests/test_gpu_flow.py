@@ -209,15 +209,28 @@ def test_host_pipeline_graph_matches_device_path():
         assert torch.equal(got, want), f"host pipeline differs (programmatic_launch={pdl})"
 
 
-def test_gqa_block_sparse_flow_through_runtime():
+@pytest.mark.parametrize("fuse", [True, False])
+def test_gqa_block_sparse_flow_through_runtime(fuse, monkeypatch):
     """The shipped gqa_block_sparse_attention flow (GeMM -> Softmax -> Max -> topK; CMean) run by the
-    runtime: selections bit-exact with the oracle's restatement of that flow, attention within tolerance."""
+    runtime: selections bit-exact with the oracle's restatement of that flow, attention within tolerance.
+    With fusion on, every sparse layer must be ONE launch (token write + selection + attention)."""
+    from vortex_torch import _cabi
     from vortex_torch.flow import build_vflow
+
+    fused_calls = []
+    real = _cabi.sparse_layer_fused
+
+    def counting(*args, **kwargs):
+        fused_calls.append(kwargs.get("gqa_softmax_scale"))
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(_cabi, "sparse_layer_fused", counting)
 
     seq, L, H, G, D, P, K, bos, eos = [2048, 1000, 4096, 300], 2, 8, 2, 128, 16, 30, 1, 1
     prob = vo.make_paged_problem(37, seq, H, G, D, P)
     flow = build_vflow("gqa_block_sparse_attention")
     rt = _runtime(prob, seq, L, H, G, D, P, K, bos, eos, torch.bfloat16, flow=flow)
+    rt.fuse_attention = fuse
     assert flow.output_func._gqa_chain is not None
     for l in range(L):
         for name in ("k", "v", "centroids"):
@@ -232,6 +245,7 @@ def test_gqa_block_sparse_flow_through_runtime():
             [nv] * L, loc.cuda(), outs)
     torch.cuda.synchronize()
     plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)
+    assert fused_calls == ([pytest.approx(0.09)] * (L - 1) if fuse else []), fused_calls
     vo.forward_indexer_gqa(prob["q"], prob["centroids"], plan, K, bos, eos, scale=0.09)
     ns = int(plan["sparse_kv_indptr"][-1])
     np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], plan["sparse_kv_indices"])

@@ -634,17 +634,21 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_quest_kernel(IndexerArgs 
 // gathers before it waits for the preceding launch: those reads touch only the planner's outputs and
 // this layer's centroid rows of non-reserved pages, which no launch between the planner and this one
 // writes.  Everything else (q, the token write, the sparse list, the output) comes after the wait.
-template <int D, int G, bool APPEND, bool EARLY>
+// MODE 0: scores of the block_sparse_attention flow (group mean . centroid); MODE 2: scores of the
+// gqa_block_sparse_attention flow (per-head product, softmax over pages, maximum over heads) on the same
+// centroid cache, so the token write is the same too.
+template <int D, int G, bool APPEND, bool EARLY, int MODE = 0>
 __global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
                                                                   AppendArgs ap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     if (!EARLY) vtx::pdl_wait();
     vtx::pdl_trigger();
     const int seg = blockIdx.x;
-    indexer_body<__nv_bfloat16, D, 0>(ia, smem_raw, seg, [&](int warp, int lane) {
+    auto side = [&](int warp, int lane) {
         if (EARLY) vtx::pdl_wait();
         if (APPEND && warp == kWarps - 1) append_token<D>(ap, seg, lane);
-    });
+    };
+    indexer_body<__nv_bfloat16, D, MODE, decltype(side), (MODE == 2 ? G : 1)>(ia, smem_raw, seg, side);
     __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
     vtxdec::decode_mma_body<G, D>(da, smem_raw, blockIdx.x);
 }
@@ -765,31 +769,33 @@ int launch_indexer_quest(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     return VTX_ERR_UNSUPPORTED;
 }
 
-template <int D, int G>
+template <int D, int G, int MODE>
 int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
                             cudaStream_t st) {
     using Gm = Geom<__nv_bfloat16, D>;
     static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
-    size_t bytes = Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
+    size_t bytes = MODE == 2 ? Gm::ring_bytes + (size_t)G * D * 4 +
+                                   (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + G * sizeof(__nv_bfloat16))
+                             : Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
     const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
     if (dec > bytes) bytes = dec;
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
     const bool early = vtx::programmatic_launch_mode() == 2;
-    auto kern = ap.loc ? (early ? sparse_layer_kernel<D, G, true, true> : sparse_layer_kernel<D, G, true, false>)
-                       : (early ? sparse_layer_kernel<D, G, false, true> : sparse_layer_kernel<D, G, false, false>);
+    auto kern = ap.loc ? (early ? sparse_layer_kernel<D, G, true, true, MODE> : sparse_layer_kernel<D, G, true, false, MODE>)
+                       : (early ? sparse_layer_kernel<D, G, false, true, MODE> : sparse_layer_kernel<D, G, false, false, MODE>);
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
     return vtx::launch(kern, dim3(eff_bs), dim3(kThreads), bytes, st, ia, da, ap);
 }
 
-template <int D>
+template <int D, int MODE>
 int launch_sparse_layer_d(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
                           int group, cudaStream_t st) {
     switch (group) {
-        case 1: return launch_sparse_layer_cfg<D, 1>(ia, da, ap, eff_bs, st);
-        case 2: return launch_sparse_layer_cfg<D, 2>(ia, da, ap, eff_bs, st);
-        case 4: return launch_sparse_layer_cfg<D, 4>(ia, da, ap, eff_bs, st);
-        case 8: return launch_sparse_layer_cfg<D, 8>(ia, da, ap, eff_bs, st);
+        case 1: return launch_sparse_layer_cfg<D, 1, MODE>(ia, da, ap, eff_bs, st);
+        case 2: return launch_sparse_layer_cfg<D, 2, MODE>(ia, da, ap, eff_bs, st);
+        case 4: return launch_sparse_layer_cfg<D, 4, MODE>(ia, da, ap, eff_bs, st);
+        case 8: return launch_sparse_layer_cfg<D, 8, MODE>(ia, da, ap, eff_bs, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
 }
@@ -889,14 +895,15 @@ extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int
                              : launch_indexer<float, 0>(a, eff_batch_size, st);
 }
 
-extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
-                                      void* out, const void* new_k, const void* new_v, const int64_t* loc,
-                                      int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
-                                      const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
-                                      const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
-                                      int head_dim, int page_size, int topk_val, int page_reserved_bos,
-                                      int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
-                                      int dtype, void* stream) {
+namespace {
+int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
+                            void* out, const void* new_k, const void* new_v, const int64_t* loc,
+                            int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                            const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                            const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                            int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                            int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
+                            int dtype, void* stream, int score_mode, float softmax_scale) {
     int rc = check_common(dense_kv_indptr, dense_kv_indices, eff_batch_size, topk_val, page_reserved_bos,
                           page_reserved_eos, max_num_pages_per_request, dtype);
     if (rc != VTX_OK) return rc;
@@ -934,6 +941,7 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
     ia.bos = page_reserved_bos;
     ia.eos = page_reserved_eos;
     ia.key_cap = key_capacity(max_num_pages_per_request);
+    ia.scale = softmax_scale;
     vtxdec::DecodeArgs da;
     da.q = q;
     da.k = k_cache;
@@ -945,11 +953,50 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
     da.P = page_size;
     da.scale_log2 = sm_scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)stream;
+    if (score_mode == 2) {
+        switch (head_dim) {
+            case 64: return launch_sparse_layer_d<64, 2>(ia, da, ap, eff_batch_size, group_size, st);
+            case 128: return launch_sparse_layer_d<128, 2>(ia, da, ap, eff_batch_size, group_size, st);
+            default: return VTX_ERR_UNSUPPORTED;
+        }
+    }
     switch (head_dim) {
-        case 64: return launch_sparse_layer_d<64>(ia, da, ap, eff_batch_size, group_size, st);
-        case 128: return launch_sparse_layer_d<128>(ia, da, ap, eff_batch_size, group_size, st);
+        case 64: return launch_sparse_layer_d<64, 0>(ia, da, ap, eff_batch_size, group_size, st);
+        case 128: return launch_sparse_layer_d<128, 0>(ia, da, ap, eff_batch_size, group_size, st);
         default: return VTX_ERR_UNSUPPORTED;
     }
+}
+}  // namespace
+
+extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
+                                      void* out, const void* new_k, const void* new_v, const int64_t* loc,
+                                      int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                      const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                                      const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                      int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                                      int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
+                                      int dtype, void* stream) {
+    return sparse_layer_fused_impl(q, centroids, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
+                                   dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                                   kv_last_page_len, eff_batch_size, group_size, head_dim, page_size, topk_val,
+                                   page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, dtype,
+                                   stream, 0, 0.f);
+}
+
+extern "C" int vtx_sparse_layer_fused_gqa_softmax(const void* q, const void* centroids, const void* k_cache,
+                                                  const void* v_cache, void* out, const void* new_k, const void* new_v,
+                                                  const int64_t* loc, int num_kv_heads, const int32_t* dense_kv_indptr,
+                                                  const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                                                  int32_t* sparse_kv_indices, const int32_t* kv_last_page_len,
+                                                  int eff_batch_size, int group_size, int head_dim, int page_size,
+                                                  int topk_val, int page_reserved_bos, int page_reserved_eos,
+                                                  int max_num_pages_per_request, float sm_scale, float softmax_scale,
+                                                  int dtype, void* stream) {
+    return sparse_layer_fused_impl(q, centroids, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
+                                   dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                                   kv_last_page_len, eff_batch_size, group_size, head_dim, page_size, topk_val,
+                                   page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, dtype,
+                                   stream, 2, softmax_scale);
 }
 
 extern "C" int vtx_indexer_gqa_softmax_fused(const void* q, const void* centroids, const int32_t* dense_kv_indptr,

@@ -38,7 +38,8 @@ class Context(ContextBase):
 
     # ---- deferred page selection (fusion of the indexer with the attention that follows it) ----
     def defer_indexer(self, enable: bool) -> None:
-        """When enabled, a fused ``q.mean -> GeMV -> topK`` chain is recorded instead of launched, so that
+        """When enabled, a fused ``q.mean -> GeMV -> topK`` (or ``GeMM -> Softmax -> Max -> topK``) chain is
+        recorded instead of launched, so that
         the caller's attention step can run selection and attention as one kernel.  The caller must call
         ``take_pending_indexer`` or ``flush_indexer`` before anything reads the sparse page list."""
         self.flush_indexer()
@@ -54,10 +55,17 @@ class Context(ContextBase):
             from .. import _cabi, _deferred
 
             _deferred.flush_all()
-            q, y, o = pend
-            _cabi.indexer_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr, self.dense_kv_indices, o,
-                                self.batch_size * self.num_kv_heads, self.topk_val, self.page_reserved_bos,
-                                self.page_reserved_eos, self.max_num_pages_per_request)
+            q, y, o = pend[:3]
+            eff_bs = self.batch_size * self.num_kv_heads
+            if len(pend) == 4:  # the gqa_block_sparse_attention chain with its softmax scale
+                _cabi.indexer_gqa_softmax_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr,
+                                                self.dense_kv_indices, o, eff_bs, self.topk_val,
+                                                self.page_reserved_bos, self.page_reserved_eos,
+                                                self.max_num_pages_per_request, pend[3])
+            else:
+                _cabi.indexer_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr, self.dense_kv_indices, o,
+                                    eff_bs, self.topk_val, self.page_reserved_bos, self.page_reserved_eos,
+                                    self.max_num_pages_per_request)
 
     def set_batch_size(self, n: int) -> None:
         self.batch_size = n

@@ -88,6 +88,10 @@ class topK(vOp):
                 op._require_fused(type(op).__name__)
             q, y = gemm._pending
             gemm._pending = None
+            if getattr(ctx, "_defer_indexer", False):
+                ctx.flush_indexer()
+                ctx._pending_indexer = (q, y, o, float(softmax.scale))  # the runtime's attention launch picks it up
+                return o
             _deferred.flush_all()
             _cabi.indexer_gqa_softmax_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
                                             o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,

@@ -157,7 +157,8 @@ class VortexDecodeRuntime:
         cache = self.pool.buffers[layer]
         pend = self.ictx.take_pending_indexer()
         if pend is not None:
-            pq, py, po = pend
+            pq, py, po = pend[:3]
+            gqa_scale = pend[3] if len(pend) == 4 else None
             if (sparse and self.dtype == torch.bfloat16 and self.D in (64, 128) and self.G in (1, 2, 4, 8)
                     and pq.data_ptr() == q.data_ptr() and pq.shape[1] == self.G
                     and po.data_ptr() == b.kv_indices_decode[1].data_ptr()):
@@ -181,7 +182,8 @@ class VortexDecodeRuntime:
                                              b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
                                              b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
                                              self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
-                                             self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc)
+                                             self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc,
+                                             gqa_softmax_scale=gqa_scale)
                 finally:
                     if early:
                         _cabi.set_programmatic_launch(1)
