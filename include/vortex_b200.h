@@ -221,6 +221,21 @@ int vtx_sparse_layer_fused_gqa_softmax(const void* q, const void* centroids, con
                                        int dtype, void* stream);
 
 /*
+ * The same single launch for the gqa_quest_sparse_attention flow: page scores are those of
+ * vtx_indexer_quest_fused from the per-page maximum and minimum caches (flow/algorithms.py:411-451); with
+ * new_k / new_v / loc set, the launch writes the new token and, for a page it closes, that page's row of
+ * both caches (what the flow's cache Max and Min operators compute, flow/algorithms.py:453-496).
+ */
+int vtx_sparse_layer_fused_quest(const void* q, const void* cache_max, const void* cache_min, const void* k_cache,
+                                 const void* v_cache, void* out, const void* new_k, const void* new_v,
+                                 const int64_t* loc, int num_kv_heads, const int32_t* dense_kv_indptr,
+                                 const int32_t* sparse_kv_indptr, const int32_t* dense_kv_indices,
+                                 int32_t* sparse_kv_indices, const int32_t* kv_last_page_len, int eff_batch_size,
+                                 int group_size, int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                                 int page_reserved_eos, int max_num_pages_per_request, float sm_scale, int dtype,
+                                 void* stream);
+
+/*
  * Paged grouped-query decode attention over each segment's page list (sparse or dense).
  * Takes the place of the flashinfer paged-decode call the SGLang fork makes on
  * sparse_kv_indptr / sparse_kv_indices / kv_last_page_len (data contract:

@@ -255,10 +255,22 @@ def test_gqa_block_sparse_flow_through_runtime(fuse, monkeypatch):
     assert bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
 
 
-def test_gqa_quest_flow_through_runtime():
+@pytest.mark.parametrize("fuse", [True, False])
+def test_gqa_quest_flow_through_runtime(fuse, monkeypatch):
     """The shipped gqa_quest_sparse_attention flow (CMax/CMin caches; Multiply x2 -> Maximum -> Sum -> Max ->
-    topK) run by the runtime: envelopes of the page the step closes exact, selections bit-exact with the oracle."""
+    topK) run by the runtime: envelopes of the page the step closes exact, selections bit-exact with the oracle.
+    With fusion on, every sparse layer must be ONE launch (token write + both envelopes + selection + attention)."""
+    from vortex_torch import _cabi
     from vortex_torch.flow import build_vflow
+
+    fused_calls = []
+    real = _cabi.sparse_layer_fused
+
+    def counting(*args, **kwargs):
+        fused_calls.append((kwargs.get("quest_min") is not None, kwargs.get("new_k") is not None or len(args) > 17))
+        return real(*args, **kwargs)
+
+    monkeypatch.setattr(_cabi, "sparse_layer_fused", counting)
 
     seq, L, H, G, D, P, K, bos, eos = [2048, 1000, 4096, 300], 2, 8, 2, 128, 16, 30, 1, 1
     prob = vo.make_paged_problem(38, seq, H, G, D, P)
@@ -266,6 +278,7 @@ def test_gqa_quest_flow_through_runtime():
     cmax, cmin = kf.max(1, keepdim=True).values.bfloat16(), kf.min(1, keepdim=True).values.bfloat16()
     flow = build_vflow("gqa_quest_sparse_attention")
     rt = _runtime(prob, seq, L, H, G, D, P, K, bos, eos, torch.bfloat16, flow=flow)
+    rt.fuse_attention = fuse
     assert flow.output_func._quest_chain is not None
     bs = len(seq)
     loc = torch.as_tensor([int(prob["req_to_token"][r, seq[r] - 1]) for r in range(bs)], dtype=torch.int64)
@@ -282,6 +295,7 @@ def test_gqa_quest_flow_through_runtime():
     rt.step(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda(), [q] * L, [nk] * L,
             [nv] * L, loc.cuda(), outs)
     torch.cuda.synchronize()
+    assert fused_calls == ([(True, True)] * (L - 1) if fuse else []), fused_calls
     assert torch.equal(rt.pool.buffers[1]["max"].cpu()[closing_rows], cmax[closing_rows])
     assert torch.equal(rt.pool.buffers[1]["min"].cpu()[closing_rows], cmin[closing_rows])
     plan = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, bos, eos, 64, 16)

@@ -318,7 +318,8 @@ struct Geom {
 struct AppendArgs {
     __nv_bfloat16* k_cache;
     __nv_bfloat16* v_cache;
-    __nv_bfloat16* centroids;
+    __nv_bfloat16* centroids;    // page mean of K; with QUEST: per-dim page maximum
+    __nv_bfloat16* centroids2;   // QUEST only: per-dim page minimum
     const __nv_bfloat16* new_k;  // [bs, H, D]
     const __nv_bfloat16* new_v;
     const int64_t* loc;          // [bs]
@@ -328,7 +329,8 @@ struct AppendArgs {
 // Executed by one warp: lanes 0 .. D/8-1 each own 8 head dims of segment s = request * H + head.
 // Writes the new token's K and V rows and, if the token closes its page, the page's mean of K
 // (rows 0 .. P-2 from the cache in ascending order, the new row last, one division, one rounding).
-template <int D>
+// QUEST: the page's per-dim maximum and minimum instead (both exact in bf16), as vtx_creduce computes them.
+template <int D, bool QUEST = false>
 __device__ __forceinline__ void append_token(const AppendArgs& ap, const int s, const int lane) {
     constexpr int NCH = D / 8;
     if (lane >= NCH) return;
@@ -346,6 +348,29 @@ __device__ __forceinline__ void append_token(const AppendArgs& ap, const int s, 
     if (tok != ap.P - 1) return;
     float acc[8], kf[8];
     nk.unpack(kf);
+    if (QUEST) {
+        float hi[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hi[j] = lo[j] = kf[j];
+        for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
+            vtx::Vec8<__nv_bfloat16> v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
+                else v[u].raw = nk.raw;  // repeats the new row: neutral for max and min
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float f[8];
+                v[u].unpack(f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { hi[j] = fmaxf(hi[j], f[j]); lo[j] = fminf(lo[j], f[j]); }
+            }
+        }
+        vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, hi);
+        vtx::store8(ap.centroids2 + pid * (int64_t)D + lane * 8, lo);
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
@@ -636,9 +661,11 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_quest_kernel(IndexerArgs 
 // writes.  Everything else (q, the token write, the sparse list, the output) comes after the wait.
 // MODE 0: scores of the block_sparse_attention flow (group mean . centroid); MODE 2: scores of the
 // gqa_block_sparse_attention flow (per-head product, softmax over pages, maximum over heads) on the same
-// centroid cache, so the token write is the same too.
+// centroid cache, so the token write is the same too; MODE 3: scores of the gqa_quest_sparse_attention flow
+// from the per-page maximum and minimum caches, which the token write then maintains instead of the mean
+// (twice the summary bytes per page: two CTAs per SM instead of four).
 template <int D, int G, bool APPEND, bool EARLY, int MODE = 0>
-__global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
+__global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
                                                                   AppendArgs ap) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     if (!EARLY) vtx::pdl_wait();
@@ -646,9 +673,9 @@ __global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs i
     const int seg = blockIdx.x;
     auto side = [&](int warp, int lane) {
         if (EARLY) vtx::pdl_wait();
-        if (APPEND && warp == kWarps - 1) append_token<D>(ap, seg, lane);
+        if (APPEND && warp == kWarps - 1) append_token<D, MODE == 3>(ap, seg, lane);
     };
-    indexer_body<__nv_bfloat16, D, MODE, decltype(side), (MODE == 2 ? G : 1)>(ia, smem_raw, seg, side);
+    indexer_body<__nv_bfloat16, D, MODE, decltype(side), (MODE >= 2 ? G : 1)>(ia, smem_raw, seg, side);
     __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
     vtxdec::decode_mma_body<G, D>(da, smem_raw, blockIdx.x);
 }
@@ -774,9 +801,13 @@ int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da,
                             cudaStream_t st) {
     using Gm = Geom<__nv_bfloat16, D>;
     static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
+    constexpr int quest_slot_b = 2 * Gm::slot_bytes;
+    constexpr int quest_slots = quest_slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2;
     size_t bytes = MODE == 2 ? Gm::ring_bytes + (size_t)G * D * 4 +
                                    (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + G * sizeof(__nv_bfloat16))
-                             : Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
+                   : MODE == 3 ? (size_t)kWarps * quest_slots * quest_slot_b + (size_t)G * D * 2 +
+                                     (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t))
+                               : Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
     const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
     if (dec > bytes) bytes = dec;
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
@@ -896,7 +927,8 @@ extern "C" int vtx_indexer_fused(const void* q, const void* centroids, const int
 }
 
 namespace {
-int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_cache, const void* v_cache,
+int sparse_layer_fused_impl(const void* q, const void* centroids, const void* centroids2, const void* k_cache,
+                            const void* v_cache,
                             void* out, const void* new_k, const void* new_v, const int64_t* loc,
                             int num_kv_heads, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
                             const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
@@ -922,6 +954,7 @@ int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_
         ap.k_cache = (__nv_bfloat16*)const_cast<void*>(k_cache);
         ap.v_cache = (__nv_bfloat16*)const_cast<void*>(v_cache);
         ap.centroids = (__nv_bfloat16*)const_cast<void*>(centroids);
+        ap.centroids2 = (__nv_bfloat16*)const_cast<void*>(centroids2);
         ap.new_k = (const __nv_bfloat16*)new_k;
         ap.new_v = (const __nv_bfloat16*)new_v;
         ap.loc = loc;
@@ -931,6 +964,7 @@ int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_
     IndexerArgs ia{};
     ia.q = q;
     ia.centroids = centroids;
+    ia.centroids2 = centroids2;
     ia.dense_indptr = dense_kv_indptr;
     ia.sparse_indptr = sparse_kv_indptr;
     ia.dense_indices = dense_kv_indices;
@@ -942,6 +976,7 @@ int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_
     ia.eos = page_reserved_eos;
     ia.key_cap = key_capacity(max_num_pages_per_request);
     ia.scale = softmax_scale;
+    if (score_mode == 3 && !centroids2) return VTX_ERR_INVALID_ARGUMENT;
     vtxdec::DecodeArgs da;
     da.q = q;
     da.k = k_cache;
@@ -953,6 +988,13 @@ int sparse_layer_fused_impl(const void* q, const void* centroids, const void* k_
     da.P = page_size;
     da.scale_log2 = sm_scale * 1.4426950408889634f;
     cudaStream_t st = (cudaStream_t)stream;
+    if (score_mode == 3) {
+        switch (head_dim) {
+            case 64: return launch_sparse_layer_d<64, 3>(ia, da, ap, eff_batch_size, group_size, st);
+            case 128: return launch_sparse_layer_d<128, 3>(ia, da, ap, eff_batch_size, group_size, st);
+            default: return VTX_ERR_UNSUPPORTED;
+        }
+    }
     if (score_mode == 2) {
         switch (head_dim) {
             case 64: return launch_sparse_layer_d<64, 2>(ia, da, ap, eff_batch_size, group_size, st);
@@ -976,11 +1018,27 @@ extern "C" int vtx_sparse_layer_fused(const void* q, const void* centroids, cons
                                       int head_dim, int page_size, int topk_val, int page_reserved_bos,
                                       int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
                                       int dtype, void* stream) {
-    return sparse_layer_fused_impl(q, centroids, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
+    return sparse_layer_fused_impl(q, centroids, nullptr, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
                                    dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
                                    kv_last_page_len, eff_batch_size, group_size, head_dim, page_size, topk_val,
                                    page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, dtype,
                                    stream, 0, 0.f);
+}
+
+extern "C" int vtx_sparse_layer_fused_quest(const void* q, const void* cache_max, const void* cache_min,
+                                            const void* k_cache, const void* v_cache, void* out, const void* new_k,
+                                            const void* new_v, const int64_t* loc, int num_kv_heads,
+                                            const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                            const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                                            const int32_t* kv_last_page_len, int eff_batch_size, int group_size,
+                                            int head_dim, int page_size, int topk_val, int page_reserved_bos,
+                                            int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
+                                            int dtype, void* stream) {
+    return sparse_layer_fused_impl(q, cache_max, cache_min, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
+                                   dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                                   kv_last_page_len, eff_batch_size, group_size, head_dim, page_size, topk_val,
+                                   page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, dtype,
+                                   stream, 3, 0.f);
 }
 
 extern "C" int vtx_sparse_layer_fused_gqa_softmax(const void* q, const void* centroids, const void* k_cache,
@@ -992,7 +1050,7 @@ extern "C" int vtx_sparse_layer_fused_gqa_softmax(const void* q, const void* cen
                                                   int topk_val, int page_reserved_bos, int page_reserved_eos,
                                                   int max_num_pages_per_request, float sm_scale, float softmax_scale,
                                                   int dtype, void* stream) {
-    return sparse_layer_fused_impl(q, centroids, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
+    return sparse_layer_fused_impl(q, centroids, nullptr, k_cache, v_cache, out, new_k, new_v, loc, num_kv_heads,
                                    dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
                                    kv_last_page_len, eff_batch_size, group_size, head_dim, page_size, topk_val,
                                    page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, dtype,

@@ -41,6 +41,7 @@ SIGNATURES = {
     "vtx_indexer_gqa_softmax_fused": [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "vtx_sparse_layer_fused": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_sparse_layer_fused_gqa_softmax": [_p] * 8 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _f, _i, _p],
+    "vtx_sparse_layer_fused_quest": [_p] * 9 + [_i] + [_p] * 5 + [_i] * 8 + [_f, _i, _p],
     "vtx_decode_gqa": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p],
     "vtx_decode_gqa_splitkv": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _p, _i64, _i, _p],
     "vtx_decode_gqa_splitkv_noalloc": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _f, _i, _i, _p],
@@ -252,12 +253,14 @@ def mla_fault_bits() -> int:
 def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
                        sparse_kv_indices, kv_last_page_len, eff_bs, page_size, topk_val, bos, eos,
                        max_pages_per_request, sm_scale, new_k=None, new_v=None, loc=None,
-                       gqa_softmax_scale=None) -> None:
+                       gqa_softmax_scale=None, quest_min=None) -> None:
     """Page selection and attention over the selected pages in one launch (bf16); with ``new_k``,
     ``new_v`` ``[bs, H, D]`` and ``loc`` ``[bs]`` the launch also writes the new token and the centroid
     of the page it closes.  ``gqa_softmax_scale`` set: page scores of the gqa_block_sparse_attention
     flow (per-head product, softmax over pages with that scale, maximum over heads) instead of the
-    group-mean product."""
+    group-mean product.  ``quest_min`` set: page scores of the gqa_quest_sparse_attention flow with
+    ``centroids`` as the per-page maximum cache and ``quest_min`` as the minimum cache (both are what a
+    token write then maintains)."""
     if not (q.dtype == centroids.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("sparse_layer_fused: q, centroids, caches and out must share a dtype")
     H = 0
@@ -266,6 +269,14 @@ def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, spa
         H = new_k.shape[1]
         if new_k.dtype != q.dtype or new_v.dtype != q.dtype:
             raise TypeError("sparse_layer_fused: new_k/new_v must have q's dtype")
+    if quest_min is not None:
+        rc = lib.vtx_sparse_layer_fused_quest(
+            ptr(q), ptr(centroids), ptr(quest_min), ptr(k_cache), ptr(v_cache), ptr(out), ptr(new_k), ptr(new_v),
+            ptr(loc), H, ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indices),
+            ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size), int(topk_val), int(bos),
+            int(eos), int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))
+        check(rc, "vtx_sparse_layer_fused_quest")
+        return
     if gqa_softmax_scale is not None:
         rc = lib.vtx_sparse_layer_fused_gqa_softmax(
             ptr(q), ptr(centroids), ptr(k_cache), ptr(v_cache), ptr(out), ptr(new_k), ptr(new_v), ptr(loc), H,

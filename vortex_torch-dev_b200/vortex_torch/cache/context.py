@@ -41,6 +41,15 @@ class Context(ContextBase):
         if pend is not None:
             from .. import _cabi
 
+            if len(pend) == 8:  # token write + page maximum [+ page minimum] of the quest flow
+                from .set_kv import set_kv_buffer_launcher
+
+                k_cache, v_cache, new_k, new_v, cmax, cmin, loc, P = pend
+                set_kv_buffer_launcher(k_cache, v_cache, new_k, new_v, loc, P)
+                _cabi.creduce(k_cache, cmax, loc, self.head_num, self.page_size, 1)
+                if cmin is not None:
+                    _cabi.creduce(k_cache, cmin, loc, self.head_num, self.page_size, 2)
+                return
             k_cache, v_cache, new_k, new_v, centroids, loc, P = pend
             _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, P)
 

@@ -54,7 +54,13 @@ class Reduce(vOp):
     def execute(self, x: torch.Tensor, output: Optional[torch.Tensor], loc: torch.Tensor,
                 ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}called before profile() (impl is None)"
-        if getattr(ctx, "_pending_append", None) is not None:
+        pa = getattr(ctx, "_pending_append", None)
+        if pa is not None:
+            if (len(pa) == 8 and pa[5] is None and self.reduce_type == ReduceType.Min
+                    and x.data_ptr() == pa[0].data_ptr() and loc.data_ptr() == pa[6].data_ptr()):
+                # second half of a recorded "token write + page maximum + page minimum"
+                ctx._pending_append = pa[:5] + (output,) + pa[6:]
+                return output
             ctx.flush_append()
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
@@ -70,6 +76,15 @@ class Reduce(vOp):
                     ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, loc, P)
                     return output
                 _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, output, loc, P)
+                return output
+            if (single and self.reduce_type == ReduceType.Max and getattr(ctx, "_defer_append", False)
+                    and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
+                    and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
+                    and new_k.shape[1] == ctx.head_num):
+                # the quest flow's cache side: token write + Max now, the Min that follows completes the record
+                ctx._pending_kv = None
+                ctx.flush_append()
+                ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, None, loc, P)
                 return output
             ctx.flush_kv_write()
         if self.reduce_type == ReduceType.Mean:

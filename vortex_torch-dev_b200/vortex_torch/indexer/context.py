@@ -57,7 +57,11 @@ class Context(ContextBase):
             _deferred.flush_all()
             q, y, o = pend[:3]
             eff_bs = self.batch_size * self.num_kv_heads
-            if len(pend) == 4:  # the gqa_block_sparse_attention chain with its softmax scale
+            if len(pend) == 4 and isinstance(pend[3], torch.Tensor):  # the quest chain with its second cache
+                _cabi.indexer_quest_fused(q, y, pend[3], self.dense_kv_indptr, self.sparse_kv_indptr,
+                                          self.dense_kv_indices, o, eff_bs, self.topk_val, self.page_reserved_bos,
+                                          self.page_reserved_eos, self.max_num_pages_per_request)
+            elif len(pend) == 4:  # the gqa_block_sparse_attention chain with its softmax scale
                 _cabi.indexer_gqa_softmax_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr,
                                                 self.dense_kv_indices, o, eff_bs, self.topk_val,
                                                 self.page_reserved_bos, self.page_reserved_eos,

@@ -77,6 +77,10 @@ class topK(vOp):
             mul_a._pending = mul_b._pending = None
             if qa.data_ptr() != qb.data_ptr():
                 raise NotImplementedError("topK: the two Multiply operators of the quest chain must share their query")
+            if getattr(ctx, "_defer_indexer", False):
+                ctx.flush_indexer()
+                ctx._pending_indexer = (qa, ya, o, yb)  # the runtime's attention launch picks it up
+                return o
             _deferred.flush_all()
             _cabi.indexer_quest_fused(qa, ya, yb, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o,
                                       eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,

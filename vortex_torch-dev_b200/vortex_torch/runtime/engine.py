@@ -158,32 +158,43 @@ class VortexDecodeRuntime:
         pend = self.ictx.take_pending_indexer()
         if pend is not None:
             pq, py, po = pend[:3]
-            gqa_scale = pend[3] if len(pend) == 4 else None
+            extra = pend[3] if len(pend) == 4 else None
+            quest_other = extra if isinstance(extra, torch.Tensor) else None  # second summary cache of the quest chain
+            gqa_scale = extra if extra is not None and quest_other is None else None
             if (sparse and self.dtype == torch.bfloat16 and self.D in (64, 128) and self.G in (1, 2, 4, 8)
                     and pq.data_ptr() == q.data_ptr() and pq.shape[1] == self.G
                     and po.data_ptr() == b.kv_indices_decode[1].data_ptr()):
                 # new-token write (if it is still pending), selection and attention of this layer in one launch
                 app = self.cctx.take_pending_append()
                 nk = nv = loc = None
+                cmax, cmin = py, quest_other
                 if app is not None:
-                    ak, av, nk, nv, ac, loc, aP = app
+                    if len(app) == 8:  # token write + page maximum + page minimum (quest flow)
+                        ak, av, nk, nv, ac, ac2, loc, aP = app
+                        ptrs = {py.data_ptr(), quest_other.data_ptr()} if quest_other is not None else set()
+                        caches_ok = ac2 is not None and {ac.data_ptr(), ac2.data_ptr()} == ptrs and len(ptrs) == 2
+                        cmax, cmin = ac, ac2
+                    else:
+                        ak, av, nk, nv, ac, loc, aP = app
+                        caches_ok = quest_other is None and ac.data_ptr() == py.data_ptr()
                     if not (ak.data_ptr() == cache["k"].data_ptr() and av.data_ptr() == cache["v"].data_ptr()
-                            and ac.data_ptr() == py.data_ptr() and aP == self.P and nk.shape[0] == self.ictx.batch_size
+                            and caches_ok and aP == self.P and nk.shape[0] == self.ictx.batch_size
                             and nk.shape[1] == self.H and self.ictx.page_reserved_eos >= 1):
                         self.cctx._pending_append = app
                         self.cctx.flush_append()
                         nk = nv = loc = None
+                        cmax, cmin = py, quest_other
                 # the early prologue reads the planner's outputs: allowed once another launch separates us from it
                 early = self.pdl_mode == 2 and self._launches_since_plan >= 1
                 if early:
                     _cabi.set_programmatic_launch(2)
                 try:
-                    _cabi.sparse_layer_fused(q, py, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
+                    _cabi.sparse_layer_fused(q, cmax, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
                                              b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
                                              b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
                                              self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
                                              self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc,
-                                             gqa_softmax_scale=gqa_scale)
+                                             gqa_softmax_scale=gqa_scale, quest_min=cmin)
                 finally:
                     if early:
                         _cabi.set_programmatic_launch(1)
