@@ -89,3 +89,40 @@ def test_config2_layer_properties_at_full_batch():
     rest_max = torch.where(mask, sc, torch.full_like(sc, -float("inf"))).max(dim=1).values
     assert bool((rest_max <= chosen_sc[:, -1]).all())
     assert torch.isfinite(out_a.float()).all()
+
+
+def test_config5_mla_full_batch_two_forms_and_properties():
+    """Config-5 size (bs128, 34 pages of 64 tokens per request out of a 16384-token context): the tcgen05
+    and the mma.sync forms of the MLA decode are independent implementations and must agree; plus two
+    properties of attention that need no oracle: permuting a request's page list leaves the output unchanged,
+    and a request whose pages all hold one repeated latent row returns that row's first 512 dims."""
+    bs, Hq, Dl, Dv, P, npg = 128, 16, 576, 512, 64, 34
+    g = torch.Generator(device="cuda").manual_seed(55)
+    pool = bs * 64
+    cache = torch.randn(pool, P, Dl, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    table = torch.stack([torch.randperm(pool, generator=g, device="cuda")[:npg] for _ in range(bs)]).int()
+    lens = torch.full((bs,), npg * P, dtype=torch.int32, device="cuda")
+    lens[1] = npg * P - 37  # one ragged request
+    const_row = torch.randn(Dl, generator=g, device="cuda").bfloat16()
+    cache[table[0].long()] = const_row  # request 0 attends to one repeated row
+    q = torch.randn(bs, Hq, Dl, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    scale = 1.0 / math.sqrt(192.0)
+    outs = {}
+    for path in (0, 1):
+        out = torch.empty(bs, Hq, Dv, dtype=torch.bfloat16, device="cuda")
+        old = _cabi.set_mla_path(path)
+        try:
+            _cabi.decode_mla(q, cache, out, table, lens, P, scale)
+        finally:
+            _cabi.set_mla_path(old)
+        outs[path] = out.float()
+    assert _cabi.mla_fault_bits() == 0
+    a, b = outs[0], outs[1]
+    assert bool(((a - b).abs() <= 2e-2 * b.abs().clamp(min=1)).all()), f"forms differ by {(a - b).abs().max()}"
+    assert bool(((a[0] - const_row[:Dv].float()).abs() <= 2e-2).all())
+    perm = torch.randperm(npg, generator=g, device="cuda")
+    table2 = table.clone()
+    table2[2:] = table[2:, perm]  # full requests only: the ragged one keeps its last page last
+    out2 = torch.empty(bs, Hq, Dv, dtype=torch.bfloat16, device="cuda")
+    _cabi.decode_mla(q, cache, out2, table2, lens, P, scale)
+    assert bool(((out2.float() - a).abs() <= 2e-2 * a.abs().clamp(min=1)).all())
