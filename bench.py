@@ -387,8 +387,12 @@ def run_mla_workload(args):
         fn()
         torch.cuda.synchronize(dev)
         gr = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gr):
-            fn()
+        _cabi.set_programmatic_launch(1 if args.pdl else 0)  # launches of the graph chained as in the headline step
+        try:
+            with torch.cuda.graph(gr):
+                fn()
+        finally:
+            _cabi.set_programmatic_launch(0)
         for _ in range(3):
             gr.replay()
         torch.cuda.synchronize(dev)
@@ -413,6 +417,7 @@ def run_mla_workload(args):
                 layer=dict(bytes=cent_b + kv_b, us=(res["indexer"] + res["decode_mla"]) * 1e6,
                            frac=(cent_b + kv_b) / (res["indexer"] + res["decode_mla"]) / 1e9 / peaks["hbm_gbs"]),
                 mla_form="mma.sync + cp.async" if args.mla_path else "tcgen05 + TMA",
+                programmatic_launch=1 if args.pdl else 0,
                 mla_fault_bits=_cabi.mla_fault_bits(),
                 peak_kind=f"of {kind}")
     print(json.dumps(line))

@@ -272,7 +272,8 @@ enum : unsigned { kFaultEmpty = 1, kFaultFull = 2, kFaultS = 4, kFaultP = 8, kFa
 __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap quad_map,
                                                                          const __grid_constant__ CUtensorMap block_map) {
     extern __shared__ unsigned char smem_unaligned[];
-    vtx::pdl_wait();
+    // Under programmatic dependent launch the set-up below (barriers, TMEM) touches nothing the preceding
+    // launch could still be writing, so it runs ahead of the wait; every global access comes after it.
     vtx::pdl_trigger();
 
     const uint32_t raw = (uint32_t)__cvta_generic_to_shared(smem_unaligned);
@@ -285,9 +286,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
 
     const int b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntok = a.seqlens[b];
-    const int n_tiles = (ntok + kTile - 1) / kTile;
-    const bool last_partial = (ntok % kTile) != 0;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kQuadSlots; ++i) { mbar_init(bar(kFullQuad + i), 1); mbar_init(bar(kEmptyQuad + i), 1); }
@@ -305,6 +303,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    vtx::pdl_wait();
+    const int ntok = a.seqlens[b];
+    const int n_tiles = (ntok + kTile - 1) / kTile;
+    const bool last_partial = (ntok % kTile) != 0;
 
     if (warp == 0 || warp == 7) {
         // ================================================= TMA producers.  Three units per tile: rope (block 8), quad 0
