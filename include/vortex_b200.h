@@ -312,6 +312,18 @@ void* vtx_mla_fault_word(void);
 int vtx_mla_fault_read(uint32_t* host_bits);
 
 /*
+ * Unary elementwise operators on a RAGGED indexer tensor (x, out: [max_rows, inner_size] bf16, the first
+ * *packed_row_count rows are processed; packed_row_count is a device pointer, normally
+ * &dense_kv_indptr[eff_batch_size]).  Replaces elementwise_rr_kernel
+ * (indexer/triton_kernels/elementwise_impl.py:8-114) behind Relu / Sigmoid / Silu / Abs / Add_Mul
+ * (indexer/elementwise.py:158-297).  op: 0 x >= alpha ? x : beta; 1 1/(1+exp(beta x+alpha));
+ * 2 x/(1+exp(beta x+alpha)); 3 |beta x+alpha|; 4 beta x+alpha.  alpha and beta are rounded to bf16 first,
+ * every bf16 operation rounds once, the logistic forms use a fixed fp32 exp.  x and out 16-byte aligned.
+ */
+int vtx_elementwise(const void* x, void* out, const int32_t* packed_row_count, int64_t max_rows,
+                    int inner_size, int op, float alpha, float beta, int dtype, void* stream);
+
+/*
  * Prefill planner.  Replaces `sglang_plan_prefill` (csrc/register.h, csrc/utils_sglang.cu:462-621).
  * cached_seq_lens, input_seq_lens [bs] i32; outputs dense_kv_indptr, qo_indptr_paged [bs*H + 1],
  * qo_indptr_ragged [bs + 1], dense_kv_indices (packed row ids), kv_last_page_len [bs*H],

@@ -477,6 +477,38 @@ def exp_canonical(x: np.ndarray) -> np.ndarray:
     return np.where(x < f(-87.0), f(0.0), p * scale).astype(f)
 
 
+def elementwise(x: torch.Tensor, op: int, alpha: float, beta: float) -> torch.Tensor:
+    """Unary elementwise operators of the indexer on bf16 values (indexer/triton_kernels/elementwise_impl.py:
+    62-104; op numbering of utils.py ElementwiseOpType: 0 relu form, 1 sigmoid, 2 silu, 3 abs, 4 add_mul).
+
+    alpha and beta are rounded to bf16 first; every bf16 operation rounds once
+    (z = bf16(bf16(beta * x) + alpha)); the logistic forms compute 1 / (1 + exp(z)) resp. x / (1 + exp(z)) in
+    fp32 with `exp_canonical` (+inf above 88) and round once.  The reference leaves the rounding of
+    beta * x + alpha and its exp to the Triton compiler: parity unpinned for ops 1, 2 and for op 3 / 4 with
+    beta != 1; ops 0 and the default Abs are exact in any order.
+    """
+    assert x.dtype == torch.bfloat16
+    f = np.float32
+    a = f(torch.tensor(alpha).bfloat16().float().item())
+    b = f(torch.tensor(beta).bfloat16().float().item())
+    xv = x.float().numpy().astype(f)
+    if op == 0:
+        out = np.where(xv >= a, xv, b)
+    else:
+        z = torch.from_numpy(b * xv).bfloat16().float().numpy()
+        z = torch.from_numpy(z + a).bfloat16().float().numpy()
+        if op in (1, 2):
+            with np.errstate(over="ignore", invalid="ignore"):
+                e = np.where(z > f(88.0), f(np.inf), exp_canonical(np.minimum(z, f(88.0))))
+                num = f(1.0) if op == 1 else xv
+                out = (num / (f(1.0) + e)).astype(f)
+        elif op == 3:
+            out = np.abs(z)
+        else:
+            out = z
+    return torch.from_numpy(np.asarray(out, dtype=f)).bfloat16()
+
+
 def canonical_sum128(v: np.ndarray) -> np.float32:
     """Sum of a vector in the order the kernels use: 128 partial sums (element i goes to partial i % 128,
     added in ascending i from +0.0), then folded in halves v[j] += v[j + w], w = 64 .. 1."""

@@ -306,3 +306,69 @@ def test_gqa_quest_flow_through_runtime(fuse, monkeypatch):
                          plan["kv_last_page_len"])
     got = outs[1].view(bs * H, G, D).float().cpu()
     assert bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
+
+
+@pytest.mark.parametrize("op,alpha,beta", [(0, 0.0, 0.0), (0, 0.5, -2.0), (1, 0.0, -1.0), (1, 0.3, 0.7), (2, 0.0, -1.0),
+                                           (3, 0.0, 1.0), (3, 0.7, -1.3), (4, 1.5, 0.3)])
+def test_elementwise_kernel_matches_oracle(op, alpha, beta):
+    """vtx_elementwise on the packed rows of a RAGGED tensor: bit-exact with the oracle, rows past the packed
+    count untouched, odd element counts (tail path) included."""
+    from vortex_torch import _cabi
+
+    g = torch.Generator().manual_seed(5 + op)
+    for S, C, D, rows in ((4096, 1, 1, 3001), (1024, 2, 3, 777), (64, 1, 8, 64)):
+        x = (torch.randn(S, C, D, generator=g) * 4).bfloat16()
+        x[0, 0, 0] = 300.0
+        x[1 % S, 0, 0] = -300.0
+        out = torch.full((S, C, D), 7.0, dtype=torch.bfloat16, device="cuda")
+        count = torch.tensor([rows], dtype=torch.int32, device="cuda")
+        _cabi.elementwise(x.cuda(), out, count, op, alpha, beta)
+        want = vo.elementwise(x[:rows], op, alpha, beta)
+        got = out.cpu()
+        assert torch.equal(got[:rows].view(torch.int16), want.view(torch.int16)), (op, S, C, D)
+        assert bool((got[rows:] == 7.0).all())
+
+
+def test_user_flow_with_elementwise_between_gemv_and_topk(tmp_path):
+    """GeMV -> Abs -> topK as a user flow: the scores are written, transformed by the elementwise kernel and
+    selected by the stand-alone top-k; selections equal the oracle's on |score|."""
+    from vortex_torch.flow import build_vflow
+
+    src = textwrap.dedent('''
+        from vortex_torch.flow import vFlow, register
+        from vortex_torch.indexer import GeMV, topK, Abs
+        from vortex_torch.cache import Mean as CMean
+
+        @register("probe_abs_scores")
+        class Probe(vFlow):
+            def __init__(self):
+                super().__init__()
+                self.gemv, self.act, self.output_func, self.reduction = GeMV(), Abs(), topK(), CMean(dim=1)
+            def forward_indexer(self, q, o, cache, ctx):
+                score = self.gemv(q.mean(dim=1, keepdim=True), cache["centroids"], ctx=ctx)
+                self.output_func(self.act(score, ctx=ctx), o, ctx=ctx)
+            def forward_cache(self, cache, loc, ctx):
+                self.reduction(cache["k"], cache["centroids"], loc=loc, ctx=ctx)
+            def create_cache(self, page_size, head_dim):
+                return {"centroids": (1, head_dim)}
+    ''')
+    f = tmp_path / "probe_abs_flow.py"
+    f.write_text(src)
+    flow = build_vflow("probe_abs_scores", {}, str(f))
+    seq, L, H, G, D, P, K = [2048, 900], 1, 4, 2, 128, 16, 10
+    prob = vo.make_paged_problem(4, seq, H, G, D, P)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16, flow=flow, skip=())
+    assert flow.gemv._score_read_elsewhere
+    for name in ("k", "v", "centroids"):
+        rt.pool.buffers[0][name].copy_(prob[name])
+    rt.plan(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda())
+    flow.forward_indexer(prob["q"].cuda(), rt.backend.kv_indices_decode[1].view(-1, 1, 1), rt.pool.buffers[0],
+                         ctx=rt.ictx)
+    ref = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, 1, 1, 64, 16)
+    eff_bs = prob["q"].shape[0]
+    scores = vo.gemv_scores(vo.q_group_mean(prob["q"]), prob["centroids"], ref["dense_kv_indptr"],
+                            ref["dense_kv_indices"], eff_bs, K, 1, 1)
+    vo.topk_select(vo.elementwise(scores.view(-1, 1, 1), 3, 0.0, 1.0).view(-1), ref["dense_kv_indptr"],
+                   ref["sparse_kv_indptr"], ref["dense_kv_indices"], ref["sparse_kv_indices"], eff_bs, K, 1, 1)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], ref["sparse_kv_indices"])

@@ -141,3 +141,21 @@ def test_config1_cpu_plumbing_matches_plain_torch():
         vv = prob["v"][torch.as_tensor(perm[:256]) * H + h][pages].reshape(-1, D)
         ref = torch.softmax((prob["q"][h] @ kk.T) / math.sqrt(D), -1) @ vv
         assert torch.allclose(out[h], ref, atol=1e-5, rtol=1e-5)
+
+
+def test_elementwise_known_answers():
+    """Unary elementwise operators of the indexer: values that are exact in any arithmetic, plus the rounding
+    points the oracle fixes (each bf16 operation rounds once)."""
+    x = torch.tensor([-3.0, -0.5, 0.0, 0.25, 2.0]).bfloat16()
+    assert vo.elementwise(x, 0, 0.0, 0.0).tolist() == [0.0, 0.0, 0.0, 0.25, 2.0]          # relu
+    assert vo.elementwise(x, 0, 0.25, -1.0).tolist() == [-1.0, -1.0, -1.0, 0.25, 2.0]     # threshold / fill
+    assert vo.elementwise(x, 3, 0.0, 1.0).tolist() == [3.0, 0.5, 0.0, 0.25, 2.0]           # abs
+    assert vo.elementwise(x, 4, 1.0, 2.0).tolist() == [-5.0, 0.0, 1.0, 1.5, 5.0]           # 2x + 1, exact
+    # 0.3 rounds to bf16 0.30078125; 0.30078125 * 2 = 0.6015625 exact; + 1.5 = 2.1015625 -> bf16 2.09375
+    assert vo.elementwise(torch.tensor([2.0]).bfloat16(), 4, 1.5, 0.3).item() == 2.09375
+    sig = vo.elementwise(x, 1, 0.0, -1.0).float()                                          # logistic sigmoid
+    assert torch.allclose(sig, torch.sigmoid(x.float()), atol=4e-3)
+    silu = vo.elementwise(x, 2, 0.0, -1.0).float()
+    assert torch.allclose(silu, torch.nn.functional.silu(x.float()), atol=8e-3)
+    big = torch.tensor([300.0, -300.0]).bfloat16()
+    assert vo.elementwise(big, 1, 0.0, 1.0).tolist() == [0.0, 1.0]                         # exp overflow / underflow

@@ -50,6 +50,7 @@ SIGNATURES = {
     "vtx_chunkwise_nh2hn": [_p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_chunkwise_hn2nh": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_decode_mla": [_p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_elementwise": [_p, _p, _p, _i64, _i, _i, _f, _f, _i, _p],
     "vtx_set_mla_path": [_i],
     "vtx_mla_fault_read": [_p],
 }
@@ -236,6 +237,17 @@ def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_sc
                             page_table.shape[1], ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_mla")
+
+
+def elementwise(x, out, packed_row_count, op: int, alpha: float, beta: float) -> None:
+    """Unary elementwise operator on the packed rows of a RAGGED tensor ``[S, C, D]`` (bf16);
+    ``packed_row_count`` is a one-element int32 device tensor (a view of ``dense_kv_indptr[eff_bs:]``)."""
+    want(packed_row_count, torch.int32, "packed_row_count")
+    if x.dtype != out.dtype or x.shape != out.shape:
+        raise TypeError("elementwise: x and out must share dtype and shape")
+    rc = lib.vtx_elementwise(ptr(x), ptr(out), ptr(packed_row_count), x.shape[0], x.shape[1] * x.shape[2],
+                             int(op), float(alpha), float(beta), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_elementwise")
 
 
 def set_mla_path(path: int) -> int:

@@ -2,11 +2,12 @@
 
 Export list of the reference's ``indexer/__init__.py:49-71``.  Built on sm_100a: ``GeMV``,
 ``topK``, ``Context``/``get_ctx``, ``utils_sglang`` and - as links of one fused kernel - ``GeMM``,
-``Softmax`` and ``Max(dim=2)``; the other names are placeholders that raise ``NotImplementedError``
-when used.
+``Softmax`` and ``Max(dim=2)``; the unary elementwise family (``Relu``, ``Sigmoid``, ``Silu``, ``Abs``,
+``Add_Mul``); the other names are placeholders that raise ``NotImplementedError`` when used.
 """
 from ._unbuilt import unbuilt as _unbuilt
 from .context import Context, get_ctx
+from .elementwise import Abs, Add_Mul, Relu, Sigmoid, Silu
 from .elementwise_binary import Add, Maximum, Minimum, Multiply
 from .matmul import GeMM, GeMV
 from .output_func import topK
@@ -16,7 +17,6 @@ from . import utils_sglang
 
 _W = "indexer"
 Transpose = _unbuilt("Transpose", _W)
-Relu, Sigmoid, Silu, Add_Mul, Abs = (_unbuilt(n, _W) for n in ("Relu", "Sigmoid", "Silu", "Add_Mul", "Abs"))
 Save, Load = _unbuilt("Save", _W), _unbuilt("Load", _W)
 
 __all__ = [
