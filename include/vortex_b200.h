@@ -324,6 +324,18 @@ int vtx_elementwise(const void* x, void* out, const int32_t* packed_row_count, i
                     int inner_size, int op, float alpha, float beta, int dtype, void* stream);
 
 /*
+ * Binary elementwise operators on two RAGGED indexer tensors x [max_rows, x_c, x_d], y [max_rows, y_c, y_d]
+ * (bf16; an inner size of 1 broadcasts), out [max_rows, max(x_c, y_c), max(x_d, y_d)], first
+ * *packed_row_count rows.  Replaces elementwise_binary_rrr_kernel
+ * (indexer/triton_kernels/elementwise_binary_impl.py:7-100) behind Maximum / Minimum / Add / Multiply on
+ * (RAGGED, RAGGED) inputs (indexer/elementwise_binary.py:211-326).  op: 0 max, 1 min,
+ * 2 bf16(alpha x) + bf16(beta y), 3 x y; one rounding per bf16 operation.
+ */
+int vtx_elementwise_binary(const void* x, const void* y, void* out, const int32_t* packed_row_count,
+                           int64_t max_rows, int x_c, int x_d, int y_c, int y_d, int op, float alpha,
+                           float beta, int dtype, void* stream);
+
+/*
  * Prefill planner.  Replaces `sglang_plan_prefill` (csrc/register.h, csrc/utils_sglang.cu:462-621).
  * cached_seq_lens, input_seq_lens [bs] i32; outputs dense_kv_indptr, qo_indptr_paged [bs*H + 1],
  * qo_indptr_ragged [bs + 1], dense_kv_indices (packed row ids), kv_last_page_len [bs*H],

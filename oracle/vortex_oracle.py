@@ -509,6 +509,25 @@ def elementwise(x: torch.Tensor, op: int, alpha: float, beta: float) -> torch.Te
     return torch.from_numpy(np.asarray(out, dtype=f)).bfloat16()
 
 
+def elementwise_binary(x: torch.Tensor, y: torch.Tensor, op: int, alpha: float = 1.0, beta: float = 1.0) -> torch.Tensor:
+    """Binary elementwise operators on bf16 RAGGED tensors ``[rows, C, D]`` with broadcasting of the inner dims
+    (indexer/triton_kernels/elementwise_binary_impl.py:72-86): 0 max, 1 min,
+    2 bf16(bf16(alpha x) + bf16(beta y)), 3 bf16(x y); alpha and beta rounded to bf16 first."""
+    assert x.dtype == y.dtype == torch.bfloat16
+    xf, yf = torch.broadcast_tensors(x.float(), y.float())
+    if op == 0:
+        out = torch.maximum(xf, yf)
+    elif op == 1:
+        out = torch.minimum(xf, yf)
+    elif op == 2:
+        a = torch.tensor(alpha).bfloat16().float()
+        b = torch.tensor(beta).bfloat16().float()
+        out = (a * xf).bfloat16().float() + (b * yf).bfloat16().float()
+    else:
+        out = xf * yf
+    return out.bfloat16()
+
+
 def canonical_sum128(v: np.ndarray) -> np.float32:
     """Sum of a vector in the order the kernels use: 128 partial sums (element i goes to partial i % 128,
     added in ascending i from +0.0), then folded in halves v[j] += v[j + w], w = 64 .. 1."""

@@ -372,3 +372,70 @@ def test_user_flow_with_elementwise_between_gemv_and_topk(tmp_path):
                    ref["sparse_kv_indptr"], ref["dense_kv_indices"], ref["sparse_kv_indices"], eff_bs, K, 1, 1)
     ns = int(ref["sparse_kv_indptr"][-1])
     np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], ref["sparse_kv_indices"])
+
+
+@pytest.mark.parametrize("op,alpha,beta", [(0, 1.0, 1.0), (1, 1.0, 1.0), (2, 1.0, 1.0), (2, 0.3, -1.7), (3, 1.0, 1.0)])
+def test_elementwise_binary_kernel_matches_oracle(op, alpha, beta):
+    """vtx_elementwise_binary on packed rows, same-shape and broadcast inner dims: bit-exact with the oracle."""
+    from vortex_torch import _cabi
+
+    g = torch.Generator().manual_seed(11 + op)
+    for S, xs, ys, rows in ((2048, (1, 1), (1, 1), 1999), (512, (2, 8), (2, 8), 300), (512, (2, 8), (1, 8), 512),
+                            (256, (4, 1), (1, 16), 77)):
+        x = (torch.randn(S, *xs, generator=g) * 3).bfloat16()
+        y = (torch.randn(S, *ys, generator=g) * 3).bfloat16()
+        oc, od = max(xs[0], ys[0]), max(xs[1], ys[1])
+        out = torch.full((S, oc, od), 7.0, dtype=torch.bfloat16, device="cuda")
+        count = torch.tensor([rows], dtype=torch.int32, device="cuda")
+        _cabi.elementwise_binary(x.cuda(), y.cuda(), out, count, op, alpha, beta)
+        want = vo.elementwise_binary(x[:rows], y[:rows], op, alpha, beta)
+        got = out.cpu()
+        assert torch.equal(got[:rows].view(torch.int16), want.view(torch.int16)), (op, xs, ys)
+        assert bool((got[rows:] == 7.0).all())
+
+
+def test_user_flow_adding_two_score_sets(tmp_path):
+    """Two GeMV score sets (group mean against the centroids, first query head against the centroids) combined by
+    Add and selected by topK: a flow outside the shipped ones, run through the plugin API."""
+    from vortex_torch.flow import build_vflow
+
+    src = textwrap.dedent('''
+        from vortex_torch.flow import vFlow, register
+        from vortex_torch.indexer import GeMV, topK, Add
+        from vortex_torch.cache import Mean as CMean
+
+        @register("probe_two_scores")
+        class Probe(vFlow):
+            def __init__(self):
+                super().__init__()
+                self.g0, self.g1, self.add, self.output_func, self.reduction = GeMV(), GeMV(), Add(0.5, 2.0), topK(), CMean(dim=1)
+            def forward_indexer(self, q, o, cache, ctx):
+                a = self.g0(q.mean(dim=1, keepdim=True), cache["centroids"], ctx=ctx)
+                b = self.g1(q[:, :1].contiguous(), cache["centroids"], ctx=ctx)
+                self.output_func(self.add(a, b, ctx=ctx), o, ctx=ctx)
+            def forward_cache(self, cache, loc, ctx):
+                self.reduction(cache["k"], cache["centroids"], loc=loc, ctx=ctx)
+            def create_cache(self, page_size, head_dim):
+                return {"centroids": (1, head_dim)}
+    ''')
+    f = tmp_path / "probe_two_scores.py"
+    f.write_text(src)
+    flow = build_vflow("probe_two_scores", {}, str(f))
+    seq, L, H, G, D, P, K = [2048, 900], 1, 4, 2, 128, 16, 10
+    prob = vo.make_paged_problem(6, seq, H, G, D, P)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16, flow=flow, skip=())
+    for name in ("k", "v", "centroids"):
+        rt.pool.buffers[0][name].copy_(prob[name])
+    rt.plan(torch.as_tensor(prob["seq_lens"]).cuda(), torch.as_tensor(prob["req_indices"]).cuda())
+    flow.forward_indexer(prob["q"].cuda(), rt.backend.kv_indices_decode[1].view(-1, 1, 1), rt.pool.buffers[0],
+                         ctx=rt.ictx)
+    ref = vo.plan_decode(prob["seq_lens"], prob["req_to_token"], prob["req_indices"], P, H, K, 1, 1, 64, 16)
+    eff_bs = prob["q"].shape[0]
+    args = (ref["dense_kv_indptr"], ref["dense_kv_indices"], eff_bs, K, 1, 1)
+    sa = vo.gemv_scores(vo.q_group_mean(prob["q"]), prob["centroids"], *args)
+    sb = vo.gemv_scores(prob["q"][:, :1].contiguous(), prob["centroids"], *args)
+    comb = vo.elementwise_binary(sa.view(-1, 1, 1), sb.view(-1, 1, 1), 2, 0.5, 2.0).view(-1)
+    vo.topk_select(comb, ref["dense_kv_indptr"], ref["sparse_kv_indptr"], ref["dense_kv_indices"],
+                   ref["sparse_kv_indices"], eff_bs, K, 1, 1)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(rt.backend.kv_indices_decode[1].cpu().numpy()[:ns], ref["sparse_kv_indices"])

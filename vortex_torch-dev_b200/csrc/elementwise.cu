@@ -68,7 +68,66 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const __nv_bfloat16* _
         out[i] = __float2bfloat16_rn(apply<OP>(__bfloat162float(x[i]), alpha, beta));
 }
 
+// Binary form on two RAGGED tensors with broadcasting over the two inner dims (a size of 1 repeats).
+// OP 0 max, 1 min, 2 bf16(bf16(alpha x) + bf16(beta y)), 3 bf16(x y)  (elementwise_binary_rrr_kernel,
+// indexer/triton_kernels/elementwise_binary_impl.py:7-100).
+template <int OP>
+__global__ void __launch_bounds__(256) elementwise_binary_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ y,
+                                                                __nv_bfloat16* __restrict__ out,
+                                                                const int32_t* __restrict__ row_count, int64_t max_rows,
+                                                                int xc, int xd, int yc, int yd, int oc, int od,
+                                                                float alpha, float beta) {
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    int64_t rows = *row_count;
+    if (rows > max_rows) rows = max_rows;
+    const int inner = oc * od;
+    const int64_t n = rows * inner;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / inner;
+        const int e = (int)(i - r * inner), c = e / od, d = e - c * od;
+        const float a = __bfloat162float(x[(r * xc + (xc == 1 ? 0 : c)) * xd + (xd == 1 ? 0 : d)]);
+        const float b = __bfloat162float(y[(r * yc + (yc == 1 ? 0 : c)) * yd + (yd == 1 ? 0 : d)]);
+        float o;
+        if (OP == 0) o = fmaxf(a, b);
+        else if (OP == 1) o = fminf(a, b);
+        else if (OP == 2) o = __fadd_rn(bf16_round(__fmul_rn(alpha, a)), bf16_round(__fmul_rn(beta, b)));
+        else o = __fmul_rn(a, b);
+        out[i] = __float2bfloat16_rn(o);
+    }
+}
+
 }  // namespace
+
+extern "C" int vtx_elementwise_binary(const void* x, const void* y, void* out, const int32_t* packed_row_count,
+                                      int64_t max_rows, int x_c, int x_d, int y_c, int y_d, int op, float alpha,
+                                      float beta, int dtype, void* stream) {
+    if (!x || !y || !out || !packed_row_count || max_rows < 0) return VTX_ERR_INVALID_ARGUMENT;
+    if (x_c < 1 || x_d < 1 || y_c < 1 || y_d < 1 || op < 0 || op > 3) return VTX_ERR_INVALID_ARGUMENT;
+    if ((x_c != y_c && x_c != 1 && y_c != 1) || (x_d != y_d && x_d != 1 && y_d != 1)) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16) return VTX_ERR_UNSUPPORTED;
+    if (max_rows == 0) return VTX_OK;
+    const int oc = x_c > y_c ? x_c : y_c, od = x_d > y_d ? x_d : y_d;
+    const float a = __bfloat162float(__float2bfloat16_rn(alpha)), b = __bfloat162float(__float2bfloat16_rn(beta));
+    const int64_t n = max_rows * oc * od;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    const auto* xp = (const __nv_bfloat16*)x;
+    const auto* yp = (const __nv_bfloat16*)y;
+    auto* op_ = (__nv_bfloat16*)out;
+    cudaStream_t st = (cudaStream_t)stream;
+#define VTX_EB_CASE(N) \
+    case N: return vtx::launch(elementwise_binary_kernel<N>, dim3(blocks), dim3(256), 0, st, xp, yp, op_, packed_row_count, \
+                               max_rows, x_c, x_d, y_c, y_d, oc, od, a, b);
+    switch (op) {
+        VTX_EB_CASE(0) VTX_EB_CASE(1) VTX_EB_CASE(2)
+        default: return vtx::launch(elementwise_binary_kernel<3>, dim3(blocks), dim3(256), 0, st, xp, yp, op_,
+                                    packed_row_count, max_rows, x_c, x_d, y_c, y_d, oc, od, a, b);
+    }
+#undef VTX_EB_CASE
+}
 
 extern "C" int vtx_elementwise(const void* x, void* out, const int32_t* packed_row_count, int64_t max_rows,
                                int inner_size, int op, float alpha, float beta, int dtype, void* stream) {

@@ -51,6 +51,7 @@ SIGNATURES = {
     "vtx_chunkwise_hn2nh": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_decode_mla": [_p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
     "vtx_elementwise": [_p, _p, _p, _i64, _i, _i, _f, _f, _i, _p],
+    "vtx_elementwise_binary": [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _f, _i, _p],
     "vtx_set_mla_path": [_i],
     "vtx_mla_fault_read": [_p],
 }
@@ -248,6 +249,19 @@ def elementwise(x, out, packed_row_count, op: int, alpha: float, beta: float) ->
     rc = lib.vtx_elementwise(ptr(x), ptr(out), ptr(packed_row_count), x.shape[0], x.shape[1] * x.shape[2],
                              int(op), float(alpha), float(beta), dtype_code(x.dtype), stream_of(x))
     check(rc, "vtx_elementwise")
+
+
+def elementwise_binary(x, y, out, packed_row_count, op: int, alpha: float = 1.0, beta: float = 1.0) -> None:
+    """Binary elementwise operator on the packed rows of two RAGGED tensors (bf16), inner dims broadcast."""
+    want(packed_row_count, torch.int32, "packed_row_count")
+    if not (x.dtype == y.dtype == out.dtype):
+        raise TypeError("elementwise_binary: x, y and out must share a dtype")
+    if out.shape[1] != max(x.shape[1], y.shape[1]) or out.shape[2] != max(x.shape[2], y.shape[2]):
+        raise ValueError("elementwise_binary: out must have the broadcast inner shape")
+    rc = lib.vtx_elementwise_binary(ptr(x), ptr(y), ptr(out), ptr(packed_row_count), out.shape[0], x.shape[1],
+                                    x.shape[2], y.shape[1], y.shape[2], int(op), float(alpha), float(beta),
+                                    dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_elementwise_binary")
 
 
 def set_mla_path(path: int) -> int:

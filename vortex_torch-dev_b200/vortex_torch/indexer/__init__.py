@@ -3,7 +3,7 @@
 Export list of the reference's ``indexer/__init__.py:49-71``.  Built on sm_100a: ``GeMV``,
 ``topK``, ``Context``/``get_ctx``, ``utils_sglang`` and - as links of one fused kernel - ``GeMM``,
 ``Softmax`` and ``Max(dim=2)``; the unary elementwise family (``Relu``, ``Sigmoid``, ``Silu``, ``Abs``,
-``Add_Mul``); the other names are placeholders that raise ``NotImplementedError`` when used.
+``Add_Mul``) and, on two RAGGED tensors, ``Add`` and ``Minimum``; the other names are placeholders that raise ``NotImplementedError`` when used.
 """
 from ._unbuilt import unbuilt as _unbuilt
 from .context import Context, get_ctx
