@@ -484,8 +484,11 @@ def run_ragged_workload(args):
 
     def layer():
         _cabi.plan_decode(seq_d, r2t_d, ridx, dip, din, sip, sin_, last, *w, P, H, K, bos, eos, 64, 16)
-        _cabi.indexer_fused(q, cent, dip, sip, din, sin_, S, K, bos, eos, maxp)
-        _cabi.decode_gqa(q, k, v, out, sip, sin_, last, S, P, scale)
+        if os.environ.get("VTX_BENCH_C3_SPLIT"):  # experiment hook: selection and attention as two launches
+            _cabi.indexer_fused(q, cent, dip, sip, din, sin_, S, K, bos, eos, maxp)
+            _cabi.decode_gqa(q, k, v, out, sip, sin_, last, S, P, scale)
+        else:
+            _cabi.sparse_layer_fused(q, cent, k, v, out, dip, sip, din, sin_, last, S, P, K, bos, eos, maxp, scale)
 
     layer()
     torch.cuda.synchronize(dev)
@@ -545,7 +548,7 @@ def run_ragged_workload(args):
     peaks, kind = measured_peaks()
     if rank == 0:
         line = dict(workload="config 3: ragged batch, 256 requests ctx U[1024,32768], 32q/8kv heads, D128, page 16, "
-                             "topk 64+1+1, one sparse layer (plan + fused indexer + decode)",
+                             "topk 64+1+1, one sparse layer (plan + selection and attention in one launch)",
                     n_gpus=world, scaling="strong", requests_per_rank=[len(x) for x in balance_requests(pages_all, world)],
                     us_per_layer=secs * 1e6, layers_per_s=1.0 / secs, algorithmic_bytes=cent_b + kv_b,
                     achieved_gbs=(cent_b + kv_b) / secs / 1e9, frac_of_n_x_peak=(cent_b + kv_b) / secs / 1e9 / (world * peaks["hbm_gbs"]),
