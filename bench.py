@@ -187,8 +187,6 @@ def build_runtime(cfg, device, seed, flow_name="block_sparse_attention"):
                              context_len=cfg["ctx"], server_args=sa, dtype=torch.bfloat16, device=device)
     g = torch.Generator().manual_seed(seed)
     perm = torch.randperm(num_pages, generator=g)
-    if os.environ.get("VTX_BENCH_IDENTITY_PAGES"):  # experiment: physical order = logical order
-        perm = torch.arange(num_pages)
     slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1)
     rt.model_runner.req_to_token_pool.req_to_token.copy_(slots.to(torch.int32))
     torch.manual_seed(seed)
@@ -254,12 +252,14 @@ def verify_sample(rt, step, cfg, slots):
     return ok
 
 
-def time_kernels(rt, step, cfg, reps):
+def time_kernels(rt, step, cfg, reps, pdl):
     """Average device time per launch of each kernel kind, from CUDA events around graph replays.
 
-    For each kind (fused indexer, sparse decode, dense decode, KV write + centroid update) one CUDA
-    graph holds that kernel's launches of every layer of a step, back to back on each layer's own
-    pool; the graph is replayed ``reps`` times between two events on the launching stream.
+    For each kind (fused sparse layer, fused indexer, sparse decode, dense decode, KV write + centroid
+    update) one CUDA graph holds that kernel's launches of every layer of a step, back to back on each
+    layer's own pool, launched the way the step launches them (``pdl``: programmatic dependent launch,
+    with the early prologue of the fused layer kernel when 2); the graph is replayed ``reps`` times
+    between two events on the launching stream.
     """
     from vortex_torch import _cabi
     from vortex_torch.cache import set_kv_buffer_launcher
@@ -294,11 +294,12 @@ def time_kernels(rt, step, cfg, reps):
     def run_fused():
         for l in sparse_layers:
             qv, ov, cache = views(l)
+            # the page lists are static here (no planner launch in this graph), so the early prologue is safe
             _cabi.sparse_layer_fused(qv, cache["centroids"], cache["k"], cache["v"], ov, b.kv_indptr_decode[0],
                                      b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
                                      b.kv_last_page_len_decode, eff_bs, rt.P, cfg["K"], cfg["bos"], cfg["eos"],
                                      rt.ictx.max_num_pages_per_request, rt.sm_scale, step.new_k[l], step.new_v[l],
-                                     step.loc)
+                                     step.loc, workspace=rt.layer_workspace, early_prologue=pdl == 2)
 
     kinds = dict(sparse_layer_fused=(run_fused, len(sparse_layers)),
                  indexer=(run_indexer, len(sparse_layers)),
@@ -317,9 +318,14 @@ def time_kernels(rt, step, cfg, reps):
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        g.replay()
+        _cabi.set_programmatic_launch(1 if pdl else 0)
+        try:
+            with torch.cuda.graph(g):
+                fn()
+        finally:
+            _cabi.set_programmatic_launch(0)
+        for _ in range(3):
+            g.replay()
         torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
@@ -331,23 +337,22 @@ def time_kernels(rt, step, cfg, reps):
     return out
 
 
-def run_mla_workload(args):
-    """Side measurement (not the headline line): the MLA block-table sparse decode configuration.
+def measure_mla(dev, steps, layers=4, mla_path=0, pdl=True):
+    """The MLA block-table sparse decode configuration (config 5), one layer = fused indexer + decode.
 
     bs128, 16 heads, 576-dim latent (values = first 512), page 64, 16384 tokens, topk 32 + 1 + 1.
-    Four distinct 2.4 GB latent pools are cycled so that consecutive launches never share L2 lines.
+    ``layers`` distinct 2.4 GB latent pools are cycled so that consecutive launches never share L2 lines.
+    Returns a dict with per-kernel and per-layer times, bytes and fractions of the measured HBM peak.
     """
+    from oracle import vortex_oracle as vo
     from vortex_torch import _cabi
 
-    _cabi.set_mla_path(args.mla_path)
-    dev = torch.device("cuda", 0)
-    bs, Hq, Dl, Dv, P, ctx, K, bos, eos, L = 128, 16, 576, 512, 64, 16384, 32, 1, 1, (args.layers or 4)
+    _cabi.set_mla_path(mla_path)
+    bs, Hq, Dl, Dv, P, ctx, K, bos, eos, L = 128, 16, 576, 512, 64, 16384, 32, 1, 1, layers
     pages_per_req = ctx // P
     num_pages = bs * pages_per_req
     g = torch.Generator().manual_seed(7)
     perm = torch.randperm(num_pages, generator=g)
-    if os.environ.get("VTX_BENCH_IDENTITY_PAGES"):  # experiment: physical order = logical order
-        perm = torch.arange(num_pages)
     slots = (perm.view(bs, pages_per_req, 1) * P + torch.arange(P).view(1, 1, P)).view(bs, -1).to(torch.int32)
     i32 = dict(dtype=torch.int32, device=dev)
     r2t = slots.to(dev)
@@ -382,12 +387,18 @@ def run_mla_workload(args):
         for l in range(L):
             _cabi.decode_mla(qs[l], lat[l], outs[l], spt, ssl, P, scale)
 
+    def run_layer():
+        for l in range(L):
+            _cabi.indexer_fused(qs[l], cent[l], dip, sip, din, sin_, bs, K, bos, eos, pages_per_req,
+                                sparse_page_table=spt)
+            _cabi.decode_mla(qs[l], lat[l], outs[l], spt, ssl, P, scale)
+
     res = {}
-    for name, fn in (("indexer", run_indexer), ("decode_mla", run_decode)):
+    for name, fn in (("indexer", run_indexer), ("decode_mla", run_decode), ("layer", run_layer)):
         fn()
         torch.cuda.synchronize(dev)
         gr = torch.cuda.CUDAGraph()
-        _cabi.set_programmatic_launch(1 if args.pdl else 0)  # launches of the graph chained as in the headline step
+        _cabi.set_programmatic_launch(1 if pdl else 0)  # launches of the graph chained as in the headline step
         try:
             with torch.cuda.graph(gr):
                 fn()
@@ -398,56 +409,61 @@ def run_mla_workload(args):
         torch.cuda.synchronize(dev)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             gr.replay()
         e1.record()
         torch.cuda.synchronize(dev)
-        res[name] = e0.elapsed_time(e1) * 1e-3 / (args.steps * L)
+        res[name] = e0.elapsed_time(e1) * 1e-3 / (steps * L)
+    # parity of request 0 of the last layer against the CPU oracle (selection bit-exact, output within 2e-2)
+    rows = dpt[0].cpu().long()
+    plan = vo.plan_decode([ctx], np.arange(ctx, dtype=np.int32).reshape(1, -1), [0], P, 1, K, bos, eos, 64, 16,
+                          page_table_stride=pages_per_req)
+    q0 = qs[-1][:1].cpu()
+    vo.forward_indexer(q0, cent[-1][rows.to(dev)].cpu(), plan, K, bos, eos)
+    want_sel = rows.numpy()[plan["sparse_kv_indices"]]
+    ok = bool(np.array_equal(spt[0, :budget].cpu().numpy(), want_sel))
+    want = vo.decode_mla(q0, lat[-1][rows.to(dev)].cpu(), plan["sparse_page_table"], plan["sparse_cache_seqlens"], Dv,
+                         scale)
+    got = outs[-1][:1].float().cpu()
+    ok = ok and bool(((got - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
     peaks, kind = measured_peaks()
     cent_b = bs * (pages_per_req - bos - eos) * Dl * 2
     kv_b = bs * budget * P * Dl * 2
     flops = bs * budget * P * (2 * Hq * Dl + 2 * Hq * Dv)
-    line = dict(workload="config 5: MLA block-table sparse decode, bs128, 16 heads x 576 latent, page 64, 16k ctx, topk 32+1+1",
+    gb = lambda nbytes, secs: nbytes / secs / 1e9
+    return dict(workload="config 5: MLA block-table sparse decode, bs128, 16 heads x 576 latent, page 64, 16k ctx, "
+                         "topk 32+1+1",
                 us=dict((k, v * 1e6) for k, v in res.items()),
-                indexer=dict(bytes=cent_b, achieved_gbs=cent_b / res["indexer"] / 1e9,
-                             frac=cent_b / res["indexer"] / 1e9 / peaks["hbm_gbs"]),
-                decode_mla=dict(bytes=kv_b, achieved_gbs=kv_b / res["decode_mla"] / 1e9,
-                                frac=kv_b / res["decode_mla"] / 1e9 / peaks["hbm_gbs"],
+                indexer=dict(bytes=cent_b, achieved_gbs=gb(cent_b, res["indexer"]),
+                             frac=gb(cent_b, res["indexer"]) / peaks["hbm_gbs"]),
+                decode_mla=dict(bytes=kv_b, achieved_gbs=gb(kv_b, res["decode_mla"]),
+                                frac=gb(kv_b, res["decode_mla"]) / peaks["hbm_gbs"],
                                 tflops=flops / res["decode_mla"] / 1e12),
-                layer=dict(bytes=cent_b + kv_b, us=(res["indexer"] + res["decode_mla"]) * 1e6,
-                           frac=(cent_b + kv_b) / (res["indexer"] + res["decode_mla"]) / 1e9 / peaks["hbm_gbs"]),
-                mla_form="mma.sync + cp.async" if args.mla_path else "tcgen05 + TMA",
-                programmatic_launch=1 if args.pdl else 0,
-                mla_fault_bits=_cabi.mla_fault_bits(),
-                peak_kind=f"of {kind}")
-    print(json.dumps(line))
+                layer=dict(bytes=cent_b + kv_b, us=res["layer"] * 1e6,
+                           achieved_gbs=gb(cent_b + kv_b, res["layer"]),
+                           frac=gb(cent_b + kv_b, res["layer"]) / peaks["hbm_gbs"]),
+                mla_form="mma.sync + cp.async" if mla_path else "tcgen05 + TMA",
+                programmatic_launch=1 if pdl else 0, mla_fault_bits=_cabi.mla_fault_bits(),
+                parity_sample_ok=ok, peak_kind=f"of {kind}")
 
 
-def run_ragged_workload(args):
-    """Side measurement (not the headline line): the ragged-batch configuration, one sparse layer.
+def run_mla_workload(args):
+    print(json.dumps(measure_mla(torch.device("cuda", 0), args.steps, layers=args.layers or 4,
+                                 mla_path=args.mla_path, pdl=bool(args.pdl))))
+
+
+def measure_ragged(dev, dist, rank, world, steps, warmup):
+    """The ragged-batch configuration (config 3), one sparse layer, sharded by request (strong scaling).
 
     256 requests, context lengths uniform in [1024, 32768], 32 q heads / 8 KV heads / head_dim 128, bf16,
-    page 16, topk 64 + 1 + 1; requests are dealt to the ranks by total page count (strong scaling: the batch
-    is fixed, each rank holds only its own requests' pool).  No collective on the timed path; NCCL gathers
-    the selections of sampled requests for verification afterwards.
+    page 16, topk 64 + 1 + 1; requests are dealt to the ranks by total page count (the batch is fixed, each
+    rank holds only its own requests' pool).  No collective on the timed path; NCCL gathers the selections
+    of sampled requests for verification afterwards.  Returns the result dict on every rank.
     """
     from oracle import vortex_oracle as vo
     from vortex_torch import _cabi
     from vortex_torch.runtime import balance_requests, gather_for_verification
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    sys.stdout.flush()
-    json_fd = os.dup(1)
-    os.dup2(2, 1)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=dev)
     nreq, Hq, H, D, P, K, bos, eos = 256, 32, 8, 128, 16, 64, 1, 1
     G = Hq // H
     g = torch.Generator().manual_seed(33)
@@ -481,48 +497,51 @@ def run_ragged_workload(args):
     q = torch.randn(S, G, D, device=dev).bfloat16()
     out = torch.empty_like(q)
     scale = 1.0 / math.sqrt(D)
+    # scratch that lets the long segments of this batch be scanned by several CTAs each
+    ws = torch.zeros(max(1, _cabi.sparse_layer_workspace_bytes(S, maxp, K, bos, eos) // 4), **i32)
 
     def layer():
         _cabi.plan_decode(seq_d, r2t_d, ridx, dip, din, sip, sin_, last, *w, P, H, K, bos, eos, 64, 16)
-        if os.environ.get("VTX_BENCH_C3_SPLIT"):  # experiment hook: selection and attention as two launches
-            _cabi.indexer_fused(q, cent, dip, sip, din, sin_, S, K, bos, eos, maxp)
-            _cabi.decode_gqa(q, k, v, out, sip, sin_, last, S, P, scale)
-        else:
-            _cabi.sparse_layer_fused(q, cent, k, v, out, dip, sip, din, sin_, last, S, P, K, bos, eos, maxp, scale)
+        _cabi.sparse_layer_fused(q, cent, k, v, out, dip, sip, din, sin_, last, S, P, K, bos, eos, maxp, scale,
+                                 workspace=ws)
 
     layer()
     torch.cuda.synchronize(dev)
     gr = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(gr):
-        layer()
-    for _ in range(max(3, args.warmup)):
+    _cabi.set_programmatic_launch(1)
+    try:
+        with torch.cuda.graph(gr):
+            layer()
+    finally:
+        _cabi.set_programmatic_launch(0)
+    for _ in range(max(3, warmup)):
         gr.replay()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize(dev)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         gr.replay()
     e1.record()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize(dev)
-    secs = e0.elapsed_time(e1) * 1e-3 / args.steps
+    secs = e0.elapsed_time(e1) * 1e-3 / steps
     if dist is not None:
         tt = torch.tensor([secs], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         secs = float(tt[0])
-    # ---- verification of two sampled local requests against the CPU oracle, then gathered over NCCL
-    sel_local, ok = {}, True
-    sip_h, dip_h = sip.cpu().numpy(), dip.cpu().numpy()
-    for i in (0, bs // 2):
+    # ---- verification of two sampled local requests (the longest one and request bs/2) against the CPU
+    # oracle, then gathered over NCCL
+    sel_local, ok = {}, _cabi.device_status() == 0
+    sip_h = sip.cpu().numpy()
+    for i in sorted({max(range(bs), key=lambda r: n[r]), bs // 2}):
         ni = n[i]
         plan = vo.plan_decode([seq[i]], (np.arange(ni * P, dtype=np.int32)).reshape(1, -1), [0], P, H, K, bos, eos, 64, 16)
         # oracle rows are page*H + h over a compact pool holding only this request, in logical order
-        kk = torch.stack([k[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
-        vv = torch.stack([v[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
-        cc = torch.stack([cent[r2t[i, pg * P].item() // P * H + h].cpu() for pg in range(ni) for h in range(H)])
+        rows = ((r2t[i, : ni * P : P].long() // P).view(-1, 1) * H + torch.arange(H).view(1, -1)).reshape(-1).to(dev)
+        kk, vv, cc = k[rows].cpu(), v[rows].cpu(), cent[rows].cpu()
         qi = q[i * H:(i + 1) * H].cpu()
         vo.forward_indexer(qi, cc, plan, K, bos, eos)
         a, b = sip_h[i * H], sip_h[(i + 1) * H]
@@ -535,7 +554,7 @@ def run_ragged_workload(args):
         gotv = out[i * H:(i + 1) * H].float().cpu()
         ok = ok and bool(((gotv - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
         sel_local[mine[i]] = torch.as_tensor(got.astype(np.int64), device=dev)
-    gathered = gather_for_verification(sel_local)
+    gathered = gather_for_verification(sel_local, dtype=torch.int64)
     flags = torch.tensor([int(ok)], device=dev, dtype=torch.int32)
     if dist is not None:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
@@ -546,13 +565,32 @@ def run_ragged_workload(args):
         toks = s_len if p <= budget else (budget - 1) * P + (s_len % P or P)
         kv_b += H * toks * D * 2 * 2
     peaks, kind = measured_peaks()
+    return dict(workload="config 3: ragged batch, 256 requests ctx U[1024,32768], 32q/8kv heads, D128, page 16, "
+                         "topk 64+1+1, one sparse layer (plan + selection and attention in one launch, long "
+                         "segments split over CTAs)",
+                n_gpus=world, scaling="strong", requests_per_rank=[len(x) for x in balance_requests(pages_all, world)],
+                us_per_layer=secs * 1e6, layers_per_s=1.0 / secs, algorithmic_bytes=cent_b + kv_b,
+                achieved_gbs=(cent_b + kv_b) / secs / 1e9,
+                frac_of_n_x_peak=(cent_b + kv_b) / secs / 1e9 / (world * peaks["hbm_gbs"]),
+                peak_kind=f"of {kind}", parity_sample_ok=bool(int(flags.item())), verified_requests=sorted(gathered))
+
+
+def run_ragged_workload(args):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    line = measure_ragged(dev, dist, rank, world, args.steps, args.warmup)
     if rank == 0:
-        line = dict(workload="config 3: ragged batch, 256 requests ctx U[1024,32768], 32q/8kv heads, D128, page 16, "
-                             "topk 64+1+1, one sparse layer (plan + selection and attention in one launch)",
-                    n_gpus=world, scaling="strong", requests_per_rank=[len(x) for x in balance_requests(pages_all, world)],
-                    us_per_layer=secs * 1e6, layers_per_s=1.0 / secs, algorithmic_bytes=cent_b + kv_b,
-                    achieved_gbs=(cent_b + kv_b) / secs / 1e9, frac_of_n_x_peak=(cent_b + kv_b) / secs / 1e9 / (world * peaks["hbm_gbs"]),
-                    peak_kind=f"of {kind}", parity_sample_ok=bool(int(flags.item())), verified_requests=sorted(gathered))
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
         dist.barrier()
@@ -691,7 +729,7 @@ def main():
         dist.all_gather(flags, torch.tensor([int(ok)], device=device, dtype=torch.int32))
         ok = all(int(f.item()) == 1 for f in flags)
 
-    kt = time_kernels(rt, step, cfg, reps=5)
+    kt = time_kernels(rt, step, cfg, reps=10, pdl=0 if args.no_graph else args.pdl)
     peaks, peak_kind = measured_peaks()
     ab = algorithmic_bytes(cfg)
     peak = float(peaks["hbm_gbs"])

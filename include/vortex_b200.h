@@ -42,16 +42,32 @@ const char* vtx_last_cuda_error(void);
 /*
  * Programmatic dependent launch for every later launch of this library in the process.
  *   0  off (the default): plain stream order.
- *   1  each kernel is launched with the programmatic stream-serialization attribute and waits for the
- *      complete preceding launch before it touches memory: results unchanged, launch latency overlaps.
- *   2  as 1, and vtx_sparse_layer_fused additionally stages its row ids and starts its first centroid
- *      gathers BEFORE that wait.  Those reads touch only vtx_plan_decode's outputs and centroid rows of
- *      non-reserved pages, so the caller must guarantee that the plan launch of the step has completed
- *      when such a kernel starts: use mode 2 only for a launch that follows, on the same stream, at least
- *      one other launch of this library issued after vtx_plan_decode.
+ *   non-zero  each kernel is launched with the programmatic stream-serialization attribute and waits for
+ *      the complete preceding launch before it touches memory: results unchanged, launch latency overlaps.
+ * A single launch may go further and start reading before that wait: see VTX_LAYER_EARLY_PROLOGUE, which is
+ * a per-call flag of vtx_sparse_layer, not part of this process-wide switch.
  * No counterpart in the reference (it launches every kernel with plain stream order).
  */
 int vtx_set_programmatic_launch(int enable);
+
+/*
+ * Sticky device status word.  A kernel that meets a condition it cannot report through a return code (its
+ * launch has already succeeded) sets one of the bits below with an atomic OR and carries on with a well
+ * defined result; the word keeps its bits until cleared.  vtx_device_status_word returns its device address
+ * on the current device (or NULL); vtx_device_status_read copies it to *host_bits with a synchronous
+ * cudaMemcpy (it waits for the device) and, with clear != 0, zeroes it afterwards.
+ *   VTX_STATUS_CANDIDATE_OVERFLOW  a segment had more candidate pages than the call's
+ *       max_num_pages_per_request allows for (that argument sizes shared memory and the grid).  The
+ *       selection written for that segment is its first topk_val candidates, not its best ones.
+ *       Precondition of every entry point that takes max_num_pages_per_request:
+ *       ceil(cached_seq_len / page_size) <= max_num_pages_per_request for every request of the batch.
+ *   VTX_STATUS_BAD_ROW  (checked builds only) a row id or cache slot outside the range the caller gave.
+ * No counterpart in the reference (it aborts with TORCH_CHECK above 4096 pages, csrc/topk.cu:200).
+ */
+#define VTX_STATUS_CANDIDATE_OVERFLOW 1u
+#define VTX_STATUS_BAD_ROW 2u
+void* vtx_device_status_word(void);
+int vtx_device_status_read(uint32_t* host_bits, int clear);
 
 /*
  * Block-table builder for one decode step.
@@ -204,6 +220,60 @@ int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_c
                            int head_dim, int page_size, int topk_val, int page_reserved_bos,
                            int page_reserved_eos, int max_num_pages_per_request, float sm_scale,
                            int dtype, void* stream);
+
+/*
+ * General form of the one-launch sparse layer (the three entry points around it are this call with a fixed
+ * score_mode, no workspace and no flags).
+ *   score_mode  VTX_SCORE_MEAN_DOT: group mean . centroid (block_sparse_attention, flow/algorithms.py:168-170),
+ *               VTX_SCORE_GQA_SOFTMAX: GeMM -> Softmax(softmax_scale) -> Max (flow/algorithms.py:281-309),
+ *               VTX_SCORE_QUEST: envelope bound from summary (page maximum) and summary2 (page minimum)
+ *               (flow/algorithms.py:411-451).
+ *   workspace   optional caller-owned device scratch of vtx_sparse_layer_workspace_bytes(...) bytes, ZEROED
+ *               ONCE by the caller after allocation (every call leaves it zeroed where that matters).  With
+ *               it, a segment with more than 512 candidate pages is scanned by several CTAs whose best keys
+ *               the last of them to arrive merges; selections are the same bits as without it.  Without it
+ *               (or for VTX_SCORE_GQA_SOFTMAX, whose softmax spans the whole segment) one CTA scans a
+ *               segment.  Calls that share a workspace must not overlap on the GPU.
+ *   flags       VTX_LAYER_EARLY_PROLOGUE: when programmatic launch is on, the kernel stages its row ids and
+ *               starts its first summary-row gathers BEFORE it waits for the preceding launch.  Those reads
+ *               touch only vtx_plan_decode's outputs and summary rows of non-reserved pages, so the caller
+ *               must guarantee that the plan launch of the step has completed when this kernel starts:
+ *               set the flag only for a launch that follows, on the same stream, at least one launch of
+ *               this library that was issued after vtx_plan_decode and that itself waits for its
+ *               predecessor before it lets its successor start (every kernel of this library does, except
+ *               vtx_decode_mla's tcgen05 form and a vtx_sparse_layer launch that carries this flag).
+ * No counterpart in the reference for workspace and flags (its Triton indexer kernels split work through
+ * the planner's workload list instead, csrc/utils_sglang.cu:188-254).
+ */
+#define VTX_SCORE_MEAN_DOT 0
+#define VTX_SCORE_GQA_SOFTMAX 2
+#define VTX_SCORE_QUEST 3
+#define VTX_LAYER_EARLY_PROLOGUE 1
+typedef struct vtx_sparse_layer_params {
+    const void* q;        /* [eff_bs, group, D] */
+    const void* summary;  /* centroids, or the page-maximum cache for VTX_SCORE_QUEST */
+    const void* summary2; /* page-minimum cache (VTX_SCORE_QUEST), else NULL */
+    const void* k_cache;
+    const void* v_cache;
+    void* out;            /* [eff_bs, group, D] */
+    const void* new_k;    /* [bs, num_kv_heads, D] or NULL */
+    const void* new_v;
+    const int64_t* loc;   /* [bs] or NULL */
+    const int32_t* dense_kv_indptr;
+    const int32_t* sparse_kv_indptr;
+    const int32_t* dense_kv_indices;
+    int32_t* sparse_kv_indices;
+    const int32_t* kv_last_page_len;
+    void* workspace;
+    int64_t workspace_bytes;
+    int32_t eff_batch_size, group_size, head_dim, page_size, num_kv_heads;
+    int32_t topk_val, page_reserved_bos, page_reserved_eos, max_num_pages_per_request;
+    int32_t score_mode, flags, dtype;
+    float sm_scale, softmax_scale;
+} vtx_sparse_layer_params;
+int64_t vtx_sparse_layer_workspace_bytes(int eff_batch_size, int max_num_pages_per_request, int topk_val,
+                                         int page_reserved_bos, int page_reserved_eos);
+int vtx_sparse_layer(const vtx_sparse_layer_params* params, void* stream);
 
 /*
  * The same single launch for the gqa_block_sparse_attention flow: page scores are those of

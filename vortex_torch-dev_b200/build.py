@@ -53,13 +53,19 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     obj_dir = HERE / "build"
     obj_dir.mkdir(exist_ok=True)
     procs = []
+    headers = list(CSRC.glob("*.cuh")) + list((ROOT / "include").glob("*.h"))
+    newest_header = max((h.stat().st_mtime for h in headers), default=0.0)
     for src in sources():
         obj = obj_dir / (src.stem + ".o")
+        objs.append(str(obj))
+        # an object is reused when it is newer than its source and every header
+        if (not force and not ptxas_info and obj.exists()
+                and obj.stat().st_mtime > max(src.stat().st_mtime, newest_header)):
+            continue
         cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
-        objs.append(str(obj))
     failed = False
     for src, p in procs:
         out, _ = p.communicate()

@@ -4,10 +4,18 @@
 #include "vtx_common.cuh"
 
 #include <atomic>
+#include <mutex>
+
+// Sticky status word of the kernels: a kernel that meets a condition it cannot report through its return
+// code (the launch has already succeeded) sets a VTX_STATUS_* bit here with atomicOr and carries on with a
+// well-defined result.  One word per device that loaded the library.
+static __device__ uint32_t g_vtx_device_status = 0;
 
 namespace {
 thread_local char g_last_error[256] = "";
 std::atomic<int> g_pdl{0};
+std::mutex g_status_mu;
+uint32_t* g_status_addr[64] = {};
 }
 
 namespace vtx {
@@ -17,7 +25,23 @@ void note_cuda_error(cudaError_t e) {
     g_last_error[sizeof(g_last_error) - 1] = '\0';
 }
 bool programmatic_launch_enabled() { return g_pdl.load(std::memory_order_relaxed) != 0; }
-int programmatic_launch_mode() { return g_pdl.load(std::memory_order_relaxed); }
+
+// Device address of the status word on the current device (looked up once per device), or null.
+uint32_t* device_status_word() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_status_mu);
+    if (g_status_addr[dev] == nullptr) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_vtx_device_status);
+        if (e != cudaSuccess) {
+            note_cuda_error(e);
+            return nullptr;
+        }
+        g_status_addr[dev] = static_cast<uint32_t*>(p);
+    }
+    return g_status_addr[dev];
+}
 }  // namespace vtx
 
 extern "C" int vtx_version(void) { return 100; /* 0.1.0 */ }
@@ -38,6 +62,21 @@ extern "C" const char* vtx_status_string(int status) {
 extern "C" const char* vtx_last_cuda_error(void) { return g_last_error; }
 
 extern "C" int vtx_set_programmatic_launch(int enable) {
-    g_pdl.store(enable < 0 ? 0 : (enable > 2 ? 2 : enable), std::memory_order_relaxed);
+    g_pdl.store(enable > 0 ? 1 : 0, std::memory_order_relaxed);
+    return VTX_OK;
+}
+
+extern "C" void* vtx_device_status_word(void) { return vtx::device_status_word(); }
+
+extern "C" int vtx_device_status_read(uint32_t* host_bits, int clear) {
+    if (!host_bits) return VTX_ERR_INVALID_ARGUMENT;
+    uint32_t* w = vtx::device_status_word();
+    if (!w) return VTX_ERR_CUDA;
+    cudaError_t e = cudaMemcpy(host_bits, w, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && clear) e = cudaMemset(w, 0, sizeof(uint32_t));
+    if (e != cudaSuccess) {
+        vtx::note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
     return VTX_OK;
 }

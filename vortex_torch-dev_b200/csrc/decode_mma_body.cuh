@@ -29,22 +29,65 @@ constexpr size_t decode_mma_smem_bytes() {
     return ring > merge ? ring : merge;
 }
 
+// Order in which a whole page list of np entries is walked: the last entry first (the only page that can
+// be partial, and - like the first entry - one the block-table builder fixes before any page is selected),
+// then entries 0 .. np-2.  Position p of that order is taken by warp p % kDecWarps.
+__device__ __forceinline__ int list_slot(int p, int np) { return p == 0 ? np - 1 : p - 1; }
+
+// Copy of one K or V tile (kDecTileTokens token rows of page `row`, from token tok0) into a ring slot,
+// rows past nvalid_page zero-filled, 16-byte chunks swizzled by (chunk ^ (row & 7)).  One warp.
+template <int D>
+__device__ __forceinline__ void issue_tile(const unsigned char* cache, int row, int P, int tok0, int nvalid_page,
+                                           uint32_t dst, int lane) {
+    constexpr int ROWB = D * 2, CH_PER_ROW = ROWB / 16, CPL = kDecTileTokens * ROWB / 16 / 32;
+    const unsigned char* src = cache + ((int64_t)row * P + tok0) * ROWB;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) {
+        const int ch = c * 32 + lane;
+        const int t = ch / CH_PER_ROW, cr = ch % CH_PER_ROW;
+        vtx::cp_async16(dst + t * ROWB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < nvalid_page);
+    }
+}
+
+// Early start of decode_mma_body for a caller that knows the rows of the list's last entry (row_last)
+// and first entry (row_first) before the rest of the list exists: warp 0 (position 0 = last entry) and
+// warp 1 (position 1 = first entry) put the first K and V tiles of those pages in flight, exactly the two
+// copy groups the body would otherwise start with.  have_last / have_first say which of the two rows is
+// already final.  Returns true for a warp that issued (pass it on as `pre_issued`).  The caller must not
+// touch the first two ring slots of warps 0 and 1, nor commit or wait for copy groups, until the body runs.
+template <int G, int D>
+__device__ __forceinline__ bool decode_mma_prefetch(const DecodeArgs& a, unsigned char* smem_raw, const int np,
+                                                    const int last_len, const int row_last, const int row_first,
+                                                    const bool have_last, const bool have_first) {
+    constexpr int TILE_BYTES = kDecTileTokens * D * 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp >= 2 || np < 2) return false;
+    if (warp == 0 ? !have_last : !have_first) return false;
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_raw + (size_t)warp * kDecSlots * TILE_BYTES);
+    const int row = warp == 0 ? row_last : row_first;
+    const int nvalid_page = warp == 0 ? last_len : a.P;
+    issue_tile<D>(reinterpret_cast<const unsigned char*>(a.k), row, a.P, 0, nvalid_page, ring, lane);
+    vtx::cp_async_commit();
+    issue_tile<D>(reinterpret_cast<const unsigned char*>(a.v), row, a.P, 0, nvalid_page, ring + TILE_BYTES, lane);
+    vtx::cp_async_commit();
+    return true;
+}
+
 // Body of the bf16 tensor-core decode for segment s; smem_raw: the CTA's dynamic shared memory
 // (decode_mma_smem_bytes<G, D>() bytes, 128-byte aligned).  Called by all kDecWarps * 32 threads.
-// pg_lo / pg_cnt: the part of the segment's page list this CTA attends to (whole list: 0 / -1).
+// pg_lo / pg_cnt: the part of the segment's page list this CTA attends to (whole list: 0 / -1; a whole
+// list is walked in the order of list_slot, a part in list order).
 // partial: null -> the normalised result goes to a.out; else the CTA's un-normalised state goes to
 // partial[g * (D + 2) + {0..D-1: sum of p*V, D: running max (log2 domain), D+1: sum of p}] (split-KV).
+// pre_issued (warp-uniform): this warp's first two copy groups were started by decode_mma_prefetch.
 template <int G, int D>
 __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned char* smem_raw, const int s,
                                                 const int pg_lo = 0, const int pg_cnt = -1,
-                                                float* partial = nullptr) {
+                                                float* partial = nullptr, const bool pre_issued = false) {
     using T = __nv_bfloat16;
     constexpr int KSTEPS = D / 16;                 // k-steps of QK^T == 16-dim tiles of the output
     constexpr int ROWB = D * 2;                    // bytes per token row
-    constexpr int CH_PER_ROW = ROWB / 16;
     constexpr int TILE_BYTES = kDecTileTokens * ROWB;
-    constexpr int CHUNKS = TILE_BYTES / 16;
-    constexpr int CPL = CHUNKS / 32;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int gid = lane >> 2, tid = lane & 3;
@@ -77,35 +120,32 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
     float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
     uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
 
-    const int np_local = pg_cnt < 0 ? npages : pg_cnt;
+    const bool whole = pg_cnt < 0;
+    const int np_local = whole ? npages : pg_cnt;
     const int my_pages = np_local > warp ? (np_local - warp + kDecWarps - 1) / kDecWarps : 0;
     const int n_items = my_pages * tiles_per_page * 2;
     const unsigned char* kc = reinterpret_cast<const unsigned char*>(a.k);
     const unsigned char* vc = reinterpret_cast<const unsigned char*>(a.v);
+    // list entry of this warp's page number po
+    auto entry_of = [&](int po) { return whole ? list_slot(warp + kDecWarps * po, npages) : pg_lo + warp + kDecWarps * po; };
     int id_base = 0;
-    int id_reg = (lane < my_pages) ? a.indices[beg + pg_lo + warp + kDecWarps * lane] : 0;
+    int id_reg = (lane < my_pages) ? a.indices[beg + entry_of(lane)] : 0;
 
     auto issue = [&](int item) {
         const int pair = item >> 1;
         const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
         const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
-        const int pg = warp + kDecWarps * po;
-        const int nvalid_page = (pg_lo + pg == npages - 1) ? last_len : P;
-        const int tok0 = tile * kDecTileTokens;
-        const unsigned char* src = ((item & 1) ? vc : kc) + ((int64_t)row * P + tok0) * ROWB;
-        const uint32_t dst = my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES);
-#pragma unroll
-        for (int c = 0; c < CPL; ++c) {
-            const int ch = c * 32 + lane;
-            const int t = ch / CH_PER_ROW, cr = ch % CH_PER_ROW;
-            vtx::cp_async16(dst + t * ROWB + ((cr ^ (t & 7)) << 4), src + (size_t)ch * 16, tok0 + t < nvalid_page);
-        }
+        const int nvalid_page = (entry_of(po) == npages - 1) ? last_len : P;
+        issue_tile<D>((item & 1) ? vc : kc, row, P, tile * kDecTileTokens, nvalid_page,
+                      my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES), lane);
     };
 
+    if (!pre_issued) {
 #pragma unroll
-    for (int i = 0; i < kDecSlots - 1; ++i) {
-        if (i < n_items) issue(i);
-        vtx::cp_async_commit();
+        for (int i = 0; i < kDecSlots - 1; ++i) {
+            if (i < n_items) issue(i);
+            vtx::cp_async_commit();
+        }
     }
 
     // ldmatrix row address of this lane inside a tile: token row and which chunk of the pair
@@ -121,7 +161,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
                 const int po = (nxt >> 1) / tiles_per_page;
                 if (po - id_base >= 32) {
                     id_base += 32;
-                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + pg_lo + warp + kDecWarps * (id_base + lane)] : 0;
+                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + entry_of(id_base + lane)] : 0;
                 }
                 issue(nxt);
             }
@@ -131,8 +171,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
         if ((item & 1) == 0) {
             const int pair = item >> 1;
             const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
-            const int pg = warp + kDecWarps * po;
-            const int nvalid = ((pg_lo + pg == npages - 1) ? last_len : P) - tile * kDecTileTokens;
+            const int nvalid = ((entry_of(po) == npages - 1) ? last_len : P) - tile * kDecTileTokens;
             float st[2][4];
 #pragma unroll
             for (int j = 0; j < 2; ++j)

@@ -1,0 +1,771 @@
+// Device code shared by the indexer kernels and the one-launch sparse layer kernels.
+//
+//
+// One CTA (4 warps) per (request, head) segment.  The fused kernel keeps the segment's scores in
+// shared memory as sortable keys, so they never travel to HBM; the stand-alone GeMV and top-k
+// kernels exist for flows that call the operators one by one and produce the same bits.
+// Behaviour follows flow/algorithms.py:168-170, indexer/triton_kernels/mv_impl.py:53-62 and
+// csrc/topk.cu:56-113 of the reference.
+//
+// Canonical score arithmetic (shared with the CPU checker, so selections are bit-exact):
+//   q_mean[d] = round_T( (q[0][d] + q[1][d] + ... in fp32, from +0.0) / G )
+//   product   = round_T( centroid[d] * q_mean[d] )          (one rounding of the exact product)
+//   the D dims are cut in chunks of 8; L = min(32, pow2ceil(D/8)) partial sums; partial l adds the
+//   products of chunks l, l+L, ... one by one in ascending order into an fp32 accumulator
+//   starting at +0.0 (no FMA); partials are folded v[i] += v[i+w], w = L/2 .. 1;
+//   score = round_T(sum).
+// Selection order: score descending, ties by ascending candidate position (a stable
+// descending sort), -0.0 equal to +0.0.
+//
+// Data movement: centroid rows are gathered global -> shared with 16-byte cp.async into a ring
+// per warp (16 rows per slot, two slots in flight while one is scored), so no registers stage
+// the loads and the only block-wide barriers are before and after the gather.  Two threads
+// score one row: the thread of parity p owns the partial sums of parity p, which keeps every
+// fold level but the last inside a thread (one shuffle per row).  Rows are stored with their
+// 16-byte pieces swizzled (piece ^ 2*(row & 3)) so the 128-bit shared loads are conflict-free.
+// The sort is a bitonic network over registers (4..16 keys per thread): strides below the
+// per-thread block are register swaps, strides inside a warp are shuffles, and only the three
+// widest strides cross warps through shared memory.
+#pragma once
+#include "decode_mma_body.cuh"
+#include "vtx_common.cuh"
+
+namespace vtxidx {
+
+struct IndexerArgs {
+    const void* q;          // [eff_bs, G, D]
+    const void* centroids;  // [rows, D]
+    const void* centroids2; // MODE 3: second summary cache (per-page minimum); centroids is the maximum
+    void* scores;           // packed, GEMV mode only
+    const int32_t* dense_indptr;
+    const int32_t* sparse_indptr;
+    const int32_t* dense_indices;
+    int32_t* sparse_indices;
+    int32_t* sparse_pt;
+    int64_t pt_stride;
+    int G, D, K, bos, eos, key_cap;
+    float scale;  // MODE 2: softmax scale
+    // A segment with more than `chunk` candidates is scanned by several CTAs (blockIdx.x = chunk number):
+    // each keeps the K best keys of its chunk in part_keys, counts itself in tickets[segment], and the CTA
+    // that arrives last sorts the union (its first K are the segment's first K: keys are unique and the
+    // order is total).  chunk == 0: one CTA per segment.
+    int chunk = 0, nch_max = 1;
+    void* part_keys = nullptr;     // [eff_bs][nch_max][K] keys
+    int32_t* tickets = nullptr;    // [eff_bs], zero between launches
+    uint32_t* status = nullptr;    // sticky device status word (VTX_STATUS_* bits)
+};
+
+// New-token write for one segment, optional part of the fused sparse-layer kernel (all pointers null
+// when unused).  Same arithmetic as set_kv_cmean_kernel in cache_ops.cu.
+struct AppendArgs {
+    __nv_bfloat16* k_cache;
+    __nv_bfloat16* v_cache;
+    __nv_bfloat16* centroids;    // page mean of K; with QUEST: per-dim page maximum
+    __nv_bfloat16* centroids2;   // QUEST only: per-dim page minimum
+    const __nv_bfloat16* new_k;  // [bs, H, D]
+    const __nv_bfloat16* new_v;
+    const int64_t* loc;          // [bs]
+    int H, P;
+};
+
+}  // namespace vtxidx
+
+namespace {
+
+using vtxidx::AppendArgs;
+using vtxidx::IndexerArgs;
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxCandidates = 16384;
+constexpr int kRowsPerSlot = 16;
+
+// ---- sortable keys: high bits order the score, low bits make lower positions win ties ----
+template <typename T>
+struct KeyOf;
+
+template <>
+struct KeyOf<__nv_bfloat16> {
+    using type = uint32_t;
+    static __device__ __forceinline__ type make(float v, int i) {
+        uint32_t b = __float_as_uint(v) >> 16;  // v is bf16-representable
+        if (b == 0x8000u) b = 0u;               // -0.0 sorts as +0.0
+        const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);
+        return (ord << 16) | (0xffffu - (uint32_t)i);
+    }
+    static __device__ __forceinline__ int index(type k) { return (int)(0xffffu - (k & 0xffffu)); }
+};
+
+template <>
+struct KeyOf<float> {
+    using type = unsigned long long;
+    static __device__ __forceinline__ type make(float v, int i) {
+        uint32_t b = __float_as_uint(v);
+        if (b == 0x80000000u) b = 0u;
+        const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+        return ((type)ord << 32) | (type)(0xffffffffu - (uint32_t)i);
+    }
+    static __device__ __forceinline__ int index(type k) { return (int)(0xffffffffu - (uint32_t)(k & 0xffffffffull)); }
+};
+
+// Descending bitonic sort of n (power of two) keys in shared memory by the whole CTA
+// (general fallback for segments with more than 2048 candidates).
+template <typename Key>
+__device__ void block_bitonic_desc(Key* keys, int n) {
+    for (int k = 2; k <= n; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < (n >> 1); i += kThreads) {
+                const int a = 2 * i - (i & (j - 1));
+                const int b = a + j;
+                const Key ka = keys[a], kb = keys[b];
+                const bool desc = (a & k) == 0;
+                if ((ka < kb) == desc) {
+                    keys[a] = kb;
+                    keys[b] = ka;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Descending bitonic sort of kThreads * EPT keys held EPT per thread, element e = thread * EPT + r.
+// xbuf: shared scratch of 2 * kThreads * EPT keys for the strides that cross warps.
+template <typename Key, int EPT>
+__device__ __forceinline__ void block_sort_desc_regs(Key (&v)[EPT], Key* xbuf) {
+    constexpr int N = kThreads * EPT;
+    const int t = threadIdx.x;
+    int buf = 0;
+#pragma unroll
+    for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j < EPT) {
+#pragma unroll
+                for (int r = 0; r < EPT; ++r) {
+                    if ((r & j) == 0) {
+                        const bool desc = (((t * EPT + r) & k) == 0);
+                        const Key x = v[r], y = v[r + j];
+                        const bool sw = (x < y) == desc;
+                        v[r] = sw ? y : x;
+                        v[r + j] = sw ? x : y;
+                    }
+                }
+            } else {
+                const int pt = j / EPT;                    // partner thread = t ^ pt
+                const bool lower = (t & pt) == 0;
+                const bool desc = (((t * EPT) & k) == 0);  // k > j >= EPT: bit k of e comes from t
+                const bool keep_max = lower == desc;
+                if (pt < 32) {
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) {
+                        const Key o = __shfl_xor_sync(0xffffffffu, v[r], pt);
+                        v[r] = keep_max ? (v[r] > o ? v[r] : o) : (v[r] < o ? v[r] : o);
+                    }
+                } else {
+                    Key* mine = xbuf + buf * N + t * EPT;
+                    const Key* theirs = xbuf + buf * N + (t ^ pt) * EPT;
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) mine[r] = v[r];
+                    __syncthreads();
+#pragma unroll
+                    for (int r = 0; r < EPT; ++r) {
+                        const Key o = theirs[r];
+                        v[r] = keep_max ? (v[r] > o ? v[r] : o) : (v[r] < o ? v[r] : o);
+                    }
+                    buf ^= 1;
+                }
+            }
+        }
+    }
+}
+
+// Sort the c keys at `keys` (shared memory, visible to all threads) in descending order and hand the
+// first K of them to emit(position, key); each position is emitted by exactly one thread.
+// xbuf: shared scratch for the register sort, sort_scratch_bytes(c) bytes, or null to force the
+// shared-memory network (which sorts `keys` in place; c may then be any size up to the key capacity).
+template <typename Key, int EPT, typename Emit>
+__device__ __forceinline__ void sort_regs_emit(const Key* keys, int c, int K, Key* xbuf, Emit& emit) {
+    Key v[EPT];
+#pragma unroll
+    for (int r = 0; r < EPT; ++r) {
+        const int e = threadIdx.x * EPT + r;
+        v[r] = e < c ? keys[e] : (Key)0;  // real keys are never 0 for finite scores
+    }
+    block_sort_desc_regs<Key, EPT>(v, xbuf);
+#pragma unroll
+    for (int r = 0; r < EPT; ++r) {
+        const int e = threadIdx.x * EPT + r;
+        if (e < K) emit(e, v[r]);
+    }
+}
+
+// Keys the register sort handles for c candidates (0: the shared-memory network takes over).
+__host__ __device__ inline int sort_width(int c) {
+    return c <= kThreads * 4 ? kThreads * 4 : (c <= kThreads * 8 ? kThreads * 8 : (c <= kThreads * 16 ? kThreads * 16 : 0));
+}
+
+template <typename Key, typename Emit>
+__device__ void sort_emit(Key* keys, int c, int K, Key* xbuf, Emit& emit) {
+    if (xbuf != nullptr && c <= kThreads * 4) return sort_regs_emit<Key, 4>(keys, c, K, xbuf, emit);
+    if (xbuf != nullptr && c <= kThreads * 8) return sort_regs_emit<Key, 8>(keys, c, K, xbuf, emit);
+    if (xbuf != nullptr && c <= kThreads * 16) return sort_regs_emit<Key, 16>(keys, c, K, xbuf, emit);
+    const int n = vtx::pow2_ceil(c);
+    for (int i = c + threadIdx.x; i < n; i += kThreads) keys[i] = (Key)0;
+    __syncthreads();
+    block_bitonic_desc<Key>(keys, n);
+    for (int j = threadIdx.x; j < K; j += kThreads) emit(j, keys[j]);
+}
+
+
+template <typename T>
+__device__ __forceinline__ float load_score(const T* p);
+template <>
+__device__ __forceinline__ float load_score<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <>
+__device__ __forceinline__ float load_score<float>(const float* p) { return *p; }
+
+template <typename T>
+__device__ __forceinline__ void store_score(T* p, float v);
+template <>
+__device__ __forceinline__ void store_score<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+template <>
+__device__ __forceinline__ void store_score<float>(float* p, float v) { *p = v; }
+
+
+// ---- asynchronous row gather ----
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr, bool valid) {
+    const int src_bytes = valid ? 16 : 0;  // 0 => zero-fill, the source is not read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr), "l"(gptr), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// ---- one chunk (8 dims) of products added one by one into acc ----
+// bf16: the packed multiply rounds each exact product once to bf16, as the canonical order asks.
+__device__ __forceinline__ void add_products(float& acc, const __nv_bfloat16* row_chunk, const __nv_bfloat16* q_chunk) {
+    const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
+    const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&rr[i]),
+                                         *reinterpret_cast<const __nv_bfloat162*>(&qq[i]));
+        const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p);
+        acc = __fadd_rn(acc, vtx::bf16lo(pw));
+        acc = __fadd_rn(acc, vtx::bf16hi(pw));
+    }
+}
+__device__ __forceinline__ void add_products(float& acc, const float* row_chunk, const float* q_chunk) {
+    const float4 r0 = *reinterpret_cast<const float4*>(row_chunk), r1 = *reinterpret_cast<const float4*>(row_chunk + 4);
+    const float4 q0 = *reinterpret_cast<const float4*>(q_chunk), q1 = *reinterpret_cast<const float4*>(q_chunk + 4);
+    acc = __fadd_rn(acc, __fmul_rn(r0.x, q0.x));
+    acc = __fadd_rn(acc, __fmul_rn(r0.y, q0.y));
+    acc = __fadd_rn(acc, __fmul_rn(r0.z, q0.z));
+    acc = __fadd_rn(acc, __fmul_rn(r0.w, q0.w));
+    acc = __fadd_rn(acc, __fmul_rn(r1.x, q1.x));
+    acc = __fadd_rn(acc, __fmul_rn(r1.y, q1.y));
+    acc = __fadd_rn(acc, __fmul_rn(r1.z, q1.z));
+    acc = __fadd_rn(acc, __fmul_rn(r1.w, q1.w));
+}
+
+// bf16 row chunk times fp32 query chunk, products kept in fp32 (the GeMM operator's arithmetic).
+__device__ __forceinline__ void add_products_f32(float& acc, const __nv_bfloat16* row_chunk, const float* q_chunk) {
+    const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
+    const float4 q0 = *reinterpret_cast<const float4*>(q_chunk), q1 = *reinterpret_cast<const float4*>(q_chunk + 4);
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.x), q0.x));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.x), q0.y));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.y), q0.z));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.y), q0.w));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.z), q1.x));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.z), q1.y));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.w), q1.z));
+    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.w), q1.w));
+}
+
+// Quest upper bound for one chunk: max(round_bf16(q*hi), round_bf16(q*lo)) per dim, added one by one.
+__device__ __forceinline__ void add_quest_bounds(float& acc, const __nv_bfloat16* hi_chunk, const __nv_bfloat16* lo_chunk,
+                                                 const __nv_bfloat16* q_chunk) {
+    const uint4 h = *reinterpret_cast<const uint4*>(hi_chunk);
+    const uint4 l = *reinterpret_cast<const uint4*>(lo_chunk);
+    const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
+    const uint32_t hh[4] = {h.x, h.y, h.z, h.w}, ll[4] = {l.x, l.y, l.z, l.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 qv = *reinterpret_cast<const __nv_bfloat162*>(&qq[i]);
+        const __nv_bfloat162 u = __hmax2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&hh[i]), qv),
+                                         __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ll[i]), qv));
+        const uint32_t uw = *reinterpret_cast<const uint32_t*>(&u);
+        acc = __fadd_rn(acc, vtx::bf16lo(uw));
+        acc = __fadd_rn(acc, vtx::bf16hi(uw));
+    }
+}
+
+// exp(x) for x <= 0 as a fixed sequence of fp32 operations, identical on CPU and GPU:
+// k = rint(x * log2 e); r = x - k*ln2_hi - k*ln2_lo; degree-6 Taylor polynomial (Horner, separate
+// multiply and add); result = p * 2^k; inputs below -87 give 0.
+__device__ __forceinline__ float exp_canonical(float x) {
+    if (x < -87.0f) return 0.f;
+    const float k = rintf(__fmul_rn(x, 1.44269504f));
+    float r = __fsub_rn(x, __fmul_rn(k, 0.693145751953125f));
+    r = __fsub_rn(r, __fmul_rn(k, 1.42860677e-6f));
+    float p = (float)(1.0 / 720.0);
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 120.0));
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 24.0));
+    p = __fadd_rn(__fmul_rn(p, r), (float)(1.0 / 6.0));
+    p = __fadd_rn(__fmul_rn(p, r), 0.5f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.0f);
+    return __fmul_rn(p, __int_as_float(((int)k + 127) << 23));
+}
+
+template <typename T, int D>
+struct Geom {
+    static constexpr int nchunk = D / 8;  // canonical chunks of 8 dims
+    static constexpr int L = nchunk > 16 ? 32 : (nchunk > 8 ? 16 : (nchunk > 4 ? 8 : 4));
+    static constexpr int row_bytes = D * (int)sizeof(T);
+    static constexpr int pieces = row_bytes / 16;        // 16-byte pieces per row
+    static constexpr int ppc = 8 * (int)sizeof(T) / 16;  // pieces per canonical chunk (1 bf16, 2 fp32)
+    static constexpr int slot_bytes = kRowsPerSlot * row_bytes;
+    static constexpr int slots = slot_bytes * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    static constexpr size_t ring_bytes = (size_t)kWarps * slots * slot_bytes;
+    static_assert(pieces % 8 == 0, "row must be a multiple of 128 bytes");
+    static_assert(nchunk % 2 == 0, "two threads share a row by parity of the partial sums");
+    // the idle ring doubles as the sort's exchange buffer (2 x 2048 keys at most)
+    static_assert(ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
+};
+
+
+// Executed by one warp: lanes 0 .. D/8-1 each own 8 head dims of segment s = request * H + head.
+// Writes the new token's K and V rows and, if the token closes its page, the page's mean of K
+// (rows 0 .. P-2 from the cache in ascending order, the new row last, one division, one rounding).
+// QUEST: the page's per-dim maximum and minimum instead (both exact in bf16), as vtx_creduce computes them.
+template <int D, bool QUEST = false>
+__device__ __forceinline__ void append_token(const AppendArgs& ap, const int s, const int lane) {
+    constexpr int NCH = D / 8;
+    if (lane >= NCH) return;
+    const int r = s / ap.H, h = s - r * ap.H;
+    const int64_t t = ap.loc[r];
+    const int64_t pid = (t / ap.P) * ap.H + h;
+    const int tok = (int)(t % ap.P);
+    __nv_bfloat16* kpage = ap.k_cache + pid * (int64_t)ap.P * D;
+    __nv_bfloat16* vpage = ap.v_cache + pid * (int64_t)ap.P * D;
+    vtx::Vec8<__nv_bfloat16> nk, nv;
+    nk.load_cached(ap.new_k + (int64_t)s * D + lane * 8);
+    nv.load_cached(ap.new_v + (int64_t)s * D + lane * 8);
+    *reinterpret_cast<uint4*>(kpage + (int64_t)tok * D + lane * 8) = nk.raw;
+    *reinterpret_cast<uint4*>(vpage + (int64_t)tok * D + lane * 8) = nv.raw;
+    if (tok != ap.P - 1) return;
+    float acc[8], kf[8];
+    nk.unpack(kf);
+    if (QUEST) {
+        float hi[8], lo[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) hi[j] = lo[j] = kf[j];
+        for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
+            vtx::Vec8<__nv_bfloat16> v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
+                else v[u].raw = nk.raw;  // repeats the new row: neutral for max and min
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                float f[8];
+                v[u].unpack(f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { hi[j] = fmaxf(hi[j], f[j]); lo[j] = fminf(lo[j], f[j]); }
+            }
+        }
+        vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, hi);
+        vtx::store8(ap.centroids2 + pid * (int64_t)D + lane * 8, lo);
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
+        vtx::Vec8<__nv_bfloat16> v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
+            else v[u].zero();
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (r0 + u < ap.P - 1) {
+                float f[8];
+                v[u].unpack(f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+            }
+        }
+    }
+    const float denom = (float)ap.P;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(__fadd_rn(acc[j], kf[j]), denom);
+    vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, acc);
+}
+
+// MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
+// `side_work(warp, lane)` is called once by every thread of a CTA that has work, at a point where its
+// first gather batches are already in flight (or right away for segments that need no selection); the
+// fused layer kernel uses it for the new-token write of one warp.
+struct NoSideWork {
+    __device__ __forceinline__ void operator()(int, int) const {}
+};
+// `pre_sort(n)` is called by every thread right before the sort after which this CTA owns the segment's
+// complete page list (n keys to sort; every ring is idle, all keys are written).  It returns the byte offset
+// in the CTA's shared memory at which the sort may put its sort_scratch_bytes(n) bytes of scratch.
+struct NoPreSort {
+    __device__ __forceinline__ int operator()(int) const { return 0; }
+};
+
+// Emits position e of a sorted key sequence: into the chunk's slot of part_keys, or - for the last sort
+// of a segment - the row id of the candidate the key names into the sparse page list (and block table).
+template <typename T>
+struct EmitSelection {
+    using Key = typename KeyOf<T>::type;
+    bool to_scratch;
+    Key* part;
+    const int32_t* ids;  // candidate position -> row id
+    int32_t* out;
+    int32_t* out_pt;
+    __device__ __forceinline__ void operator()(int e, Key k) const {
+        if (to_scratch) {
+            part[e] = k;
+            return;
+        }
+        const int32_t row = ids[KeyOf<T>::index(k)];
+        out[e] = row;
+        if (out_pt) out_pt[e] = row;
+    }
+};
+
+// MODE 2 (bf16 only, GQ = query heads per KV head): the gqa_block_sparse_attention scores, i.e.
+// per query head the fp32-product dot with the page's row rounded to bf16, a softmax of scale * score over
+// the segment's candidates (canonical exp and sum) rounded to bf16, and the maximum over the heads.
+// Returns true when this CTA leaves with the segment's page list complete (it is the only CTA of the
+// segment, or the last of its chunks to arrive), false when it has nothing more to do for the segment.
+template <typename T, int D, int MODE, typename SideWork = NoSideWork, int GQ = 1, typename PreSort = NoPreSort>
+__device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s, const int j,
+                                             SideWork side_work = SideWork(), PreSort pre_sort = PreSort()) {
+    // MODE 3 (bf16 only): the gqa_quest_sparse_attention scores from two summary caches (per-page max and min):
+    // per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
+    constexpr int NQ = MODE >= 2 ? GQ : 1;                          // score accumulators per row
+    constexpr int NSRC = MODE == 3 ? 2 : 1;                         // summary rows gathered per page
+    constexpr int QBYTES = MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : D * (int)sizeof(T));
+    using Key = typename KeyOf<T>::type;
+    using Gm = Geom<T, D>;
+    constexpr int L = Gm::L, HALF = L / 2;
+    constexpr int SLOT_B = NSRC * Gm::slot_bytes;
+    constexpr int SLOTS = SLOT_B * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
+    // layout: [ring][q_mean][keys][ids]
+    unsigned char* ring = smem_raw;
+    T* qbar = reinterpret_cast<T*>(smem_raw + RING_B);
+    Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + QBYTES);
+    int32_t* ids = reinterpret_cast<int32_t*>(keys + a.key_cap);
+    __nv_bfloat16* sbuf = reinterpret_cast<__nv_bfloat16*>(ids + a.key_cap);  // MODE 2: [candidate][head] scores
+    float* qf32 = reinterpret_cast<float*>(qbar);                               // MODE 2: [head][D]
+    __shared__ int s_last_arrival;
+
+    const int beg = a.dense_indptr[s] + a.bos;
+    const int c = a.dense_indptr[s + 1] - a.eos - beg;  // candidates of the whole segment
+    const bool split = MODE != 2 && a.chunk > 0 && c > a.chunk;
+    const int nch = split ? (c + a.chunk - 1) / a.chunk : 1;
+    if (j >= nch) return false;
+    if (c <= a.K) {  // nothing to select: the block-table builder already wrote the whole list
+        side_work(threadIdx.x >> 5, threadIdx.x & 31);
+        return true;
+    }
+    if (split ? nch > a.nch_max : (MODE != 1 && c > a.key_cap)) {
+        // More candidates than the caller's max_num_pages_per_request promised: shared memory (or the grid)
+        // cannot hold them.  Flag it and select the first K candidates so that the list stays well defined.
+        if (j != 0) return false;
+        side_work(threadIdx.x >> 5, threadIdx.x & 31);
+        if (threadIdx.x == 0 && a.status) atomicOr(a.status, (uint32_t)VTX_STATUS_CANDIDATE_OVERFLOW);
+        if (MODE != 1) {
+            const int o0 = a.sparse_indptr[s] + a.bos;
+            for (int e = threadIdx.x; e < a.K; e += kThreads) {
+                const int32_t row = a.dense_indices[beg + e];
+                a.sparse_indices[o0 + e] = row;
+                if (a.sparse_pt) a.sparse_pt[(int64_t)s * a.pt_stride + a.bos + e] = row;
+            }
+        }
+        return true;
+    }
+    const int lo = split ? j * a.chunk : 0;             // this CTA's candidates: [lo, lo + cnt)
+    const int cnt = split ? min(a.chunk, c - lo) : c;
+    const int32_t* row_ids = a.dense_indices + beg + lo;
+    if (MODE != 1) {
+        for (int i = threadIdx.x; i < cnt; i += kThreads) ids[i] = row_ids[i];
+        row_ids = ids;
+    }
+    __syncthreads();  // row ids are staged
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
+    unsigned char* my_ring = ring + (size_t)warp * SLOTS * SLOT_B;
+    const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
+    const unsigned char* cent = reinterpret_cast<const unsigned char*>(a.centroids);
+    const unsigned char* cent2 = reinterpret_cast<const unsigned char*>(a.centroids2);
+    const int n_batches = (cnt + kRowsPerSlot - 1) / kRowsPerSlot;
+    const int my_batches = n_batches > warp ? (n_batches - warp + kWarps - 1) / kWarps : 0;
+    constexpr int pieces_per_slot = kRowsPerSlot * Gm::pieces;
+
+    auto issue = [&](int ord) {
+        const int row0 = (warp + ord * kWarps) * kRowsPerSlot;
+        const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * SLOT_B);
+#pragma unroll
+        for (int pc = lane; pc < pieces_per_slot; pc += 32) {
+            const int r = pc / Gm::pieces, pr = pc - r * Gm::pieces;
+            const int i = row0 + r;
+            const bool valid = i < cnt;
+            const int64_t row = valid ? row_ids[i] : 0;
+            const uint32_t off = r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4);
+            cp_async16(dst + off, cent + row * Gm::row_bytes + pr * 16, valid);
+            if (NSRC == 2) cp_async16(dst + Gm::slot_bytes + off, cent2 + row * Gm::row_bytes + pr * 16, valid);
+        }
+    };
+
+#pragma unroll
+    for (int i = 0; i < SLOTS - 1; ++i) {
+        if (i < my_batches) issue(i);
+        cp_async_commit();
+    }
+    side_work(warp, lane);
+    if (MODE == 3) {  // the group's query heads as they are
+        const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
+        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
+    }
+    if (MODE == 2) {  // the group's query heads, widened to fp32
+        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
+        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
+            vtx::Vec8<T> v;
+            v.load_cached(qs + ch * 8);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) qf32[ch * 8 + jj] = f[jj];
+        }
+    }
+    // grouped-query mean, one canonical chunk per thread
+    for (int ch = threadIdx.x; MODE < 2 && ch < Gm::nchunk; ch += kThreads) {
+        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
+        float acc[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
+        for (int g = 0; g < a.G; ++g) {
+            vtx::Vec8<T> v;
+            v.load_cached(qs + (int64_t)g * D);
+            float f[8];
+            v.unpack(f);
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) acc[jj] = __fadd_rn(acc[jj], f[jj]);
+        }
+        const float g_f = (float)a.G;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) acc[jj] = __fdiv_rn(acc[jj], g_f);
+        vtx::store8(qbar + ch * 8, acc);  // rounds once to T
+    }
+    __syncthreads();  // q_mean is staged
+    for (int ord = 0; ord < my_batches; ++ord) {
+        cp_async_wait<SLOTS - 2>();
+        __syncwarp();
+        if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
+        cp_async_commit();
+        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
+        const int sw = (r_in & 3) << 1;
+        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;  // position inside this CTA's chunk
+        float best = -INFINITY;  // MODE 3: running maximum over the heads
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) {
+            float acc[HALF];
+#pragma unroll
+            for (int ii = 0; ii < HALF; ++ii) acc[ii] = 0.f;
+            // this thread owns partial sums 2*ii + par; partial l takes chunks l, l + L, ...
+#pragma unroll
+            for (int k = 0; k * L < Gm::nchunk; ++k) {
+#pragma unroll
+                for (int ii = 0; ii < HALF; ++ii) {
+                    if (k * L + 2 * ii < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
+                        const int ch = k * L + 2 * ii + par;
+                        // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
+                        const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
+                        if constexpr (MODE == 3)
+                            add_quest_bounds(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             reinterpret_cast<const __nv_bfloat16*>(
+                                                 reinterpret_cast<const unsigned char*>(src) + Gm::slot_bytes),
+                                             reinterpret_cast<const __nv_bfloat16*>(qbar) + g * D + ch * 8);
+                        else if constexpr (MODE == 2)
+                            add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             qf32 + g * D + ch * 8);
+                        else
+                            add_products(acc[ii], src, qbar + ch * 8);
+                    }
+                }
+            }
+#pragma unroll
+            for (int w = HALF / 2; w > 0; w >>= 1)
+#pragma unroll
+                for (int ii = 0; ii < w; ++ii) acc[ii] = __fadd_rn(acc[ii], acc[ii + w]);
+            const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
+            if (par == 0 && i < cnt) {
+                const float sc = vtx::round_to<T>(total);
+                if (MODE == 0) keys[i] = KeyOf<T>::make(sc, lo + i);
+                else if (MODE == 2) sbuf[i * NQ + g] = __float2bfloat16_rn(sc);
+                else if (MODE == 3) best = fmaxf(best, sc);
+                else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + lo + i, sc);
+            }
+        }
+        if (MODE == 3 && par == 0 && i < cnt) keys[i] = KeyOf<T>::make(best, lo + i);
+    }
+    cp_async_wait<0>();
+    if constexpr (MODE == 2) {
+        __syncthreads();  // all head scores written; the rings are idle and lend their space to the reductions
+        float* red = reinterpret_cast<float*>(ring);  // [NQ][kThreads]
+        float mx[NQ], l[NQ];
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) mx[g] = -INFINITY;
+        for (int i = threadIdx.x; i < c; i += kThreads)
+#pragma unroll
+            for (int g = 0; g < NQ; ++g)
+                mx[g] = fmaxf(mx[g], __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale));
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) red[g * kThreads + threadIdx.x] = mx[g];
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) {
+            float m = red[g * kThreads];
+            for (int t = 1; t < kThreads; ++t) m = fmaxf(m, red[g * kThreads + t]);
+            mx[g] = m;
+        }
+        __syncthreads();
+        // sum of exp: partial t takes candidates t, t + 128, ... in ascending order, then halves are folded
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) l[g] = 0.f;
+        for (int i = threadIdx.x; i < c; i += kThreads)
+#pragma unroll
+            for (int g = 0; g < NQ; ++g) {
+                const float t = __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale);
+                l[g] = __fadd_rn(l[g], exp_canonical(__fsub_rn(t, mx[g])));
+            }
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) red[g * kThreads + threadIdx.x] = l[g];
+        __syncthreads();
+        for (int w = kThreads / 2; w > 0; w >>= 1) {
+            if (threadIdx.x < w)
+#pragma unroll
+                for (int g = 0; g < NQ; ++g)
+                    red[g * kThreads + threadIdx.x] =
+                        __fadd_rn(red[g * kThreads + threadIdx.x], red[g * kThreads + threadIdx.x + w]);
+            __syncthreads();
+        }
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) l[g] = red[g * kThreads];
+        for (int i = threadIdx.x; i < c; i += kThreads) {
+            float best = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < NQ; ++g) {
+                const float t = __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale);
+                const float pr = __fdiv_rn(exp_canonical(__fsub_rn(t, mx[g])), l[g]);
+                best = fmaxf(best, vtx::round_to<T>(pr));
+            }
+            keys[i] = KeyOf<T>::make(best, i);
+        }
+    }
+    if (MODE != 1) {
+        __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
+        const int o0 = a.sparse_indptr[s] + a.bos;
+        Key* part = reinterpret_cast<Key*>(a.part_keys) + ((size_t)s * a.nch_max) * a.K;  // this segment's chunks
+        EmitSelection<T> emit;
+        emit.part = part + (size_t)j * a.K;
+        emit.ids = split ? a.dense_indices + beg : ids;  // keys name candidates by their position in the segment
+        emit.out = a.sparse_indices + o0;
+        emit.out_pt = a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr;
+        int n_sort = cnt;
+        bool partial = split;
+        for (;;) {
+            const int xoff = partial ? 0 : pre_sort(n_sort);
+            emit.to_scratch = partial;
+            sort_emit<Key>(keys, n_sort, a.K, reinterpret_cast<Key*>(smem_raw + xoff), emit);
+            if (!partial) break;
+            // publish this chunk's keys, then find out whether every other chunk of the segment is in
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const int t = atomicAdd(a.tickets + s, 1);
+                const int last = t == nch - 1;
+                if (last) a.tickets[s] = 0;  // every chunk has counted itself: ready for the next launch
+                __threadfence();
+                s_last_arrival = last;
+            }
+            __syncthreads();
+            if (!s_last_arrival) return false;
+            n_sort = nch * a.K;
+            for (int i = threadIdx.x; i < n_sort; i += kThreads) keys[i] = __ldcg(part + i);
+            __syncthreads();
+            partial = false;
+        }
+    }
+    return true;
+}
+
+template <typename Kern>
+int set_smem(Kern kern, size_t bytes) {
+    if (bytes > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) {
+            vtx::note_cuda_error(e);
+            return VTX_ERR_CUDA;
+        }
+    }
+    return VTX_OK;
+}
+
+int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int bos, int eos, int maxp,
+                 int dtype) {
+    if (!dip || !din) return VTX_ERR_INVALID_ARGUMENT;
+    if (eff_bs < 0 || K < 1 || bos < 0 || eos < 0 || maxp < 1) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    if (maxp > kMaxCandidates) return VTX_ERR_UNSUPPORTED;
+    return VTX_OK;
+}
+
+// Candidate capacity of one segment (sizes the key and row-id arrays in shared memory).
+int key_capacity(int max_pages) { return vtx::pow2_ceil(max_pages); }
+
+// Candidates one CTA scans when a workspace allows a segment's scan to be split.
+constexpr int kChunk = 512;
+
+int split_chunks(int max_pages, int bos, int eos) {
+    const int cand = max_pages - bos - eos;
+    return cand > kChunk ? (cand + kChunk - 1) / kChunk : 1;
+}
+
+int64_t split_workspace_bytes(int eff_bs, int max_pages, int K, int bos, int eos) {
+    const int nch = split_chunks(max_pages, bos, eos);
+    if (nch == 1) return 0;
+    const int64_t tickets = ((int64_t)eff_bs * 4 + 255) / 256 * 256;
+    return tickets + (int64_t)eff_bs * nch * K * 8;  // keys are at most 8 bytes
+}
+
+// Fill the split fields of `a` (and shrink its key capacity to one chunk) when the caller's workspace
+// allows it; otherwise leave the one-CTA-per-segment form.
+void plan_split(IndexerArgs& a, int eff_bs, int max_pages, void* workspace, int64_t workspace_bytes) {
+    a.status = vtx::device_status_word();
+    const int nch = split_chunks(max_pages, a.bos, a.eos);
+    if (workspace == nullptr || nch == 1) return;
+    if (workspace_bytes < split_workspace_bytes(eff_bs, max_pages, a.K, a.bos, a.eos)) return;
+    a.chunk = kChunk;
+    a.nch_max = nch;
+    a.key_cap = vtx::pow2_ceil(nch * a.K > kChunk ? nch * a.K : kChunk);
+    a.tickets = reinterpret_cast<int32_t*>(workspace);
+    a.part_keys = reinterpret_cast<unsigned char*>(workspace) + ((int64_t)eff_bs * 4 + 255) / 256 * 256;
+}
+
+}  // namespace

@@ -1,0 +1,96 @@
+// The one-launch sparse layer kernel (token write + page selection + attention); instantiated per score
+// mode in sparse_layer_m0.cu / _m2.cu / _m3.cu so that the modes compile in parallel.
+#pragma once
+#include "indexer_body.cuh"
+
+namespace {
+
+// One launch per sparse layer: page selection, then attention over the selected pages, by the same CTA.
+// The decode phase of one segment overlaps the scan phase of its neighbours on the SM, so neither phase
+// pays its own launch and ramp-up; the selected rows still go to the sparse page list (the decode reads
+// them back after the block barrier).  bf16 only (the decode phase is the tensor-core body).
+// Grid (chunks, segments): a segment with more than ia.chunk candidates is scanned by several CTAs and the
+// one that arrives last merges their best keys and runs the decode phase (see IndexerArgs); the others exit.
+// With a token to append (ap.loc set) the segment's first CTA writes the new token (and the centroid of the page it closes):
+// the page is the segment's last one, which is never a candidate (eos >= 1), and the decode phase reads
+// it only after block barriers (and, across CTAs, after the arrival counter), so the write needs no kernel
+// of its own.
+// With `early` set the CTA stages its row ids and starts its first centroid gathers before it waits for the
+// preceding launch: those reads touch only the block-table builder's outputs and this layer's summary rows of
+// non-reserved pages, which no launch between the builder and this one writes.  Everything else (q, the
+// token write, the sparse list, the scratch of a split segment, the output) comes after the wait.
+// While the keys are sorted the memory system would idle: the CTA that will run the decode phase puts the
+// K and V tiles of the reserved pages it already knows (the list's last and first entry) in flight before
+// the sort, and leaves the sort's scratch to the ring space of the two warps that hold no such tile.
+// MODE 0: scores of the block_sparse_attention flow (group mean . centroid); MODE 2: scores of the
+// gqa_block_sparse_attention flow (per-head product, softmax over pages, maximum over heads) on the same
+// centroid cache, so the token write is the same too; MODE 3: scores of the gqa_quest_sparse_attention flow
+// from the per-page maximum and minimum caches, which the token write then maintains instead of the mean
+// (twice the summary bytes per page: two CTAs per SM instead of four).
+template <int D, int G, int MODE = 0>
+__global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
+                                                                  AppendArgs ap, const int early) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    if (!early) vtx::pdl_wait();
+    vtx::pdl_trigger();
+    const int seg = blockIdx.y, chunk_no = blockIdx.x;
+    // what the early start of the decode phase needs, all of it written by the block-table builder
+    const int dbeg = ia.dense_indptr[seg], dend = ia.dense_indptr[seg + 1];
+    const int np = da.indptr[seg + 1] - da.indptr[seg];
+    const int last_len = da.last_len[seg];
+    const int row_first = dend > dbeg ? ia.dense_indices[dbeg] : 0;
+    const int row_last = dend > dbeg ? ia.dense_indices[dend - 1] : 0;
+    bool pre_issued = false;
+    auto side = [&](int warp, int lane) {
+        if (early) vtx::pdl_wait();
+        if (ap.loc != nullptr && chunk_no == 0 && warp == kWarps - 1) append_token<D, MODE == 3>(ap, seg, lane);
+    };
+    auto pre_sort = [&](int n_sort) -> int {
+        constexpr int kTile = vtxdec::kDecTileTokens * D * 2;
+        constexpr int kFree = 2 * vtxdec::kDecSlots * kTile;  // ring space of decode warps 2 and 3
+        if (2 * sort_width(n_sort) * (int)sizeof(uint32_t) > kFree) return 0;
+        pre_issued = vtxdec::decode_mma_prefetch<G, D>(da, smem_raw, np, last_len, row_last, row_first, ia.eos >= 1,
+                                                       ia.bos >= 1);
+        return kFree;
+    };
+    const bool owner = indexer_body<__nv_bfloat16, D, MODE, decltype(side), (MODE >= 2 ? G : 1), decltype(pre_sort)>(
+        ia, smem_raw, seg, chunk_no, side, pre_sort);
+    if (!owner) return;
+    __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
+    vtxdec::decode_mma_body<G, D>(da, smem_raw, seg, 0, -1, nullptr, pre_issued);
+}
+
+template <int D, int G, int MODE>
+int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
+                            bool early, cudaStream_t st) {
+    using Gm = Geom<__nv_bfloat16, D>;
+    static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
+    constexpr int quest_slot_b = 2 * Gm::slot_bytes;
+    constexpr int quest_slots = quest_slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    size_t bytes = MODE == 2 ? Gm::ring_bytes + (size_t)G * D * 4 +
+                                   (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + G * sizeof(__nv_bfloat16))
+                   : MODE == 3 ? (size_t)kWarps * quest_slots * quest_slot_b + (size_t)G * D * 2 +
+                                     (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t))
+                               : Gm::ring_bytes + Gm::row_bytes + (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
+    const size_t dec = vtxdec::decode_mma_smem_bytes<G, D>();
+    if (dec > bytes) bytes = dec;
+    if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
+    auto kern = sparse_layer_kernel<D, G, MODE>;
+    int rc = set_smem(kern, bytes);
+    if (rc != VTX_OK) return rc;
+    return vtx::launch(kern, dim3(ia.nch_max, eff_bs), dim3(kThreads), bytes, st, ia, da, ap, early ? 1 : 0);
+}
+
+template <int D, int MODE>
+int launch_sparse_layer_d(const IndexerArgs& ia, const vtxdec::DecodeArgs& da, const AppendArgs& ap, int eff_bs,
+                          int group, bool early, cudaStream_t st) {
+    switch (group) {
+        case 1: return launch_sparse_layer_cfg<D, 1, MODE>(ia, da, ap, eff_bs, early, st);
+        case 2: return launch_sparse_layer_cfg<D, 2, MODE>(ia, da, ap, eff_bs, early, st);
+        case 4: return launch_sparse_layer_cfg<D, 4, MODE>(ia, da, ap, eff_bs, early, st);
+        case 8: return launch_sparse_layer_cfg<D, 8, MODE>(ia, da, ap, eff_bs, early, st);
+        default: return VTX_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace

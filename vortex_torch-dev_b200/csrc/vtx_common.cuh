@@ -30,7 +30,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 bool programmatic_launch_enabled();
-int programmatic_launch_mode();  // 0 off, 1 on, 2 on and kernels may run their read-only prologue before waiting
+uint32_t* device_status_word();  // device address of the sticky status word on the current device, or null
 
 template <typename... KArgs, typename... Args>
 inline int launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

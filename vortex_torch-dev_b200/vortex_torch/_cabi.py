@@ -59,6 +59,32 @@ for _name, _args in SIGNATURES.items():
     _fn = getattr(lib, _name)
     _fn.argtypes = _args
     _fn.restype = _i
+
+
+class SparseLayerParams(C.Structure):
+    """``vtx_sparse_layer_params`` of the header, field for field."""
+    _fields_ = ([(n, _p) for n in ("q", "summary", "summary2", "k_cache", "v_cache", "out", "new_k", "new_v", "loc",
+                                    "dense_kv_indptr", "sparse_kv_indptr", "dense_kv_indices", "sparse_kv_indices",
+                                    "kv_last_page_len", "workspace")]
+                + [("workspace_bytes", _i64)]
+                + [(n, C.c_int32) for n in ("eff_batch_size", "group_size", "head_dim", "page_size", "num_kv_heads",
+                                             "topk_val", "page_reserved_bos", "page_reserved_eos",
+                                             "max_num_pages_per_request", "score_mode", "flags", "dtype")]
+                + [("sm_scale", _f), ("softmax_scale", _f)])
+
+
+SCORE_MEAN_DOT, SCORE_GQA_SOFTMAX, SCORE_QUEST = 0, 2, 3
+LAYER_EARLY_PROLOGUE = 1
+STATUS_CANDIDATE_OVERFLOW, STATUS_BAD_ROW = 1, 2
+
+lib.vtx_sparse_layer.argtypes = [C.POINTER(SparseLayerParams), _p]
+lib.vtx_sparse_layer.restype = _i
+lib.vtx_sparse_layer_workspace_bytes.argtypes = [_i, _i, _i, _i, _i]
+lib.vtx_sparse_layer_workspace_bytes.restype = _i64
+lib.vtx_device_status_word.argtypes = []
+lib.vtx_device_status_word.restype = _p
+lib.vtx_device_status_read.argtypes = [_p, _i]
+lib.vtx_device_status_read.restype = _i
 lib.vtx_decode_gqa_splitkv_workspace_bytes.argtypes = [_i, _i, _i, _i]
 lib.vtx_decode_gqa_splitkv_workspace_bytes.restype = _i64
 lib.vtx_mla_fault_word.argtypes = []
@@ -72,13 +98,30 @@ lib.vtx_last_cuda_error.restype = C.c_char_p
 
 EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error",
                                     "vtx_set_programmatic_launch", "vtx_decode_gqa_splitkv_workspace_bytes",
-                                    "vtx_mla_fault_word"])
+                                    "vtx_mla_fault_word", "vtx_sparse_layer", "vtx_sparse_layer_workspace_bytes",
+                                    "vtx_device_status_word", "vtx_device_status_read"])
 
 
 def set_programmatic_launch(mode) -> None:
-    """0/False off, 1/True on, 2 on with the fused layer kernel's read-only prologue ahead of its wait
-    (see the header for the condition under which 2 is safe).  Results are unchanged in every mode."""
+    """0/False off, anything else on (kernels are chained by programmatic dependent launch; each still waits
+    for its whole predecessor).  Results are unchanged.  The early prologue of the fused layer kernel is a
+    per-call flag of ``sparse_layer_fused`` (``early_prologue``)."""
     lib.vtx_set_programmatic_launch(int(mode))
+
+
+def device_status(clear: bool = False) -> int:
+    """The sticky status word of the kernels on the current device (``STATUS_*`` bits; 0 = nothing to report).
+    Synchronises with the device."""
+    host = C.c_uint32(0xFFFFFFFF)
+    check(lib.vtx_device_status_read(C.byref(host), int(bool(clear))), "vtx_device_status_read")
+    return int(host.value)
+
+
+def sparse_layer_workspace_bytes(eff_bs: int, max_pages_per_request: int, topk_val: int, bos: int, eos: int) -> int:
+    """Bytes of zero-initialised device scratch that lets ``sparse_layer_fused`` split long segments (0: no
+    segment of that length is ever split)."""
+    return int(lib.vtx_sparse_layer_workspace_bytes(int(eff_bs), int(max_pages_per_request), int(topk_val),
+                                                    int(bos), int(eos)))
 
 
 def version() -> int:
@@ -279,14 +322,16 @@ def mla_fault_bits() -> int:
 def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
                        sparse_kv_indices, kv_last_page_len, eff_bs, page_size, topk_val, bos, eos,
                        max_pages_per_request, sm_scale, new_k=None, new_v=None, loc=None,
-                       gqa_softmax_scale=None, quest_min=None) -> None:
+                       gqa_softmax_scale=None, quest_min=None, workspace=None, early_prologue=False) -> None:
     """Page selection and attention over the selected pages in one launch (bf16); with ``new_k``,
     ``new_v`` ``[bs, H, D]`` and ``loc`` ``[bs]`` the launch also writes the new token and the centroid
     of the page it closes.  ``gqa_softmax_scale`` set: page scores of the gqa_block_sparse_attention
     flow (per-head product, softmax over pages with that scale, maximum over heads) instead of the
     group-mean product.  ``quest_min`` set: page scores of the gqa_quest_sparse_attention flow with
     ``centroids`` as the per-page maximum cache and ``quest_min`` as the minimum cache (both are what a
-    token write then maintains)."""
+    token write then maintains).  ``workspace``: zero-initialised device scratch of
+    ``sparse_layer_workspace_bytes(...)`` bytes that lets long segments be scanned by several CTAs.
+    ``early_prologue``: see ``VTX_LAYER_EARLY_PROLOGUE`` in the header."""
     if not (q.dtype == centroids.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("sparse_layer_fused: q, centroids, caches and out must share a dtype")
     H = 0
@@ -295,29 +340,21 @@ def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, spa
         H = new_k.shape[1]
         if new_k.dtype != q.dtype or new_v.dtype != q.dtype:
             raise TypeError("sparse_layer_fused: new_k/new_v must have q's dtype")
-    if quest_min is not None:
-        rc = lib.vtx_sparse_layer_fused_quest(
-            ptr(q), ptr(centroids), ptr(quest_min), ptr(k_cache), ptr(v_cache), ptr(out), ptr(new_k), ptr(new_v),
-            ptr(loc), H, ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indices),
-            ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size), int(topk_val), int(bos),
-            int(eos), int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))
-        check(rc, "vtx_sparse_layer_fused_quest")
-        return
-    if gqa_softmax_scale is not None:
-        rc = lib.vtx_sparse_layer_fused_gqa_softmax(
-            ptr(q), ptr(centroids), ptr(k_cache), ptr(v_cache), ptr(out), ptr(new_k), ptr(new_v), ptr(loc), H,
-            ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indices),
-            ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size), int(topk_val), int(bos),
-            int(eos), int(max_pages_per_request), float(sm_scale), float(gqa_softmax_scale), dtype_code(q.dtype),
-            stream_of(q))
-        check(rc, "vtx_sparse_layer_fused_gqa_softmax")
-        return
-    rc = lib.vtx_sparse_layer_fused(ptr(q), ptr(centroids), ptr(k_cache), ptr(v_cache), ptr(out),
-                                    ptr(new_k), ptr(new_v), ptr(loc), H, ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
-                                    ptr(sparse_kv_indices), ptr(kv_last_page_len), int(eff_bs), q.shape[1],
-                                    q.shape[2], int(page_size), int(topk_val), int(bos), int(eos),
-                                    int(max_pages_per_request), float(sm_scale), dtype_code(q.dtype), stream_of(q))
-    check(rc, "vtx_sparse_layer_fused")
+    mode = SCORE_QUEST if quest_min is not None else (SCORE_GQA_SOFTMAX if gqa_softmax_scale is not None
+                                                     else SCORE_MEAN_DOT)
+    p = SparseLayerParams(
+        q=ptr(q), summary=ptr(centroids), summary2=ptr(quest_min), k_cache=ptr(k_cache), v_cache=ptr(v_cache),
+        out=ptr(out), new_k=ptr(new_k), new_v=ptr(new_v), loc=ptr(loc), dense_kv_indptr=ptr(dense_kv_indptr),
+        sparse_kv_indptr=ptr(sparse_kv_indptr), dense_kv_indices=ptr(dense_kv_indices),
+        sparse_kv_indices=ptr(sparse_kv_indices), kv_last_page_len=ptr(kv_last_page_len),
+        workspace=ptr(workspace),
+        workspace_bytes=0 if workspace is None else workspace.numel() * workspace.element_size(),
+        eff_batch_size=int(eff_bs), group_size=q.shape[1], head_dim=q.shape[2], page_size=int(page_size),
+        num_kv_heads=H, topk_val=int(topk_val), page_reserved_bos=int(bos), page_reserved_eos=int(eos),
+        max_num_pages_per_request=int(max_pages_per_request), score_mode=mode,
+        flags=LAYER_EARLY_PROLOGUE if early_prologue else 0, dtype=dtype_code(q.dtype),
+        sm_scale=float(sm_scale), softmax_scale=float(gqa_softmax_scale or 0.0))
+    check(lib.vtx_sparse_layer(C.byref(p), stream_of(q)), "vtx_sparse_layer")
 
 
 def splitkv_workspace_bytes(eff_bs: int, group: int, head_dim: int, num_splits: int) -> int:

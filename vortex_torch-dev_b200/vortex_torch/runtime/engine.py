@@ -124,6 +124,14 @@ class VortexDecodeRuntime:
             self.split_workspace = torch.empty(nbytes // 4, dtype=torch.float32, device=self.device)
         self.ictx = IndexerContext().create(self.backend, self.model_runner)
         self.cctx = CacheContext().create(self.pool, self.model_runner)
+        # scratch that lets the one-launch layer spread a long segment's scan over several CTAs
+        self.layer_workspace = None
+        if self.device.type == "cuda":
+            nbytes = _cabi.sparse_layer_workspace_bytes(segs, pages_per_req, self.sa.vortex_topk_val,
+                                                        self.sa.vortex_page_reserved_bos,
+                                                        self.sa.vortex_page_reserved_eos)
+            if nbytes > 0:
+                self.layer_workspace = torch.zeros(nbytes // 4, dtype=torch.int32, device=self.device)
         self._profile(max_bs)
 
     # ------------------------------------------------------------------ profile pass
@@ -184,20 +192,16 @@ class VortexDecodeRuntime:
                         self.cctx.flush_append()
                         nk = nv = loc = None
                         cmax, cmin = py, quest_other
-                # the early prologue reads the planner's outputs: allowed once another launch separates us from it
+                # the early prologue reads the planner's outputs: allowed once a launch that waits for its
+                # predecessor before releasing its successor separates us from the planner
                 early = self.pdl_mode == 2 and self._launches_since_plan >= 1
-                if early:
-                    _cabi.set_programmatic_launch(2)
-                try:
-                    _cabi.sparse_layer_fused(q, cmax, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
-                                             b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
-                                             b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
-                                             self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
-                                             self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc,
-                                             gqa_softmax_scale=gqa_scale, quest_min=cmin)
-                finally:
-                    if early:
-                        _cabi.set_programmatic_launch(1)
+                _cabi.sparse_layer_fused(q, cmax, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
+                                         b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
+                                         b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
+                                         self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
+                                         self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc,
+                                         gqa_softmax_scale=gqa_scale, quest_min=cmin,
+                                         workspace=self.layer_workspace, early_prologue=early)
                 self._launches_since_plan += 1
                 return out
             self.ictx._pending_indexer = pend

@@ -27,12 +27,17 @@ def balance_requests(page_counts: Sequence[int], world_size: int) -> List[List[i
     return [sorted(x) for x in out]
 
 
-def gather_for_verification(local: dict, group=None) -> dict:
+_DTYPE_CODES = [torch_name for torch_name in ("float32", "bfloat16", "float16", "int32", "int64", "int16", "uint8")]
+
+
+def gather_for_verification(local: dict, group=None, dtype=None) -> dict:
     """Collect per-request results from every rank (verification only; never on the hot path).
 
     ``local`` maps a global request id to a tensor (any shape, any device).  Every rank gets back the
     union.  Tensors are moved through ``torch.distributed.all_gather`` after padding to a common length,
     so the call works on NCCL (device tensors over NVLink) and on gloo (CPU tensors) alike.
+    ``dtype``: the payload dtype, the same on every rank.  When it is not given the ranks agree on one first
+    (a rank that holds no request has nothing to infer it from), and a disagreement raises on every rank.
     """
     import torch
     import torch.distributed as dist
@@ -44,7 +49,15 @@ def gather_for_verification(local: dict, group=None) -> dict:
     dev = torch.device("cuda", torch.cuda.current_device()) if backend == "nccl" else torch.device("cpu")
     ids = sorted(local)
     # header: per request (id, numel, ndim, dims...) as int64; payload: flattened values as one dtype
-    dtype = next(iter(local.values())).dtype if local else torch.float32
+    if dtype is None:
+        # agree on the payload dtype: code of the local dtype (or -1 for "nothing to send"), max over ranks
+        mine = _DTYPE_CODES.index(str(next(iter(local.values())).dtype).replace("torch.", "")) if local else -1
+        codes = [torch.zeros(1, dtype=torch.int64, device=dev) for _ in range(world)]
+        dist.all_gather(codes, torch.tensor([mine], dtype=torch.int64, device=dev), group=group)
+        seen = {int(c.item()) for c in codes} - {-1}
+        if len(seen) > 1:
+            raise TypeError("gather_for_verification: ranks hold different dtypes; pass dtype= explicitly")
+        dtype = getattr(torch, _DTYPE_CODES[seen.pop()]) if seen else torch.float32
     header, chunks = [], []
     for i in ids:
         t = local[i]
