@@ -48,6 +48,19 @@ def bf16_rne(x: torch.Tensor) -> torch.Tensor:
     return x.to(torch.float32).to(torch.bfloat16).to(torch.float32)
 
 
+def bf16_trunc(x: torch.Tensor) -> torch.Tensor:
+    """Truncate an fp32 tensor to bf16 (drop the low 16 bits) and return it as fp32.  Not a rounding any
+    kernel uses: it is how the CPU interpreter of Triton converts to bf16, so the golden-vector tests ask for
+    it when they compare with outputs recorded under that interpreter."""
+    return (x.to(torch.float32).contiguous().view(torch.int32) & -65536).view(torch.float32)
+
+
+def _round_bf16(x: torch.Tensor, rounding: str) -> torch.Tensor:
+    """fp32 -> bf16 tensor with the named rounding ("rne": what the kernels do; "trunc": see `bf16_trunc`)."""
+    assert rounding in ("rne", "trunc")
+    return (bf16_trunc(x) if rounding == "trunc" else x.to(torch.float32)).to(torch.bfloat16)
+
+
 def _pow2_ceil(n: int) -> int:
     p = 1
     while p < n:
@@ -545,37 +558,163 @@ def canonical_sum128(v: np.ndarray) -> np.float32:
     return part[0]
 
 
+def candidate_windows(dense_indptr, eff_bs: int, topk_val: int, bos: int, eos: int):
+    """Packed row ranges the indexer operators work on: the non-reserved candidates
+    ``[indptr[s] + bos, indptr[s+1] - eos)`` of every segment that has more than ``topk_val`` of them
+    (the planner's workload windows, csrc/utils_sglang.cu:219-251)."""
+    for s in range(eff_bs):
+        a = int(dense_indptr[s]) + bos
+        b = int(dense_indptr[s + 1]) - eos
+        if b - a > topk_val:
+            yield s, a, b
+
+
+def gemm_bpr(q, table, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos,
+             out: Optional[torch.Tensor] = None, rounding: str = "rne") -> torch.Tensor:
+    """The ``GeMM`` indexer operator on (BATCHED, PAGED) inputs (indexer/matmul.py:194-399 over
+    ``mm_bpr_kernel``, indexer/triton_kernels/matmul_impl.py:6-113): ``out[p, c, g] = table[row_p, c, :] . q[s, g, :]``
+    for every candidate position p of segment s, bf16 values widened to fp32, fp32 products and sum (canonical
+    order of `canonical_dot`), one rounding to bf16.  q [S, G, D], table [R, C, D] -> [N, C, G]."""
+    assert q.dtype == torch.bfloat16 and table.dtype == torch.bfloat16
+    total = int(dense_indptr[eff_bs])
+    G, C = q.shape[1], table.shape[1]
+    if out is None:
+        out = torch.zeros(total, C, G, dtype=torch.bfloat16)
+    for s, a, b in candidate_windows(dense_indptr, eff_bs, topk_val, bos, eos):
+        rows = table[torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)].to(torch.float32)
+        for c in range(C):
+            for g in range(G):
+                dot = canonical_dot(rows[:, c], q[s, g].to(torch.float32), bf16_products=False)
+                out[a:b, c, g] = _round_bf16(dot, rounding)
+    return out
+
+
+def softmax_ragged(x, dense_indptr, eff_bs, topk_val, bos, eos, scale: float, rounding: str = "rne") -> torch.Tensor:
+    """The in-place ``Softmax(dim=0, scale)`` indexer operator (indexer/scan.py over
+    ``softmax_inplace_r_kernel``, indexer/triton_kernels/softmax_impl.py:6-105): for every inner element
+    [r, c] of the RAGGED tensor x [N, r, c], softmax of ``scale * x`` over the candidate pages of each
+    segment, rounded to bf16.  Canonical arithmetic: t = fp32(x) * scale, m = max t, e = `exp_canonical`(t - m),
+    l = `canonical_sum128`(e), result = bf16(e / l).  (The reference accumulates (m, l) in blocks of 256
+    pages with rescaling and uses the compiler's exp: same value up to rounding.)"""
+    assert x.dtype == torch.bfloat16
+    sc32 = np.float32(scale)
+    N, R, C = x.shape
+    for s, a, b in candidate_windows(dense_indptr, eff_bs, topk_val, bos, eos):
+        blk = x[a:b].to(torch.float32).numpy()
+        res = np.empty_like(blk)
+        for r in range(R):
+            for c in range(C):
+                t = blk[:, r, c].astype(np.float32) * sc32
+                e = exp_canonical(t - t.max())
+                l = canonical_sum128(e)
+                res[:, r, c] = (e / l).astype(np.float32)
+        x[a:b] = _round_bf16(torch.from_numpy(res), rounding)
+    return x
+
+
+def canonical_sum_lastdim(vals: torch.Tensor) -> torch.Tensor:
+    """fp32 sum over the last axis in the canonical order of `canonical_dot`: the axis is padded with +0.0 to
+    a multiple of 8 and summed as chunks of 8 by L = min(32, pow2ceil(chunks)) partial sums folded in halves."""
+    shape = vals.shape
+    D = shape[-1]
+    v = vals.reshape(-1, D).to(torch.float32)
+    pad = (-D) % 8
+    if pad:
+        v = torch.cat([v, torch.zeros(v.shape[0], pad)], dim=1)
+    return canonical_rowsum(v).reshape(shape[:-1])
+
+
+REDUCE_MEAN, REDUCE_MAX, REDUCE_MIN, REDUCE_L2NORM, REDUCE_SUM = 0, 1, 2, 3, 4
+
+
+def reduce_ragged(x, dim: int, kind: int, dense_indptr, eff_bs, topk_val, bos, eos,
+                  out: Optional[torch.Tensor] = None, rounding: str = "rne") -> torch.Tensor:
+    """The RAGGED reductions ``Mean / Max / Min / L2Norm / Sum (dim=1 | 2)`` of the indexer
+    (indexer/reduce.py:165-309 over ``reduce_rr_kernel``, indexer/triton_kernels/reduce_impl.py:8-120):
+    x [N, r, c] -> [N, 1, c] (dim 1) or [N, r, 1] (dim 2) on the candidate rows, fp32 arithmetic, one
+    rounding to bf16.  Canonical orders: over dim 2 `canonical_sum_lastdim`; over dim 1 sequential in
+    ascending order from +0.0.  Mean divides the sum by the axis length; L2Norm is the correctly rounded
+    square root of the sum of the (exact) squares.  kind: REDUCE_* (the reference's ReduceType values)."""
+    assert x.dtype == torch.bfloat16 and dim in (1, 2)
+    N, R, C = x.shape
+    if out is None:
+        out = torch.zeros((N, 1, C) if dim == 1 else (N, R, 1), dtype=torch.bfloat16)
+    for s, a, b in candidate_windows(dense_indptr, eff_bs, topk_val, bos, eos):
+        blk = x[a:b].to(torch.float32)
+        if kind == REDUCE_MAX:
+            red = blk.max(dim=dim).values
+        elif kind == REDUCE_MIN:
+            red = blk.min(dim=dim).values
+        else:
+            v = blk * blk if kind == REDUCE_L2NORM else blk
+            if dim == 2:
+                red = canonical_sum_lastdim(v)
+            else:
+                red = torch.zeros(b - a, C, dtype=torch.float32)
+                for r in range(R):
+                    red = red + v[:, r]
+            if kind == REDUCE_MEAN:
+                red = red / float(blk.shape[dim])
+            elif kind == REDUCE_L2NORM:
+                red = torch.sqrt(red)
+        out[a:b] = _round_bf16(red.unsqueeze(dim), rounding)
+    return out
+
+
+BINARY_MAX, BINARY_MIN, BINARY_ADD, BINARY_MUL = 0, 1, 2, 3
+
+
+def binary_bpr(q, table, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos, op: int, alpha: float = 1.0,
+               beta: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``Maximum / Minimum / Add / Multiply`` on (BATCHED, PAGED) inputs (indexer/elementwise_binary.py over
+    ``elementwise_binary_bpr_kernel``, indexer/triton_kernels/elementwise_binary_impl.py:167-307):
+    ``out[p] = op(q[s], table[row_p])`` with the inner dims broadcast, one rounding per bf16 operation
+    (Add: bf16(bf16(alpha q) + bf16(beta y)) with alpha, beta rounded to bf16).  q [S, a0, a1],
+    table [R, b0, b1] -> [N, max(a0, b0), max(a1, b1)]."""
+    assert q.dtype == torch.bfloat16 and table.dtype == torch.bfloat16
+    total = int(dense_indptr[eff_bs])
+    d0, d1 = max(q.shape[1], table.shape[1]), max(q.shape[2], table.shape[2])
+    if out is None:
+        out = torch.zeros(total, d0, d1, dtype=torch.bfloat16)
+    for s, a, b in candidate_windows(dense_indptr, eff_bs, topk_val, bos, eos):
+        rows = table[torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)]
+        out[a:b] = elementwise_binary(q[s:s + 1].expand(b - a, -1, -1), rows, op, alpha, beta)
+    return out
+
+
+def normalize_ragged(x, dense_indptr, eff_bs, topk_val, bos, eos, eps: float = 1e-12) -> torch.Tensor:
+    """The in-place ``Normalize(dim=0)`` indexer operator (``normalize_inplace_r_kernel``,
+    indexer/triton_kernels/normalize_impl.py:6-119): every inner element [r, c] divided by the L2 norm of
+    that element over the candidate pages of its segment (at least eps), rounded to bf16.  Canonical
+    arithmetic: exact squares, `canonical_sum128` over the pages, correctly rounded sqrt and division."""
+    assert x.dtype == torch.bfloat16
+    N, R, C = x.shape
+    for s, a, b in candidate_windows(dense_indptr, eff_bs, topk_val, bos, eos):
+        blk = x[a:b].to(torch.float32).numpy()
+        res = np.empty_like(blk)
+        for r in range(R):
+            for c in range(C):
+                v = blk[:, r, c].astype(np.float32)
+                nrm = np.maximum(np.sqrt(canonical_sum128(v * v)), np.float32(eps)).astype(np.float32)
+                res[:, r, c] = (v / nrm).astype(np.float32)
+        x[a:b] = torch.from_numpy(res).to(torch.bfloat16)
+    return x
+
+
 def gqa_softmax_scores(q, centroids, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos, scale: float,
                        out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Aggregated page scores of the ``gqa_block_sparse_attention`` flow (flow/algorithms.py:238-352):
     ``GeMM(q, centroids)`` -> ``Softmax(dim=0, scale)`` over the candidate pages -> ``Max(dim=2)`` over the
-    query heads of the group, every operator output rounded to bf16 as in the reference
-    (indexer/triton_kernels/matmul_impl.py:81-88 fp32 products and sum, bf16 out;
-    softmax_impl.py:33-73 scaled softmax over candidates of segments with more than topk_val of them,
-    bf16 out; reduce_impl.py:58-75 max over the last axis).  Reduction orders and exp are the canonical
-    ones of this file (`canonical_dot`, `exp_canonical`, `canonical_sum128`).
-    """
+    query heads of the group, every operator output rounded to bf16 as in the reference: the composition
+    of `gemm_bpr`, `softmax_ragged` and `reduce_ragged`."""
     assert q.dtype == torch.bfloat16, "this flow's operators are bf16 in the reference"
-    total = int(dense_indptr[eff_bs])
+    args = (dense_indptr, eff_bs, topk_val, bos, eos)
+    mm = gemm_bpr(q, centroids, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos)
+    softmax_ragged(mm, *args, scale)
+    red = reduce_ragged(mm, 2, REDUCE_MAX, *args).view(-1)
     if out is None:
-        out = torch.zeros(total, dtype=torch.bfloat16)
-    G = q.shape[1]
-    cf = centroids.view(centroids.shape[0], -1)
-    sc32 = np.float32(scale)
-    for s in range(eff_bs):
-        a = int(dense_indptr[s]) + bos
-        b = int(dense_indptr[s + 1]) - eos
-        if b - a <= topk_val:
-            continue
-        rows = cf[torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)].to(torch.float32)
-        probs = []
-        for g in range(G):
-            dot = bf16_rne(canonical_dot(rows, q[s, g].to(torch.float32), bf16_products=False)).numpy()
-            t = dot.astype(np.float32) * sc32
-            e = exp_canonical(t - t.max())
-            l = canonical_sum128(e)
-            probs.append(bf16_rne(torch.from_numpy((e / l).astype(np.float32))))
-        out.view(-1)[a:b] = torch.stack(probs).max(dim=0).values.to(torch.bfloat16)
+        return red
+    out.view(-1)[: red.numel()] = red
     return out
 
 
@@ -628,29 +767,18 @@ def canonical_rowsum(vals: torch.Tensor) -> torch.Tensor:
 def quest_scores(q, cache_max, cache_min, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Aggregated page scores of the ``gqa_quest_sparse_attention`` flow (flow/algorithms.py:356-496):
-    ``Multiply(q, max)`` and ``Multiply(q, min)`` (bf16 products, elementwise_binary_impl.py:167-260),
-    ``Maximum`` of the two, ``Sum(dim=2)`` over the head dim (fp32 sum, bf16 result, reduce_impl.py:58-75),
-    ``Max(dim=1)`` over the query heads.  The fp32 sum uses the canonical order of `canonical_rowsum`."""
+    ``Multiply(q, max)`` and ``Multiply(q, min)`` (bf16 products), ``Maximum`` of the two, ``Sum(dim=2)`` over the
+    head dim (fp32 sum, bf16 result), ``Max(dim=1)`` over the query heads: the composition of `binary_bpr`,
+    `elementwise_binary` and `reduce_ragged`."""
     assert q.dtype == torch.bfloat16
-    total = int(dense_indptr[eff_bs])
+    args = (dense_indptr, eff_bs, topk_val, bos, eos)
+    hi = binary_bpr(q, cache_max, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos, BINARY_MUL)
+    lo = binary_bpr(q, cache_min, dense_indptr, dense_indices, eff_bs, topk_val, bos, eos, BINARY_MUL)
+    u = elementwise_binary(hi, lo, BINARY_MAX)
+    red = reduce_ragged(reduce_ragged(u, 2, REDUCE_SUM, *args), 1, REDUCE_MAX, *args).view(-1)
     if out is None:
-        out = torch.zeros(total, dtype=torch.bfloat16)
-    G = q.shape[1]
-    mx = cache_max.view(cache_max.shape[0], -1)
-    mn = cache_min.view(cache_min.shape[0], -1)
-    for s in range(eff_bs):
-        a = int(dense_indptr[s]) + bos
-        b = int(dense_indptr[s + 1]) - eos
-        if b - a <= topk_val:
-            continue
-        rows = torch.as_tensor(np.asarray(dense_indices[a:b]), dtype=torch.long)
-        hi, lo = mx[rows].to(torch.float32), mn[rows].to(torch.float32)
-        per_head = []
-        for g in range(G):
-            qg = q[s, g].to(torch.float32).unsqueeze(0)
-            u = torch.maximum(bf16_rne(hi * qg), bf16_rne(lo * qg))
-            per_head.append(bf16_rne(canonical_rowsum(u)))
-        out.view(-1)[a:b] = torch.stack(per_head).max(dim=0).values.to(torch.bfloat16)
+        return red
+    out.view(-1)[: red.numel()] = red
     return out
 
 

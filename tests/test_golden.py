@@ -93,3 +93,119 @@ def test_gemv_matches_reference_triton_kernel_within_one_ulp():
         rows = cents[idx[off:off + ln]]
         s = vo.bf16_rne(vo.canonical_dot(rows, x[q], bf16_products=True))
         assert bool(((s - want[off:off + ln]).abs() <= 0.25).all())
+
+
+# --------------------------------------------------------------------------- operators of the two other shipped flows
+# tests/golden/ref_triton_ops.npz: outputs of the reference's own Triton kernels (GeMM, Softmax, RAGGED
+# reductions, elementwise binary, cache-side page reductions) under the Triton interpreter, made by
+# tests/golden/make_golden_ref_triton_ops.py.  Maxima, minima and products must agree exactly, sums (whose
+# order the interpreter takes from numpy) within one bf16 ulp.
+OPS = np.load(Path(__file__).parent / "golden" / "ref_triton_ops.npz")
+
+
+def _ops_layout():
+    return OPS["indptr"], OPS["indices"], 3, int(OPS["topk"]), int(OPS["bos"]), int(OPS["eos"])
+
+
+def _window_mask(total):
+    indptr, _, eff, K, bos, eos = _ops_layout()
+    m = torch.zeros(total, dtype=torch.bool)
+    for _, a, b in vo.candidate_windows(indptr, eff, K, bos, eos):
+        m[a:b] = True
+    return m
+
+
+def test_candidate_windows_are_the_reference_workloads():
+    covered = np.zeros(int(OPS["indptr"][-1]), dtype=bool)
+    for off, ln in zip(OPS["woff"], OPS["wlen"]):
+        covered[off:off + ln] = True
+    assert bool((torch.from_numpy(covered) == _window_mask(len(covered))).all())
+    assert int(covered.sum()) == 12 + 298 + 7   # candidates of the 14-, 300- and 9-page segments (topk 4)
+
+
+def _same_up_to_sum_order(got: torch.Tensor, want: torch.Tensor) -> bool:
+    """The interpreter converts to bf16 by truncation; with the oracle asked to truncate too, the two differ
+    only where the order of an fp32 sum moves the value across a bf16 boundary: never by more than one ulp
+    and in under 1 % of the entries."""
+    return _within_one_bf16_ulp(got, want) and float((got != want).float().mean()) < 0.01
+
+
+def test_gemm_matches_reference_triton_kernel():
+    indptr, indices, eff, K, bos, eos = _ops_layout()
+    q, table = torch.from_numpy(OPS["q"]).bfloat16(), torch.from_numpy(OPS["table"]).bfloat16()
+    want = torch.from_numpy(OPS["mm_out"])
+    m = _window_mask(want.shape[0])
+    got = vo.gemm_bpr(q, table, indptr, indices, eff, K, bos, eos, rounding="trunc").float()
+    assert _same_up_to_sum_order(got[m], want[m])
+    got = vo.gemm_bpr(q, table, indptr, indices, eff, K, bos, eos).float()   # the kernels' rounding
+    assert _within_one_bf16_ulp(got[m], want[m])
+
+
+def test_softmax_matches_reference_triton_kernel_within_one_ulp():
+    """Input = the reference's own GeMM output, so that only the softmax is compared.  The 298-candidate
+    segment exercises the reference's blocked accumulation (two blocks of 256 pages)."""
+    indptr, _, eff, K, bos, eos = _ops_layout()
+    want = torch.from_numpy(OPS["softmax_out"])
+    m = _window_mask(want.shape[0])
+    x = torch.from_numpy(OPS["mm_out"]).bfloat16()
+    vo.softmax_ragged(x, indptr, eff, K, bos, eos, float(OPS["softmax_scale"]), rounding="trunc")
+    assert _same_up_to_sum_order(x.float()[m], want[m])
+    x = torch.from_numpy(OPS["mm_out"]).bfloat16()
+    vo.softmax_ragged(x, indptr, eff, K, bos, eos, float(OPS["softmax_scale"]))
+    assert _within_one_bf16_ulp(x.float()[m], want[m])
+    assert torch.equal(x.float()[~m], torch.from_numpy(OPS["mm_out"])[~m])   # reserved pages untouched
+
+
+def test_ragged_reductions_match_reference_triton_kernel():
+    indptr, _, eff, K, bos, eos = _ops_layout()
+    args = (indptr, eff, K, bos, eos)
+    sm = torch.from_numpy(OPS["softmax_out"]).bfloat16()
+    m = _window_mask(sm.shape[0])
+    got = vo.reduce_ragged(sm, 2, vo.REDUCE_MAX, *args).float()
+    assert torch.equal(got[m], torch.from_numpy(OPS["max_dim2_out"])[m])
+    x = torch.from_numpy(OPS["reduce_in"]).bfloat16()
+    kinds = dict(mean=vo.REDUCE_MEAN, max=vo.REDUCE_MAX, min=vo.REDUCE_MIN, l2norm=vo.REDUCE_L2NORM, sum=vo.REDUCE_SUM)
+    for name, kind in kinds.items():
+        for dim in (1, 2):
+            got = vo.reduce_ragged(x, dim, kind, *args).float()
+            want = torch.from_numpy(OPS[f"reduce_{name}_dim{dim}"])
+            if name in ("max", "min"):
+                assert torch.equal(got[m], want[m]), (name, dim)
+            else:
+                assert _within_one_bf16_ulp(got[m], want[m]), (name, dim)
+                got = vo.reduce_ragged(x, dim, kind, *args, rounding="trunc").float()
+                assert _same_up_to_sum_order(got[m], want[m]), (name, dim)
+
+
+def test_binary_operators_match_reference_triton_kernel():
+    indptr, indices, eff, K, bos, eos = _ops_layout()
+    q, table = torch.from_numpy(OPS["q"]).bfloat16(), torch.from_numpy(OPS["table"]).bfloat16()
+    rows = torch.from_numpy(OPS["bpr_rows"]).long()
+    m = _window_mask(int(indptr[-1]))[rows]
+    for name, op in (("mul", vo.BINARY_MUL), ("max", vo.BINARY_MAX), ("min", vo.BINARY_MIN)):
+        got = vo.binary_bpr(q, table, indptr, indices, eff, K, bos, eos, op).float()[rows]
+        # with fp32 stand-ins for bf16 inputs the reference kernel returns the unrounded product: round it once
+        want = vo.bf16_rne(torch.from_numpy(OPS[f"bpr_{name}_out"]))
+        assert torch.equal(got[m], want[m]), name
+    a, b = torch.from_numpy(OPS["rrr_a"]).bfloat16(), torch.from_numpy(OPS["rrr_b"]).bfloat16()
+    m = _window_mask(a.shape[0])
+    for name, op in (("max", vo.BINARY_MAX), ("min", vo.BINARY_MIN)):
+        got = vo.elementwise_binary(a, b, op).float()
+        assert torch.equal(got[m], torch.from_numpy(OPS[f"rrr_{name}_out"])[m]), name
+    # this kernel converts its product to bf16 itself, which the interpreter does by truncation
+    exact = a.float() * b.float()
+    assert torch.equal(vo.bf16_trunc(exact)[m], torch.from_numpy(OPS["rrr_mul_out"])[m])
+    assert torch.equal(vo.elementwise_binary(a, b, vo.BINARY_MUL).float(), vo.bf16_rne(exact))
+
+
+def test_cache_page_reductions_match_reference_triton_kernel():
+    H, P = int(OPS["cache_H"]), int(OPS["cache_P"])
+    k = torch.from_numpy(OPS["cache_k"]).bfloat16()
+    loc = torch.from_numpy(OPS["cache_loc"])
+    for op in ("max", "min"):
+        out = torch.zeros(k.shape[0], 1, k.shape[2], dtype=torch.bfloat16)
+        vo.cminmax(k, out, loc, P, H, op)
+        assert torch.equal(out.float(), torch.from_numpy(OPS[f"cache_{op}_out"])), op
+    out = torch.zeros(k.shape[0], 1, k.shape[2], dtype=torch.bfloat16)
+    vo.cmean(k, out, loc, P, H)
+    assert _within_one_bf16_ulp(out.float(), torch.from_numpy(OPS["cache_mean_out"]))
