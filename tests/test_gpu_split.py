@@ -157,13 +157,13 @@ def test_indexer_fused_above_2048_candidates(dtype):
 def test_understated_page_bound_raises_the_status_word():
     """max_num_pages_per_request below a request's real page count: the call still succeeds, the segment gets
     its first topk_val candidates (a well-defined list) and the sticky status word reports it."""
-    seq, H, G, D, P, K, bos, eos = [2048, 300], 2, 2, 128, 16, 30, 1, 1
+    seq, H, G, D, P, K, bos, eos = [8192, 300], 2, 2, 128, 16, 30, 1, 1
     prob, dp, ref = _problem(59, seq, H, G, D, P, K, bos, eos)
     d = to_dev(prob)
     assert _cabi.device_status(clear=True) == 0
     sel = dp.sparse_indices.clone()
     _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel, dp.S, K, bos,
-                        eos, 64)  # request 0 has 128 pages
+                        eos, 64)  # request 0 has 512 pages (the kernels always make room for 256 candidates)
     assert _cabi.device_status() & _cabi.STATUS_CANDIDATE_OVERFLOW
     got = sel.cpu().numpy()
     dip, sip, din = ref["dense_kv_indptr"], ref["sparse_kv_indptr"], ref["dense_kv_indices"]

@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_gqa_kernel(IndexerArgs a)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<__nv_bfloat16, D, 2, NoSideWork, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
+    indexer_body<__nv_bfloat16, D, 2, NoHooks, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
 }
 
 // gqa_quest_sparse_attention indexer: envelope bound per head -> Max over heads -> top-k, one launch.
@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_quest_kernel(IndexerArgs 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<__nv_bfloat16, D, 3, NoSideWork, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
+    indexer_body<__nv_bfloat16, D, 3, NoHooks, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
 }
 
 template <typename T>
@@ -69,7 +69,7 @@ template <typename T, int D, int MODE>
 int launch_indexer_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     using Gm = Geom<T, D>;
     using Key = typename KeyOf<T>::type;
-    size_t bytes = Gm::ring_bytes + Gm::row_bytes;
+    size_t bytes = Gm::ring_bytes + (size_t)q_stage_bytes<T, D, MODE, 1>();
     if (MODE == 0) bytes += (size_t)a.key_cap * (sizeof(Key) + sizeof(int32_t));
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;
     auto kern = indexer_kernel<T, D, MODE>;

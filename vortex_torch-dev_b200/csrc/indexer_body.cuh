@@ -27,6 +27,8 @@
 // per-thread block are register swaps, strides inside a warp are shuffles, and only the three
 // widest strides cross warps through shared memory.
 #pragma once
+#include <type_traits>
+
 #include "decode_mma_body.cuh"
 #include "vtx_common.cuh"
 
@@ -206,7 +208,7 @@ __host__ __device__ inline int sort_width(int c) {
 }
 
 template <typename Key, typename Emit>
-__device__ void sort_emit(Key* keys, int c, int K, Key* xbuf, Emit& emit) {
+__device__ __forceinline__ void sort_emit(Key* keys, int c, int K, Key* xbuf, Emit& emit) {
     if (xbuf != nullptr && c <= kThreads * 4) return sort_regs_emit<Key, 4>(keys, c, K, xbuf, emit);
     if (xbuf != nullptr && c <= kThreads * 8) return sort_regs_emit<Key, 8>(keys, c, K, xbuf, emit);
     if (xbuf != nullptr && c <= kThreads * 16) return sort_regs_emit<Key, 16>(keys, c, K, xbuf, emit);
@@ -340,88 +342,162 @@ struct Geom {
 };
 
 
-// Executed by one warp: lanes 0 .. D/8-1 each own 8 head dims of segment s = request * H + head.
-// Writes the new token's K and V rows and, if the token closes its page, the page's mean of K
-// (rows 0 .. P-2 from the cache in ascending order, the new row last, one division, one rounding).
-// QUEST: the page's per-dim maximum and minimum instead (both exact in bf16), as vtx_creduce computes them.
+// ---- new-token write of one segment s = request * H + head, executed by one warp ----
+// Lanes 0 .. D/8-1 each own 8 head dims.  The write is cut in two so that its loads can be in flight together
+// with the other loads a warp issues after the launch's inputs become readable:
+//   append_load   reads the token's K and V rows and its cache slot;
+//   append_finish writes the two rows and, if the token closes its page, the page's summary: the mean of K
+//                 (rows 0 .. P-2 in ascending order, the new row last, one division, one rounding - the
+//                 arithmetic of set_kv_cmean_kernel in cache_ops.cu) or, with QUEST, the per-dim maximum and
+//                 minimum (exact in bf16, as vtx_creduce computes them).  The page's older rows come from
+//                 `rows_smem` when the caller copied them there (row r at rows_smem + r * D * 2), else from
+//                 the cache.
+struct AppendRegs {
+    uint4 k, v;
+    int64_t slot;
+};
+
+template <int D>
+__device__ __forceinline__ AppendRegs append_load(const AppendArgs& ap, const int s, const int lane) {
+    AppendRegs r{};
+    if (lane >= D / 8) return r;
+    r.k = *reinterpret_cast<const uint4*>(ap.new_k + (int64_t)s * D + lane * 8);
+    r.v = *reinterpret_cast<const uint4*>(ap.new_v + (int64_t)s * D + lane * 8);
+    r.slot = ap.loc[s / ap.H];
+    return r;
+}
+
 template <int D, bool QUEST = false>
-__device__ __forceinline__ void append_token(const AppendArgs& ap, const int s, const int lane) {
+__device__ __forceinline__ void append_finish(const AppendArgs& ap, const int s, const int lane, const AppendRegs& in,
+                                              const unsigned char* rows_smem) {
     constexpr int NCH = D / 8;
     if (lane >= NCH) return;
-    const int r = s / ap.H, h = s - r * ap.H;
-    const int64_t t = ap.loc[r];
-    const int64_t pid = (t / ap.P) * ap.H + h;
-    const int tok = (int)(t % ap.P);
+    const int h = s % ap.H;
+    const int64_t pid = (in.slot / ap.P) * ap.H + h;
+    const int tok = (int)(in.slot % ap.P);
     __nv_bfloat16* kpage = ap.k_cache + pid * (int64_t)ap.P * D;
     __nv_bfloat16* vpage = ap.v_cache + pid * (int64_t)ap.P * D;
-    vtx::Vec8<__nv_bfloat16> nk, nv;
-    nk.load_cached(ap.new_k + (int64_t)s * D + lane * 8);
-    nv.load_cached(ap.new_v + (int64_t)s * D + lane * 8);
-    *reinterpret_cast<uint4*>(kpage + (int64_t)tok * D + lane * 8) = nk.raw;
-    *reinterpret_cast<uint4*>(vpage + (int64_t)tok * D + lane * 8) = nv.raw;
+    *reinterpret_cast<uint4*>(kpage + (int64_t)tok * D + lane * 8) = in.k;
+    *reinterpret_cast<uint4*>(vpage + (int64_t)tok * D + lane * 8) = in.v;
     if (tok != ap.P - 1) return;
-    float acc[8], kf[8];
+    vtx::Vec8<__nv_bfloat16> nk;
+    nk.raw = in.k;
+    float kf[8];
     nk.unpack(kf);
-    if (QUEST) {
-        float hi[8], lo[8];
+    float a0[8], a1[8];  // mean: running sum (a1 unused); QUEST: running maximum and minimum
 #pragma unroll
-        for (int j = 0; j < 8; ++j) hi[j] = lo[j] = kf[j];
-        for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
-            vtx::Vec8<__nv_bfloat16> v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
-                else v[u].raw = nk.raw;  // repeats the new row: neutral for max and min
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                float f[8];
-                v[u].unpack(f);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { hi[j] = fmaxf(hi[j], f[j]); lo[j] = fminf(lo[j], f[j]); }
-            }
-        }
-        vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, hi);
-        vtx::store8(ap.centroids2 + pid * (int64_t)D + lane * 8, lo);
-        return;
+    for (int j = 0; j < 8; ++j) {
+        a0[j] = QUEST ? kf[j] : 0.f;
+        a1[j] = kf[j];
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int r0 = 0; r0 < ap.P - 1; r0 += 8) {
         vtx::Vec8<__nv_bfloat16> v[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            if (r0 + u < ap.P - 1) v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
-            else v[u].zero();
+            if (r0 + u < ap.P - 1) {
+                if (rows_smem != nullptr)
+                    v[u].raw = *reinterpret_cast<const uint4*>(rows_smem + (size_t)(r0 + u) * (D * 2) + lane * 16);
+                else
+                    v[u].load(kpage + (int64_t)(r0 + u) * D + lane * 8);
+            } else {
+                v[u].raw = in.k;  // placeholder, skipped (mean) or neutral (max / min) below
+            }
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            if (r0 + u < ap.P - 1) {
-                float f[8];
-                v[u].unpack(f);
+            float f[8];
+            v[u].unpack(f);
+            if (QUEST) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(acc[j], f[j]);
+                for (int j = 0; j < 8; ++j) { a0[j] = fmaxf(a0[j], f[j]); a1[j] = fminf(a1[j], f[j]); }
+            } else if (r0 + u < ap.P - 1) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a0[j] = __fadd_rn(a0[j], f[j]);
             }
         }
     }
+    if (QUEST) {
+        vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, a0);
+        vtx::store8(ap.centroids2 + pid * (int64_t)D + lane * 8, a1);
+        return;
+    }
     const float denom = (float)ap.P;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(__fadd_rn(acc[j], kf[j]), denom);
-    vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, acc);
+    for (int j = 0; j < 8; ++j) a0[j] = __fdiv_rn(__fadd_rn(a0[j], kf[j]), denom);
+    vtx::store8(ap.centroids + pid * (int64_t)D + lane * 8, a0);
 }
 
-// MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
-// `side_work(warp, lane)` is called once by every thread of a CTA that has work, at a point where its
-// first gather batches are already in flight (or right away for segments that need no selection); the
-// fused layer kernel uses it for the new-token write of one warp.
-struct NoSideWork {
-    __device__ __forceinline__ void operator()(int, int) const {}
-};
-// `pre_sort(n)` is called by every thread right before the sort after which this CTA owns the segment's
-// complete page list (n keys to sort; every ring is idle, all keys are written).  It returns the byte offset
-// in the CTA's shared memory at which the sort may put its sort_scratch_bytes(n) bytes of scratch.
-struct NoPreSort {
-    __device__ __forceinline__ int operator()(int) const { return 0; }
+// ---- the best keys of a warp, kept sorted in registers while the warp scores its rows ----
+// 32 * KPL keys per warp, element e = lane * KPL + r, descending in e.  Keys are unique and never 0 for
+// finite scores; 0 marks an empty place.
+template <typename Key, int KPL>
+__device__ __forceinline__ void warp_bitonic_desc(Key (&v)[KPL], const int lane, const int k_first) {
+    // bitonic network over the warp's 32 * KPL elements; stages k = k_first .. N (k_first = 2: full sort of
+    // any input; k_first = N: the last merge only, which sorts a bitonic sequence)
+    constexpr int N = 32 * KPL;
+#pragma unroll
+    for (int k = 2; k <= N; k <<= 1) {
+        if (k < k_first) continue;
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            if (j < KPL) {
+#pragma unroll
+                for (int r = 0; r < KPL; ++r) {
+                    if ((r & j) == 0) {
+                        const bool desc = (((lane * KPL + r) & k) == 0);
+                        const Key x = v[r], y = v[r + j];
+                        const bool sw = (x < y) == desc;
+                        v[r] = sw ? y : x;
+                        v[r + j] = sw ? x : y;
+                    }
+                }
+            } else {
+                const int pt = j / KPL;
+                const bool keep_max = ((lane & pt) == 0) == (((lane * KPL) & k) == 0);
+#pragma unroll
+                for (int r = 0; r < KPL; ++r) {
+                    const Key o = __shfl_xor_sync(0xffffffffu, v[r], pt);
+                    v[r] = keep_max ? (v[r] > o ? v[r] : o) : (v[r] < o ? v[r] : o);
+                }
+            }
+        }
+    }
+}
+
+// run <- the best 32 * KPL keys of run (sorted) and add (any order)
+template <typename Key, int KPL>
+__device__ __forceinline__ void warp_topk_merge(Key (&run)[KPL], Key (&add)[KPL], const int lane) {
+    warp_bitonic_desc<Key, KPL>(add, lane, 2);
+    // element e of run against element N-1-e of add: a descending and an ascending sequence, whose
+    // elementwise maximum is a bitonic sequence holding the best N of the union
+#pragma unroll
+    for (int r = 0; r < KPL; ++r) {
+        const Key o = __shfl_sync(0xffffffffu, add[KPL - 1 - r], 31 - lane);
+        run[r] = run[r] > o ? run[r] : o;
+    }
+    warp_bitonic_desc<Key, KPL>(run, lane, 32 * KPL);
+}
+
+// Hooks of the fused layer kernel into the indexer body (the stand-alone indexer kernels use the no-op form).
+//   issue_extra(warp, lane, spare)  between the issue and the commit of a warp's last prologue gather batch:
+//                                   may start asynchronous copies into the warp's still unused ring slot
+//                                   (shared address `spare`), which then belong to that copy group;
+//   wait()                          first point at which the launch's own inputs (q, new token) are read;
+//   load(warp, lane) / finish(warp, lane, spare_ptr)  per-warp extra work around the query staging: `load`
+//                                   issues global loads only, `finish` runs once the warp's prologue copies
+//                                   have landed (it may read the spare slot) and before the gather loop;
+//   pre_sort(n)                     by every thread right before the step after which this CTA owns the
+//                                   segment's complete page list (every ring is idle, n keys are left to
+//                                   order); returns the byte offset in the CTA's shared memory at which
+//                                   that step may put its scratch.
+struct NoHooks {
+    struct Regs {};
+    __device__ __forceinline__ void issue_extra(int, int, uint32_t) const {}
+    __device__ __forceinline__ void wait() const {}
+    __device__ __forceinline__ Regs load(int, int) const { return Regs{}; }
+    __device__ __forceinline__ bool needs_spare(int) const { return false; }
+    __device__ __forceinline__ void finish(int, int, const Regs&, const unsigned char*) const {}
+    __device__ __forceinline__ int pre_sort(int) const { return 0; }
 };
 
 // Emits position e of a sorted key sequence: into the chunk's slot of part_keys, or - for the last sort
@@ -445,26 +521,130 @@ struct EmitSelection {
     }
 };
 
+// Keys a warp keeps per lane for top-k values up to 32 * kpl (0: the keys go to shared memory and are
+// sorted by the whole CTA afterwards).
+__host__ __device__ inline int stream_kpl(int K) { return K <= 32 ? 1 : (K <= 64 ? 2 : 0); }
+
+// Shared-memory bytes of the query staging area.
+template <typename T, int D, int MODE, int GQ>
+constexpr int q_stage_bytes() {
+    return MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : kWarps * D * (int)sizeof(T));
+}
+
+// The gather-and-score loop of one warp.  KPL > 0: the warp's best 32 * KPL keys stay in `run` (registers);
+// KPL == 0: every key goes to keys[] in shared memory (MODE 0, 3) or every score to sbuf / global (MODE 2, 1).
+template <typename T, int D, int MODE, int GQ, int KPL, int SLOTS, int SLOT_B, typename Issue>
+__device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, const int my_batches, const int warp,
+                                           const int lane, const unsigned char* my_ring, const T* qv, const float* qf32,
+                                           typename KeyOf<T>::type* keys, __nv_bfloat16* sbuf, const int beg,
+                                           const int lo, const int cnt,
+                                           typename KeyOf<T>::type (&run)[KPL > 0 ? KPL : 1]) {
+    using Key = typename KeyOf<T>::type;
+    using Gm = Geom<T, D>;
+    constexpr int NQ = MODE >= 2 ? GQ : 1;
+    constexpr int L = Gm::L, HALF = L / 2;
+    constexpr int KP = KPL > 0 ? KPL : 1;
+    const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
+    Key pend[KP];
+#pragma unroll
+    for (int r = 0; r < KP; ++r) pend[r] = (Key)0;
+    int filled = 0;  // batches whose keys sit in pend
+    for (int ord = 0; ord < my_batches; ++ord) {
+        cp_async_wait<SLOTS - 2>();
+        __syncwarp();
+        if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
+        cp_async_commit();
+        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
+        const int sw = (r_in & 3) << 1;
+        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;  // position inside this CTA's chunk
+        float best = -INFINITY;  // MODE 3: running maximum over the heads
+        float row_score = 0.f;
+#pragma unroll
+        for (int g = 0; g < NQ; ++g) {
+            float acc[HALF];
+#pragma unroll
+            for (int ii = 0; ii < HALF; ++ii) acc[ii] = 0.f;
+            // this thread owns partial sums 2*ii + par; partial l takes chunks l, l + L, ...
+#pragma unroll
+            for (int k = 0; k * L < Gm::nchunk; ++k) {
+#pragma unroll
+                for (int ii = 0; ii < HALF; ++ii) {
+                    if (k * L + 2 * ii < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
+                        const int ch = k * L + 2 * ii + par;
+                        // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
+                        const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
+                        if constexpr (MODE == 3)
+                            add_quest_bounds(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             reinterpret_cast<const __nv_bfloat16*>(
+                                                 reinterpret_cast<const unsigned char*>(src) + Gm::slot_bytes),
+                                             reinterpret_cast<const __nv_bfloat16*>(qv) + g * D + ch * 8);
+                        else if constexpr (MODE == 2)
+                            add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
+                                             qf32 + g * D + ch * 8);
+                        else
+                            add_products(acc[ii], src, qv + ch * 8);
+                    }
+                }
+            }
+#pragma unroll
+            for (int w = HALF / 2; w > 0; w >>= 1)
+#pragma unroll
+                for (int ii = 0; ii < w; ++ii) acc[ii] = __fadd_rn(acc[ii], acc[ii + w]);
+            const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
+            const float sc = vtx::round_to<T>(total);
+            if (MODE == 3) best = fmaxf(best, sc);
+            else row_score = sc;
+            if (par == 0 && i < cnt) {
+                if (MODE == 2) sbuf[i * NQ + g] = __float2bfloat16_rn(sc);
+                else if (MODE == 1) store_score<T>(reinterpret_cast<T*>(a.scores) + beg + lo + i, sc);
+            }
+        }
+        if (MODE == 0 || MODE == 3) {
+            const Key key = (par == 0 && i < cnt) ? KeyOf<T>::make(MODE == 3 ? best : row_score, lo + i) : (Key)0;
+            if (KPL == 0) {
+                if (par == 0 && i < cnt) keys[i] = key;
+            } else {
+                // two batches fill one 32-key row of pend: even batches in the even lanes, odd batches moved
+                // to the odd lanes
+                const Key moved = __shfl_up_sync(0xffffffffu, key, 1);
+                const Key mine = (filled & 1) ? (par ? moved : (Key)0) : key;
+#pragma unroll
+                for (int r = 0; r < KP; ++r)
+                    if (r == (filled >> 1)) pend[r] = pend[r] | mine;  // disjoint lanes: OR keeps both batches
+                if (++filled == 2 * KP) {
+                    warp_topk_merge<Key, KP>(run, pend, lane);
+#pragma unroll
+                    for (int r = 0; r < KP; ++r) pend[r] = (Key)0;
+                    filled = 0;
+                }
+            }
+        }
+    }
+    if (KPL > 0 && filled > 0) warp_topk_merge<Key, KP>(run, pend, lane);
+    cp_async_wait<0>();
+}
+
+// MODE 0: fused mean + GeMV + top-k.  MODE 1: GeMV only (scores to global memory).
 // MODE 2 (bf16 only, GQ = query heads per KV head): the gqa_block_sparse_attention scores, i.e.
 // per query head the fp32-product dot with the page's row rounded to bf16, a softmax of scale * score over
 // the segment's candidates (canonical exp and sum) rounded to bf16, and the maximum over the heads.
+// MODE 3 (bf16 only): the gqa_quest_sparse_attention scores from two summary caches (per-page max and min):
+// per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
 // Returns true when this CTA leaves with the segment's page list complete (it is the only CTA of the
 // segment, or the last of its chunks to arrive), false when it has nothing more to do for the segment.
-template <typename T, int D, int MODE, typename SideWork = NoSideWork, int GQ = 1, typename PreSort = NoPreSort>
+template <typename T, int D, int MODE, typename HooksRef = NoHooks, int GQ = 1>
 __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s, const int j,
-                                             SideWork side_work = SideWork(), PreSort pre_sort = PreSort()) {
-    // MODE 3 (bf16 only): the gqa_quest_sparse_attention scores from two summary caches (per-page max and min):
-    // per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
+                                             HooksRef hooks = HooksRef()) {
+    using Hooks = typename std::remove_reference<HooksRef>::type;
     constexpr int NQ = MODE >= 2 ? GQ : 1;                          // score accumulators per row
     constexpr int NSRC = MODE == 3 ? 2 : 1;                         // summary rows gathered per page
-    constexpr int QBYTES = MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : D * (int)sizeof(T));
+    constexpr int QBYTES = q_stage_bytes<T, D, MODE, GQ>();
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
-    constexpr int L = Gm::L, HALF = L / 2;
     constexpr int SLOT_B = NSRC * Gm::slot_bytes;
     constexpr int SLOTS = SLOT_B * 3 * kWarps <= 96 * 1024 ? 3 : 2;
     constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
-    // layout: [ring][q_mean][keys][ids]
+    // layout: [ring][query staging][keys][ids]
     unsigned char* ring = smem_raw;
     T* qbar = reinterpret_cast<T*>(smem_raw + RING_B);
     Key* keys = reinterpret_cast<Key*>(reinterpret_cast<unsigned char*>(qbar) + QBYTES);
@@ -472,28 +652,31 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     __nv_bfloat16* sbuf = reinterpret_cast<__nv_bfloat16*>(ids + a.key_cap);  // MODE 2: [candidate][head] scores
     float* qf32 = reinterpret_cast<float*>(qbar);                               // MODE 2: [head][D]
     __shared__ int s_last_arrival;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;  // candidates of the whole segment
     const bool split = MODE != 2 && a.chunk > 0 && c > a.chunk;
     const int nch = split ? (c + a.chunk - 1) / a.chunk : 1;
     if (j >= nch) return false;
-    if (c <= a.K) {  // nothing to select: the block-table builder already wrote the whole list
-        side_work(threadIdx.x >> 5, threadIdx.x & 31);
-        return true;
-    }
-    if (split ? nch > a.nch_max : (MODE != 1 && c > a.key_cap)) {
-        // More candidates than the caller's max_num_pages_per_request promised: shared memory (or the grid)
-        // cannot hold them.  Flag it and select the first K candidates so that the list stays well defined.
+    const bool overflow = split ? nch > a.nch_max : (MODE != 1 && c > a.key_cap);
+    if (c <= a.K || overflow) {
+        // Nothing to select (the block-table builder already wrote the whole list), or more candidates than
+        // the caller's max_num_pages_per_request promised (shared memory or the grid cannot hold them: flag it
+        // and select the first K candidates so that the list stays well defined).
         if (j != 0) return false;
-        side_work(threadIdx.x >> 5, threadIdx.x & 31);
-        if (threadIdx.x == 0 && a.status) atomicOr(a.status, (uint32_t)VTX_STATUS_CANDIDATE_OVERFLOW);
-        if (MODE != 1) {
-            const int o0 = a.sparse_indptr[s] + a.bos;
-            for (int e = threadIdx.x; e < a.K; e += kThreads) {
-                const int32_t row = a.dense_indices[beg + e];
-                a.sparse_indices[o0 + e] = row;
-                if (a.sparse_pt) a.sparse_pt[(int64_t)s * a.pt_stride + a.bos + e] = row;
+        hooks.wait();
+        const typename Hooks::Regs hr = hooks.load(warp, lane);
+        hooks.finish(warp, lane, hr, nullptr);
+        if (c > a.K) {
+            if (threadIdx.x == 0 && a.status) atomicOr(a.status, (uint32_t)VTX_STATUS_CANDIDATE_OVERFLOW);
+            if (MODE != 1) {
+                const int o0 = a.sparse_indptr[s] + a.bos;
+                for (int e = threadIdx.x; e < a.K; e += kThreads) {
+                    const int32_t row = a.dense_indices[beg + e];
+                    a.sparse_indices[o0 + e] = row;
+                    if (a.sparse_pt) a.sparse_pt[(int64_t)s * a.pt_stride + a.bos + e] = row;
+                }
             }
         }
         return true;
@@ -507,8 +690,6 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     }
     __syncthreads();  // row ids are staged
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
     unsigned char* my_ring = ring + (size_t)warp * SLOTS * SLOT_B;
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
     const unsigned char* cent = reinterpret_cast<const unsigned char*>(a.centroids);
@@ -532,99 +713,87 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         }
     };
 
+    // prologue: SLOTS - 1 batches in flight; the last slot stays free until the loop's first iteration
+    const uint32_t spare_addr = my_ring_addr + (uint32_t)((SLOTS - 1) * SLOT_B);
+    const unsigned char* spare = my_ring + (size_t)(SLOTS - 1) * SLOT_B;
 #pragma unroll
     for (int i = 0; i < SLOTS - 1; ++i) {
         if (i < my_batches) issue(i);
+        if (i == SLOTS - 2) hooks.issue_extra(warp, lane, spare_addr);
         cp_async_commit();
     }
-    side_work(warp, lane);
-    if (MODE == 3) {  // the group's query heads as they are
-        const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
-        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
-    }
-    if (MODE == 2) {  // the group's query heads, widened to fp32
-        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
-        for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
-            vtx::Vec8<T> v;
-            v.load_cached(qs + ch * 8);
-            float f[8];
-            v.unpack(f);
+    hooks.wait();
+    T* my_q = qbar + (MODE < 2 ? warp * D : 0);
+    if constexpr (MODE < 2) {
+        // grouped-query mean, by every warp for itself (no block barrier between the wait and the first score):
+        // one canonical chunk per lane and pass; all loads of a pass are issued before anything is stored
+        const typename Hooks::Regs hr = hooks.load(warp, lane);
+        constexpr int GMAX = 8;
+        for (int ch0 = 0; ch0 < Gm::nchunk; ch0 += 32) {
+            const int ch = ch0 + lane;
+            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
+            float acc[8];
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) qf32[ch * 8 + jj] = f[jj];
-        }
-    }
-    // grouped-query mean, one canonical chunk per thread
-    for (int ch = threadIdx.x; MODE < 2 && ch < Gm::nchunk; ch += kThreads) {
-        const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
-        float acc[8];
+            for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
+            if (ch < Gm::nchunk) {
+                for (int g0 = 0; g0 < a.G; g0 += GMAX) {
+                    vtx::Vec8<T> v[GMAX];
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
-        for (int g = 0; g < a.G; ++g) {
-            vtx::Vec8<T> v;
-            v.load_cached(qs + (int64_t)g * D);
-            float f[8];
-            v.unpack(f);
+                    for (int g = 0; g < GMAX; ++g)
+                        if (g0 + g < a.G) v[g].load_cached(qs + (int64_t)(g0 + g) * D);
 #pragma unroll
-            for (int jj = 0; jj < 8; ++jj) acc[jj] = __fadd_rn(acc[jj], f[jj]);
-        }
-        const float g_f = (float)a.G;
+                    for (int g = 0; g < GMAX; ++g) {
+                        if (g0 + g < a.G) {
+                            float f[8];
+                            v[g].unpack(f);
 #pragma unroll
-        for (int jj = 0; jj < 8; ++jj) acc[jj] = __fdiv_rn(acc[jj], g_f);
-        vtx::store8(qbar + ch * 8, acc);  // rounds once to T
-    }
-    __syncthreads();  // q_mean is staged
-    for (int ord = 0; ord < my_batches; ++ord) {
-        cp_async_wait<SLOTS - 2>();
-        __syncwarp();
-        if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
-        cp_async_commit();
-        const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
-        const int sw = (r_in & 3) << 1;
-        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;  // position inside this CTA's chunk
-        float best = -INFINITY;  // MODE 3: running maximum over the heads
-#pragma unroll
-        for (int g = 0; g < NQ; ++g) {
-            float acc[HALF];
-#pragma unroll
-            for (int ii = 0; ii < HALF; ++ii) acc[ii] = 0.f;
-            // this thread owns partial sums 2*ii + par; partial l takes chunks l, l + L, ...
-#pragma unroll
-            for (int k = 0; k * L < Gm::nchunk; ++k) {
-#pragma unroll
-                for (int ii = 0; ii < HALF; ++ii) {
-                    if (k * L + 2 * ii < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
-                        const int ch = k * L + 2 * ii + par;
-                        // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
-                        const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
-                        if constexpr (MODE == 3)
-                            add_quest_bounds(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
-                                             reinterpret_cast<const __nv_bfloat16*>(
-                                                 reinterpret_cast<const unsigned char*>(src) + Gm::slot_bytes),
-                                             reinterpret_cast<const __nv_bfloat16*>(qbar) + g * D + ch * 8);
-                        else if constexpr (MODE == 2)
-                            add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
-                                             qf32 + g * D + ch * 8);
-                        else
-                            add_products(acc[ii], src, qbar + ch * 8);
+                            for (int jj = 0; jj < 8; ++jj) acc[jj] = __fadd_rn(acc[jj], f[jj]);
+                        }
                     }
                 }
-            }
+                const float g_f = (float)a.G;
 #pragma unroll
-            for (int w = HALF / 2; w > 0; w >>= 1)
-#pragma unroll
-                for (int ii = 0; ii < w; ++ii) acc[ii] = __fadd_rn(acc[ii], acc[ii + w]);
-            const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
-            if (par == 0 && i < cnt) {
-                const float sc = vtx::round_to<T>(total);
-                if (MODE == 0) keys[i] = KeyOf<T>::make(sc, lo + i);
-                else if (MODE == 2) sbuf[i * NQ + g] = __float2bfloat16_rn(sc);
-                else if (MODE == 3) best = fmaxf(best, sc);
-                else store_score<T>(reinterpret_cast<T*>(a.scores) + beg + lo + i, sc);
+                for (int jj = 0; jj < 8; ++jj) acc[jj] = __fdiv_rn(acc[jj], g_f);
+                vtx::store8(my_q + ch * 8, acc);  // rounds once to T
             }
         }
-        if (MODE == 3 && par == 0 && i < cnt) keys[i] = KeyOf<T>::make(best, lo + i);
+        if (hooks.needs_spare(warp)) cp_async_wait<0>();  // the copies of issue_extra have landed (this lane's part)
+        __syncwarp();                                      // ... every lane's part; the warp's query mean is staged
+        hooks.finish(warp, lane, hr, spare);
+        __syncwarp();                                      // the spare slot may be refilled from here on
+    } else {
+        const typename Hooks::Regs hr = hooks.load(warp, lane);
+        if (MODE == 3) {  // the group's query heads as they are
+            const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
+            for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
+        } else {          // the group's query heads, widened to fp32
+            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
+            for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
+                vtx::Vec8<T> v;
+                v.load_cached(qs + ch * 8);
+                float f[8];
+                v.unpack(f);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj) qf32[ch * 8 + jj] = f[jj];
+            }
+        }
+        if (hooks.needs_spare(warp)) cp_async_wait<0>();
+        __syncwarp();
+        hooks.finish(warp, lane, hr, spare);
+        __syncthreads();  // the query heads are staged
     }
-    cp_async_wait<0>();
+
+    const int kpl = (MODE == 0 || MODE == 3) ? stream_kpl(a.K) : 0;
+    Key run1[1] = {(Key)0}, run2[2] = {(Key)0, (Key)0};
+    if (kpl == 1)
+        score_rows<T, D, MODE, GQ, 1, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+                                                     cnt, run1);
+    else if (kpl == 2)
+        score_rows<T, D, MODE, GQ, 2, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+                                                     cnt, run2);
+    else
+        score_rows<T, D, MODE, GQ, 0, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+                                                     cnt, run1);
     if constexpr (MODE == 2) {
         __syncthreads();  // all head scores written; the rings are idle and lend their space to the reductions
         float* red = reinterpret_cast<float*>(ring);  // [NQ][kThreads]
@@ -679,7 +848,6 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         }
     }
     if (MODE != 1) {
-        __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
         const int o0 = a.sparse_indptr[s] + a.bos;
         Key* part = reinterpret_cast<Key*>(a.part_keys) + ((size_t)s * a.nch_max) * a.K;  // this segment's chunks
         EmitSelection<T> emit;
@@ -687,13 +855,56 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         emit.ids = split ? a.dense_indices + beg : ids;  // keys name candidates by their position in the segment
         emit.out = a.sparse_indices + o0;
         emit.out_pt = a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride + a.bos : nullptr;
+        emit.to_scratch = split;
+        bool merged = false;  // this CTA's own keys are dealt with
+        if (kpl > 0) {
+            // every warp holds its best 32 * kpl keys in registers: hand them over through keys[] and let warp 0
+            // fold the four sorted lists into one (each fold: elementwise maximum against the reversed other
+            // list, then one bitonic merge)
+            const int n = 32 * kpl;
+            if (kpl == 1) keys[warp * n + lane] = run1[0];
+            else { keys[warp * n + lane * 2] = run2[0]; keys[warp * n + lane * 2 + 1] = run2[1]; }
+            __syncthreads();  // lists are visible, every ring is idle
+            if (!split) hooks.pre_sort(0);
+            if (warp == 0) {
+                if (kpl == 1) {
+#pragma unroll
+                    for (int w = 1; w < kWarps; ++w) {
+                        const Key o = keys[w * n + 31 - lane];
+                        run1[0] = run1[0] > o ? run1[0] : o;
+                        warp_bitonic_desc<Key, 1>(run1, lane, 32);
+                    }
+                    if (lane < a.K) emit(lane, run1[0]);
+                } else {
+#pragma unroll
+                    for (int w = 1; w < kWarps; ++w) {
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            const Key o = keys[w * n + (31 - lane) * 2 + (1 - r)];
+                            run2[r] = run2[r] > o ? run2[r] : o;
+                        }
+                        warp_bitonic_desc<Key, 2>(run2, lane, 64);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 2; ++r)
+                        if (lane * 2 + r < a.K) emit(lane * 2 + r, run2[r]);
+                }
+            }
+            merged = true;
+            if (!split) return true;  // the caller's block barrier publishes the list to the CTA
+        } else {
+            __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
+        }
         int n_sort = cnt;
         bool partial = split;
         for (;;) {
-            const int xoff = partial ? 0 : pre_sort(n_sort);
-            emit.to_scratch = partial;
-            sort_emit<Key>(keys, n_sort, a.K, reinterpret_cast<Key*>(smem_raw + xoff), emit);
-            if (!partial) break;
+            if (!merged) {
+                const int xoff = partial ? 0 : hooks.pre_sort(n_sort);
+                emit.to_scratch = partial;
+                sort_emit<Key>(keys, n_sort, a.K, reinterpret_cast<Key*>(smem_raw + xoff), emit);
+                if (!partial) break;
+            }
+            merged = false;
             // publish this chunk's keys, then find out whether every other chunk of the segment is in
             __threadfence();
             __syncthreads();
@@ -737,7 +948,7 @@ int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int 
 }
 
 // Candidate capacity of one segment (sizes the key and row-id arrays in shared memory).
-int key_capacity(int max_pages) { return vtx::pow2_ceil(max_pages); }
+int key_capacity(int max_pages) { return vtx::pow2_ceil(max_pages < 256 ? 256 : max_pages); }  // >= 4 warps x 64 keys
 
 // Candidates one CTA scans when a workspace allows a segment's scan to be split.
 constexpr int kChunk = 512;
