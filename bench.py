@@ -59,6 +59,16 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
 
 
+def ncu_traffic_bytes(name: str):
+    """DRAM bytes (read + written) of one launch of a kernel, from the figures recorded beside its ncu summary
+    (``profiles/<name>_ncu.json``); None when no capture has been recorded."""
+    f = ROOT / "profiles" / f"{name}_ncu.json"
+    if not f.exists():
+        return None
+    d = json.loads(f.read_text())
+    return float(d["dram_bytes_read"]) + float(d["dram_bytes_write"])
+
+
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -632,6 +642,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="debug: smaller batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-side", action="store_true", help="skip the side measurements (configs 3 and 5)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch inside the step graph: 0 off, 1 on, 2 on + early prologue")
     ap.add_argument("--flow", default="block_sparse_attention",
@@ -730,6 +741,13 @@ def main():
         ok = all(int(f.item()) == 1 for f in flags)
 
     kt = time_kernels(rt, step, cfg, reps=10, pdl=0 if args.no_graph else args.pdl)
+    # ---- side measurements, outside the timed region of the headline workload: the ragged batch sharded by
+    # request over the same ranks (its strong-scaling point at this N) and, on rank 0, the MLA configuration
+    side = None
+    if not args.no_side:
+        side = dict(c3=measure_ragged(device, dist, rank, world, steps=20, warmup=3))
+        if rank == 0:
+            side["c5"] = measure_mla(device, steps=20)
     peaks, peak_kind = measured_peaks()
     ab = algorithmic_bytes(cfg)
     peak = float(peaks["hbm_gbs"])
@@ -752,10 +770,9 @@ def main():
                      d2h_bytes_per_step=step.d2h_bytes),
             gpu_launches=launches_per_step * args.steps, clocks=clocks, parity_sample_ok=ok,
             cuda_graph=not args.no_graph, programmatic_launch=int(args.pdl if not args.no_graph else 0),
-            # traffic: dram__bytes_read + dram__bytes_write of one launch, from the ncu capture summarised in
-            # profiles/sparse_layer_kernel_c2_ncu.md (204.9 MB read + 7.4 MB written)
             roofline=dict(kernel="sparse_layer_kernel (token write + indexer + decode, 27 launches per step)",
-                          traffic=212.3e6, algorithmic_bytes_per_launch=ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
+                          traffic=ncu_traffic_bytes("sparse_layer_kernel_c2"),
+                          algorithmic_bytes_per_launch=ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
                           **roof(ab["centroids_per_layer"] + ab["sparse_kv_per_layer"], kt["sparse_layer_fused"])),
             kernels=dict(sparse_layer_fused=roof(ab["centroids_per_layer"] + ab["sparse_kv_per_layer"],
                                                  kt["sparse_layer_fused"]),
@@ -767,6 +784,8 @@ def main():
                           frac_of_measured_peak=ab["step"] * args.steps / dev_s / 1e9 / peak,
                           frac_of_nominal_8000=ab["step"] * args.steps / dev_s / 1e9 / 8000.0),
         )
+        if side is not None:
+            line["side"] = side
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(cfg)
         elif not args.no_cpu_baseline:

@@ -131,6 +131,10 @@ int vtx_creduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int n
  * reduce_pp Mean (cache/triton_kernels/reduce_impl.py:7-89) that the runtime issues back to back
  * for flows whose forward_cache is `CMean(dim=1)(cache["k"], cache["centroids"])`
  * (flow/algorithms.py:172-205).  centroids [num_pages*H, 1, D].
+ * Decode (one new token per page) and prefill (many rows of a page in one call) alike, on one condition:
+ * the rows of one page that a call writes are consecutive entries of loc in ascending slot order, which is
+ * what a prefill produces (each page id appears once, flow/algorithms.py:15).  Rows of the page written by
+ * earlier calls are read from the cache.  For any other order of loc use vtx_set_kv then vtx_cmean.
  */
 int vtx_set_kv_cmean(void* k_cache, void* v_cache, const void* new_k, const void* new_v,
                      void* centroids, const int64_t* loc, int64_t nnz, int num_kv_heads,

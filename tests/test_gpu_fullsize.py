@@ -40,6 +40,62 @@ def test_config4b_prefill_32768_tokens():
     assert torch.equal(out.cpu()[:, 0].view(torch.int16), vo.cmean_pages(k, rows).view(torch.int16))
 
 
+def test_config4b_prefill_write_and_centroids_in_one_launch():
+    """Prefill of a 32768-token request through the fused KV write + page mean: caches and all 2048 x 8
+    centroids equal set_kv followed by the mean, bit for bit, and equal the oracle."""
+    P, H, D, pages, extra = 16, 8, 128, 2048, 64
+    g = torch.Generator().manual_seed(44)
+    perm = torch.randperm(pages + extra, generator=g)[:pages]       # physical pages of the request, in token order
+    loc = (perm.view(-1, 1) * P + torch.arange(P).view(1, -1)).reshape(-1)
+    nk = torch.randn(pages * P, H, D, generator=g).bfloat16().cuda()
+    nv = torch.randn(pages * P, H, D, generator=g).bfloat16().cuda()
+    res = []
+    for fused in (True, False):
+        k = torch.zeros((pages + extra) * H, P, D, dtype=torch.bfloat16, device="cuda")
+        v = torch.zeros_like(k)
+        c = torch.zeros((pages + extra) * H, 1, D, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            _cabi.set_kv_cmean(k, v, nk, nv, c, loc.cuda(), P)
+        else:
+            _cabi.set_kv(k, v, nk, nv, loc.cuda(), P)
+            _cabi.cmean(k, c, loc.cuda(), H, P)
+        res.append((k, v, c))
+    for a, b in zip(*res):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    rows = (perm.view(-1, 1) * H + torch.arange(H).view(1, -1)).reshape(-1)
+    want = vo.cmean_pages(res[0][0].cpu(), rows)
+    assert torch.equal(res[0][2].cpu()[rows, 0].view(torch.int16), want.view(torch.int16))
+
+
+def test_prefill_chunk_that_continues_and_leaves_partial_pages():
+    """A chunked prefill: the chunk starts in the middle of a page written earlier (its first rows come from
+    the cache), spans whole pages and ends in a partial one; two requests in one call."""
+    P, H, D, pages = 16, 4, 128, 40
+    g = torch.Generator().manual_seed(45)
+    k0 = torch.randn(pages * H, P, D, generator=g).bfloat16()
+    v0 = torch.randn(pages * H, P, D, generator=g).bfloat16()
+    perm = torch.randperm(pages, generator=g)
+    # request A: pages perm[0:6], chunk covers slots 5 .. 5+70; request B: pages perm[10:13], slots 0 .. 40
+    slot = lambda pgs, a, b: torch.as_tensor([int(pgs[i // P]) * P + i % P for i in range(a, b)], dtype=torch.int64)
+    loc = torch.cat([slot(perm[0:6], 5, 75), slot(perm[10:13], 0, 40)])
+    nnz = loc.numel()
+    nk = torch.randn(nnz, H, D, generator=g).bfloat16().cuda()
+    nv = torch.randn(nnz, H, D, generator=g).bfloat16().cuda()
+    res = []
+    for fused in (True, False):
+        k, v = k0.cuda(), v0.cuda()
+        c = torch.zeros(pages * H, 1, D, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            _cabi.set_kv_cmean(k, v, nk, nv, c, loc.cuda(), P)
+        else:
+            _cabi.set_kv(k, v, nk, nv, loc.cuda(), P)
+            _cabi.cmean(k, c, loc.cuda(), H, P)
+        res.append((k, v, c))
+    for a, b in zip(*res):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    assert int((res[0][2].float().abs().sum(dim=(1, 2)) > 0).sum()) == (4 + 2) * H   # pages closed: 4 of A, 2 of B
+
+
 def test_config2_layer_properties_at_full_batch():
     """bs64 x 8192 tokens, one layer: the one-launch layer equals the separate kernels bit for bit, is
     idempotent, and its selection is a sorted prefix under the (score desc, position asc) order."""
@@ -89,6 +145,18 @@ def test_config2_layer_properties_at_full_batch():
     rest_max = torch.where(mask, sc, torch.full_like(sc, -float("inf"))).max(dim=1).values
     assert bool((rest_max <= chosen_sc[:, -1]).all())
     assert torch.isfinite(out_a.float()).all()
+    # requests 0, 31 and 63 against the CPU oracle: selection bit-exact, attention within 2e-2
+    for r in (0, 31, 63):
+        rows_r = ((slots[r, ::P].long() // P).view(-1, 1) * H + torch.arange(H).view(1, -1)).reshape(-1)
+        plan = vo.plan_decode([ctx], np.arange(ctx, dtype=np.int32).reshape(1, -1), [0], P, H, K, bos, eos, 64, 16)
+        kk, vv, cc = k[rows_r.cuda()].cpu(), v[rows_r.cuda()].cpu(), cent[rows_r.cuda()].cpu()
+        qi = q[r * H:(r + 1) * H].cpu()
+        vo.forward_indexer(qi, cc, plan, K, bos, eos)
+        got = sel_a.view(dp.S, K + bos + eos)[r * H:(r + 1) * H].reshape(-1).cpu().numpy()
+        np.testing.assert_array_equal(got, rows_r.numpy()[plan["sparse_kv_indices"]])
+        want = vo.decode_gqa(qi, kk, vv, plan["sparse_kv_indptr"], plan["sparse_kv_indices"], plan["kv_last_page_len"])
+        err = (out_a[r * H:(r + 1) * H].float().cpu() - want.float()).abs()
+        assert bool((err <= 2e-2 * want.float().abs().clamp(min=1)).all())
 
 
 def test_config5_mla_full_batch_two_forms_and_properties():

@@ -103,3 +103,38 @@ def test_topk_equals_reference_kernel(ref, seq, H, K, bos, eos, ties):
                     dp.max_pages)
     torch.cuda.synchronize()
     assert torch.equal(mine, theirs)
+
+
+def test_indexer_selection_equals_recorded_reference_run():
+    """The fused indexer and the one-launch layer against what the reference's own kernels (mv_bpr_kernel under
+    Triton on a B200, then topk_output) selected on the same seeded bf16 batch of the config-2 shape
+    (tests/golden/ref_gpu_triton_kernels.npz): the same pages in the same order for every segment, and the
+    stand-alone GeMV returns the reference's score bits."""
+    from pathlib import Path
+
+    from _util import to_dev
+
+    g = np.load(Path(__file__).parent / "golden" / "ref_gpu_triton_kernels.npz")
+    c = {k: int(g[k]) for k in ("seed", "H", "G", "D", "P", "K", "bos", "eos", "chunk")}
+    seq = [int(x) for x in g["seq"]]
+    prob = vo.make_paged_problem(c["seed"], seq, c["H"], c["G"], c["D"], c["P"])
+    dp = DevicePlan(prob, c["P"], c["H"], c["K"], c["bos"], c["eos"], max_chunk=c["chunk"], min_chunk=16)
+    d = to_dev(prob)
+    ns = len(g["selected"])
+    sel = dp.sparse_indices.clone()
+    _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices, sel, dp.S,
+                        c["K"], c["bos"], c["eos"], dp.max_pages)
+    np.testing.assert_array_equal(sel.cpu().numpy()[:ns], g["selected"])
+    sel2 = dp.sparse_indices.clone()
+    out = torch.empty_like(d["q"])
+    _cabi.sparse_layer_fused(d["q"], d["centroids"], d["k"], d["v"], out, dp.dense_indptr, dp.sparse_indptr,
+                             dp.dense_indices, sel2, dp.last_page_len, dp.S, c["P"], c["K"], c["bos"], c["eos"],
+                             dp.max_pages, 1.0 / np.sqrt(c["D"]))
+    np.testing.assert_array_equal(sel2.cpu().numpy()[:ns], g["selected"])
+    qm = vo.q_group_mean(prob["q"]).cuda()
+    scores = torch.zeros(len(g["scores_bits"]), dtype=torch.bfloat16, device="cuda")
+    _cabi.gemv(qm, d["centroids"], scores, dp.dense_indptr, dp.dense_indices, dp.S, c["K"], c["bos"], c["eos"])
+    got = scores.view(torch.int16).cpu().numpy()
+    ref_plan = dp.oracle(prob)
+    for _, a, b in vo.candidate_windows(ref_plan["dense_kv_indptr"], dp.S, c["K"], c["bos"], c["eos"]):
+        np.testing.assert_array_equal(got[a:b], g["scores_bits"][a:b])

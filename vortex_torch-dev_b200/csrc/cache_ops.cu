@@ -83,10 +83,14 @@ __global__ void __launch_bounds__(256) creduce_kernel(const T* __restrict__ x, T
     }
 }
 
-// KV write fused with the centroid update of the page the new token completes (if it does).
+// KV write fused with the centroid update of the pages the new tokens complete.
 // One group of LANES threads per (new token, head); each lane owns chunks of eight columns.
-// The mean adds the page's rows in ascending order with the new row (still in registers) last,
-// so the result has the same bits as set_kv_kernel followed by cmean_kernel.
+// The mean adds the page's rows in ascending order, the new row (still in registers) last, so the result
+// has the same bits as set_kv_kernel followed by the mean kernel.  An older row of the page is taken from
+// the cache unless this same launch writes it: a launch may write several rows of one page (a prefill) as
+// long as they are consecutive entries of loc in ascending slot order, in which case the row written by
+// entry i - d sits d slots below entry i's slot and is read from new_k instead (the cache copy of that row
+// may not have landed yet).
 template <typename T, int LANES>
 __global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cache, T* __restrict__ v_cache,
                                                           const T* __restrict__ new_k, const T* __restrict__ new_v,
@@ -101,13 +105,19 @@ __global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cac
     const float denom = (float)P;
     for (int64_t it = (int64_t)blockIdx.x * GROUPS + threadIdx.x / LANES; it < items;
          it += (int64_t)gridDim.x * GROUPS) {
-        const int64_t t = loc[it / H];
+        const int64_t idx = it / H;  // entry of loc
+        const int64_t t = loc[idx];
         const int h = (int)(it % H);
         const int64_t pid = (t / P) * H + h;
         const int tok = (int)(t % P);
         T* kpage = k_cache + pid * (int64_t)P * D;
         T* vpage = v_cache + pid * (int64_t)P * D;
         const bool closes = tok == P - 1;
+        // how many of the page's older rows this launch writes itself: entries idx-1, idx-2, ... while their
+        // slots count down from t-1
+        int own = 0;
+        if (closes)
+            while (own < P - 1 && idx - (own + 1) >= 0 && loc[idx - (own + 1)] == t - (own + 1)) ++own;
         for (int c = lane; c < nchunk; c += LANES) {
             vtx::Vec8<T> nk, nv;
             nk.load_cached(new_k + it * D + c * 8);
@@ -121,13 +131,15 @@ __global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cac
             float acc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-            // rows 0 .. P-2 come from the cache, eight loads in flight at a time (predicated tail)
+            // rows 0 .. P-2, eight loads in flight at a time (predicated tail): row r is P-1-r slots below
             for (int r = 0; r < P - 1; r += 8) {
                 vtx::Vec8<T> v[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    if (r + u < P - 1) v[u].load(kpage + (int64_t)(r + u) * D + c * 8);
-                    else v[u].zero();
+                    const int back = P - 1 - (r + u);
+                    if (r + u >= P - 1) v[u].zero();
+                    else if (back <= own) v[u].load_cached(new_k + ((idx - back) * H + h) * (int64_t)D + c * 8);
+                    else v[u].load(kpage + (int64_t)(r + u) * D + c * 8);
                 }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {

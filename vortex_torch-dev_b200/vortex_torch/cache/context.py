@@ -55,17 +55,19 @@ class Context(ContextBase):
 
     # ---- deferred KV write (fusion of set_kv with the flow's first cache operator) ----
     def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int,
-                       single_token_pages: bool = False) -> None:
+                       single_token_pages: bool = False, page_ordered: bool = False) -> None:
         """Record a KV write instead of launching it.  The next cache operator either folds it into
         its own kernel (``Mean(dim=1)`` over the same K cache and ``loc``) or launches it first;
         the caller must call ``flush_kv_write`` after ``forward_cache`` in case no operator ran.
 
         ``single_token_pages``: the caller guarantees that no two slots of ``loc`` fall into the same
-        page (a decode step: one new token per request).  Only then may the write be folded into the
-        mean, which reads the page's other rows from the cache; a prefill, where one launch writes many
-        rows of a page, must leave it False."""
+        page (a decode step: one new token per request).  ``page_ordered``: the rows of one page that this
+        write holds are consecutive entries of ``loc`` in ascending slot order (a prefill).  With either
+        guarantee the write may be folded into the mean (one launch); only the first also allows folding
+        both into the layer's attention launch.  Without a guarantee the write is launched on its own."""
         self.flush_kv_write()
-        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size, bool(single_token_pages))
+        mode = "single" if single_token_pages else ("ordered" if page_ordered else None)
+        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size, mode)
 
     def flush_kv_write(self) -> None:
         self.flush_append()

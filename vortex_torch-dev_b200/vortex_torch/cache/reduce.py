@@ -64,14 +64,15 @@ class Reduce(vOp):
             ctx.flush_append()
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
-            k_cache, v_cache, new_k, new_v, ploc, P, single = pend
-            if (single and self.reduce_type == ReduceType.Mean
+            k_cache, v_cache, new_k, new_v, ploc, P, mode = pend
+            single = mode == "single"
+            if (mode is not None and self.reduce_type == ReduceType.Mean
                     and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
                     and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
                     and new_k.shape[1] == ctx.head_num):
                 # the runtime's KV write and this mean touch the same page: one kernel does both
                 ctx._pending_kv = None
-                if getattr(ctx, "_defer_append", False):
+                if single and getattr(ctx, "_defer_append", False):
                     ctx.flush_append()
                     ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, loc, P)
                     return output
