@@ -410,6 +410,56 @@ int vtx_elementwise_binary(const void* x, const void* y, void* out, const int32_
                            float beta, int dtype, void* stream);
 
 /*
+ * Stand-alone forms of the indexer operators that the shipped flows chain.  (The flows themselves run them as
+ * links of vtx_indexer_gqa_softmax_fused / vtx_indexer_quest_fused; these entry points serve flows that
+ * compose the operators differently or read an intermediate, and return the same bits.)  All work on the
+ * candidate window of every segment - packed positions [dense_kv_indptr[s] + bos, dense_kv_indptr[s+1] - eos)
+ * of segments with more than topk_val candidates, the rows the reference's workload list covers
+ * (csrc/utils_sglang.cu:219-251) - and leave other rows untouched.  bf16 only; one rounding per operator output.
+ *
+ * vtx_gemm_bpr       out[p, c, g] = table[row_p, c, :] . q[s, g, :] (fp32 products and sum); q [eff_bs, G, D],
+ *                    table [rows, C, D], out [N, C, G].  Replaces mm_bpr (indexer/triton_kernels/matmul_impl.py:6-113).
+ * vtx_softmax_ragged in place on x [N, inner]: softmax of scale * x over a segment's candidates, per inner
+ *                    element.  Replaces softmax_inplace_r (indexer/triton_kernels/softmax_impl.py:6-105).
+ * vtx_normalize_ragged  in place: x divided by max(L2 norm over the segment's candidates, eps), per inner
+ *                    element.  Replaces normalize_inplace_r (indexer/triton_kernels/normalize_impl.py:6-119).
+ * vtx_reduce_ragged  x [N, rows, cols] -> out [N, 1, cols] (dim 1) or [N, rows, 1] (dim 2); kind 0 mean, 1 max,
+ *                    2 min, 3 l2norm, 4 sum (the reference's ReduceType values).  Replaces reduce_rr
+ *                    (indexer/triton_kernels/reduce_impl.py:8-120).
+ * vtx_binary_bpr     out[p] = op(q[s], table[row_p]) with the inner dims broadcast; q [eff_bs, q_c, q_d],
+ *                    table [rows, table_c, table_d]; op 0 max, 1 min, 2 bf16(alpha x) + bf16(beta y), 3 x y.
+ *                    With x_is_ragged the left operand is the RAGGED row q[p] ([N, q_c, q_d]) instead.
+ *                    Replaces elementwise_binary_bpr and _rpr
+ *                    (indexer/triton_kernels/elementwise_binary_impl.py:167-307, 348-476).
+ * vtx_transpose_ragged  out[p, c, r] = x[p, r, c].  Replaces transpose_rr (indexer/triton_kernels/transpose_impl.py:6-101).
+ * vtx_save_load_ragged  save != 0: paged[row_p] = ragged[p]; save == 0: ragged[p] = paged[row_p], inner_size
+ *                    elements per row.  Replaces save_rp / load_pr (indexer/triton_kernels/save_load_impl.py:6-229).
+ */
+int vtx_gemm_bpr(const void* q, const void* table, void* out, const int32_t* dense_kv_indptr,
+                 const int32_t* dense_kv_indices, int eff_batch_size, int group_size, int table_rows,
+                 int head_dim, int topk_val, int page_reserved_bos, int page_reserved_eos, int dtype,
+                 void* stream);
+int vtx_softmax_ragged(void* x, const int32_t* dense_kv_indptr, int eff_batch_size, int inner_size,
+                       int topk_val, int page_reserved_bos, int page_reserved_eos, float scale, int dtype,
+                       void* stream);
+int vtx_normalize_ragged(void* x, const int32_t* dense_kv_indptr, int eff_batch_size, int inner_size,
+                         int topk_val, int page_reserved_bos, int page_reserved_eos, float eps, int dtype,
+                         void* stream);
+int vtx_reduce_ragged(const void* x, void* out, const int32_t* dense_kv_indptr, int eff_batch_size,
+                      int rows, int cols, int dim, int kind, int topk_val, int page_reserved_bos,
+                      int page_reserved_eos, int dtype, void* stream);
+int vtx_binary_bpr(const void* q, const void* table, void* out, const int32_t* dense_kv_indptr,
+                   const int32_t* dense_kv_indices, int eff_batch_size, int q_c, int q_d, int table_c,
+                   int table_d, int op, float alpha, float beta, int x_is_ragged, int topk_val,
+                   int page_reserved_bos, int page_reserved_eos, int dtype, void* stream);
+int vtx_transpose_ragged(const void* x, void* out, const int32_t* dense_kv_indptr, int eff_batch_size,
+                         int rows, int cols, int topk_val, int page_reserved_bos, int page_reserved_eos,
+                         int dtype, void* stream);
+int vtx_save_load_ragged(void* ragged, void* paged, const int32_t* dense_kv_indptr,
+                         const int32_t* dense_kv_indices, int eff_batch_size, int inner_size, int save,
+                         int topk_val, int page_reserved_bos, int page_reserved_eos, int dtype, void* stream);
+
+/*
  * Prefill planner.  Replaces `sglang_plan_prefill` (csrc/register.h, csrc/utils_sglang.cu:462-621).
  * cached_seq_lens, input_seq_lens [bs] i32; outputs dense_kv_indptr, qo_indptr_paged [bs*H + 1],
  * qo_indptr_ragged [bs + 1], dense_kv_indices (packed row ids), kv_last_page_len [bs*H],

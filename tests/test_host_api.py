@@ -127,15 +127,11 @@ def test_profile_pass_allocates_and_detects_fusion():
     assert rt.flow.run_indexer_virtual(2, 16, 128, device="cpu") == 128
 
 
-def test_unbuilt_ops_fail_loudly():
+def test_every_shipped_flow_can_be_built():
     from vortex_torch.flow import build_vflow
-    from vortex_torch.indexer import Context
 
-    from vortex_torch.indexer import Normalize
-
-    build_vflow("gqa_quest_sparse_attention")  # every operator of the shipped flows can be constructed
-    with pytest.raises(NotImplementedError, match="no sm_100a kernel"):
-        Normalize()(None, ctx=Context())
+    for name in ("block_sparse_attention", "gqa_block_sparse_attention", "gqa_quest_sparse_attention"):
+        build_vflow(name)  # every operator of the shipped flows can be constructed
 
 
 def test_balance_requests():
@@ -150,7 +146,7 @@ def test_balance_requests():
     assert balance_requests(pages, 2) == balance_requests(pages, 2)
 
 
-def test_gqa_chain_is_recognised_and_unchained_use_fails():
+def test_gqa_chain_is_recognised_and_stand_alone_use_needs_the_gpu():
     from vortex_torch.abs import FORMAT, as_vtensor
     from vortex_torch.indexer import Context, GeMM, Max, Softmax
     from vortex_torch.runtime import ServerArgs, VortexDecodeRuntime
@@ -159,15 +155,24 @@ def test_gqa_chain_is_recognised_and_unchained_use_fails():
                              server_args=ServerArgs(vortex_module_name="gqa_block_sparse_attention"))
     f = rt.flow
     assert f.output_func._gqa_chain == (f.gemm, f.softmax, f.max_op)
+    assert f.output_func.chain_intact() and f.gemm._runs_fused() and f.max_op._runs_fused()
     assert f.gemm.output_buffer.shape == (rt.ictx.max_num_pages, 1, 4) and f.max_op.output_buffer.shape[1:] == (1, 1)
-    # a GeMM whose result does not end in the fused chain has nothing to run
+    # a GeMM whose result does not end in a fused chain runs its own kernel: on CPU tensors that is an error
+    # (there is no CPU fallback), never a silent no-op
     ctx = Context()
     ctx.max_num_pages = 8
     g = GeMM()
-    g.profile(as_vtensor(torch.zeros(1, 2, 16), FORMAT.BATCHED), as_vtensor(torch.zeros(4, 1, 16), FORMAT.PAGED), ctx)
-    with pytest.raises(NotImplementedError, match="no stand-alone sm_100a kernel"):
-        g.execute(torch.zeros(1, 2, 16), torch.zeros(4, 1, 16), ctx)
-    with pytest.raises(NotImplementedError):
-        Softmax(dim=0, scale=0.5).execute(torch.zeros(1, 1, 1), ctx)
-    with pytest.raises(NotImplementedError):
-        Max(dim=2).execute(torch.zeros(1, 1, 1), ctx)
+    bf = torch.bfloat16
+    out = g.profile(as_vtensor(torch.zeros(1, 2, 16, dtype=bf), FORMAT.BATCHED),
+                    as_vtensor(torch.zeros(4, 1, 16, dtype=bf), FORMAT.PAGED), ctx)
+    assert out.shape == (8, 1, 2) and not g._runs_fused()
+    sm = Softmax(dim=0, scale=0.5)
+    sm.profile(out, ctx)
+    mx = Max(dim=2)
+    assert mx.profile(out, ctx).shape == (8, 1, 1)
+    rt.ictx.set_batch_size(1)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        g.execute(torch.zeros(1, 2, 16, dtype=bf), torch.zeros(4, 1, 16, dtype=bf), rt.ictx)
+    with pytest.raises(NotImplementedError, match="bfloat16"):
+        GeMM().profile(as_vtensor(torch.zeros(1, 2, 16), FORMAT.BATCHED), as_vtensor(torch.zeros(4, 1, 16), FORMAT.PAGED),
+                       ctx)

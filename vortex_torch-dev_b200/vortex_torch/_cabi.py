@@ -52,6 +52,13 @@ SIGNATURES = {
     "vtx_decode_mla": [_p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
     "vtx_elementwise": [_p, _p, _p, _i64, _i, _i, _f, _f, _i, _p],
     "vtx_elementwise_binary": [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _f, _i, _p],
+    "vtx_gemm_bpr": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_softmax_ragged": [_p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_normalize_ragged": [_p, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_reduce_ragged": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_binary_bpr": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _p],
+    "vtx_transpose_ragged": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_save_load_ragged": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_set_mla_path": [_i],
     "vtx_mla_fault_read": [_p],
 }
@@ -470,3 +477,62 @@ def chunkwise_hn2nh(x, y, indptr, batch_table, num_qo_heads, num_kv_heads, head_
                                  int(num_kv_heads), G, int(head_dim), stream_of(x))
     check(rc, "vtx_chunkwise_hn2nh")
     return x_out, y_out
+
+
+# --------------------------------------------------------------------------- stand-alone chained operators
+def _win(ctx):
+    """(dense_kv_indptr, eff_bs, topk_val, bos, eos) of an indexer context."""
+    return ctx.dense_kv_indptr, ctx.batch_size * ctx.num_kv_heads, ctx.topk_val, ctx.page_reserved_bos, \
+        ctx.page_reserved_eos
+
+
+def gemm_bpr(q, table, out, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos) -> None:
+    """``out[p, c, g] = table[row_p, c, :] . q[s, g, :]`` on every candidate row (bf16, fp32 products and sum)."""
+    if not (q.dtype == table.dtype == out.dtype):
+        raise TypeError("gemm_bpr: q, table and out must share a dtype")
+    rc = lib.vtx_gemm_bpr(ptr(q), ptr(table), ptr(out), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
+                          q.shape[1], table.shape[1], q.shape[2], int(topk_val), int(bos), int(eos),
+                          dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_gemm_bpr")
+
+
+def softmax_ragged(x, dense_kv_indptr, eff_bs, topk_val, bos, eos, scale: float) -> None:
+    rc = lib.vtx_softmax_ragged(ptr(x), ptr(dense_kv_indptr), int(eff_bs), x.shape[1] * x.shape[2], int(topk_val),
+                                int(bos), int(eos), float(scale), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_softmax_ragged")
+
+
+def normalize_ragged(x, dense_kv_indptr, eff_bs, topk_val, bos, eos, eps: float = 1e-12) -> None:
+    rc = lib.vtx_normalize_ragged(ptr(x), ptr(dense_kv_indptr), int(eff_bs), x.shape[1] * x.shape[2], int(topk_val),
+                                  int(bos), int(eos), float(eps), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_normalize_ragged")
+
+
+def reduce_ragged(x, out, dim: int, kind: int, dense_kv_indptr, eff_bs, topk_val, bos, eos) -> None:
+    """kind: 0 mean, 1 max, 2 min, 3 l2norm, 4 sum over axis ``dim`` (1 or 2) of ``x`` ``[N, r, c]``."""
+    rc = lib.vtx_reduce_ragged(ptr(x), ptr(out), ptr(dense_kv_indptr), int(eff_bs), x.shape[1], x.shape[2], int(dim),
+                               int(kind), int(topk_val), int(bos), int(eos), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_reduce_ragged")
+
+
+def binary_bpr(q, table, out, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos, op: int,
+               alpha: float = 1.0, beta: float = 1.0, x_is_ragged: bool = False) -> None:
+    """op 0 max, 1 min, 2 alpha q + beta y, 3 q y between ``q[s]`` (or, with ``x_is_ragged``, the RAGGED row
+    ``q[p]``) and ``table[row_p]`` (inner dims broadcast)."""
+    rc = lib.vtx_binary_bpr(ptr(q), ptr(table), ptr(out), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
+                            q.shape[1], q.shape[2], table.shape[1], table.shape[2], int(op), float(alpha), float(beta),
+                            int(bool(x_is_ragged)), int(topk_val), int(bos), int(eos), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_binary_bpr")
+
+
+def transpose_ragged(x, out, dense_kv_indptr, eff_bs, topk_val, bos, eos) -> None:
+    rc = lib.vtx_transpose_ragged(ptr(x), ptr(out), ptr(dense_kv_indptr), int(eff_bs), x.shape[1], x.shape[2],
+                                  int(topk_val), int(bos), int(eos), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_transpose_ragged")
+
+
+def save_load_ragged(ragged, paged, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos, save: bool) -> None:
+    rc = lib.vtx_save_load_ragged(ptr(ragged), ptr(paged), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
+                                  ragged.shape[1] * ragged.shape[2], int(bool(save)), int(topk_val), int(bos), int(eos),
+                                  dtype_code(ragged.dtype), stream_of(ragged))
+    check(rc, "vtx_save_load_ragged")

@@ -76,11 +76,13 @@ class GeMV(vOp):
 
 
 class GeMM(vOp, ChainedOp):
-    """``GeMM()(x, y, ctx=ctx)`` computes ``O[s] = Y[s] X^T`` per page (reference: ``indexer/matmul.py:194-399``
-    over ``mm_bpr``): ``x`` BATCHED ``[S, G, D]``, ``y`` PAGED ``[num_pages*H, C, D]`` -> RAGGED
-    ``[max_num_pages, C, G]`` (fp32 products and sum, rounded once to the input dtype).
+    """``GeMM()(x, y, ctx=ctx)`` computes ``O[p] = Y[row_p] X[s]^T`` per candidate page (reference:
+    ``indexer/matmul.py:194-399`` over ``mm_bpr``): ``x`` BATCHED ``[S, G, D]``, ``y`` PAGED ``[num_pages*H, C, D]`` ->
+    RAGGED ``[max_num_pages, C, G]`` (fp32 products and sum, rounded once to the input dtype).
 
-    On sm_100a it exists as the head of the fused chain ``GeMM -> Softmax -> Max -> topK`` (``C == 1``).
+    Kernel: ``vtx_gemm_bpr``; with ``C == 1`` it is also the head of the fused chain
+    ``GeMM -> Softmax -> Max -> topK``.  The RAGGED-operand forms of the reference (``mm_rrr``, ``mm_rpr``) are
+    not built.
     """
 
     def __init__(self):
@@ -95,7 +97,10 @@ class GeMM(vOp, ChainedOp):
         assert x.dim() == 3 and y.dim() == 3, f"{p}expected 3D inputs; got x.ndim={x.dim()}, y.ndim={y.dim()}"
         assert x.shape[2] == y.shape[2], f"{p}last dimension mismatch: {x.shape[2]} vs {y.shape[2]}"
         key = (x._format, y._format)
-        assert key == (FORMAT.BATCHED, FORMAT.PAGED), f"{p}no implementation for (x_fmt, y_fmt) = {key}"
+        if key != (FORMAT.BATCHED, FORMAT.PAGED):
+            raise NotImplementedError(f"{p}only (BATCHED, PAGED) operands have an sm_100a kernel; got {key}")
+        if x.dtype != torch.bfloat16 or y.dtype != torch.bfloat16:
+            raise NotImplementedError(f"{p}the GeMM kernel is built for bfloat16")
         self.output_format = FORMAT.RAGGED
         self.output_buffer = torch.empty((ctx.max_num_pages, y.shape[1], x.shape[1]), device=x.device, dtype=x.dtype)
         ctx.add_aux_memory(self.output_buffer)
@@ -105,6 +110,12 @@ class GeMM(vOp, ChainedOp):
         return out
 
     def execute(self, x: torch.Tensor, y: torch.Tensor, ctx: Context) -> torch.Tensor:
-        self._require_fused("GeMM")
-        self._pending = (materialize(x), y)
+        assert self.output_buffer is not None, f"{self._prefix()}execute called before profile()"
+        x = materialize(x)
+        if self._runs_fused():
+            self._pending = (x, y)  # the chain's last operator launches the fused kernel
+            return self.output_buffer
+        _deferred.flush_all()
+        ptr, eff, K, bos, eos = _cabi._win(ctx)
+        _cabi.gemm_bpr(x, y, self.output_buffer, ptr, ctx.dense_kv_indices, eff, K, bos, eos)
         return self.output_buffer

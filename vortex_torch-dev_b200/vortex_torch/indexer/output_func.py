@@ -12,7 +12,7 @@ import torch
 
 from .. import _cabi, _deferred
 from ..abs import FORMAT, vOp, vTensor
-from ._chain import chain_of
+from ._chain import chain_of, note_consumer
 from .context import Context
 
 
@@ -39,6 +39,7 @@ class topK(vOp):
         assert x.device == o.device, (
             f"{p}x and o must be on the same device (x.device={x.device}, o.device={o.device})")
         self.impl = _cabi.topk
+        note_consumer(x)
         # GeMM -> Softmax(dim=0) -> Max(dim=2) -> topK: one fused kernel owned by this operator
         names = [l[0] for l in chain_of(x)]
         if names == ["gemm", "softmax", "max"]:
@@ -62,16 +63,19 @@ class topK(vOp):
                 return
         # Fuse with the producing GeMV when its scores are read by this operator only.
         producer = getattr(x, "_vtx_producer", None)
-        if producer is not None and getattr(producer, "_fused_consumer", None) is None:
+        if producer is not None and hasattr(producer, "_fused_consumer") and producer._fused_consumer is None:
             producer._fused_consumer = self
             self._fused_producer = producer
+
+    def chain_intact(self) -> bool:
+        """True while every link of the chain this operator claimed feeds only the next link."""
+        chain = self._quest_chain or self._gqa_chain
+        return chain is not None and all(op._link_intact() for op in chain)
 
     def execute(self, x: torch.Tensor, o: torch.Tensor, ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}execute called before profile() (impl is None)"
         eff_bs = ctx.batch_size * ctx.num_kv_heads
-        if self._quest_chain is not None:
-            for op in self._quest_chain:
-                op._require_fused(type(op).__name__)
+        if self._quest_chain is not None and self.chain_intact():
             mul_a, mul_b = self._quest_chain[0], self._quest_chain[1]
             (qa, ya), (qb, yb) = mul_a._pending, mul_b._pending
             mul_a._pending = mul_b._pending = None
@@ -86,10 +90,8 @@ class topK(vOp):
                                       eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
                                       ctx.max_num_pages_per_request)
             return o
-        if self._gqa_chain is not None:
+        if self._gqa_chain is not None and self.chain_intact():
             gemm, softmax, mx = self._gqa_chain
-            for op in self._gqa_chain:
-                op._require_fused(type(op).__name__)
             q, y = gemm._pending
             gemm._pending = None
             if getattr(ctx, "_defer_indexer", False):
