@@ -410,6 +410,42 @@ int vtx_elementwise_binary(const void* x, const void* y, void* out, const int32_
                            float beta, int dtype, void* stream);
 
 /*
+ * Cache-side operators beyond the page mean: every layout of the page-completion reductions, GeMM, unary and
+ * binary elementwise.  Like vtx_cmean they act, for every slot t of loc with (t + 1) % page_size == 0 and every
+ * KV head h, on one block per operand.  A PAGED operand keeps that block at row (t / page_size) * H + h of a
+ * [num_pages * H, ...] cache, a RAGGED one at row i * H + h of a [nnz * H, ...] tensor (i = the slot's index in
+ * loc); the *_is_ragged flags say which.  bf16 only, fp32 arithmetic, one rounding per output.
+ *
+ * vtx_cache_reduce      x block [rows, cols] -> vector of cols (dim 1, reduced over rows) or rows (dim 2) values;
+ *                       kind 0 mean, 1 max, 2 min, 3 l2norm.  Replaces reduce_pp / _rp / _pr / _rr
+ *                       (cache/triton_kernels/reduce_impl.py:7-508) behind cache Mean / Max / Min / L2Norm
+ *                       (cache/reduce.py:354-525).
+ * vtx_cache_elementwise the unary family of vtx_elementwise on a block of inner_size values.  Replaces
+ *                       elementwise_pp / _pr / _rp / _rr (cache/triton_kernels/elementwise_impl.py) behind cache
+ *                       Relu / Silu / Sigmoid / Abs / Add_Mul (cache/elementwise.py).
+ * vtx_cache_binary      x block [x_c, x_d] with y block [y_c, y_d] (a size of 1 repeats); op 0 max, 1 min,
+ *                       2 bf16(alpha x) + bf16(beta y), 3 x y; x and y share a layout.  Replaces
+ *                       elementwise_binary_ppp / _ppr / _rrp / _rrr
+ *                       (cache/triton_kernels/elementwise_binary_impl.py) behind cache Maximum / Minimum / Add /
+ *                       Multiply (cache/elementwise_binary.py).
+ * vtx_cache_gemm        out block [y_rows, x_rows] = Y [y_rows, inner_dim] . X [x_rows, inner_dim]^T, fp32 products
+ *                       and sum.  Replaces gemm_ppp / _ppr / _rrp / _rrr (cache/triton_kernels/matmul_impl.py)
+ *                       behind cache GeMM (cache/matmul.py).
+ */
+int vtx_cache_reduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads,
+                     int rows, int cols, int page_size, int dim, int kind, int x_is_ragged,
+                     int out_is_ragged, int dtype, void* stream);
+int vtx_cache_elementwise(const void* x, void* out, const int64_t* loc, int64_t nnz, int num_kv_heads,
+                          int inner_size, int page_size, int op, float alpha, float beta, int x_is_ragged,
+                          int out_is_ragged, int dtype, void* stream);
+int vtx_cache_binary(const void* x, const void* y, void* out, const int64_t* loc, int64_t nnz,
+                     int num_kv_heads, int x_c, int x_d, int y_c, int y_d, int page_size, int op, float alpha,
+                     float beta, int inputs_are_ragged, int out_is_ragged, int dtype, void* stream);
+int vtx_cache_gemm(const void* x, const void* y, void* out, const int64_t* loc, int64_t nnz,
+                   int num_kv_heads, int x_rows, int y_rows, int inner_dim, int page_size,
+                   int inputs_are_ragged, int out_is_ragged, int dtype, void* stream);
+
+/*
  * Stand-alone forms of the indexer operators that the shipped flows chain.  (The flows themselves run them as
  * links of vtx_indexer_gqa_softmax_fused / vtx_indexer_quest_fused; these entry points serve flows that
  * compose the operators differently or read an intermediate, and return the same bits.)  All work on the

@@ -745,6 +745,67 @@ def cminmax(x: torch.Tensor, out: torch.Tensor, loc: torch.Tensor, page_size: in
             out[pid, 0] = red.to(out.dtype)
 
 
+def _cache_items(loc, page_size: int, num_kv_heads: int):
+    """(paged row, ragged row) of every (slot of loc that closes a page, head): the blocks a cache-side
+    operator touches (cache/triton_kernels/reduce_impl.py:21-32, 139-152, 260-275 of the reference)."""
+    for i, t in enumerate(loc.tolist()):
+        if (t + 1) % page_size != 0:
+            continue
+        for h in range(num_kv_heads):
+            yield (t // page_size) * num_kv_heads + h, i * num_kv_heads + h
+
+
+def cache_reduce(x, out, loc, page_size, num_kv_heads, dim: int, kind: int, x_ragged=False, out_ragged=False):
+    """Cache-side ``Mean / Max / Min / L2Norm (dim)`` in every layout (cache/reduce.py:354-525 over
+    reduce_pp / _rp / _pr / _rr): block [r, c] -> [1, c] (dim 1) or [r, 1] (dim 2).  fp32, canonical orders of
+    `reduce_ragged` (rows: sequential; columns: `canonical_sum_lastdim`), one rounding."""
+    for prow, rrow in _cache_items(loc, page_size, num_kv_heads):
+        blk = x[rrow if x_ragged else prow].to(torch.float32)
+        if kind == REDUCE_MAX:
+            red = blk.max(dim=dim - 1).values
+        elif kind == REDUCE_MIN:
+            red = blk.min(dim=dim - 1).values
+        else:
+            v = blk * blk if kind == REDUCE_L2NORM else blk
+            if dim == 2:
+                red = canonical_sum_lastdim(v)
+            else:
+                red = torch.zeros(blk.shape[1], dtype=torch.float32)
+                for r in range(blk.shape[0]):
+                    red = red + v[r]
+            red = red / float(blk.shape[dim - 1]) if kind == REDUCE_MEAN else torch.sqrt(red)
+        out[rrow if out_ragged else prow] = red.to(out.dtype).view(out.shape[1:])
+    return out
+
+
+def cache_elementwise(x, out, loc, page_size, num_kv_heads, op, alpha, beta, x_ragged=False, out_ragged=False):
+    """Cache-side ``Relu / Sigmoid / Silu / Abs / Add_Mul`` (cache/elementwise.py): `elementwise` on every
+    triggered block."""
+    for prow, rrow in _cache_items(loc, page_size, num_kv_heads):
+        out[rrow if out_ragged else prow] = elementwise(x[rrow if x_ragged else prow], op, alpha, beta)
+    return out
+
+
+def cache_binary(x, y, out, loc, page_size, num_kv_heads, op, alpha=1.0, beta=1.0, in_ragged=False, out_ragged=False):
+    """Cache-side ``Maximum / Minimum / Add / Multiply`` (cache/elementwise_binary.py): `elementwise_binary` on
+    every triggered pair of blocks."""
+    for prow, rrow in _cache_items(loc, page_size, num_kv_heads):
+        src = rrow if in_ragged else prow
+        out[rrow if out_ragged else prow] = elementwise_binary(x[src:src + 1], y[src:src + 1], op, alpha, beta)[0]
+    return out
+
+
+def cache_gemm(x, y, out, loc, page_size, num_kv_heads, in_ragged=False, out_ragged=False):
+    """Cache-side ``GeMM`` (cache/matmul.py over gemm_ppp / _ppr / _rrp / _rrr): ``O = Y X^T`` per triggered
+    block, fp32 products, canonical sum over the inner dim, one rounding."""
+    for prow, rrow in _cache_items(loc, page_size, num_kv_heads):
+        src = rrow if in_ragged else prow
+        xb, yb = x[src].to(torch.float32), y[src].to(torch.float32)
+        prod = yb[:, None, :] * xb[None, :, :]                       # [ny, nx, k], exact for bf16 inputs
+        out[rrow if out_ragged else prow] = canonical_sum_lastdim(prod).to(out.dtype)
+    return out
+
+
 def canonical_rowsum(vals: torch.Tensor) -> torch.Tensor:
     """Sum of every row of ``vals`` [R, D] (fp32) in the order of `canonical_dot` (chunks of 8, L partial
     sums taking chunks l, l+L, ..., folded in halves)."""

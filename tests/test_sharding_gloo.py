@@ -65,3 +65,41 @@ def test_two_rank_sharding_matches_single_process():
     for r in range(len(SEQ)):
         np.testing.assert_array_equal(sel[r], want_sel[r].numpy())
         np.testing.assert_array_equal(out[r], want_out[r].numpy())
+
+
+def _worker_sparse(rank, world, port, q):
+    for p in (str(ROOT), str(ROOT / "vortex_torch-dev_b200")):
+        sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vortex_torch.runtime import balance_requests, gather_for_verification
+
+    pages = [(s + P - 1) // P for s in SEQ[:2]]        # two requests on three ranks: one rank holds nothing
+    parts = balance_requests(pages, world)
+    sel, out = _selection_for(parts[rank])
+    all_sel = gather_for_verification(sel)               # the empty rank has to learn the dtype from the others
+    all_out = gather_for_verification(out, dtype=torch.float32)
+    if rank == 0:
+        q.put((parts, {k: v.numpy() for k, v in all_sel.items()}, {k: v.numpy() for k, v in all_out.items()}))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_more_ranks_than_requests():
+    """A rank without requests takes part in the verification gather with the payload dtype of the others."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31000 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_worker_sparse, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    parts, sel, out = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(len(x) for x in parts) == [0, 1, 1]
+    want_sel, want_out = _selection_for(range(2))
+    for r in range(2):
+        np.testing.assert_array_equal(sel[r], want_sel[r].numpy())
+        assert sel[r].dtype == np.int64
+        np.testing.assert_array_equal(out[r], want_out[r].numpy())

@@ -59,6 +59,10 @@ SIGNATURES = {
     "vtx_binary_bpr": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _p],
     "vtx_transpose_ragged": [_p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_save_load_ragged": [_p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_cache_reduce": [_p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _i, _p],
+    "vtx_cache_elementwise": [_p, _p, _p, _i64, _i, _i, _i, _i, _f, _f, _i, _i, _i, _p],
+    "vtx_cache_binary": [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _p],
+    "vtx_cache_gemm": [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _i, _p],
     "vtx_set_mla_path": [_i],
     "vtx_mla_fault_read": [_p],
 }
@@ -536,3 +540,40 @@ def save_load_ragged(ragged, paged, dense_kv_indptr, dense_kv_indices, eff_bs, t
                                   ragged.shape[1] * ragged.shape[2], int(bool(save)), int(topk_val), int(bos), int(eos),
                                   dtype_code(ragged.dtype), stream_of(ragged))
     check(rc, "vtx_save_load_ragged")
+
+
+# --------------------------------------------------------------------------- cache-side operators, every layout
+def cache_reduce(x, out, loc, num_kv_heads, page_size, dim: int, kind: int, x_ragged=False, out_ragged=False) -> None:
+    """kind 0 mean, 1 max, 2 min, 3 l2norm over axis ``dim`` of the triggered blocks of ``x`` ``[*, r, c]``."""
+    want(loc, torch.int64, "loc")
+    rc = lib.vtx_cache_reduce(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
+                              int(page_size), int(dim), int(kind), int(bool(x_ragged)), int(bool(out_ragged)),
+                              dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_cache_reduce")
+
+
+def cache_elementwise(x, out, loc, num_kv_heads, page_size, op: int, alpha: float, beta: float, x_ragged=False,
+                      out_ragged=False) -> None:
+    want(loc, torch.int64, "loc")
+    rc = lib.vtx_cache_elementwise(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads),
+                                   x.shape[1] * x.shape[2], int(page_size), int(op), float(alpha), float(beta),
+                                   int(bool(x_ragged)), int(bool(out_ragged)), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_cache_elementwise")
+
+
+def cache_binary(x, y, out, loc, num_kv_heads, page_size, op: int, alpha: float = 1.0, beta: float = 1.0,
+                 in_ragged=False, out_ragged=False) -> None:
+    want(loc, torch.int64, "loc")
+    rc = lib.vtx_cache_binary(ptr(x), ptr(y), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1],
+                              x.shape[2], y.shape[1], y.shape[2], int(page_size), int(op), float(alpha), float(beta),
+                              int(bool(in_ragged)), int(bool(out_ragged)), dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_cache_binary")
+
+
+def cache_gemm(x, y, out, loc, num_kv_heads, page_size, in_ragged=False, out_ragged=False) -> None:
+    """``out block = y block . (x block)^T`` for every triggered (token, head)."""
+    want(loc, torch.int64, "loc")
+    rc = lib.vtx_cache_gemm(ptr(x), ptr(y), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1],
+                            y.shape[1], x.shape[2], int(page_size), int(bool(in_ragged)), int(bool(out_ragged)),
+                            dtype_code(x.dtype), stream_of(x))
+    check(rc, "vtx_cache_gemm")

@@ -3,8 +3,11 @@
 ``Mean(dim=1)(x, output, loc=loc, ctx=ctx)`` — the ``CMean`` of the shipped flows: for every new
 token slot in ``loc`` that closes a page, and every KV head, reduce that page's block of ``x``
 (``[rows, cols]``) over its rows and write ``output[row, 0, :]``.  Accumulation is fp32 in row
-order with one rounding to the cache dtype.  Only PAGED -> PAGED with ``dim=1`` has an sm_100a
-kernel; other layouts raise ``NotImplementedError`` in the profile pass.
+order with one rounding to the cache dtype.  ``Mean / Max / Min / L2Norm`` with ``dim`` 1 or 2 and ``x`` / ``output``
+PAGED or RAGGED in any combination are built (reference kernels ``reduce_pp / _rp / _pr / _rr``); without
+``output`` the operator owns a RAGGED buffer.  PAGED -> PAGED ``Mean / Max / Min (dim=1)`` take the tuned kernel
+(``vtx_creduce``) that the runtime can also fold into its KV write and attention launches; everything else
+goes through ``vtx_cache_reduce``.
 """
 from __future__ import annotations
 
@@ -29,31 +32,43 @@ class Reduce(vOp):
         self.output_buffer: Optional[torch.Tensor] = None
 
     def profile(self, x: vTensor, output: Optional[vTensor], loc: torch.Tensor, ctx: Context) -> vTensor:
+        from ._common import check_operand, resolve_output
+
         p = self._prefix()
         assert isinstance(x, vTensor), f"{p}x must be vTensor, got {type(x)}"
         assert isinstance(loc, torch.Tensor), f"{p}loc must be torch.Tensor, got {type(loc)}"
         assert x.dim() == 3, f"{p}x must be 3D, got ndim={x.dim()} shape={tuple(x.shape)}"
-        if output is None:
-            raise NotImplementedError(f"{p}RAGGED-output reductions have no sm_100a kernel in this build")
-        assert isinstance(output, vTensor), f"{p}output must be vTensor, got {type(output)}"
-        assert output.dim() == 3, f"{p}output must be 3D, got ndim={output.dim()} shape={tuple(output.shape)}"
-        if (x._format, output._format) != (FORMAT.PAGED, FORMAT.PAGED) or self.dim != 1 \
-                or self.reduce_type not in (ReduceType.Mean, ReduceType.Max, ReduceType.Min):
-            raise NotImplementedError(
-                f"{p}only Mean/Max/Min(dim=1) PAGED->PAGED have sm_100a kernels; got {self.reduce_type}, "
-                f"dim={self.dim}, ({x._format}, {output._format})")
-        assert output.shape[1] == 1, f"{p}profile(dim=1): expected output.shape[1] == 1, got {tuple(output.shape)}"
-        assert output.shape[2] == x.shape[2], (
-            f"{p}profile(dim=1): expected output.shape[2] == x.shape[2], got {output.shape[2]} vs {x.shape[2]}")
-        assert x.device == output.device, (
-            f"{p}x and output must be on the same device (x.device={x.device}, output.device={output.device})")
-        self.impl = _cabi.cmean
-        self.output_format = FORMAT.PAGED
-        return output
+        inner = (1, x.shape[2]) if self.dim == 1 else (x.shape[1], 1)
+        fast = (output is not None and isinstance(output, vTensor) and (x._format, output._format) == (FORMAT.PAGED, FORMAT.PAGED)
+                and self.dim == 1 and self.reduce_type in (ReduceType.Mean, ReduceType.Max, ReduceType.Min))
+        if fast:
+            assert output.dim() == 3, f"{p}output must be 3D, got ndim={output.dim()} shape={tuple(output.shape)}"
+            assert output.shape[1] == 1, f"{p}profile(dim=1): expected output.shape[1] == 1, got {tuple(output.shape)}"
+            assert output.shape[2] == x.shape[2], (
+                f"{p}profile(dim=1): expected output.shape[2] == x.shape[2], got {output.shape[2]} vs {x.shape[2]}")
+            assert x.device == output.device, (
+                f"{p}x and output must be on the same device (x.device={x.device}, output.device={output.device})")
+            self.impl = _cabi.cmean
+            self.output_format = FORMAT.PAGED
+            self._layout = None
+            return output
+        check_operand(p, "x", x)
+        out, self.output_buffer = resolve_output(p, x, output, inner, ctx)
+        self.impl = _cabi.cache_reduce
+        self.output_format = out._format
+        self._layout = (x._format == FORMAT.RAGGED, out._format == FORMAT.RAGGED)
+        return out
 
     def execute(self, x: torch.Tensor, output: Optional[torch.Tensor], loc: torch.Tensor,
                 ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}called before profile() (impl is None)"
+        if getattr(self, "_layout", None) is not None:  # any layout, any dim, L2Norm: the general kernel
+            out = self.output_buffer if output is None else output
+            ctx.flush_append()
+            ctx.flush_kv_write()
+            _cabi.cache_reduce(x, out, loc, ctx.head_num, ctx.page_size, self.dim, self.reduce_type.value,
+                               x_ragged=self._layout[0], out_ragged=self._layout[1])
+            return out
         pa = getattr(ctx, "_pending_append", None)
         if pa is not None:
             if (len(pa) == 8 and pa[5] is None and self.reduce_type == ReduceType.Min
@@ -111,3 +126,9 @@ class Min(Reduce):
     def __init__(self, dim: int = 1):
         super().__init__(dim)
         self.reduce_type = ReduceType.Min
+
+
+class L2Norm(Reduce):
+    def __init__(self, dim: int = 1):
+        super().__init__(dim)
+        self.reduce_type = ReduceType.L2Norm
