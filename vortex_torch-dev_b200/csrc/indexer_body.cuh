@@ -723,14 +723,17 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         cp_async_commit();
     }
     hooks.wait();
-    T* my_q = qbar + (MODE < 2 ? warp * D : 0);
+    // Grouped-query mean.  Small groups: every warp computes it for itself (no block barrier between the wait
+    // and the first score).  Large groups (many heads or a long latent): the CTA computes it once.
+    const bool shared_q = MODE < 2 && a.G * Gm::nchunk > 4 * 32;
+    T* my_q = qbar + ((MODE < 2 && !shared_q) ? warp * D : 0);
     if constexpr (MODE < 2) {
-        // grouped-query mean, by every warp for itself (no block barrier between the wait and the first score):
-        // one canonical chunk per lane and pass; all loads of a pass are issued before anything is stored
+        // one canonical chunk per thread and pass; all loads of a pass are issued before anything is stored
         const typename Hooks::Regs hr = hooks.load(warp, lane);
         constexpr int GMAX = 8;
-        for (int ch0 = 0; ch0 < Gm::nchunk; ch0 += 32) {
-            const int ch = ch0 + lane;
+        const int tid = shared_q ? (int)threadIdx.x : lane, nthr = shared_q ? kThreads : 32;
+        for (int ch0 = 0; ch0 < Gm::nchunk; ch0 += nthr) {
+            const int ch = ch0 + tid;
             const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
             float acc[8];
 #pragma unroll
@@ -760,7 +763,8 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         if (hooks.needs_spare(warp)) cp_async_wait<0>();  // the copies of issue_extra have landed (this lane's part)
         __syncwarp();                                      // ... every lane's part; the warp's query mean is staged
         hooks.finish(warp, lane, hr, spare);
-        __syncwarp();                                      // the spare slot may be refilled from here on
+        if (shared_q) __syncthreads();                     // the CTA's query mean is staged
+        else __syncwarp();                                 // the spare slot may be refilled from here on
     } else {
         const typename Hooks::Regs hr = hooks.load(warp, lane);
         if (MODE == 3) {  // the group's query heads as they are

@@ -329,12 +329,16 @@ class GraphedDecodeStep:
     def d2h_bytes(self) -> int:
         return self.out.numel() * self.out.element_size()
 
-    def capture_host_pipeline(self, programmatic_launch=0) -> None:
+    def capture_host_pipeline(self, programmatic_launch=0, layers_per_gate: int = 7) -> None:
         """Capture the host-buffer step as one graph in which the copies overlap the kernels.
 
         Three branches inside the graph: an input branch copies the step's pinned host inputs layer by
-        layer, the compute branch starts layer l as soon as its inputs have landed, and an output branch
-        copies layer l's attention output back while layer l+1 computes.  ``run_from_host`` replays it.
+        layer, the compute branch starts a group of ``layers_per_gate`` layers as soon as that group's inputs
+        have landed, and an output branch copies layer l's attention output back while layer l+1 computes.
+        ``run_from_host`` replays it.  The inputs arrive far ahead of the compute branch (a layer's inputs
+        take a few microseconds of PCIe time, the layer tens), so the gates cost nothing in waiting; they are
+        kept few because a kernel that waits for a copy node cannot be chained to its predecessor by
+        programmatic dependent launch.
         """
         h = self.host_buffers()
         dev = self.rt.device
@@ -342,12 +346,12 @@ class GraphedDecodeStep:
         torch.cuda.synchronize(dev)
         self.rt.pdl_mode = int(programmatic_launch)
         try:
-            self._capture_host_pipeline(h, dev)
+            self._capture_host_pipeline(h, dev, max(1, int(layers_per_gate)))
         finally:
             self.rt.pdl_mode = 0
             _cabi.set_programmatic_launch(0)
 
-    def _capture_host_pipeline(self, h, dev) -> None:
+    def _capture_host_pipeline(self, h, dev, gate: int) -> None:
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         L = self.rt.num_layers
         g = torch.cuda.CUDAGraph()
@@ -355,26 +359,34 @@ class GraphedDecodeStep:
             main = torch.cuda.current_stream(dev)
             s_in.wait_stream(main)
             s_out.wait_stream(main)
-            ev_in = [torch.cuda.Event() for _ in range(L + 1)]
+            ev_meta = torch.cuda.Event()
+            ev_in = {}
             with torch.cuda.stream(s_in):
                 for n in ("seq_lens", "req_indices", "loc"):
                     getattr(self, n).copy_(h[n], non_blocking=True)
-                ev_in[L].record(s_in)
-                for l in range(L):
-                    self.q[l].copy_(h["q"][l], non_blocking=True)
-                    self.new_k[l].copy_(h["new_k"][l], non_blocking=True)
-                    self.new_v[l].copy_(h["new_v"][l], non_blocking=True)
-                    ev_in[l].record(s_in)
-            main.wait_event(ev_in[L])
+                ev_meta.record(s_in)
+                for l0 in range(0, L, gate):
+                    l1 = min(L, l0 + gate)
+                    # one copy per input tensor and group: the per-layer buffers of a group are contiguous
+                    self.q[l0:l1].copy_(h["q"][l0:l1], non_blocking=True)
+                    self.new_k[l0:l1].copy_(h["new_k"][l0:l1], non_blocking=True)
+                    self.new_v[l0:l1].copy_(h["new_v"][l0:l1], non_blocking=True)
+                    ev_in[l0] = torch.cuda.Event()
+                    ev_in[l0].record(s_in)
+            main.wait_event(ev_meta)
             self.rt.plan(self.seq_lens, self.req_indices)
             for l in range(L):
-                main.wait_event(ev_in[l])
+                if l in ev_in:
+                    main.wait_event(ev_in[l])
                 self.rt.layer(l, self.q[l], self.new_k[l], self.new_v[l], self.loc, self.out[l])
-                ev = torch.cuda.Event()
-                ev.record(main)
-                s_out.wait_event(ev)
-                with torch.cuda.stream(s_out):
-                    h["out"][l].copy_(self.out[l], non_blocking=True)
+                if (l + 1) % gate == 0 or l == L - 1:
+                    # outputs go back group by group too, while the next group computes
+                    l0 = (l // gate) * gate
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    s_out.wait_event(ev)
+                    with torch.cuda.stream(s_out):
+                        h["out"][l0:l + 1].copy_(self.out[l0:l + 1], non_blocking=True)
             main.wait_stream(s_in)
             main.wait_stream(s_out)
         self.graph_host = g
