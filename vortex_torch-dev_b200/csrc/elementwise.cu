@@ -15,7 +15,8 @@
 namespace {
 
 // exp for fp32 with a fixed operation sequence (no FMA contraction, no fast-math): range reduction by
-// ln 2 split in two, degree-6 polynomial, scaling by 2^k.  Same sequence as the oracle's exp_canonical.
+// ln 2 split in two, degree-6 polynomial, scaling by 2^k.  The CPU checker of the test-suite
+// restates the same sequence, so results compare bit for bit.
 __device__ __forceinline__ float exp_canonical(float x) {
     if (x > 88.f) return __int_as_float(0x7f800000);
     if (x < -87.0f) return 0.f;

@@ -39,19 +39,7 @@ class Context(ContextBase):
     def flush_append(self) -> None:
         pend = self.take_pending_append()
         if pend is not None:
-            from .. import _cabi
-
-            if len(pend) == 8:  # token write + page maximum [+ page minimum] of the quest flow
-                from .set_kv import set_kv_buffer_launcher
-
-                k_cache, v_cache, new_k, new_v, cmax, cmin, loc, P = pend
-                set_kv_buffer_launcher(k_cache, v_cache, new_k, new_v, loc, P)
-                _cabi.creduce(k_cache, cmax, loc, self.head_num, self.page_size, 1)
-                if cmin is not None:
-                    _cabi.creduce(k_cache, cmin, loc, self.head_num, self.page_size, 2)
-                return
-            k_cache, v_cache, new_k, new_v, centroids, loc, P = pend
-            _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, P)
+            pend.launch(self)
 
     # ---- deferred KV write (fusion of set_kv with the flow's first cache operator) ----
     def defer_kv_write(self, k_cache, v_cache, new_k, new_v, loc, page_size: int,
@@ -65,18 +53,20 @@ class Context(ContextBase):
         write holds are consecutive entries of ``loc`` in ascending slot order (a prefill).  With either
         guarantee the write may be folded into the mean (one launch); only the first also allows folding
         both into the layer's attention launch.  Without a guarantee the write is launched on its own."""
+        from .._deferred import PendingKVWrite
+
         self.flush_kv_write()
         mode = "single" if single_token_pages else ("ordered" if page_ordered else None)
-        self._pending_kv = (k_cache, v_cache, new_k, new_v, loc, page_size, mode)
+        self._pending_kv = PendingKVWrite(k_cache, v_cache, new_k, new_v, loc, page_size, mode)
 
-    def flush_kv_write(self) -> None:
-        self.flush_append()
-        pend = self._pending_kv
+    def flush_kv_write(self, keep_append: bool = False) -> None:
+        """Launch a recorded write that no operator took.  ``keep_append``: leave a recorded append (write +
+        page summary) for the caller's attention step instead of launching it here."""
+        if not keep_append:
+            self.flush_append()
+        pend, self._pending_kv = self._pending_kv, None
         if pend is not None:
-            self._pending_kv = None
-            from .set_kv import set_kv_buffer_launcher
-
-            set_kv_buffer_launcher(*pend[:6])
+            pend.launch()
 
     def create(self, parent: Any, model_runner: Any, *, overwrite: bool = False) -> "Context":
         """``parent`` is the KV pool (page_size, num_pages, head_num, head_dim)."""

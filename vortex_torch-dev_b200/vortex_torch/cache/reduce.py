@@ -69,38 +69,31 @@ class Reduce(vOp):
             _cabi.cache_reduce(x, out, loc, ctx.head_num, ctx.page_size, self.dim, self.reduce_type.value,
                                x_ragged=self._layout[0], out_ragged=self._layout[1])
             return out
+        from .._deferred import PendingAppend
+
         pa = getattr(ctx, "_pending_append", None)
         if pa is not None:
-            if (len(pa) == 8 and pa[5] is None and self.reduce_type == ReduceType.Min
-                    and x.data_ptr() == pa[0].data_ptr() and loc.data_ptr() == pa[6].data_ptr()):
-                # second half of a recorded "token write + page maximum + page minimum"
-                ctx._pending_append = pa[:5] + (output,) + pa[6:]
+            if (pa.kind == "minmax" and pa.summary2 is None and self.reduce_type == ReduceType.Min
+                    and pa.write.reduces(x, loc, ctx)):
+                pa.summary2 = output  # second half of a recorded "token write + page maximum + page minimum"
                 return output
             ctx.flush_append()
         pend = getattr(ctx, "_pending_kv", None)
         if pend is not None:
-            k_cache, v_cache, new_k, new_v, ploc, P, mode = pend
-            single = mode == "single"
-            if (mode is not None and self.reduce_type == ReduceType.Mean
-                    and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
-                    and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
-                    and new_k.shape[1] == ctx.head_num):
-                # the runtime's KV write and this mean touch the same page: one kernel does both
+            defer = pend.pages == "single" and getattr(ctx, "_defer_append", False)
+            if self.reduce_type == ReduceType.Mean and pend.reduces(x, loc, ctx):
+                # the runtime's KV write and this mean touch the same pages: one kernel does both
                 ctx._pending_kv = None
-                if single and getattr(ctx, "_defer_append", False):
-                    ctx.flush_append()
-                    ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, loc, P)
-                    return output
-                _cabi.set_kv_cmean(k_cache, v_cache, new_k, new_v, output, loc, P)
+                app = PendingAppend(pend, "mean", output)
+                if defer:
+                    ctx._pending_append = app  # the caller's attention step may take it along
+                else:
+                    app.launch(ctx)
                 return output
-            if (single and self.reduce_type == ReduceType.Max and getattr(ctx, "_defer_append", False)
-                    and x.data_ptr() == k_cache.data_ptr() and loc.data_ptr() == ploc.data_ptr()
-                    and loc.shape == ploc.shape and x.shape[1] == P == ctx.page_size
-                    and new_k.shape[1] == ctx.head_num):
+            if self.reduce_type == ReduceType.Max and defer and pend.reduces(x, loc, ctx):
                 # the quest flow's cache side: token write + Max now, the Min that follows completes the record
                 ctx._pending_kv = None
-                ctx.flush_append()
-                ctx._pending_append = (k_cache, v_cache, new_k, new_v, output, None, loc, P)
+                ctx._pending_append = PendingAppend(pend, "minmax", output)
                 return output
             ctx.flush_kv_write()
         if self.reduce_type == ReduceType.Mean:

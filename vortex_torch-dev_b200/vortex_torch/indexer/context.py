@@ -49,27 +49,56 @@ class Context(ContextBase):
         pend, self._pending_indexer = self._pending_indexer, None
         return pend
 
+    def record_or_launch(self, selection) -> None:
+        """Called by the operator that owns a fused page selection (`_deferred.PendingSelection`): keep it for the
+        caller's attention step when that was asked for, else launch it now."""
+        from .. import _deferred
+
+        self.flush_indexer()
+        if self._defer_indexer:
+            self._pending_indexer = selection
+            return
+        _deferred.flush_all()
+        selection.launch(self)
+
     def flush_indexer(self) -> None:
         pend = self.take_pending_indexer()
         if pend is not None:
-            from .. import _cabi, _deferred
+            from .. import _deferred
 
             _deferred.flush_all()
-            q, y, o = pend[:3]
-            eff_bs = self.batch_size * self.num_kv_heads
-            if len(pend) == 4 and isinstance(pend[3], torch.Tensor):  # the quest chain with its second cache
-                _cabi.indexer_quest_fused(q, y, pend[3], self.dense_kv_indptr, self.sparse_kv_indptr,
-                                          self.dense_kv_indices, o, eff_bs, self.topk_val, self.page_reserved_bos,
-                                          self.page_reserved_eos, self.max_num_pages_per_request)
-            elif len(pend) == 4:  # the gqa_block_sparse_attention chain with its softmax scale
-                _cabi.indexer_gqa_softmax_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr,
-                                                self.dense_kv_indices, o, eff_bs, self.topk_val,
-                                                self.page_reserved_bos, self.page_reserved_eos,
-                                                self.max_num_pages_per_request, pend[3])
-            else:
-                _cabi.indexer_fused(q, y, self.dense_kv_indptr, self.sparse_kv_indptr, self.dense_kv_indices, o,
-                                    eff_bs, self.topk_val, self.page_reserved_bos, self.page_reserved_eos,
-                                    self.max_num_pages_per_request)
+            pend.launch(self)
+
+    def run_sparse_layer(self, q, k_cache, v_cache, out, kv_last_page_len, sm_scale: float, cache_ctx=None,
+                         workspace=None, early_prologue: bool = False) -> bool:
+        """The attention step of a sparse layer, for a backend that called ``defer_indexer(True)`` before
+        ``flow.forward_indexer`` (and ``cache_ctx.defer_append(True)`` before ``flow.forward_cache``).
+
+        If the flow recorded a page selection on ``q`` that the one-launch layer kernel supports, this runs
+        token write (when ``cache_ctx`` holds a matching recorded append) + selection + attention over the
+        selected pages into ``out`` as ONE kernel and returns True.  Otherwise everything recorded is launched
+        as the separate kernels, the sparse page list is complete on return, and the result is False: the
+        caller then runs its own paged attention over ``sparse_kv_indptr / sparse_kv_indices``.
+        Call order of the reference's hook: ``flow/algorithms.py:114-205`` (forward_cache, forward_indexer,
+        then the backend's paged decode)."""
+        from .. import _deferred
+
+        sel = self.take_pending_indexer()
+        if sel is None or not (_deferred._same(sel.q, q) and sel.out.data_ptr() == self.sparse_kv_indices.data_ptr()
+                               and _deferred.sparse_layer_supported(sel, self, k_cache)):
+            if sel is not None:
+                self._pending_indexer = sel
+                self.flush_indexer()
+            if cache_ctx is not None:
+                cache_ctx.flush_append()
+            return False
+        app = cache_ctx.take_pending_append() if cache_ctx is not None else None
+        if app is not None and not _deferred.append_joins(app, sel, self, k_cache, v_cache, self.page_size):
+            app.launch(cache_ctx)
+            app = None
+        _deferred.sparse_layer_launch(sel, app, self, k_cache, v_cache, out, kv_last_page_len, self.page_size, sm_scale,
+                                      workspace=workspace, early_prologue=early_prologue)
+        return True
 
     def set_batch_size(self, n: int) -> None:
         self.batch_size = n

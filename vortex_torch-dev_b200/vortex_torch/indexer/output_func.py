@@ -74,51 +74,34 @@ class topK(vOp):
 
     def execute(self, x: torch.Tensor, o: torch.Tensor, ctx: Context) -> torch.Tensor:
         assert self.impl is not None, f"{self._prefix()}execute called before profile() (impl is None)"
+        sel = self._fused_selection(x, o)
+        if sel is not None:
+            ctx.record_or_launch(sel)  # the caller's attention step may run it as part of one layer kernel
+            return o
+        _deferred.flush_all()  # eager launch: anything recorded earlier must reach the GPU first
+        ctx.flush_indexer()
         eff_bs = ctx.batch_size * ctx.num_kv_heads
+        self.impl(x, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o, eff_bs, ctx.topk_val,
+                  ctx.page_reserved_bos, ctx.page_reserved_eos, ctx.max_num_pages_per_request)
+        return o
+
+    def _fused_selection(self, x: torch.Tensor, o: torch.Tensor):
+        """The chain this operator owns, as one `PendingSelection`, or None when the scores in ``x`` are real."""
         if self._quest_chain is not None and self.chain_intact():
             mul_a, mul_b = self._quest_chain[0], self._quest_chain[1]
             (qa, ya), (qb, yb) = mul_a._pending, mul_b._pending
             mul_a._pending = mul_b._pending = None
             if qa.data_ptr() != qb.data_ptr():
                 raise NotImplementedError("topK: the two Multiply operators of the quest chain must share their query")
-            if getattr(ctx, "_defer_indexer", False):
-                ctx.flush_indexer()
-                ctx._pending_indexer = (qa, ya, o, yb)  # the runtime's attention launch picks it up
-                return o
-            _deferred.flush_all()
-            _cabi.indexer_quest_fused(qa, ya, yb, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o,
-                                      eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
-                                      ctx.max_num_pages_per_request)
-            return o
+            return _deferred.PendingSelection("quest", qa, ya, o, summary2=yb)
         if self._gqa_chain is not None and self.chain_intact():
-            gemm, softmax, mx = self._gqa_chain
+            gemm, softmax, _ = self._gqa_chain
             q, y = gemm._pending
             gemm._pending = None
-            if getattr(ctx, "_defer_indexer", False):
-                ctx.flush_indexer()
-                ctx._pending_indexer = (q, y, o, float(softmax.scale))  # the runtime's attention launch picks it up
-                return o
-            _deferred.flush_all()
-            _cabi.indexer_gqa_softmax_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
-                                            o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
-                                            ctx.max_num_pages_per_request, softmax.scale)
-            return o
+            return _deferred.PendingSelection("gqa_softmax", q, y, o, softmax_scale=float(softmax.scale))
         prod = self._fused_producer
         if prod is not None and prod._pending is not None and x.data_ptr() == prod.output_buffer.data_ptr():
             q, y = prod._pending
             prod._pending = None
-            if getattr(ctx, "_defer_indexer", False):
-                ctx.flush_indexer()
-                ctx._pending_indexer = (q, y, o)  # the runtime's attention launch picks it up
-                return o
-            _deferred.flush_all()
-            _cabi.indexer_fused(q, y, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices,
-                                o, eff_bs, ctx.topk_val, ctx.page_reserved_bos, ctx.page_reserved_eos,
-                                ctx.max_num_pages_per_request)
-            return o
-        _deferred.flush_all()  # eager launch: anything recorded earlier must reach the GPU first
-        if getattr(ctx, "_pending_indexer", None) is not None:
-            ctx.flush_indexer()
-        self.impl(x, ctx.dense_kv_indptr, ctx.sparse_kv_indptr, ctx.dense_kv_indices, o, eff_bs, ctx.topk_val,
-                  ctx.page_reserved_bos, ctx.page_reserved_eos, ctx.max_num_pages_per_request)
-        return o
+            return _deferred.PendingSelection("mean_dot", q, y, o)
+        return None

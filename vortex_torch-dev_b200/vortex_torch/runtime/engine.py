@@ -163,50 +163,17 @@ class VortexDecodeRuntime:
         which = 1 if sparse else 0
         eff_bs = self.ictx.batch_size * self.H
         cache = self.pool.buffers[layer]
-        pend = self.ictx.take_pending_indexer()
-        if pend is not None:
-            pq, py, po = pend[:3]
-            extra = pend[3] if len(pend) == 4 else None
-            quest_other = extra if isinstance(extra, torch.Tensor) else None  # second summary cache of the quest chain
-            gqa_scale = extra if extra is not None and quest_other is None else None
-            if (sparse and self.dtype == torch.bfloat16 and self.D in (64, 128) and self.G in (1, 2, 4, 8)
-                    and pq.data_ptr() == q.data_ptr() and pq.shape[1] == self.G
-                    and po.data_ptr() == b.kv_indices_decode[1].data_ptr()):
-                # new-token write (if it is still pending), selection and attention of this layer in one launch
-                app = self.cctx.take_pending_append()
-                nk = nv = loc = None
-                cmax, cmin = py, quest_other
-                if app is not None:
-                    if len(app) == 8:  # token write + page maximum + page minimum (quest flow)
-                        ak, av, nk, nv, ac, ac2, loc, aP = app
-                        ptrs = {py.data_ptr(), quest_other.data_ptr()} if quest_other is not None else set()
-                        caches_ok = ac2 is not None and {ac.data_ptr(), ac2.data_ptr()} == ptrs and len(ptrs) == 2
-                        cmax, cmin = ac, ac2
-                    else:
-                        ak, av, nk, nv, ac, loc, aP = app
-                        caches_ok = quest_other is None and ac.data_ptr() == py.data_ptr()
-                    if not (ak.data_ptr() == cache["k"].data_ptr() and av.data_ptr() == cache["v"].data_ptr()
-                            and caches_ok and aP == self.P and nk.shape[0] == self.ictx.batch_size
-                            and nk.shape[1] == self.H and self.ictx.page_reserved_eos >= 1):
-                        self.cctx._pending_append = app
-                        self.cctx.flush_append()
-                        nk = nv = loc = None
-                        cmax, cmin = py, quest_other
-                # the early prologue reads the planner's outputs: allowed once a launch that waits for its
-                # predecessor before releasing its successor separates us from the planner
-                early = self.pdl_mode == 2 and self._launches_since_plan >= 1
-                _cabi.sparse_layer_fused(q, cmax, cache["k"], cache["v"], out, b.kv_indptr_decode[0],
-                                         b.kv_indptr_decode[1], b.kv_indices_decode[0], b.kv_indices_decode[1],
-                                         b.kv_last_page_len_decode, eff_bs, self.P, self.ictx.topk_val,
-                                         self.ictx.page_reserved_bos, self.ictx.page_reserved_eos,
-                                         self.ictx.max_num_pages_per_request, self.sm_scale, nk, nv, loc,
-                                         gqa_softmax_scale=gqa_scale, quest_min=cmin,
-                                         workspace=self.layer_workspace, early_prologue=early)
+        if sparse:
+            # the early prologue reads the planner's outputs: allowed once a launch that waits for its
+            # predecessor before releasing its successor separates us from the planner
+            early = self.pdl_mode == 2 and self._launches_since_plan >= 1
+            if self.ictx.run_sparse_layer(q, cache["k"], cache["v"], out, b.kv_last_page_len_decode, self.sm_scale,
+                                          cache_ctx=self.cctx, workspace=self.layer_workspace, early_prologue=early):
                 self._launches_since_plan += 1
                 return out
-            self.ictx._pending_indexer = pend
+        else:
             self.ictx.flush_indexer()
-        self.cctx.flush_append()
+            self.cctx.flush_append()
         if self.num_splits > 1:
             _cabi.decode_gqa_splitkv(q, cache["k"], cache["v"], out, b.kv_indptr_decode[which],
                                      b.kv_indices_decode[which], b.kv_last_page_len_decode, eff_bs, self.P,
@@ -229,9 +196,7 @@ class VortexDecodeRuntime:
         self.cctx.defer_append(self.fuse_attention and layer not in self.skip)
         self.cctx.defer_kv_write(cache["k"], cache["v"], new_k, new_v, loc, self.P, single_token_pages=True)
         self.flow.forward_cache(cache, loc, ctx=self.cctx)
-        pend_append = self.cctx.take_pending_append()  # keep a recorded append across the flush below
-        self.cctx.flush_kv_write()
-        self.cctx._pending_append = pend_append
+        self.cctx.flush_kv_write(keep_append=True)
         qv = q.view(-1, self.G, self.D)
         ov = out.view(-1, self.G, self.D)
         if layer in self.skip:
