@@ -70,6 +70,25 @@ void* vtx_device_status_word(void);
 int vtx_device_status_read(uint32_t* host_bits, int clear);
 
 /*
+ * Checked build.  The library built with -DVTX_CHECKED (``build.py --checked``, a second file
+ * ``libvortex_b200_checked.so`` with the same entry points) compares every index that a kernel reads from a
+ * caller's array and then uses as an address with the limits given here: rows of the K/V caches
+ * (kv_rows = pages x KV heads), rows of a page-summary cache (summary_rows), token slots of ``loc`` and of the
+ * request-to-token table (loc_tokens = pages x page_size), rows of the request-to-token table (req_rows).
+ * A negative limit leaves that kind unchecked.  An index outside [0, limit) raises VTX_STATUS_BAD_ROW and is
+ * replaced by 0: the kernel touches only valid memory and finishes.  The limits are set by a one-thread kernel
+ * on ``stream`` (ordered with the launches that follow, legal inside a stream capture) and hold until set again.
+ * vtx_checked_build returns 1 in that library and 0 in the normal one, where vtx_checked_set_limits and
+ * vtx_checked_get_limits return VTX_ERR_UNSUPPORTED and the kernels carry no checks.  The reference has no counterpart (its device-side
+ * guards are the TORCH_CHECKs of its launchers, e.g. csrc/utils_sglang.cu:322-340, csrc/topk.cu:190-204).
+ */
+int vtx_checked_build(void);
+int vtx_checked_set_limits(int64_t kv_rows, int64_t summary_rows, int64_t loc_tokens, int64_t req_rows,
+                           void* stream);
+/* The limits in force on the device, in the argument order above, into host_limits[4]; waits for the device. */
+int vtx_checked_get_limits(int64_t* host_limits);
+
+/*
  * Block-table builder for one decode step.
  * Replaces `sglang_plan_decode` (csrc/register.h:15-36, csrc/utils_sglang.cu:313-460;
  * kernels :123-184, :188-254, :257-309) and, when the four trailing table pointers

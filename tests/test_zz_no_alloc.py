@@ -24,6 +24,7 @@ pytestmark = pytest.mark.gpu
 
 def _call_noalloc(q, k, v, out, indptr, indices, last, eff_bs, P, scale, splits):
     fn = _cabi.lib.vtx_decode_gqa_splitkv_noalloc
+    _cabi._limits(q, kv=k.shape[0])  # a no-op unless the checked library is loaded
     return fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), indptr.data_ptr(), indices.data_ptr(),
               last.data_ptr(), eff_bs, q.shape[1], q.shape[2], P, ctypes.c_float(scale), splits, _cabi.VTX_BF16,
               torch.cuda.current_stream().cuda_stream)

@@ -16,6 +16,11 @@ ROOT = HERE.parent
 CSRC = HERE / "csrc"
 LIB_DIR = HERE / "lib"
 LIB_PATH = LIB_DIR / "libvortex_b200.so"
+# The same sources with -DVTX_CHECKED: every index a kernel reads and then uses as an address is compared with
+# limits set through vtx_checked_set_limits.  Relocatable device code, because the limits live in one
+# translation unit and are read from all of them.
+CHECKED_LIB_PATH = LIB_DIR / "libvortex_b200_checked.so"
+CHECKED_FLAGS = ["-DVTX_CHECKED", "-rdc=true"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -36,21 +41,24 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def needs_build() -> bool:
-    if not LIB_PATH.exists():
+def needs_build(checked: bool = False) -> bool:
+    lib = CHECKED_LIB_PATH if checked else LIB_PATH
+    if not lib.exists():
         return True
-    t = LIB_PATH.stat().st_mtime
+    t = lib.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list((ROOT / "include").glob("*.h"))
     return any(p.stat().st_mtime > t for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; return its path."""
-    if not force and not needs_build():
-        return LIB_PATH
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, checked: bool = False) -> Path:
+    """Compile the library (``checked``: its checked twin) if it is missing or older than its sources; return its
+    path."""
+    lib = CHECKED_LIB_PATH if checked else LIB_PATH
+    if not force and not needs_build(checked):
+        return lib
     LIB_DIR.mkdir(exist_ok=True)
     objs = []
-    obj_dir = HERE / "build"
+    obj_dir = HERE / ("build_checked" if checked else "build")
     obj_dir.mkdir(exist_ok=True)
     procs = []
     headers = list(CSRC.glob("*.cuh")) + list((ROOT / "include").glob("*.h"))
@@ -62,7 +70,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
         if (not force and not ptxas_info and obj.exists()
                 and obj.stat().st_mtime > max(src.stat().st_mtime, newest_header)):
             continue
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(CHECKED_FLAGS if checked else []), "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -76,12 +84,15 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("vortex_b200: compilation failed")
-    tmp = LIB_PATH.with_suffix(".so.tmp")
+    tmp = lib.with_suffix(".so.tmp")
     cmd = [_nvcc(), "-shared", "-o", str(tmp), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    if checked:
+        cmd += ["-Xcompiler", "-fPIC"]  # the device-link step compiles a stub of its own
     subprocess.run(cmd, check=True)
-    os.replace(tmp, LIB_PATH)
-    return LIB_PATH
+    os.replace(tmp, lib)
+    return lib
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv,
+                checked="--checked" in sys.argv))

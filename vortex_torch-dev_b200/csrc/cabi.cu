@@ -11,6 +11,25 @@
 // well-defined result.  One word per device that loaded the library.
 static __device__ uint32_t g_vtx_device_status = 0;
 
+#ifdef VTX_CHECKED
+// Limits and status bits of the index checks; visible to every translation unit (relocatable device code).
+namespace vtx {
+__device__ long long g_checked_limit[kNumLimits] = {-1, -1, -1, -1};
+__device__ uint32_t g_checked_status = 0;
+}
+namespace {
+__global__ void set_limits_kernel(long long kv_rows, long long summary_rows, long long loc_tokens,
+                                  long long req_rows) {
+    vtx::pdl_wait();
+    vtx::pdl_trigger();
+    vtx::g_checked_limit[vtx::kLimKvRows] = kv_rows;
+    vtx::g_checked_limit[vtx::kLimSummaryRows] = summary_rows;
+    vtx::g_checked_limit[vtx::kLimLocTokens] = loc_tokens;
+    vtx::g_checked_limit[vtx::kLimReqRows] = req_rows;
+}
+}  // namespace
+#endif
+
 namespace {
 thread_local char g_last_error[256] = "";
 std::atomic<int> g_pdl{0};
@@ -74,9 +93,55 @@ extern "C" int vtx_device_status_read(uint32_t* host_bits, int clear) {
     if (!w) return VTX_ERR_CUDA;
     cudaError_t e = cudaMemcpy(host_bits, w, sizeof(uint32_t), cudaMemcpyDeviceToHost);
     if (e == cudaSuccess && clear) e = cudaMemset(w, 0, sizeof(uint32_t));
+#ifdef VTX_CHECKED
+    if (e == cudaSuccess) {  // the index checks keep their bits in a word of their own
+        uint32_t chk = 0;
+        e = cudaMemcpyFromSymbol(&chk, vtx::g_checked_status, sizeof(chk));
+        *host_bits |= chk;
+        if (e == cudaSuccess && clear) {
+            chk = 0;
+            e = cudaMemcpyToSymbol(vtx::g_checked_status, &chk, sizeof(chk));
+        }
+    }
+#endif
     if (e != cudaSuccess) {
         vtx::note_cuda_error(e);
         return VTX_ERR_CUDA;
     }
     return VTX_OK;
+}
+
+extern "C" int vtx_checked_build(void) {
+#ifdef VTX_CHECKED
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+extern "C" int vtx_checked_set_limits(int64_t kv_rows, int64_t summary_rows, int64_t loc_tokens, int64_t req_rows,
+                                      void* stream) {
+#ifdef VTX_CHECKED
+    return vtx::launch(set_limits_kernel, dim3(1), dim3(1), 0, static_cast<cudaStream_t>(stream),
+                       (long long)kv_rows, (long long)summary_rows, (long long)loc_tokens, (long long)req_rows);
+#else
+    (void)kv_rows; (void)summary_rows; (void)loc_tokens; (void)req_rows; (void)stream;
+    return VTX_ERR_UNSUPPORTED;
+#endif
+}
+
+extern "C" int vtx_checked_get_limits(int64_t* host_limits) {
+    if (!host_limits) return VTX_ERR_INVALID_ARGUMENT;
+#ifdef VTX_CHECKED
+    long long v[vtx::kNumLimits];
+    cudaError_t e = cudaMemcpyFromSymbol(v, vtx::g_checked_limit, sizeof(v));
+    if (e != cudaSuccess) {
+        vtx::note_cuda_error(e);
+        return VTX_ERR_CUDA;
+    }
+    for (int i = 0; i < vtx::kNumLimits; ++i) host_limits[i] = v[i];
+    return VTX_OK;
+#else
+    return VTX_ERR_UNSUPPORTED;
+#endif
 }

@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(256) set_kv_kernel(uint4* __restrict__ k_cache
         const int64_t th = i / vec_per_row;
         const int h = (int)(th % H);
         const int64_t tok = th / H;
-        const int64_t t = loc[tok];
+        const int64_t t = VTX_CHECK_LOC(loc[tok]);
         const int64_t dst = (((t / P) * H + h) * P + (t % P)) * vec_per_row + c;
         k_cache[dst] = new_k[i];
         v_cache[dst] = new_v[i];
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(256) creduce_kernel(const T* __restrict__ x, T
     const float denom = (float)rows;
     for (int64_t it = (int64_t)blockIdx.x * GROUPS + threadIdx.x / LANES; it < items;
          it += (int64_t)gridDim.x * GROUPS) {
-        const int64_t t = loc[it / H];
+        const int64_t t = VTX_CHECK_LOC(loc[it / H]);
         if ((t + 1) % P != 0) continue;
         const int h = (int)(it % H);
         const int64_t pid = (t / P) * H + h;
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(256) set_kv_cmean_kernel(T* __restrict__ k_cac
     for (int64_t it = (int64_t)blockIdx.x * GROUPS + threadIdx.x / LANES; it < items;
          it += (int64_t)gridDim.x * GROUPS) {
         const int64_t idx = it / H;  // entry of loc
-        const int64_t t = loc[idx];
+        const int64_t t = VTX_CHECK_LOC(loc[idx]);
         const int h = (int)(it % H);
         const int64_t pid = (t / P) * H + h;
         const int tok = (int)(t % P);

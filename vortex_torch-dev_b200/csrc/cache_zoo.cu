@@ -27,7 +27,7 @@ struct Item {
 __device__ __forceinline__ Item item_of(const int64_t* loc, int64_t it, int H, int P) {
     const int64_t i = it / H;
     const int h = (int)(it - i * H);
-    const int64_t t = loc[i];
+    const int64_t t = VTX_CHECK_LOC(loc[i]);
     Item r;
     r.active = (t + 1) % P == 0;
     r.paged_row = (t / P) * H + h;

@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
 
     // Row ids of up to 32 of this warp's pages live in one register per lane.
     int id_base = 0;
-    int id_reg = (lane < my_pages) ? a.indices[beg + warp + kWarps * lane] : 0;
+    int id_reg = (lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + warp + kWarps * lane]) : 0;
 
     auto issue = [&](int item) {
         // item -> (page ordinal, tile, K or V)
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
                 const int po = (nxt >> 1) / tiles_per_page;
                 if (po - id_base >= 32) {  // refill the per-lane page ids (warp-uniform branch)
                     id_base += 32;
-                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + warp + kWarps * (id_base + lane)] : 0;
+                    id_reg = (id_base + lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + warp + kWarps * (id_base + lane)]) : 0;
                 }
                 issue(nxt);
             }

@@ -129,7 +129,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
     // list entry of this warp's page number po
     auto entry_of = [&](int po) { return whole ? list_slot(warp + kDecWarps * po, npages) : pg_lo + warp + kDecWarps * po; };
     int id_base = 0;
-    int id_reg = (lane < my_pages) ? a.indices[beg + entry_of(lane)] : 0;
+    int id_reg = (lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + entry_of(lane)]) : 0;
 
     auto issue = [&](int item) {
         const int pair = item >> 1;
@@ -161,7 +161,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
                 const int po = (nxt >> 1) / tiles_per_page;
                 if (po - id_base >= 32) {
                     id_base += 32;
-                    id_reg = (id_base + lane < my_pages) ? a.indices[beg + entry_of(id_base + lane)] : 0;
+                    id_reg = (id_base + lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + entry_of(id_base + lane)]) : 0;
                 }
                 issue(nxt);
             }

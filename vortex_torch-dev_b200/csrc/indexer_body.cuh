@@ -363,7 +363,7 @@ __device__ __forceinline__ AppendRegs append_load(const AppendArgs& ap, const in
     if (lane >= D / 8) return r;
     r.k = *reinterpret_cast<const uint4*>(ap.new_k + (int64_t)s * D + lane * 8);
     r.v = *reinterpret_cast<const uint4*>(ap.new_v + (int64_t)s * D + lane * 8);
-    r.slot = ap.loc[s / ap.H];
+    r.slot = VTX_CHECK_LOC(ap.loc[s / ap.H]);
     return r;
 }
 
@@ -706,7 +706,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
             const int r = pc / Gm::pieces, pr = pc - r * Gm::pieces;
             const int i = row0 + r;
             const bool valid = i < cnt;
-            const int64_t row = valid ? row_ids[i] : 0;
+            const int64_t row = valid ? VTX_CHECK_SUMMARY_ROW(row_ids[i]) : 0;
             const uint32_t off = r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4);
             cp_async16(dst + off, cent + row * Gm::row_bytes + pr * 16, valid);
             if (NSRC == 2) cp_async16(dst + Gm::slot_bytes + off, cent2 + row * Gm::row_bytes + pr * 16, valid);

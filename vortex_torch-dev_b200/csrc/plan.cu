@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
         }
     }
 
-    const int32_t* toks = a.req_to_token + a.req_indices[r] * a.r2t_stride;
+    const int32_t* toks = a.req_to_token + VTX_CHECK_REQ_ROW(a.req_indices[r]) * a.r2t_stride;
     int32_t* dense = a.dense_indices + d0;
     int32_t* sparse = a.sparse_indices + s0;
     int32_t* dpt = a.dense_pt ? a.dense_pt + (int64_t)s * a.pt_stride : nullptr;
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     const bool copy_all = n <= budget;
 
     for (int p = tx; p < n; p += kPlanThreads) {
-        const int row = (toks[(int64_t)p * a.P] / a.P) * a.H + h;
+        const int row = (VTX_CHECK_LOC(toks[(int64_t)p * a.P]) / a.P) * a.H + h;
         dense[p] = row;
         if (dpt) dpt[p] = row;
         int slot = -1;

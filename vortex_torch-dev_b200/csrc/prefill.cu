@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(kThreads) prefill_plan_kernel(
             qo_ragged[bs] = before.x + in_r;
         }
     }
-    const int32_t* toks = r2t + req_indices[r] * r2t_stride;
-    for (int p = tx; p < np; p += kThreads) kv_indices[kv0 + p] = (toks[(int64_t)p * P] / P) * H + h;
+    const int32_t* toks = r2t + VTX_CHECK_REQ_ROW(req_indices[r]) * r2t_stride;
+    for (int p = tx; p < np; p += kThreads) kv_indices[kv0 + p] = (VTX_CHECK_LOC(toks[(int64_t)p * P]) / P) * H + h;
     if (h == 0)
         for (int p = tx; p < in_r; p += kThreads) batch_table[before.x + p] = (uint16_t)r;
 }
@@ -76,9 +76,9 @@ __global__ void __launch_bounds__(kThreads) prefill_plan_fa3_kernel(
     const int r = blockIdx.x, h = blockIdx.y, tx = threadIdx.x;
     const int s = r * H + h;
     const int np = (cached_per_seg[s] + P - 1) / P;
-    const int32_t* toks = r2t + req_indices[r] * r2t_stride;
+    const int32_t* toks = r2t + VTX_CHECK_REQ_ROW(req_indices[r]) * r2t_stride;
     int32_t* out = page_table + (int64_t)s * pt_stride;
-    for (int p = tx; p < np; p += kThreads) out[p] = (toks[(int64_t)p * P] / P) * H + h;
+    for (int p = tx; p < np; p += kThreads) out[p] = (VTX_CHECK_LOC(toks[(int64_t)p * P]) / P) * H + h;
     if (h == 0) {
         const int q_len = cu_q[s + 1] - cu_q[s];
         uint16_t* bt = batch_table + cu_q[s] / H;

@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kThreads) gemm_bpr_kernel(const __nv_bfloat16*
     for (int item = warp; item < w.cnt * C; item += kThreads / 32) {
         const int i = item / C, c = item - i * C;
         const int p = w.beg + i;
-        const __nv_bfloat16* row = table + ((int64_t)indices[p] * C + c) * D;
+        const __nv_bfloat16* row = table + ((int64_t)VTX_CHECK_SUMMARY_ROW(indices[p]) * C + c) * D;
         for (int g = 0; g < G; ++g) {
             float acc = 0.f;
             if (lane < L)
@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(kThreads) binary_bpr_kernel(const __nv_bfloat1
         const int64_t p = w.beg + i;
         const __nv_bfloat16* xs = x_ragged ? q + p * a0 * a1 : qs;  // left operand: the row itself or the segment's query
         const float a = ld_bf16(xs + (a0 == 1 ? 0 : c) * a1 + (a1 == 1 ? 0 : d));
-        const float b = ld_bf16(table + ((int64_t)indices[p] * b0 + (b0 == 1 ? 0 : c)) * b1 + (b1 == 1 ? 0 : d));
+        const float b = ld_bf16(table + ((int64_t)VTX_CHECK_SUMMARY_ROW(indices[p]) * b0 + (b0 == 1 ? 0 : c)) * b1 + (b1 == 1 ? 0 : d));
         float o;
         if (op == 0) o = fmaxf(a, b);
         else if (op == 1) o = fminf(a, b);
@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(kThreads) save_load_kernel(__nv_bfloat16* __re
     for (int64_t item = threadIdx.x; item < (int64_t)w.cnt * inner; item += kThreads) {
         const int i = (int)(item / inner), e = (int)(item - (int64_t)i * inner);
         const int64_t p = w.beg + i;
-        const int64_t r = indices[p];
+        const int64_t r = VTX_CHECK_SUMMARY_ROW(indices[p]);
         if (SAVE) paged[r * inner + e] = ragged[p * inner + e];
         else ragged[p * inner + e] = paged[r * inner + e];
     }

@@ -29,7 +29,7 @@ struct LayerHooks {
     __device__ __forceinline__ void issue_extra(int warp, int lane, uint32_t spare) const {
         if (!needs_spare(warp)) return;
         // loc is an input of the step that is final before the step's first launch, like the page lists
-        const int64_t t = ap.loc[seg / ap.H];
+        const int64_t t = VTX_CHECK_LOC(ap.loc[seg / ap.H]);
         if ((int)(t % ap.P) != ap.P - 1) return;  // the token does not close its page: nothing to average
         const unsigned char* page = reinterpret_cast<const unsigned char*>(ap.k_cache) +
                                     ((t / ap.P) * ap.H + seg % ap.H) * (int64_t)ap.P * (D * 2);
@@ -93,8 +93,8 @@ __global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kern
         const int dbeg = ia.dense_indptr[seg], dend = ia.dense_indptr[seg + 1];
         s_pre[0] = da.indptr[seg + 1] - da.indptr[seg];
         s_pre[1] = da.last_len[seg];
-        s_pre[2] = dend > dbeg ? ia.dense_indices[dend - 1] : 0;
-        s_pre[3] = dend > dbeg ? ia.dense_indices[dbeg] : 0;
+        s_pre[2] = dend > dbeg ? VTX_CHECK_KV_ROW(ia.dense_indices[dend - 1]) : 0;
+        s_pre[3] = dend > dbeg ? VTX_CHECK_KV_ROW(ia.dense_indices[dbeg]) : 0;
     }
     LayerHooks<D, G, MODE> hooks{ia, da, ap, smem_raw, s_pre, seg, chunk_no, early != 0, false};
     const bool owner = indexer_body<__nv_bfloat16, D, MODE, LayerHooks<D, G, MODE>&, (MODE >= 2 ? G : 1)>(

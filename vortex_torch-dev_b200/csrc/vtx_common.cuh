@@ -29,6 +29,36 @@ inline int finish_launch() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- checked build (-DVTX_CHECKED, relocatable device code) ----
+// Every index that a kernel reads from a caller's array and then uses as an address (a row of the K/V cache, a
+// row of a page-summary cache, a token slot of ``loc`` or of the request-to-token table, a row of that table) goes
+// through one of the VTX_CHECK_* macros.  In the checked build the macro compares the index with the limit set by
+// vtx_checked_set_limits (a negative limit = not set = not compared); an index outside [0, limit) raises
+// VTX_STATUS_BAD_ROW in the sticky status word and is replaced by 0, so the bad address is never touched and the
+// kernel finishes.  In the normal build the macros are the identity and cost nothing.
+#ifdef VTX_CHECKED
+enum { kLimKvRows = 0, kLimSummaryRows = 1, kLimLocTokens = 2, kLimReqRows = 3, kNumLimits = 4 };
+extern __device__ long long g_checked_limit[kNumLimits];
+extern __device__ uint32_t g_checked_status;
+__device__ __forceinline__ long long checked_index(long long idx, int which) {
+    const long long lim = g_checked_limit[which];
+    if (lim >= 0 && (idx < 0 || idx >= lim)) {
+        atomicOr(&g_checked_status, (uint32_t)VTX_STATUS_BAD_ROW);
+        return 0;
+    }
+    return idx;
+}
+#define VTX_CHECK_KV_ROW(i) ((int)vtx::checked_index((i), vtx::kLimKvRows))
+#define VTX_CHECK_SUMMARY_ROW(i) ((int)vtx::checked_index((i), vtx::kLimSummaryRows))
+#define VTX_CHECK_LOC(i) (vtx::checked_index((i), vtx::kLimLocTokens))
+#define VTX_CHECK_REQ_ROW(i) (vtx::checked_index((i), vtx::kLimReqRows))
+#else
+#define VTX_CHECK_KV_ROW(i) (i)
+#define VTX_CHECK_SUMMARY_ROW(i) (i)
+#define VTX_CHECK_LOC(i) (i)
+#define VTX_CHECK_REQ_ROW(i) (i)
+#endif
+
 bool programmatic_launch_enabled();
 uint32_t* device_status_word();  // device address of the sticky status word on the current device, or null
 

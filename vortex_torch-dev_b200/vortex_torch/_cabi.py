@@ -15,7 +15,11 @@ import torch
 VTX_BF16, VTX_F32 = 0, 1
 
 _PKG_ROOT = Path(__file__).resolve().parent.parent
-LIB_PATH = Path(os.environ.get("VORTEX_B200_LIB", _PKG_ROOT / "lib" / "libvortex_b200.so"))
+# VORTEX_B200_CHECKED=1 loads the checked twin of the library (``build.py --checked``): same entry points, every
+# index a kernel reads and then uses as an address compared with the sizes of the tensors the wrappers below see.
+_CHECKED_ENV = os.environ.get("VORTEX_B200_CHECKED", "0") not in ("", "0")
+LIB_PATH = Path(os.environ.get("VORTEX_B200_LIB", _PKG_ROOT / "lib" / (
+    "libvortex_b200_checked.so" if _CHECKED_ENV else "libvortex_b200.so")))
 
 if not LIB_PATH.exists():
     raise ImportError(
@@ -100,6 +104,15 @@ lib.vtx_decode_gqa_splitkv_workspace_bytes.argtypes = [_i, _i, _i, _i]
 lib.vtx_decode_gqa_splitkv_workspace_bytes.restype = _i64
 lib.vtx_mla_fault_word.argtypes = []
 lib.vtx_mla_fault_word.restype = _p
+lib.vtx_checked_build.argtypes = []
+lib.vtx_checked_build.restype = _i
+lib.vtx_checked_set_limits.argtypes = [_i64, _i64, _i64, _i64, _p]
+lib.vtx_checked_set_limits.restype = _i
+lib.vtx_checked_get_limits.argtypes = [C.POINTER(_i64)]
+lib.vtx_checked_get_limits.restype = _i
+CHECKED = bool(lib.vtx_checked_build())
+if _CHECKED_ENV and not CHECKED:
+    raise ImportError(f"VORTEX_B200_CHECKED is set but {LIB_PATH} is not a checked build")
 lib.vtx_set_programmatic_launch.argtypes = [_i]
 lib.vtx_set_programmatic_launch.restype = _i
 lib.vtx_version.restype = _i
@@ -110,7 +123,8 @@ lib.vtx_last_cuda_error.restype = C.c_char_p
 EXPORTED = sorted(list(SIGNATURES) + ["vtx_version", "vtx_status_string", "vtx_last_cuda_error",
                                     "vtx_set_programmatic_launch", "vtx_decode_gqa_splitkv_workspace_bytes",
                                     "vtx_mla_fault_word", "vtx_sparse_layer", "vtx_sparse_layer_workspace_bytes",
-                                    "vtx_device_status_word", "vtx_device_status_read"])
+                                    "vtx_device_status_word", "vtx_device_status_read", "vtx_checked_build",
+                                    "vtx_checked_set_limits", "vtx_checked_get_limits"])
 
 
 def set_programmatic_launch(mode) -> None:
@@ -174,6 +188,34 @@ def stream_of(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+def _limits(ref: torch.Tensor, kv=None, summary=None, loc=None, req=None) -> None:
+    """Checked build only: tell the kernels of the next launch on ``ref``'s stream how many rows the K/V cache
+    (``kv``) and the page-summary cache (``summary``) have, how many token slots ``loc`` may address and how many
+    rows the request-to-token table has.  None = unknown to this call = not compared."""
+    if not CHECKED:
+        return
+    n = lambda v: -1 if v is None else int(v)
+    check(lib.vtx_checked_set_limits(n(kv), n(summary), n(loc), n(req), stream_of(ref)), "vtx_checked_set_limits")
+
+
+def checked_limits():
+    """(kv_rows, summary_rows, loc_tokens, req_rows) in force on the device (checked library only)."""
+    v = (_i64 * 4)()
+    check(lib.vtx_checked_get_limits(v), "vtx_checked_get_limits")
+    return tuple(int(x) for x in v)
+
+
+def _slots(cache: torch.Tensor, num_kv_heads: int, page_size: int) -> int:
+    """Token slots of a paged cache ``[pages * heads, ...]``."""
+    return cache.shape[0] // max(1, int(num_kv_heads)) * int(page_size)
+
+
+def _paged_slots(num_kv_heads: int, page_size: int, *operands):
+    """Token slots that ``loc`` may address: the smallest PAGED operand decides (None if all are RAGGED)."""
+    n = [_slots(t, num_kv_heads, page_size) for t, ragged in operands if t is not None and not ragged]
+    return min(n) if n else None
+
+
 def want(t: torch.Tensor, dt: torch.dtype, name: str) -> None:
     if t.dtype != dt:
         raise TypeError(f"{name} must be {dt}, got {t.dtype}")
@@ -204,6 +246,7 @@ def plan_decode(cached_seq_lens, req_to_token, req_indices, dense_kv_indptr, den
         stride = dense_page_table.shape[1]
         if sparse_page_table.shape[1] != stride:
             raise ValueError("dense and sparse page tables must have the same row stride")
+    _limits(cached_seq_lens, req=req_to_token.shape[0])
     rc = lib.vtx_plan_decode(
         ptr(cached_seq_lens), ptr(req_to_token), req_to_token.shape[1], ptr(req_indices),
         ptr(dense_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indptr), ptr(sparse_kv_indices),
@@ -218,6 +261,7 @@ def plan_decode(cached_seq_lens, req_to_token, req_indices, dense_kv_indptr, den
 def set_kv(k_cache, v_cache, new_k, new_v, loc, page_size) -> None:
     want(loc, torch.int64, "loc")
     nnz, H, D = new_k.shape
+    _limits(k_cache, kv=k_cache.shape[0], loc=_slots(k_cache, H, page_size))
     rc = lib.vtx_set_kv(ptr(k_cache), ptr(v_cache), ptr(new_k), ptr(new_v), ptr(loc), nnz, H, D,
                         int(page_size), dtype_code(k_cache.dtype), stream_of(k_cache))
     check(rc, "vtx_set_kv")
@@ -227,6 +271,7 @@ def cmean(x, out, loc, num_kv_heads, page_size) -> None:
     want(loc, torch.int64, "loc")
     if out.dtype != x.dtype:
         raise TypeError("cmean: x and out must share a dtype")
+    _limits(x, kv=x.shape[0], summary=out.shape[0], loc=_slots(x, num_kv_heads, page_size))
     rc = lib.vtx_cmean(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
                        int(page_size), dtype_code(x.dtype), stream_of(x))
     check(rc, "vtx_cmean")
@@ -237,6 +282,7 @@ def set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, page_size) -> N
     nnz, H, D = new_k.shape
     if not (k_cache.dtype == v_cache.dtype == new_k.dtype == new_v.dtype == centroids.dtype):
         raise TypeError("set_kv_cmean: caches, new tokens and centroids must share a dtype")
+    _limits(k_cache, kv=k_cache.shape[0], summary=centroids.shape[0], loc=_slots(k_cache, H, page_size))
     rc = lib.vtx_set_kv_cmean(ptr(k_cache), ptr(v_cache), ptr(new_k), ptr(new_v), ptr(centroids), ptr(loc), nnz, H,
                               D, int(page_size), dtype_code(k_cache.dtype), stream_of(k_cache))
     check(rc, "vtx_set_kv_cmean")
@@ -245,6 +291,7 @@ def set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, page_size) -> N
 def gemv(q_mean, centroids, scores, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos) -> None:
     if not (q_mean.dtype == centroids.dtype == scores.dtype):
         raise TypeError("gemv: q_mean, centroids and scores must share a dtype")
+    _limits(q_mean, summary=centroids.shape[0])
     rc = lib.vtx_gemv(ptr(q_mean), ptr(centroids), ptr(scores), ptr(dense_kv_indptr), ptr(dense_kv_indices),
                       int(eff_bs), q_mean.shape[-1], int(topk_val), int(bos), int(eos),
                       dtype_code(q_mean.dtype), stream_of(q_mean))
@@ -265,6 +312,7 @@ def indexer_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, dense_kv_indi
     if q.dtype != centroids.dtype:
         raise TypeError("indexer_fused: q and centroids must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    _limits(q, summary=centroids.shape[0])
     rc = lib.vtx_indexer_fused(ptr(q), ptr(centroids), ptr(dense_kv_indptr), ptr(sparse_kv_indptr),
                                ptr(dense_kv_indices), ptr(sparse_kv_indices), ptr(sparse_page_table), stride,
                                int(eff_bs), q.shape[1], q.shape[2], int(topk_val), int(bos), int(eos),
@@ -276,6 +324,7 @@ def decode_gqa(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len
                sm_scale) -> None:
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("decode_gqa: q, caches and out must share a dtype")
+    _limits(q, kv=min(k_cache.shape[0], v_cache.shape[0]))
     rc = lib.vtx_decode_gqa(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(kv_indptr), ptr(kv_indices),
                             ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
@@ -365,6 +414,9 @@ def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, spa
         max_num_pages_per_request=int(max_pages_per_request), score_mode=mode,
         flags=LAYER_EARLY_PROLOGUE if early_prologue else 0, dtype=dtype_code(q.dtype),
         sm_scale=float(sm_scale), softmax_scale=float(gqa_softmax_scale or 0.0))
+    _limits(q, kv=min(k_cache.shape[0], v_cache.shape[0]),
+            summary=centroids.shape[0] if quest_min is None else min(centroids.shape[0], quest_min.shape[0]),
+            loc=None if new_k is None else _slots(k_cache, H, page_size))
     check(lib.vtx_sparse_layer(C.byref(p), stream_of(q)), "vtx_sparse_layer")
 
 
@@ -378,6 +430,7 @@ def decode_gqa_splitkv(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_
     ``splitkv_workspace_bytes(...)`` bytes that the call overwrites."""
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("decode_gqa_splitkv: q, caches and out must share a dtype")
+    _limits(q, kv=min(k_cache.shape[0], v_cache.shape[0]))
     rc = lib.vtx_decode_gqa_splitkv(ptr(q), ptr(k_cache), ptr(v_cache), ptr(out), ptr(kv_indptr), ptr(kv_indices),
                                     ptr(kv_last_page_len), int(eff_bs), q.shape[1], q.shape[2], int(page_size),
                                     float(sm_scale), int(num_splits), ptr(workspace),
@@ -392,6 +445,7 @@ def indexer_gqa_softmax_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, d
     if q.dtype != centroids.dtype:
         raise TypeError("indexer_gqa_softmax_fused: q and centroids must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    _limits(q, summary=centroids.shape[0])
     rc = lib.vtx_indexer_gqa_softmax_fused(ptr(q), ptr(centroids), ptr(dense_kv_indptr), ptr(sparse_kv_indptr),
                                            ptr(dense_kv_indices), ptr(sparse_kv_indices), ptr(sparse_page_table),
                                            stride, int(eff_bs), q.shape[1], q.shape[2], int(topk_val), int(bos),
@@ -405,6 +459,7 @@ def creduce(x, out, loc, num_kv_heads, page_size, op: int) -> None:
     want(loc, torch.int64, "loc")
     if out.dtype != x.dtype:
         raise TypeError("creduce: x and out must share a dtype")
+    _limits(x, kv=x.shape[0], summary=out.shape[0], loc=_slots(x, num_kv_heads, page_size))
     rc = lib.vtx_creduce(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
                          int(page_size), int(op), dtype_code(x.dtype), stream_of(x))
     check(rc, "vtx_creduce")
@@ -417,6 +472,7 @@ def indexer_quest_fused(q, cache_max, cache_min, dense_kv_indptr, sparse_kv_indp
     if not (q.dtype == cache_max.dtype == cache_min.dtype):
         raise TypeError("indexer_quest_fused: q and the two caches must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
+    _limits(q, summary=min(cache_max.shape[0], cache_min.shape[0]))
     rc = lib.vtx_indexer_quest_fused(ptr(q), ptr(cache_max), ptr(cache_min), ptr(dense_kv_indptr),
                                      ptr(sparse_kv_indptr), ptr(dense_kv_indices), ptr(sparse_kv_indices),
                                      ptr(sparse_page_table), stride, int(eff_bs), q.shape[1], q.shape[2],
@@ -435,6 +491,7 @@ def plan_prefill(cached_seq_lens, dense_kv_indptr, dense_kv_indices, input_seq_l
         want(t, torch.int32, n)
     want(req_indices, torch.int64, "req_indices")
     want(batch_table, torch.uint16, "batch_table")
+    _limits(cached_seq_lens, req=req_to_token.shape[0])
     rc = lib.vtx_plan_prefill(ptr(cached_seq_lens), ptr(input_seq_lens), ptr(req_to_token), req_to_token.shape[1],
                               ptr(req_indices), ptr(dense_kv_indptr), ptr(dense_kv_indices), ptr(qo_indptr_ragged),
                               ptr(qo_indptr_paged), ptr(kv_last_page_len), ptr(batch_table),
@@ -449,6 +506,7 @@ def plan_prefill_fa3(cached_seq_lens, cu_seqlens_q, req_to_token, req_indices, p
         want(t, torch.int32, n)
     want(req_indices, torch.int64, "req_indices")
     want(batch_table, torch.uint16, "batch_table")
+    _limits(req_indices, req=req_to_token.shape[0])
     rc = lib.vtx_plan_prefill_fa3(ptr(cached_seq_lens), ptr(cu_seqlens_q), ptr(req_to_token), req_to_token.shape[1],
                                   ptr(req_indices), ptr(page_table), page_table.shape[1], ptr(batch_table),
                                   req_indices.shape[0], int(page_size), int(num_kv_heads), stream_of(req_indices))
@@ -494,6 +552,7 @@ def gemm_bpr(q, table, out, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val,
     """``out[p, c, g] = table[row_p, c, :] . q[s, g, :]`` on every candidate row (bf16, fp32 products and sum)."""
     if not (q.dtype == table.dtype == out.dtype):
         raise TypeError("gemm_bpr: q, table and out must share a dtype")
+    _limits(q, summary=table.shape[0])
     rc = lib.vtx_gemm_bpr(ptr(q), ptr(table), ptr(out), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
                           q.shape[1], table.shape[1], q.shape[2], int(topk_val), int(bos), int(eos),
                           dtype_code(q.dtype), stream_of(q))
@@ -523,6 +582,7 @@ def binary_bpr(q, table, out, dense_kv_indptr, dense_kv_indices, eff_bs, topk_va
                alpha: float = 1.0, beta: float = 1.0, x_is_ragged: bool = False) -> None:
     """op 0 max, 1 min, 2 alpha q + beta y, 3 q y between ``q[s]`` (or, with ``x_is_ragged``, the RAGGED row
     ``q[p]``) and ``table[row_p]`` (inner dims broadcast)."""
+    _limits(q, summary=table.shape[0])
     rc = lib.vtx_binary_bpr(ptr(q), ptr(table), ptr(out), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
                             q.shape[1], q.shape[2], table.shape[1], table.shape[2], int(op), float(alpha), float(beta),
                             int(bool(x_is_ragged)), int(topk_val), int(bos), int(eos), dtype_code(q.dtype), stream_of(q))
@@ -536,6 +596,7 @@ def transpose_ragged(x, out, dense_kv_indptr, eff_bs, topk_val, bos, eos) -> Non
 
 
 def save_load_ragged(ragged, paged, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos, save: bool) -> None:
+    _limits(ragged, summary=paged.shape[0])
     rc = lib.vtx_save_load_ragged(ptr(ragged), ptr(paged), ptr(dense_kv_indptr), ptr(dense_kv_indices), int(eff_bs),
                                   ragged.shape[1] * ragged.shape[2], int(bool(save)), int(topk_val), int(bos), int(eos),
                                   dtype_code(ragged.dtype), stream_of(ragged))
@@ -546,6 +607,7 @@ def save_load_ragged(ragged, paged, dense_kv_indptr, dense_kv_indices, eff_bs, t
 def cache_reduce(x, out, loc, num_kv_heads, page_size, dim: int, kind: int, x_ragged=False, out_ragged=False) -> None:
     """kind 0 mean, 1 max, 2 min, 3 l2norm over axis ``dim`` of the triggered blocks of ``x`` ``[*, r, c]``."""
     want(loc, torch.int64, "loc")
+    _limits(x, loc=_paged_slots(num_kv_heads, page_size, (x, x_ragged), (out, out_ragged)))
     rc = lib.vtx_cache_reduce(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1], x.shape[2],
                               int(page_size), int(dim), int(kind), int(bool(x_ragged)), int(bool(out_ragged)),
                               dtype_code(x.dtype), stream_of(x))
@@ -555,6 +617,7 @@ def cache_reduce(x, out, loc, num_kv_heads, page_size, dim: int, kind: int, x_ra
 def cache_elementwise(x, out, loc, num_kv_heads, page_size, op: int, alpha: float, beta: float, x_ragged=False,
                       out_ragged=False) -> None:
     want(loc, torch.int64, "loc")
+    _limits(x, loc=_paged_slots(num_kv_heads, page_size, (x, x_ragged), (out, out_ragged)))
     rc = lib.vtx_cache_elementwise(ptr(x), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads),
                                    x.shape[1] * x.shape[2], int(page_size), int(op), float(alpha), float(beta),
                                    int(bool(x_ragged)), int(bool(out_ragged)), dtype_code(x.dtype), stream_of(x))
@@ -564,6 +627,7 @@ def cache_elementwise(x, out, loc, num_kv_heads, page_size, op: int, alpha: floa
 def cache_binary(x, y, out, loc, num_kv_heads, page_size, op: int, alpha: float = 1.0, beta: float = 1.0,
                  in_ragged=False, out_ragged=False) -> None:
     want(loc, torch.int64, "loc")
+    _limits(x, loc=_paged_slots(num_kv_heads, page_size, (x, in_ragged), (y, in_ragged), (out, out_ragged)))
     rc = lib.vtx_cache_binary(ptr(x), ptr(y), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1],
                               x.shape[2], y.shape[1], y.shape[2], int(page_size), int(op), float(alpha), float(beta),
                               int(bool(in_ragged)), int(bool(out_ragged)), dtype_code(x.dtype), stream_of(x))
@@ -573,6 +637,7 @@ def cache_binary(x, y, out, loc, num_kv_heads, page_size, op: int, alpha: float 
 def cache_gemm(x, y, out, loc, num_kv_heads, page_size, in_ragged=False, out_ragged=False) -> None:
     """``out block = y block . (x block)^T`` for every triggered (token, head)."""
     want(loc, torch.int64, "loc")
+    _limits(x, loc=_paged_slots(num_kv_heads, page_size, (x, in_ragged), (y, in_ragged), (out, out_ragged)))
     rc = lib.vtx_cache_gemm(ptr(x), ptr(y), ptr(out), ptr(loc), loc.shape[0], int(num_kv_heads), x.shape[1],
                             y.shape[1], x.shape[2], int(page_size), int(bool(in_ragged)), int(bool(out_ragged)),
                             dtype_code(x.dtype), stream_of(x))
