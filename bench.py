@@ -462,24 +462,26 @@ def run_mla_workload(args):
                                  mla_path=args.mla_path, pdl=bool(args.pdl))))
 
 
-def measure_ragged(dev, dist, rank, world, steps, warmup):
-    """The ragged-batch configuration (config 3), one sparse layer, sharded by request (strong scaling).
+def measure_ragged(dev, dist, rank, world, steps, warmup, head_shards=1):
+    """The ragged-batch configuration (config 3), one sparse layer, sharded over the ranks (strong scaling).
 
     256 requests, context lengths uniform in [1024, 32768], 32 q heads / 8 KV heads / head_dim 128, bf16,
-    page 16, topk 64 + 1 + 1; requests are dealt to the ranks by total page count (the batch is fixed, each
-    rank holds only its own requests' pool).  No collective on the timed path; NCCL gathers the selections
+    page 16, topk 64 + 1 + 1.  The ranks form a grid of (world / head_shards) request shards x head_shards head
+    shards: requests are dealt to the request shards by total page count, and a rank holds a pool with only its
+    own requests' pages and its own KV heads.  No collective on the timed path; NCCL gathers the selections
     of sampled requests for verification afterwards.  Returns the result dict on every rank.
     """
     from oracle import vortex_oracle as vo
     from vortex_torch import _cabi
-    from vortex_torch.runtime import balance_requests, gather_for_verification
+    from vortex_torch.runtime import gather_for_verification, shard_grid
 
-    nreq, Hq, H, D, P, K, bos, eos = 256, 32, 8, 128, 16, 64, 1, 1
-    G = Hq // H
+    nreq, Hq, H_all, D, P, K, bos, eos = 256, 32, 8, 128, 16, 64, 1, 1
+    G = Hq // H_all
     g = torch.Generator().manual_seed(33)
     seq_all = torch.randint(1024, 32769, (nreq,), generator=g).tolist()
     pages_all = [(x + P - 1) // P for x in seq_all]
-    mine = balance_requests(pages_all, world)[rank]
+    grid = shard_grid(pages_all, H_all, world, head_shards)
+    mine, H = list(grid[rank].requests), grid[rank].num_heads   # from here on H is this rank's head count
     seq = [seq_all[r] for r in mine]
     n = [pages_all[r] for r in mine]
     bs, total, maxp = len(mine), sum(n), max(n)
@@ -563,26 +565,27 @@ def measure_ragged(dev, dist, rank, world, steps, warmup):
         want = vo.decode_gqa(qi, kk, vv, plan["sparse_kv_indptr"], plan["sparse_kv_indices"], plan["kv_last_page_len"])
         gotv = out[i * H:(i + 1) * H].float().cpu()
         ok = ok and bool(((gotv - want.float()).abs() <= 2e-2 * want.float().abs().clamp(min=1)).all())
-        sel_local[mine[i]] = torch.as_tensor(got.astype(np.int64), device=dev)
+        sel_local[mine[i] * H_all + grid[rank].head_lo] = torch.as_tensor(got.astype(np.int64), device=dev)
     gathered = gather_for_verification(sel_local, dtype=torch.int64)
     flags = torch.tensor([int(ok)], device=dev, dtype=torch.int32)
     if dist is not None:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     # ---- algorithmic bytes of the whole batch (all ranks)
-    cent_b = sum(H * max(0, p - bos - eos) * D * 2 for p in pages_all if p - bos - eos > K)
+    cent_b = sum(H_all * max(0, p - bos - eos) * D * 2 for p in pages_all if p - bos - eos > K)
     kv_b = 0
     for s_len, p in zip(seq_all, pages_all):
         toks = s_len if p <= budget else (budget - 1) * P + (s_len % P or P)
-        kv_b += H * toks * D * 2 * 2
+        kv_b += H_all * toks * D * 2 * 2
     peaks, kind = measured_peaks()
     return dict(workload="config 3: ragged batch, 256 requests ctx U[1024,32768], 32q/8kv heads, D128, page 16, "
                          "topk 64+1+1, one sparse layer (plan + selection and attention in one launch, long "
                          "segments split over CTAs)",
-                n_gpus=world, scaling="strong", requests_per_rank=[len(x) for x in balance_requests(pages_all, world)],
+                n_gpus=world, scaling="strong", sharding=f"{world // head_shards} request shards x {head_shards} head shards",
+                requests_per_rank=[len(x.requests) for x in grid], kv_heads_per_rank=H,
                 us_per_layer=secs * 1e6, layers_per_s=1.0 / secs, algorithmic_bytes=cent_b + kv_b,
                 achieved_gbs=(cent_b + kv_b) / secs / 1e9,
                 frac_of_n_x_peak=(cent_b + kv_b) / secs / 1e9 / (world * peaks["hbm_gbs"]),
-                peak_kind=f"of {kind}", parity_sample_ok=bool(int(flags.item())), verified_requests=sorted(gathered))
+                peak_kind=f"of {kind}", parity_sample_ok=bool(int(flags.item())), verified_requests=sorted({int(x) // H_all for x in gathered}))
 
 
 def run_ragged_workload(args):
@@ -599,7 +602,7 @@ def run_ragged_workload(args):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
-    line = measure_ragged(dev, dist, rank, world, args.steps, args.warmup)
+    line = measure_ragged(dev, dist, rank, world, args.steps, args.warmup, head_shards=args.head_shards)
     if rank == 0:
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if dist is not None:
@@ -642,6 +645,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="debug: smaller batch")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--head-shards", type=int, default=1,
+                    help="--workload c3: ranks per request shard that split its KV heads (divides --gpus and 8)")
     ap.add_argument("--no-side", action="store_true", help="skip the side measurements (configs 3 and 5)")
     ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
                     help="programmatic dependent launch inside the step graph: 0 off, 1 on, 2 on + early prologue")
@@ -746,6 +751,9 @@ def main():
     side = None
     if not args.no_side:
         side = dict(c3=measure_ragged(device, dist, rank, world, steps=20, warmup=3))
+        if world > 1:  # the same batch with every request's KV heads spread over the ranks as well
+            t = max(d for d in (1, 2, 4, 8) if world % d == 0)
+            side["c3_head_split"] = measure_ragged(device, dist, rank, world, steps=20, warmup=3, head_shards=t)
         if rank == 0:
             side["c5"] = measure_mla(device, steps=20)
     peaks, peak_kind = measured_peaks()

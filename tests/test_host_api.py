@@ -176,3 +176,40 @@ def test_gqa_chain_is_recognised_and_stand_alone_use_needs_the_gpu():
     with pytest.raises(NotImplementedError, match="bfloat16"):
         GeMM().profile(as_vtensor(torch.zeros(1, 2, 16), FORMAT.BATCHED), as_vtensor(torch.zeros(4, 1, 16), FORMAT.PAGED),
                        ctx)
+
+
+def test_head_shards_and_grid():
+    from vortex_torch.runtime import (Shard, choose_head_shards, head_range, local_row_to_global, shard_grid,
+                                      slice_heads)
+
+    assert [head_range(8, 4, i) for i in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
+    with pytest.raises(ValueError):
+        head_range(8, 3, 0)
+    with pytest.raises(ValueError):
+        head_range(8, 2, 2)
+    pages = [100, 7, 64, 2048, 33, 900]
+    grid = shard_grid(pages, 8, 8, head_shards=4)
+    assert len(grid) == 8 and all(isinstance(g, Shard) for g in grid)
+    # ranks 0-3 share the requests of request shard 0 and split its heads; every (request, head) has one owner
+    assert grid[0].requests == grid[3].requests and grid[4].requests == grid[7].requests
+    owners = {}
+    for rank, g in enumerate(grid):
+        for r in g.requests:
+            for hd in range(g.head_lo, g.head_hi):
+                assert (r, hd) not in owners
+                owners[(r, hd)] = rank
+    assert len(owners) == len(pages) * 8
+    with pytest.raises(ValueError):
+        shard_grid(pages, 8, 8, head_shards=3)
+    # one huge request: splitting heads is the only way to spread it
+    assert choose_head_shards([4096, 10, 10], 8, 8) == 8
+    # many equal requests: request sharding alone is already even, fewer head shards win the tie
+    assert choose_head_shards([64] * 64, 8, 8) == 1
+    x = torch.arange(3 * 4 * 2).view(3 * 4, 2)            # 3 pages x 4 heads
+    y = slice_heads(x, 4, 1, 3)
+    assert y.shape == (6, 2) and torch.equal(y[:, 0], torch.tensor([2, 4, 10, 12, 18, 20]))
+    qx = torch.arange(2 * 4 * 3).view(2 * 4, 3, 1)        # queries [bs*H, G, D]
+    assert torch.equal(slice_heads(qx, 4, 2, 4), qx.view(2, 4, 3, 1)[:, 2:4].reshape(4, 3, 1))
+    sh = Shard((0,), 2, 4)
+    rows = torch.tensor([0, 1, 2, 3, 9])                  # page*2 + local head
+    assert local_row_to_global(rows, 8, sh).tolist() == [2, 3, 10, 11, 35]

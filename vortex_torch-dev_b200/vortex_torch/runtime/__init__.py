@@ -8,7 +8,9 @@ reference's ``Context.create`` methods read, runs the profile pass, and drives o
 """
 from .engine import (AttentionBackendStub, GraphedDecodeStep, KVPool, ModelConfig, ModelRunnerStub, ReqToTokenPool, ServerArgs,
                      VortexDecodeRuntime)
-from .sharding import balance_requests, gather_for_verification
+from .sharding import (Shard, balance_requests, choose_head_shards, gather_for_verification, head_range,
+                       local_row_to_global, shard_grid, slice_heads)
 
 __all__ = ["ServerArgs", "ModelConfig", "ReqToTokenPool", "ModelRunnerStub", "KVPool", "AttentionBackendStub",
-           "VortexDecodeRuntime", "GraphedDecodeStep", "balance_requests", "gather_for_verification"]
+           "VortexDecodeRuntime", "GraphedDecodeStep", "balance_requests", "gather_for_verification", "Shard", "shard_grid",
+           "head_range", "choose_head_shards", "slice_heads", "local_row_to_global"]
