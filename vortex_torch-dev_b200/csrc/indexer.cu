@@ -9,7 +9,7 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_kernel(IndexerArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<T, D, MODE>(a, smem_raw, blockIdx.y, blockIdx.x);
+    indexer_body<T, D, MODE>(a, smem_raw, blockIdx.x, blockIdx.y);
 }
 
 // gqa_block_sparse_attention indexer: GeMM -> Softmax over pages -> Max over heads -> top-k, one launch.
@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(kThreads, 4) indexer_gqa_kernel(IndexerArgs a)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<__nv_bfloat16, D, 2, NoHooks, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
+    indexer_body<__nv_bfloat16, D, 2, NoHooks, GQ>(a, smem_raw, blockIdx.x, blockIdx.y);
 }
 
 // gqa_quest_sparse_attention indexer: envelope bound per head -> Max over heads -> top-k, one launch.
@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_quest_kernel(IndexerArgs 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    indexer_body<__nv_bfloat16, D, 3, NoHooks, GQ>(a, smem_raw, blockIdx.y, blockIdx.x);
+    indexer_body<__nv_bfloat16, D, 3, NoHooks, GQ>(a, smem_raw, blockIdx.x, blockIdx.y);
 }
 
 template <typename T>
@@ -75,7 +75,7 @@ int launch_indexer_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     auto kern = indexer_kernel<T, D, MODE>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    return vtx::launch(kern, dim3(a.nch_max, eff_bs), dim3(kThreads), bytes, st, a);
+    return vtx::launch(kern, dim3(eff_bs, a.nch_max), dim3(kThreads), bytes, st, a);
 }
 
 template <typename T, int MODE>
@@ -110,7 +110,7 @@ int launch_indexer_gqa_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     auto kern = indexer_gqa_kernel<D, GQ>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    return vtx::launch(kern, dim3(a.nch_max, eff_bs), dim3(kThreads), bytes, st, a);
+    return vtx::launch(kern, dim3(eff_bs, a.nch_max), dim3(kThreads), bytes, st, a);
 }
 
 int launch_indexer_gqa(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
@@ -133,7 +133,7 @@ int launch_indexer_quest_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) 
     auto kern = indexer_quest_kernel<D, GQ>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    return vtx::launch(kern, dim3(a.nch_max, eff_bs), dim3(kThreads), bytes, st, a);
+    return vtx::launch(kern, dim3(eff_bs, a.nch_max), dim3(kThreads), bytes, st, a);
 }
 
 int launch_indexer_quest(const IndexerArgs& a, int eff_bs, cudaStream_t st) {

@@ -47,7 +47,9 @@ struct IndexerArgs {
     int64_t pt_stride;
     int G, D, K, bos, eos, key_cap;
     float scale;  // MODE 2: softmax scale
-    // A segment with more than `chunk` candidates is scanned by several CTAs (blockIdx.x = chunk number):
+    // A segment with more than `chunk` candidates is scanned by several CTAs (blockIdx.y = chunk number; the grid is
+    // (segments, chunks), so the chunk numbers that only long segments have are placed last and the CTAs that
+    // find nothing to do do not hold up the ones that do):
     // each keeps the K best keys of its chunk in part_keys, counts itself in tickets[segment], and the CTA
     // that arrives last sorts the union (its first K are the segment's first K: keys are unique and the
     // order is total).  chunk == 0: one CTA per segment.

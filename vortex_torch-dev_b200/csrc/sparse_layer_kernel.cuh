@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kern
     extern __shared__ __align__(128) unsigned char smem_raw[];
     if (!early) vtx::pdl_wait();
     vtx::pdl_trigger();
-    const int seg = blockIdx.y, chunk_no = blockIdx.x;
+    const int seg = blockIdx.x, chunk_no = blockIdx.y;
     // What the early start of the decode phase needs, all of it written by the block-table builder; fetched
     // now (off the critical path) and parked in shared memory so that it costs no registers until the sort.
     __shared__ int s_pre[4];  // pages listed, tokens of the last page, row of the last / first list entry
@@ -124,7 +124,7 @@ int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da,
     auto kern = sparse_layer_kernel<D, G, MODE>;
     int rc = set_smem(kern, bytes);
     if (rc != VTX_OK) return rc;
-    return vtx::launch(kern, dim3(ia.nch_max, eff_bs), dim3(kThreads), bytes, st, ia, da, ap, early ? 1 : 0);
+    return vtx::launch(kern, dim3(eff_bs, ia.nch_max), dim3(kThreads), bytes, st, ia, da, ap, early ? 1 : 0);
 }
 
 template <int D, int MODE>
