@@ -441,7 +441,9 @@ int vtx_elementwise_binary(const void* x, const void* y, void* out, const int32_
  *                       (cache/reduce.py:354-525).
  * vtx_cache_elementwise the unary family of vtx_elementwise on a block of inner_size values.  Replaces
  *                       elementwise_pp / _pr / _rp / _rr (cache/triton_kernels/elementwise_impl.py) behind cache
- *                       Relu / Silu / Sigmoid / Abs / Add_Mul (cache/elementwise.py).
+ *                       Relu / Silu / Sigmoid / Abs / Add_Mul (cache/elementwise.py).  op 5 writes bf16(alpha) to
+ *                       the whole block without reading x (pass x = out): fill_p_kernel
+ *                       (cache/triton_kernels/fill_impl.py:6-49) behind cache/fill.py:8-165.
  * vtx_cache_binary      x block [x_c, x_d] with y block [y_c, y_d] (a size of 1 repeats); op 0 max, 1 min,
  *                       2 bf16(alpha x) + bf16(beta y), 3 x y; x and y share a layout.  Replaces
  *                       elementwise_binary_ppp / _ppr / _rrp / _rrr

@@ -786,6 +786,15 @@ def cache_elementwise(x, out, loc, page_size, num_kv_heads, op, alpha, beta, x_r
     return out
 
 
+def cache_fill(x, loc, page_size, num_kv_heads, alpha):
+    """Cache-side ``Fill`` (cache/fill.py:8-165 over fill_p_kernel, cache/triton_kernels/fill_impl.py:6-49): the
+    whole block of every triggered (page, head) row of the PAGED tensor ``x`` becomes ``alpha`` rounded to x's
+    dtype; nothing else changes.  In place."""
+    for prow, _ in _cache_items(loc, page_size, num_kv_heads):
+        x[prow] = torch.tensor(float(alpha), dtype=torch.float32).to(x.dtype)
+    return x
+
+
 def cache_binary(x, y, out, loc, page_size, num_kv_heads, op, alpha=1.0, beta=1.0, in_ragged=False, out_ragged=False):
     """Cache-side ``Maximum / Minimum / Add / Multiply`` (cache/elementwise_binary.py): `elementwise_binary` on
     every triggered pair of blocks."""

@@ -127,3 +127,28 @@ def test_cache_operator_classes_through_a_context():
     want_mx = vo.cache_binary(want_mm, want_ab, torch.zeros_like(want_mm), loc, P, H, 0, in_ragged=True, out_ragged=True)
     touched = [r for _, r in vo._cache_items(loc, P, H)]
     assert _eq(mm[touched], want_mm[touched]) and _eq(ab[touched], want_ab[touched]) and _eq(mx[touched], want_mx[touched])
+
+
+@pytest.mark.parametrize("alpha", [0.0, -1.0, 0.3, float("-inf")])
+def test_cache_fill_in_place(alpha):
+    """Fill(alpha): triggered blocks become bf16(alpha) even where they held NaN or inf; the others keep their bits."""
+    from vortex_torch.abs import FORMAT, as_vtensor
+    from vortex_torch.cache.fill import Fill
+    from vortex_torch.runtime import ServerArgs, VortexDecodeRuntime
+
+    rt = VortexDecodeRuntime(1, H * 2, H, 128, num_pages=PAGES, max_bs=NNZ, context_len=PAGES * P,
+                             server_args=ServerArgs(page_size=P, vortex_topk_val=4))
+    ctx = rt.cctx
+    loc = _loc(23)
+    x = _operand(False, 3, 40, 24)
+    x[::2, 0, 0] = float("nan")
+    x[1::2, 1, 1] = float("inf")
+    want = vo.cache_fill(x.clone(), loc, P, H, alpha)
+    xd = x.cuda()
+    op = Fill(alpha)
+    ctx.profile()
+    assert op(as_vtensor(xd, FORMAT.PAGED), loc=loc.cuda(), ctx=ctx)._format == FORMAT.PAGED
+    ctx.execute()
+    assert op(xd, loc=loc.cuda(), ctx=ctx) is xd
+    assert _eq(xd, want)
+    assert len(list(vo._cache_items(loc, P, H))) == 9 * H

@@ -115,9 +115,11 @@ __global__ void __launch_bounds__(kThreads) cache_reduce_kernel(const __nv_bfloa
     }
 }
 
-// unary op: 0 x >= alpha ? x : beta; 1 1/(1+exp(beta x+alpha)); 2 x/(1+exp(beta x+alpha)); 3 |beta x+alpha|; 4 beta x+alpha
+// unary op: 0 x >= alpha ? x : beta; 1 1/(1+exp(beta x+alpha)); 2 x/(1+exp(beta x+alpha)); 3 |beta x+alpha|; 4 beta x+alpha;
+// 5 alpha (a fill: x is not read)
 __device__ __forceinline__ float unary(int op, float x, float alpha, float beta) {
     if (op == 0) return x >= alpha ? x : beta;
+    if (op == 5) return alpha;
     const float z = bf16_round(__fadd_rn(bf16_round(__fmul_rn(beta, x)), alpha));
     if (op == 1) return __fdiv_rn(1.f, __fadd_rn(1.f, exp_canonical(z)));
     if (op == 2) return __fdiv_rn(x, __fadd_rn(1.f, exp_canonical(z)));
@@ -140,7 +142,8 @@ __global__ void __launch_bounds__(kThreads) cache_elementwise_kernel(const __nv_
         if (!m.active) continue;
         const __nv_bfloat16* src = x + (x_ragged ? m.ragged_row : m.paged_row) * (int64_t)inner;
         __nv_bfloat16* dst = out + (out_ragged ? m.ragged_row : m.paged_row) * (int64_t)inner;
-        for (int e = lane; e < inner; e += 32) dst[e] = __float2bfloat16_rn(unary(op, ld(src + e), alpha, beta));
+        for (int e = lane; e < inner; e += 32)
+            dst[e] = __float2bfloat16_rn(unary(op, op == 5 ? 0.f : ld(src + e), alpha, beta));
     }
 }
 
@@ -236,7 +239,7 @@ extern "C" int vtx_cache_elementwise(const void* x, void* out, const int64_t* lo
                                      int out_is_ragged, int dtype, void* stream) {
     int rc = common_check(x, out, loc, nnz, num_kv_heads, page_size, dtype);
     if (rc != VTX_OK) return rc;
-    if (inner_size < 1 || op < 0 || op > 4) return VTX_ERR_INVALID_ARGUMENT;
+    if (inner_size < 1 || op < 0 || op > 5) return VTX_ERR_INVALID_ARGUMENT;
     if (nnz == 0) return VTX_OK;
     const float a = __bfloat162float(__float2bfloat16_rn(alpha)), b = __bfloat162float(__float2bfloat16_rn(beta));
     return vtx::launch(cache_elementwise_kernel, dim3(grid_for(nnz * num_kv_heads)), dim3(kThreads), 0,
