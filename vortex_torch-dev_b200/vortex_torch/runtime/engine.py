@@ -294,7 +294,8 @@ class GraphedDecodeStep:
     def d2h_bytes(self) -> int:
         return self.out.numel() * self.out.element_size()
 
-    def capture_host_pipeline(self, programmatic_launch=0, layers_per_gate: int = 7) -> None:
+    def capture_host_pipeline(self, programmatic_launch=0, layers_per_gate: int = 7, first_group: int = 1,
+                              last_group: int = 1, layers_per_output: Optional[int] = None) -> None:
         """Capture the host-buffer step as one graph in which the copies overlap the kernels.
 
         Three branches inside the graph: an input branch copies the step's pinned host inputs layer by
@@ -303,7 +304,11 @@ class GraphedDecodeStep:
         ``run_from_host`` replays it.  The inputs arrive far ahead of the compute branch (a layer's inputs
         take a few microseconds of PCIe time, the layer tens), so the gates cost nothing in waiting; they are
         kept few because a kernel that waits for a copy node cannot be chained to its predecessor by
-        programmatic dependent launch.
+        programmatic dependent launch.  The first input group holds only ``first_group`` layers, so that compute
+        starts after a fraction of the inputs has crossed PCIe (the rest arrives under it), and the last
+        ``last_group`` layers' outputs go back as a copy of their own, so that little is left to copy once the
+        last kernel has finished; in between, outputs go back every ``layers_per_output`` layers (default: the
+        input group size).
         """
         h = self.host_buffers()
         dev = self.rt.device
@@ -311,12 +316,21 @@ class GraphedDecodeStep:
         torch.cuda.synchronize(dev)
         self.rt.pdl_mode = int(programmatic_launch)
         try:
-            self._capture_host_pipeline(h, dev, max(1, int(layers_per_gate)))
+            L = self.rt.num_layers
+            gate = max(1, int(layers_per_gate))
+            first = min(L, max(1, int(first_group)))
+            in_starts = [0] + list(range(first, L, gate))
+            last = min(L, max(1, int(last_group)))
+            og = gate if layers_per_output is None else max(1, int(layers_per_output))
+            out_ends = sorted(set(list(range(first + og, L - last + 1, og)) + [first, L - last, L]) - {0})
+            self._capture_host_pipeline(h, dev, in_starts, out_ends)
         finally:
             self.rt.pdl_mode = 0
             _cabi.set_programmatic_launch(0)
 
-    def _capture_host_pipeline(self, h, dev, gate: int) -> None:
+    def _capture_host_pipeline(self, h, dev, in_starts, out_ends) -> None:
+        """``in_starts``: first layer of every input group; ``out_ends``: layer counts after which the outputs
+        computed since the previous such point are copied back."""
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         L = self.rt.num_layers
         g = torch.cuda.CUDAGraph()
@@ -330,8 +344,7 @@ class GraphedDecodeStep:
                 for n in ("seq_lens", "req_indices", "loc"):
                     getattr(self, n).copy_(h[n], non_blocking=True)
                 ev_meta.record(s_in)
-                for l0 in range(0, L, gate):
-                    l1 = min(L, l0 + gate)
+                for l0, l1 in zip(in_starts, in_starts[1:] + [L]):
                     # one copy per input tensor and group: the per-layer buffers of a group are contiguous
                     self.q[l0:l1].copy_(h["q"][l0:l1], non_blocking=True)
                     self.new_k[l0:l1].copy_(h["new_k"][l0:l1], non_blocking=True)
@@ -344,9 +357,9 @@ class GraphedDecodeStep:
                 if l in ev_in:
                     main.wait_event(ev_in[l])
                 self.rt.layer(l, self.q[l], self.new_k[l], self.new_v[l], self.loc, self.out[l])
-                if (l + 1) % gate == 0 or l == L - 1:
+                if l + 1 in out_ends:
                     # outputs go back group by group too, while the next group computes
-                    l0 = (l // gate) * gate
+                    l0 = max([e for e in out_ends if e <= l], default=0)
                     ev = torch.cuda.Event()
                     ev.record(main)
                     s_out.wait_event(ev)
