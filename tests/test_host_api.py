@@ -213,3 +213,24 @@ def test_head_shards_and_grid():
     sh = Shard((0,), 2, 4)
     rows = torch.tensor([0, 1, 2, 3, 9])                  # page*2 + local head
     assert local_row_to_global(rows, 8, sh).tolist() == [2, 3, 10, 11, 35]
+
+
+@pytest.mark.parametrize("G", [1, 3, 5, 8, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_unfused_group_mean_follows_the_canonical_order(G, dtype):
+    """The mean a flow sees when nothing is fused (any group size) is the oracle's, bit for bit, also where the
+    order of the fp32 sum matters (values spread over 30 binades)."""
+    from oracle import vortex_oracle as vo
+    from vortex_torch.abs import FORMAT, as_vtensor
+    from vortex_torch.abs.tensor import materialize
+
+    g = torch.Generator().manual_seed(G)
+    q = (torch.randn(6, G, 64, generator=g) * torch.exp2(torch.randint(-15, 15, (6, G, 64), generator=g).float())).to(dtype)
+    want = vo.q_group_mean(q)
+    eager = as_vtensor(q.clone(), FORMAT.BATCHED).mean(dim=1, keepdim=True)
+    assert torch.equal(torch.Tensor(eager).view(torch.int16 if dtype == torch.bfloat16 else torch.int32),
+                       want.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+    lazy_src = as_vtensor(q.clone(), FORMAT.BATCHED)
+    lazy_src._vtx_allow_lazy_mean = True
+    lazy = lazy_src.mean(dim=1, keepdim=True)
+    assert torch.equal(torch.Tensor(materialize(lazy)), torch.Tensor(eager))

@@ -104,12 +104,23 @@ def lazy_group_mean_source(x: Any) -> Optional[torch.Tensor]:
     return getattr(x, "_vtx_lazy_src", None)
 
 
+def canonical_group_mean(src: torch.Tensor) -> torch.Tensor:
+    """``src.mean(dim=1, keepdim=True)`` of a 3-D tensor in the arithmetic every kernel of the library uses for
+    the grouped-query mean: an fp32 sum over the group in ascending order from +0.0, one division by the group
+    size, one rounding to the dtype.  (torch's own ``mean`` leaves the order of the sum to its reduction
+    kernel; with a fixed order the un-fused path selects exactly the pages the fused kernels select.)"""
+    acc = torch.zeros((src.shape[0], src.shape[2]), dtype=torch.float32, device=src.device)
+    for g in range(src.shape[1]):
+        acc = acc + src[:, g].to(torch.float32)
+    return (acc / float(src.shape[1])).to(src.dtype).unsqueeze(1)
+
+
 def materialize(x: Any) -> Any:
     """Replace a stand-in for ``q.mean(dim=1, keepdim=True)`` by the computed mean."""
     src = lazy_group_mean_source(x)
     if src is None:
         return x
-    plain = _plain(src).mean(dim=1, keepdim=True)
+    plain = canonical_group_mean(_plain(src))
     return vTensor._wrap(plain, x._format) if isinstance(x, vTensor) else plain
 
 
@@ -166,6 +177,8 @@ class vTensor(torch.Tensor):
             if getattr(src, "_vtx_allow_lazy_mean", False):
                 out = cls._wrap(_plain(src).narrow(1, 0, 1), fmt)
                 out._vtx_lazy_src = src
+            elif src.dim() == 3 and src.dtype in (torch.bfloat16, torch.float32, torch.float16):
+                out = cls._wrap(canonical_group_mean(_plain(src)), fmt)
             else:
                 out = _retag(super().__torch_function__(func, types, args, kwargs), fmt)
             out._vtx_origin = "group_mean"
