@@ -634,11 +634,11 @@ def run_ragged_workload(args):
         dist.destroy_process_group()
 
 
-def side_flow_measurement(args, cfg, rt, step):
+def side_flow_measurement(args, cfg, rt, step, json_fd):
     """Side measurement (not the headline line): the same decode step with another shipped flow choosing
     the pages.  Prints steps/s of the graphed step; parity of these flows is covered by the tests."""
     dev = rt.device
-    step.capture(programmatic_launch=min(args.pdl, 1))
+    step.capture(programmatic_launch=args.pdl)
     for _ in range(max(3, args.warmup)):
         step.replay()
     torch.cuda.synchronize(dev)
@@ -654,9 +654,11 @@ def side_flow_measurement(args, cfg, rt, step):
     n_sparse = cfg["layers"] - len(cfg["skip"])
     extra = ab["centroids_per_layer"] * n_sparse if args.flow == "gqa_quest_sparse_attention" else 0  # two summary rows
     total = ab["step"] + extra
-    print(json.dumps(dict(flow=args.flow, workload=workload_config(cfg, 1)["workload"], steps_per_s=1.0 / secs,
-                          ms_per_step=secs * 1e3, algorithmic_bytes=total, achieved_gbs=total / secs / 1e9,
-                          frac=total / secs / 1e9 / peaks["hbm_gbs"], peak_kind=f"of {kind}")))
+    line = dict(flow=args.flow, workload=workload_config(cfg, 1)["workload"], steps_per_s=1.0 / secs,
+                ms_per_step=secs * 1e3, algorithmic_bytes=total, achieved_gbs=total / secs / 1e9,
+                frac=total / secs / 1e9 / peaks["hbm_gbs"], peak_kind=f"of {kind}", programmatic_launch=int(args.pdl))
+    sys.stdout.flush()
+    os.write(json_fd, (json.dumps(line) + "\n").encode())
 
 
 def main():
@@ -718,7 +720,7 @@ def main():
 
     rt, step, slots = build_runtime(cfg, device, seed=1234 + rank, flow_name=args.flow)
     if args.flow != "block_sparse_attention":
-        side_flow_measurement(args, cfg, rt, step)
+        side_flow_measurement(args, cfg, rt, step, json_fd)
         return
     if not args.no_graph:
         step.capture(programmatic_launch=args.pdl)

@@ -146,18 +146,23 @@ def test_vortex_torch_C_shim_signatures():
     np.testing.assert_array_equal(sin_.cpu().numpy()[:ns], ref["sparse_kv_indices"])
 
 
-def test_graphed_step_with_programmatic_launch_matches_eager():
-    """The CUDA-graph replay of a step, kernels chained by programmatic dependent launch, gives the
-    eager results bit for bit (and keeps doing so over repeated replays)."""
+@pytest.mark.parametrize("flow_name", ["block_sparse_attention", "gqa_block_sparse_attention",
+                                       "gqa_quest_sparse_attention"])
+def test_graphed_step_with_programmatic_launch_matches_eager(flow_name):
+    """The CUDA-graph replay of a step, kernels chained by programmatic dependent launch (with and without the
+    early prologue of the layer kernel), gives the eager results bit for bit over repeated replays, for each of
+    the three shipped flows."""
+    from vortex_torch.flow import build_vflow
     from vortex_torch.runtime import GraphedDecodeStep
 
-    seq, L, H, G, D, P, K = [2048, 1000, 4096, 300], 3, 8, 2, 128, 16, 30
+    seq, L, H, G, D, P, K = [2048, 1000, 4096, 300], 4, 8, 2, 128, 16, 30
     prob = vo.make_paged_problem(17, seq, H, G, D, P)
-    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16)
+    rt = _runtime(prob, seq, L, H, G, D, P, K, 1, 1, torch.bfloat16, flow=build_vflow(flow_name))
     for l in range(L):
         pl = vo.make_paged_problem(200 + l, seq, H, G, D, P)
-        for name in ("k", "v", "centroids"):
-            rt.pool.buffers[l][name].copy_(pl[name])
+        for name, buf in rt.pool.buffers[l].items():
+            # k, v and whatever page summaries the flow keeps (seeded with something page-shaped)
+            buf.copy_(pl[name] if name in pl else pl["centroids"] * (1.5 if "max" in name else 0.5))
     bs = len(seq)
     step = GraphedDecodeStep(rt, bs)
     step.seq_lens.copy_(torch.as_tensor(prob["seq_lens"]))
