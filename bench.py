@@ -348,7 +348,8 @@ def time_kernels(rt, step, cfg, reps, pdl):
 
 
 def measure_mla(dev, steps, layers=4, mla_path=0, pdl=True):
-    """The MLA block-table sparse decode configuration (config 5), one layer = fused indexer + decode.
+    """The MLA block-table sparse decode configuration (config 5), one layer = page selection + decode in one
+    launch (`vtx_mla_sparse_layer`); the two kernels are also timed on their own and as two launches.
 
     bs128, 16 heads, 576-dim latent (values = first 512), page 64, 16384 tokens, topk 32 + 1 + 1.
     ``layers`` distinct 2.4 GB latent pools are cycled so that consecutive launches never share L2 lines.
@@ -397,14 +398,20 @@ def measure_mla(dev, steps, layers=4, mla_path=0, pdl=True):
         for l in range(L):
             _cabi.decode_mla(qs[l], lat[l], outs[l], spt, ssl, P, scale)
 
-    def run_layer():
+    def run_layer():  # selection + decode as one launch (two in the mma.sync form)
+        for l in range(L):
+            _cabi.mla_sparse_layer(qs[l], cent[l], lat[l], outs[l], dip, sip, din, sin_, spt, ssl, P, K, bos, eos,
+                                   pages_per_req, scale)
+
+    def run_two_launches():
         for l in range(L):
             _cabi.indexer_fused(qs[l], cent[l], dip, sip, din, sin_, bs, K, bos, eos, pages_per_req,
                                 sparse_page_table=spt)
             _cabi.decode_mla(qs[l], lat[l], outs[l], spt, ssl, P, scale)
 
     res = {}
-    for name, fn in (("indexer", run_indexer), ("decode_mla", run_decode), ("layer", run_layer)):
+    for name, fn in (("indexer", run_indexer), ("decode_mla", run_decode), ("layer_two_launches", run_two_launches),
+                     ("layer", run_layer)):
         fn()
         torch.cuda.synchronize(dev)
         gr = torch.cuda.CUDAGraph()

@@ -400,6 +400,23 @@ int vtx_decode_mla(const void* q, const void* latent_cache, int64_t num_cache_pa
                    const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
                    int batch_size, int num_heads, int latent_dim, int value_dim, int page_size,
                    float sm_scale, int dtype, void* stream);
+
+/*
+ * One MLA sparse layer in one launch: the page selection of vtx_indexer_fused (query mean over the heads,
+ * scores of the candidate pages' summary rows, top-k, written to sparse_kv_indices and to the request's row of
+ * sparse_page_table) followed by vtx_decode_mla over that row.  Arguments as in those two entry points
+ * (summary [num_cache_pages, 1, latent_dim]; one KV head, so eff_batch_size = batch_size).  The tcgen05 form of
+ * the decode runs the selection as its first phase when topk_val <= 64 and the candidates fit its scratch;
+ * otherwise, and in the mma.sync form, the call issues the two launches.  Results are those of the two calls,
+ * bit for bit.  No counterpart in the reference (it has no MLA path).
+ */
+int vtx_mla_sparse_layer(const void* q, const void* summary, const void* latent_cache, int64_t num_cache_pages,
+                         void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                         const int32_t* dense_kv_indices, int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                         int64_t page_table_stride, const int32_t* sparse_cache_seqlens, int batch_size,
+                         int num_heads, int latent_dim, int value_dim, int page_size, int topk_val,
+                         int page_reserved_bos, int page_reserved_eos, int max_num_pages_per_request,
+                         float sm_scale, int dtype, void* stream);
 int vtx_set_mla_path(int path);
 void* vtx_mla_fault_word(void);
 int vtx_mla_fault_read(uint32_t* host_bits);

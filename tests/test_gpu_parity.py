@@ -421,6 +421,51 @@ def test_mla_page_sizes_both_forms(P, path):
     assert close(out, want, BF16_TOL), f"max err {(out.float().cpu() - want.float()).abs().max()}"
 
 
+@pytest.mark.parametrize("path", [0, 1])
+@pytest.mark.parametrize("seq,K", [([4096, 1300, 64, 65, 1, 700, 16384], 32), ([100, 3000, 9000], 5),
+                                    ([16384, 2100 * 4], 64), ([5000, 6000], 100)])
+def test_mla_sparse_layer_one_launch_equals_two(seq, K, path):
+    """vtx_mla_sparse_layer (the selection as the first phase of the tcgen05 decode kernel; two launches for the
+    mma.sync form and for more than 64 selected pages) against vtx_indexer_fused + vtx_decode_mla: the same
+    packed selection, the same page-table rows, the same output bits; selection also against the oracle."""
+    H, G, D, P, bos, eos = 1, 16, 576, 64, 1, 1
+    prob = vo.make_paged_problem(37, seq, H, G, D, P, v_dim=8)
+    ref = None
+    res = []
+    scale = 1.0 / math.sqrt(192.0)
+    old = _cabi.set_mla_path(path)
+    try:
+        for fused in (False, True, True):  # the fused form twice: its scratch is the ring the decode just used
+            dp = DevicePlan(prob, P, H, K, bos, eos, tables=True)
+            ref = ref or dp.oracle(prob)
+            d = to_dev(prob)
+            out = torch.full((len(seq), G, 512), float("nan"), dtype=torch.bfloat16, device="cuda")
+            if fused:
+                _cabi.mla_sparse_layer(d["q"], d["centroids"], d["k"], out, dp.dense_indptr, dp.sparse_indptr,
+                                       dp.dense_indices, dp.sparse_indices, dp.tables[2], dp.tables[3], P, K, bos, eos,
+                                       dp.max_pages, scale)
+            else:
+                _cabi.indexer_fused(d["q"], d["centroids"], dp.dense_indptr, dp.sparse_indptr, dp.dense_indices,
+                                    dp.sparse_indices, dp.S, K, bos, eos, dp.max_pages, sparse_page_table=dp.tables[2])
+                _cabi.decode_mla(d["q"], d["k"], out, dp.tables[2], dp.tables[3], P, scale)
+            torch.cuda.synchronize()
+            res.append((dp.sparse_indices.clone(), dp.tables[2].clone(), out))
+    finally:
+        _cabi.set_mla_path(old)
+    assert _cabi.mla_fault_bits() == 0 and _cabi.device_status() == 0
+    vo.forward_indexer(prob["q"], prob["centroids"], ref, K, bos, eos)
+    ns = int(ref["sparse_kv_indptr"][-1])
+    np.testing.assert_array_equal(res[0][0].cpu().numpy()[:ns], ref["sparse_kv_indices"])
+    for other in res[1:]:
+        assert torch.equal(other[0][:ns], res[0][0][:ns])
+        for b in range(len(seq)):
+            n = int(ref["sparse_kv_indptr"][b + 1] - ref["sparse_kv_indptr"][b])
+            assert torch.equal(other[1][b, :n], res[0][1][b, :n])
+        assert torch.equal(other[2].view(torch.int16), res[0][2].view(torch.int16))
+    want = vo.decode_mla(prob["q"], prob["k"], ref["sparse_page_table"], ref["sparse_cache_seqlens"], 512, scale)
+    assert close(res[1][2], want, BF16_TOL)
+
+
 def test_mla_rejects_other_shapes():
     z = torch.zeros(1, 8, 576, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(RuntimeError, match="not supported"):

@@ -328,6 +328,12 @@ int launch_decode_mla_tc(const void* q, const void* latent_cache, int64_t num_ca
                          const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
                          int batch_size, int page_size, float sm_scale, cudaStream_t stream);
 void* mla_fault_word();
+int launch_mla_sparse_layer_tc(const void* q, const void* summary, const void* latent_cache, int64_t num_cache_pages,
+                               void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                               const int32_t* dense_kv_indices, int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                               int64_t page_table_stride, const int32_t* sparse_cache_seqlens, int batch_size,
+                               int page_size, int topk_val, int bos, int eos, int max_pages, float sm_scale,
+                               cudaStream_t stream);
 }  // namespace vtx
 
 extern "C" int vtx_set_mla_path(int path) {
@@ -378,4 +384,39 @@ extern "C" int vtx_decode_mla(const void* q, const void* latent_cache, int64_t n
         return VTX_ERR_CUDA;
     }
     return vtx::launch(decode_mla_kernel, dim3(batch_size), dim3(kGroups * kWarps * 32), bytes, (cudaStream_t)stream, a);
+}
+
+extern "C" int vtx_mla_sparse_layer(const void* q, const void* summary, const void* latent_cache, int64_t num_cache_pages,
+                                    void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                                    const int32_t* dense_kv_indices, int32_t* sparse_kv_indices,
+                                    int32_t* sparse_page_table, int64_t page_table_stride,
+                                    const int32_t* sparse_cache_seqlens, int batch_size, int num_heads, int latent_dim,
+                                    int value_dim, int page_size, int topk_val, int page_reserved_bos,
+                                    int page_reserved_eos, int max_num_pages_per_request, float sm_scale, int dtype,
+                                    void* stream) {
+    if (!q || !summary || !latent_cache || !out || !dense_kv_indptr || !sparse_kv_indptr || !dense_kv_indices ||
+        !sparse_kv_indices || !sparse_page_table || !sparse_cache_seqlens)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (batch_size < 0 || page_table_stride < 1 || page_size < 1 || num_cache_pages < 1 || topk_val < 1 ||
+        page_reserved_bos < 0 || page_reserved_eos < 0 || max_num_pages_per_request < 1)
+        return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 && dtype != VTX_F32) return VTX_ERR_INVALID_ARGUMENT;
+    if (dtype != VTX_BF16 || num_heads != kHeads || latent_dim != kDl || value_dim != kDv || page_size % kTile != 0)
+        return VTX_ERR_UNSUPPORTED;
+    if (batch_size == 0) return VTX_OK;
+    if (g_mla_path == 0 && vtx::mla_tc_supported(page_size)) {
+        const int rc = vtx::launch_mla_sparse_layer_tc(
+            q, summary, latent_cache, num_cache_pages, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
+            sparse_kv_indices, sparse_page_table, page_table_stride, sparse_cache_seqlens, batch_size, page_size,
+            topk_val, page_reserved_bos, page_reserved_eos, max_num_pages_per_request, sm_scale, (cudaStream_t)stream);
+        if (rc != VTX_ERR_UNSUPPORTED) return rc;
+    }
+    // the two launches
+    const int rc = vtx_indexer_fused(q, summary, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
+                                     sparse_page_table, page_table_stride, batch_size, num_heads, latent_dim, topk_val,
+                                     page_reserved_bos, page_reserved_eos, max_num_pages_per_request, dtype, stream);
+    if (rc != VTX_OK) return rc;
+    return vtx_decode_mla(q, latent_cache, num_cache_pages, out, sparse_page_table, page_table_stride,
+                          sparse_cache_seqlens, batch_size, num_heads, latent_dim, value_dim, page_size, sm_scale, dtype,
+                          stream);
 }

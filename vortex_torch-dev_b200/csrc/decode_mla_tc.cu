@@ -27,9 +27,13 @@
 // host can read, drains the copies in flight and leaves through the common exit that frees TMEM.
 #include <cuda.h>
 
+#include "indexer_body.cuh"
 #include "vtx_common.cuh"
 
 namespace {
+namespace mla {  // own scope: the indexer body included above has constants of the same names for its 128 threads
+
+using vtxidx::IndexerArgs;
 
 constexpr int kHeads = 16;
 constexpr int kDl = 576;                  // latent row: keys
@@ -269,7 +273,14 @@ __device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((
 // fault codes (bits of g_mla_fault): which kind of barrier a wait gave up on
 enum : unsigned { kFaultEmpty = 1, kFaultFull = 2, kFaultS = 4, kFaultP = 8, kFaultO = 16, kFaultFixed = 32, kFaultQ = 64, kFaultDrain = 128 };
 
-__global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, const __grid_constant__ CUtensorMap quad_map,
+// FUSED: the request's page selection (query mean over the heads, scores of its candidate pages' summary rows,
+// top-K; the body of the stand-alone indexer kernel) runs first, on warps 0-3 with the tile ring as its scratch,
+// and writes the page-table row the decode then walks.  One launch instead of two, and none of the second
+// launch's start-up between the selection and the first tile.
+// FUSED = the ring slots per warp of that phase (3, or 2 when the candidates' keys need the room), 0 = decode only.
+template <int FUSED>
+__global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, const IndexerArgs ia,
+                                                                         const __grid_constant__ CUtensorMap quad_map,
                                                                          const __grid_constant__ CUtensorMap block_map) {
     extern __shared__ unsigned char smem_unaligned[];
     // Under programmatic dependent launch the set-up below (barriers, TMEM) touches nothing the preceding
@@ -304,6 +315,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     vtx::pdl_wait();
+    if constexpr (FUSED != 0) {
+        // The ring and the q / P areas are idle until the first copy is issued below; barriers, the TMEM slot and
+        // the abort flag live behind them (kOffBars) and stay untouched: the host checked that the body's
+        // shared memory ends before kOffWmax.
+        if (warp < 4)
+            indexer_body<__nv_bfloat16, kDl, 0, NoHooks, 1, /*BAR=*/2, /*SLOTS=*/FUSED>(ia, gbase + kOffQuads, b, 0);
+        __syncthreads();  // the page-table row of this request is complete and visible to the CTA
+    }
     const int ntok = a.seqlens[b];
     const int n_tiles = (ntok + kTile - 1) / kTile;
     const bool last_partial = (ntok % kTile) != 0;
@@ -689,45 +708,47 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+}  // namespace mla
 }  // namespace
 
 namespace vtx {
 
 bool mla_tc_supported(int page_size) {
-    return page_size >= 16 && (page_size & (page_size - 1)) == 0 && encode_tiled_fn() != nullptr;
+    return page_size >= 16 && (page_size & (page_size - 1)) == 0 && mla::encode_tiled_fn() != nullptr;
 }
 
 // Launches the tcgen05 form.  `num_cache_pages` bounds the token rows the tensor map may address.
-int launch_decode_mla_tc(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
-                         const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
-                         int batch_size, int page_size, float sm_scale, cudaStream_t stream) {
-    const int box_tok = page_size < kTile ? page_size : kTile;
+static int launch_tc(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
+                     const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
+                     int batch_size, int page_size, float sm_scale, const vtxidx::IndexerArgs* ia, int ring_slots_fused,
+                     cudaStream_t stream) {
+    const int box_tok = page_size < mla::kTile ? page_size : mla::kTile;
     const cuuint64_t tokens = (cuuint64_t)num_cache_pages * (cuuint64_t)page_size;
     if (tokens == 0 || tokens > 0x7fffffffull) return VTX_ERR_INVALID_ARGUMENT;
     void* gaddr = const_cast<void*>(latent_cache);
     // 2-d view [576 dims][tokens], box = one block of one page-box; 3-d view [64 dims][tokens][9 blocks], box = 4 blocks
     CUtensorMap block_map, quad_map;
     {
-        const cuuint64_t gdim[2] = {(cuuint64_t)kDl, tokens};
-        const cuuint64_t gstride[1] = {(cuuint64_t)kDl * 2};
-        const cuuint32_t box[2] = {(cuuint32_t)kBlockDims, (cuuint32_t)box_tok};
+        const cuuint64_t gdim[2] = {(cuuint64_t)mla::kDl, tokens};
+        const cuuint64_t gstride[1] = {(cuuint64_t)mla::kDl * 2};
+        const cuuint32_t box[2] = {(cuuint32_t)mla::kBlockDims, (cuuint32_t)box_tok};
         const cuuint32_t estr[2] = {1, 1};
-        if (encode_tiled_fn()(&block_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gaddr, gdim, gstride, box, estr,
+        if (mla::encode_tiled_fn()(&block_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, gaddr, gdim, gstride, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return VTX_ERR_INVALID_ARGUMENT;
     }
     {
-        const cuuint64_t gdim[3] = {(cuuint64_t)kBlockDims, tokens, (cuuint64_t)(kDl / kBlockDims)};
-        const cuuint64_t gstride[2] = {(cuuint64_t)kDl * 2, (cuuint64_t)kBlockDims * 2};
-        const cuuint32_t box[3] = {(cuuint32_t)kBlockDims, (cuuint32_t)box_tok, 4};
+        const cuuint64_t gdim[3] = {(cuuint64_t)mla::kBlockDims, tokens, (cuuint64_t)(mla::kDl / mla::kBlockDims)};
+        const cuuint64_t gstride[2] = {(cuuint64_t)mla::kDl * 2, (cuuint64_t)mla::kBlockDims * 2};
+        const cuuint32_t box[3] = {(cuuint32_t)mla::kBlockDims, (cuuint32_t)box_tok, 4};
         const cuuint32_t estr[3] = {1, 1, 1};
-        if (encode_tiled_fn()(&quad_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, gaddr, gdim, gstride, box, estr,
+        if (mla::encode_tiled_fn()(&quad_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, gaddr, gdim, gstride, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return VTX_ERR_INVALID_ARGUMENT;
     }
-    TcArgs a;
+    mla::TcArgs a;
     a.q = (const __nv_bfloat16*)q;
     a.out = (__nv_bfloat16*)out;
     a.page_table = page_table;
@@ -735,18 +756,63 @@ int launch_decode_mla_tc(const void* q, const void* latent_cache, int64_t num_ca
     a.seqlens = cache_seqlens;
     a.P = page_size;
     a.box_tok = box_tok;
-    a.scale_log2 = sm_scale * kLog2e;
-    cudaError_t e = cudaFuncSetAttribute(decode_mla_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    a.scale_log2 = sm_scale * mla::kLog2e;
+    (void)ring_slots_fused;
+    auto kern = !ia ? mla::decode_mla_tc_kernel<0> : mla::decode_mla_tc_kernel<2>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mla::kSmemBytes);
     if (e != cudaSuccess) {
         note_cuda_error(e);
         return VTX_ERR_CUDA;
     }
-    return launch(decode_mla_tc_kernel, dim3(batch_size), dim3(kThreads), (size_t)kSmemBytes, stream, a, quad_map, block_map);
+    return launch(kern, dim3(batch_size), dim3(mla::kThreads), (size_t)mla::kSmemBytes, stream, a,
+                  ia ? *ia : vtxidx::IndexerArgs{}, quad_map, block_map);
+}
+
+int launch_decode_mla_tc(const void* q, const void* latent_cache, int64_t num_cache_pages, void* out,
+                         const int32_t* page_table, int64_t page_table_stride, const int32_t* cache_seqlens,
+                         int batch_size, int page_size, float sm_scale, cudaStream_t stream) {
+    return launch_tc(q, latent_cache, num_cache_pages, out, page_table, page_table_stride, cache_seqlens, batch_size,
+                     page_size, sm_scale, nullptr, 0, stream);
+}
+
+// Page selection + decode in one launch.  VTX_ERR_UNSUPPORTED when the selection cannot run as a phase of the
+// decode kernel (more than 64 pages to select, or more candidates than its scratch holds): the caller then
+// issues the two launches.
+int launch_mla_sparse_layer_tc(const void* q, const void* summary, const void* latent_cache, int64_t num_cache_pages,
+                               void* out, const int32_t* dense_kv_indptr, const int32_t* sparse_kv_indptr,
+                               const int32_t* dense_kv_indices, int32_t* sparse_kv_indices, int32_t* sparse_page_table,
+                               int64_t page_table_stride, const int32_t* sparse_cache_seqlens, int batch_size,
+                               int page_size, int topk_val, int bos, int eos, int max_pages, float sm_scale,
+                               cudaStream_t stream) {
+    using Gm = Geom<__nv_bfloat16, mla::kDl>;
+    vtxidx::IndexerArgs ia{};
+    ia.q = q;
+    ia.centroids = summary;
+    ia.dense_indptr = dense_kv_indptr;
+    ia.sparse_indptr = sparse_kv_indptr;
+    ia.dense_indices = dense_kv_indices;
+    ia.sparse_indices = sparse_kv_indices;
+    ia.sparse_pt = sparse_page_table;
+    ia.pt_stride = page_table_stride;
+    ia.G = mla::kHeads;
+    ia.D = mla::kDl;
+    ia.K = topk_val;
+    ia.bos = bos;
+    ia.eos = eos;
+    ia.key_cap = key_capacity(max_pages);
+    ia.status = device_status_word();
+    const size_t rest = (size_t)q_stage_bytes<__nv_bfloat16, mla::kDl, 0, 1>() +
+                        (size_t)ia.key_cap * (sizeof(KeyOf<__nv_bfloat16>::type) + sizeof(int32_t));
+    const size_t slot = (size_t)kWarps * Gm::slot_bytes;
+    const int slots = 2;  // three were measured and lose (see ring_slots)
+    if (stream_kpl(topk_val) == 0 || slots * slot + rest > (size_t)mla::kOffWmax) return VTX_ERR_UNSUPPORTED;
+    return launch_tc(q, latent_cache, num_cache_pages, out, sparse_page_table, page_table_stride, sparse_cache_seqlens,
+                     batch_size, page_size, sm_scale, &ia, slots, stream);
 }
 
 void* mla_fault_word() {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_mla_fault) != cudaSuccess) return nullptr;
+    if (cudaGetSymbolAddress(&p, mla::g_mla_fault) != cudaSuccess) return nullptr;
     return p;
 }
 

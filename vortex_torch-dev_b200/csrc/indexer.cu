@@ -126,7 +126,7 @@ template <int D, int GQ>
 int launch_indexer_quest_cfg(const IndexerArgs& a, int eff_bs, cudaStream_t st) {
     using Gm = Geom<__nv_bfloat16, D>;
     constexpr int slot_b = 2 * Gm::slot_bytes;
-    constexpr int slots = slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    constexpr int slots = ring_slots(slot_b);
     const size_t bytes = (size_t)kWarps * slots * slot_b + (size_t)GQ * D * 2 +
                          (size_t)a.key_cap * (sizeof(uint32_t) + sizeof(int32_t));
     if (bytes > 227 * 1024) return VTX_ERR_UNSUPPORTED;

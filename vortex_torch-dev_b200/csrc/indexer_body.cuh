@@ -84,6 +84,15 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxCandidates = 16384;
 constexpr int kRowsPerSlot = 16;
 
+// Barrier of the kThreads threads that run an indexer body.  BAR == 0: they are the whole CTA.  BAR > 0: they
+// are the first kThreads threads of a larger CTA (the body runs as a phase of another kernel) and meet at named
+// barrier BAR, which nothing else of that kernel may use during the phase.
+template <int BAR>
+__device__ __forceinline__ void body_sync() {
+    if constexpr (BAR == 0) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(kThreads) : "memory");
+}
+
 // ---- sortable keys: high bits order the score, low bits make lower positions win ties ----
 template <typename T>
 struct KeyOf;
@@ -327,6 +336,11 @@ __device__ __forceinline__ float exp_canonical(float x) {
     return __fmul_rn(p, __int_as_float(((int)k + 127) << 23));
 }
 
+// Slots of a warp's gather ring: three where four CTAs per SM still fit (ring <= 96 KB), else two.  (Three slots
+// for the wide rows of the MLA latent, where one CTA per SM is all that fits anyway, were measured: the scan is
+// no faster and the decode that follows is slower.)
+constexpr int ring_slots(int slot_b) { return slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2; }
+
 template <typename T, int D>
 struct Geom {
     static constexpr int nchunk = D / 8;  // canonical chunks of 8 dims
@@ -335,7 +349,7 @@ struct Geom {
     static constexpr int pieces = row_bytes / 16;        // 16-byte pieces per row
     static constexpr int ppc = 8 * (int)sizeof(T) / 16;  // pieces per canonical chunk (1 bf16, 2 fp32)
     static constexpr int slot_bytes = kRowsPerSlot * row_bytes;
-    static constexpr int slots = slot_bytes * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    static constexpr int slots = ring_slots(slot_bytes);
     static constexpr size_t ring_bytes = (size_t)kWarps * slots * slot_bytes;
     static_assert(pieces % 8 == 0, "row must be a multiple of 128 bytes");
     static_assert(nchunk % 2 == 0, "two threads share a row by parity of the partial sums");
@@ -530,7 +544,9 @@ __host__ __device__ inline int stream_kpl(int K) { return K <= 32 ? 1 : (K <= 64
 // Shared-memory bytes of the query staging area.
 template <typename T, int D, int MODE, int GQ>
 constexpr int q_stage_bytes() {
-    return MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : kWarps * D * (int)sizeof(T));
+    // MODE 0 / 1: one copy of the query mean per warp; rows of 1 KB and more (one CTA per SM, every byte of
+    // shared memory wanted by the ring) share a single copy
+    return MODE == 2 ? GQ * D * 4 : (MODE == 3 ? GQ * D * 2 : (D * (int)sizeof(T) >= 1024 ? 1 : kWarps) * D * (int)sizeof(T));
 }
 
 // The gather-and-score loop of one warp.  KPL > 0: the warp's best 32 * KPL keys stay in `run` (registers);
@@ -634,7 +650,7 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
 // per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
 // Returns true when this CTA leaves with the segment's page list complete (it is the only CTA of the
 // segment, or the last of its chunks to arrive), false when it has nothing more to do for the segment.
-template <typename T, int D, int MODE, typename HooksRef = NoHooks, int GQ = 1>
+template <typename T, int D, int MODE, typename HooksRef = NoHooks, int GQ = 1, int BAR = 0, int SLOTS_FORCE = 0>
 __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s, const int j,
                                              HooksRef hooks = HooksRef()) {
     using Hooks = typename std::remove_reference<HooksRef>::type;
@@ -644,7 +660,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     using Key = typename KeyOf<T>::type;
     using Gm = Geom<T, D>;
     constexpr int SLOT_B = NSRC * Gm::slot_bytes;
-    constexpr int SLOTS = SLOT_B * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    constexpr int SLOTS = SLOTS_FORCE ? SLOTS_FORCE : ring_slots(SLOT_B);
     constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
     // layout: [ring][query staging][keys][ids]
     unsigned char* ring = smem_raw;
@@ -690,7 +706,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         for (int i = threadIdx.x; i < cnt; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
-    __syncthreads();  // row ids are staged
+    body_sync<BAR>();  // row ids are staged
 
     unsigned char* my_ring = ring + (size_t)warp * SLOTS * SLOT_B;
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
@@ -727,7 +743,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     hooks.wait();
     // Grouped-query mean.  Small groups: every warp computes it for itself (no block barrier between the wait
     // and the first score).  Large groups (many heads or a long latent): the CTA computes it once.
-    const bool shared_q = MODE < 2 && a.G * Gm::nchunk > 4 * 32;
+    const bool shared_q = MODE < 2 && (a.G * Gm::nchunk > 4 * 32 || Gm::row_bytes >= 1024);
     T* my_q = qbar + ((MODE < 2 && !shared_q) ? warp * D : 0);
     if constexpr (MODE < 2) {
         // one canonical chunk per thread and pass; all loads of a pass are issued before anything is stored
@@ -765,7 +781,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         if (hooks.needs_spare(warp)) cp_async_wait<0>();  // the copies of issue_extra have landed (this lane's part)
         __syncwarp();                                      // ... every lane's part; the warp's query mean is staged
         hooks.finish(warp, lane, hr, spare);
-        if (shared_q) __syncthreads();                     // the CTA's query mean is staged
+        if (shared_q) body_sync<BAR>();                    // the CTA's query mean is staged
         else __syncwarp();                                 // the spare slot may be refilled from here on
     } else {
         const typename Hooks::Regs hr = hooks.load(warp, lane);
@@ -870,7 +886,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
             const int n = 32 * kpl;
             if (kpl == 1) keys[warp * n + lane] = run1[0];
             else { keys[warp * n + lane * 2] = run2[0]; keys[warp * n + lane * 2 + 1] = run2[1]; }
-            __syncthreads();  // lists are visible, every ring is idle
+            body_sync<BAR>();  // lists are visible, every ring is idle
             if (!split) hooks.pre_sort(0);
             if (warp == 0) {
                 if (kpl == 1) {
@@ -901,6 +917,9 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         } else {
             __syncthreads();  // all keys written, every ring is idle: its space becomes the sort's scratch
         }
+        // As a phase of another kernel only the streaming form above exists (MODE 0, K <= 64, no split: the
+        // host checks); the block-wide sorts below use the CTA barrier.
+        if constexpr (BAR != 0) return true;
         int n_sort = cnt;
         bool partial = split;
         for (;;) {

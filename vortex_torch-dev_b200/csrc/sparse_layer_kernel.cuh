@@ -111,7 +111,7 @@ int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da,
     using Gm = Geom<__nv_bfloat16, D>;
     static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
     constexpr int quest_slot_b = 2 * Gm::slot_bytes;
-    constexpr int quest_slots = quest_slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2;
+    constexpr int quest_slots = ring_slots(quest_slot_b);
     size_t bytes = MODE == 2 ? Gm::ring_bytes + (size_t)G * D * 4 +
                                    (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + G * sizeof(__nv_bfloat16))
                    : MODE == 3 ? (size_t)kWarps * quest_slots * quest_slot_b + (size_t)G * D * 2 +

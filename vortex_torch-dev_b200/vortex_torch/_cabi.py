@@ -54,6 +54,7 @@ SIGNATURES = {
     "vtx_chunkwise_nh2hn": [_p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_chunkwise_hn2nh": [_p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _p],
     "vtx_decode_mla": [_p, _p, _i64, _p, _p, _i64, _p, _i, _i, _i, _i, _i, _f, _i, _p],
+    "vtx_mla_sparse_layer": [_p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _p] + [_i] * 9 + [_f, _i, _p],
     "vtx_elementwise": [_p, _p, _p, _i64, _i, _i, _f, _f, _i, _p],
     "vtx_elementwise_binary": [_p, _p, _p, _p, _i64, _i, _i, _i, _i, _i, _f, _f, _i, _p],
     "vtx_gemm_bpr": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i, _i, _p],
@@ -341,6 +342,25 @@ def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_sc
                             page_table.shape[1], ptr(cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2], int(page_size),
                             float(sm_scale), dtype_code(q.dtype), stream_of(q))
     check(rc, "vtx_decode_mla")
+
+
+def mla_sparse_layer(q, summary, latent_cache, out, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices,
+                     sparse_kv_indices, sparse_page_table, sparse_cache_seqlens, page_size, topk_val, bos, eos,
+                     max_pages_per_request, sm_scale) -> None:
+    """Page selection (as `indexer_fused` with ``sparse_page_table``) and `decode_mla` over the selected pages in
+    one launch where the tcgen05 form allows it, else as the two launches; same results either way."""
+    want(sparse_page_table, torch.int32, "sparse_page_table")
+    want(sparse_cache_seqlens, torch.int32, "sparse_cache_seqlens")
+    if not (q.dtype == summary.dtype == latent_cache.dtype == out.dtype):
+        raise TypeError("mla_sparse_layer: q, summary, latent cache and out must share a dtype")
+    _limits(q, kv=latent_cache.shape[0], summary=summary.shape[0])
+    rc = lib.vtx_mla_sparse_layer(ptr(q), ptr(summary), ptr(latent_cache), latent_cache.shape[0], ptr(out),
+                                  ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
+                                  ptr(sparse_kv_indices), ptr(sparse_page_table), sparse_page_table.shape[1],
+                                  ptr(sparse_cache_seqlens), q.shape[0], q.shape[1], q.shape[2], out.shape[2],
+                                  int(page_size), int(topk_val), int(bos), int(eos), int(max_pages_per_request),
+                                  float(sm_scale), dtype_code(q.dtype), stream_of(q))
+    check(rc, "vtx_mla_sparse_layer")
 
 
 def elementwise(x, out, packed_row_count, op: int, alpha: float, beta: float) -> None:
