@@ -260,6 +260,19 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // ---- one chunk (8 dims) of products added one by one into acc ----
 // bf16: the packed multiply rounds each exact product once to bf16, as the canonical order asks.
+// acc + (the bf16 value x widened to fp32), rounded to nearest even: the mixed-precision add of sm_100 does the
+// (exact) widening and the addition in one instruction.
+__device__ __forceinline__ float add_bf16(float acc, uint16_t x) {
+    float d;
+    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(x), "f"(acc));
+    return d;
+}
+__device__ __forceinline__ void add_pair(float& acc, uint32_t packed) {  // low half first, then the high half
+    uint16_t lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(packed));
+    acc = add_bf16(acc, lo);
+    acc = add_bf16(acc, hi);
+}
 __device__ __forceinline__ void add_products(float& acc, const __nv_bfloat16* row_chunk, const __nv_bfloat16* q_chunk) {
     const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
     const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
@@ -268,9 +281,7 @@ __device__ __forceinline__ void add_products(float& acc, const __nv_bfloat16* ro
     for (int i = 0; i < 4; ++i) {
         const __nv_bfloat162 p = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&rr[i]),
                                          *reinterpret_cast<const __nv_bfloat162*>(&qq[i]));
-        const uint32_t pw = *reinterpret_cast<const uint32_t*>(&p);
-        acc = __fadd_rn(acc, vtx::bf16lo(pw));
-        acc = __fadd_rn(acc, vtx::bf16hi(pw));
+        add_pair(acc, *reinterpret_cast<const uint32_t*>(&p));
     }
 }
 __device__ __forceinline__ void add_products(float& acc, const float* row_chunk, const float* q_chunk) {
@@ -312,9 +323,7 @@ __device__ __forceinline__ void add_quest_bounds(float& acc, const __nv_bfloat16
         const __nv_bfloat162 qv = *reinterpret_cast<const __nv_bfloat162*>(&qq[i]);
         const __nv_bfloat162 u = __hmax2(__hmul2(*reinterpret_cast<const __nv_bfloat162*>(&hh[i]), qv),
                                          __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&ll[i]), qv));
-        const uint32_t uw = *reinterpret_cast<const uint32_t*>(&u);
-        acc = __fadd_rn(acc, vtx::bf16lo(uw));
-        acc = __fadd_rn(acc, vtx::bf16hi(uw));
+        add_pair(acc, *reinterpret_cast<const uint32_t*>(&u));
     }
 }
 
@@ -701,6 +710,20 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     }
     const int lo = split ? j * a.chunk : 0;             // this CTA's candidates: [lo, lo + cnt)
     const int cnt = split ? min(a.chunk, c - lo) : c;
+    // Wide rows (1 KB and more: one CTA per SM, registers to spare, many query heads): the heads' chunks this
+    // thread will average are requested now, so that their round trip overlaps the dependent loads below
+    // (segment bounds -> row ids -> first gathers) instead of following them.
+    constexpr bool WIDE = MODE < 2 && Gm::row_bytes >= 1024 && std::is_same<Hooks, NoHooks>::value;
+    constexpr int GW = 16;
+    vtx::Vec8<T> qpre[WIDE ? GW : 1];
+    if constexpr (WIDE) {
+        if ((int)threadIdx.x < Gm::nchunk) {
+            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + threadIdx.x * 8;
+#pragma unroll
+            for (int g = 0; g < GW; ++g)
+                if (g < a.G) qpre[g].load_cached(qs + (int64_t)g * D);
+        }
+    }
     const int32_t* row_ids = a.dense_indices + beg + lo;
     if (MODE != 1) {
         for (int i = threadIdx.x; i < cnt; i += kThreads) ids[i] = row_ids[i];
@@ -757,7 +780,22 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
 #pragma unroll
             for (int jj = 0; jj < 8; ++jj) acc[jj] = 0.f;
             if (ch < Gm::nchunk) {
-                for (int g0 = 0; g0 < a.G; g0 += GMAX) {
+                int g_first = 0;
+                if constexpr (WIDE) {
+                    if (ch0 == 0) {  // this pass's first GW heads are already in registers (same order of additions)
+#pragma unroll
+                        for (int g = 0; g < GW; ++g) {
+                            if (g < a.G) {
+                                float f[8];
+                                qpre[g].unpack(f);
+#pragma unroll
+                                for (int jj = 0; jj < 8; ++jj) acc[jj] = __fadd_rn(acc[jj], f[jj]);
+                            }
+                        }
+                        g_first = GW;
+                    }
+                }
+                for (int g0 = g_first; g0 < a.G; g0 += GMAX) {
                     vtx::Vec8<T> v[GMAX];
 #pragma unroll
                     for (int g = 0; g < GMAX; ++g)
