@@ -264,7 +264,8 @@ int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_c
  *               set the flag only for a launch that follows, on the same stream, at least one launch of
  *               this library that was issued after vtx_plan_decode and that itself waits for its
  *               predecessor before it lets its successor start (every kernel of this library does, except
- *               vtx_decode_mla's tcgen05 form and a vtx_sparse_layer launch that carries this flag).
+ *               the tcgen05 form of vtx_decode_mla / vtx_mla_sparse_layer and a vtx_sparse_layer launch that
+ *               carries this flag).
  * No counterpart in the reference for workspace and flags (its Triton indexer kernels split work through
  * the planner's workload list instead, csrc/utils_sglang.cu:188-254).
  */
