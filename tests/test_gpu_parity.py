@@ -473,3 +473,32 @@ def test_mla_rejects_other_shapes():
                          torch.zeros(1, 8, 512, dtype=torch.bfloat16, device="cuda"),
                          torch.zeros(1, 4, dtype=torch.int32, device="cuda"), torch.ones(1, dtype=torch.int32, device="cuda"),
                          64, 0.1)
+
+
+def test_empty_batches_are_no_ops():
+    """bs = 0 (or no new tokens): every entry point on the path returns OK and leaves its outputs untouched.
+    (torch hands out null pointers for empty tensors and the C ABI refuses null pointers, so the Python wrappers
+    return before the call; the planner's C entry point also accepts null per-request inputs at batch size 0.)"""
+    P, H, G, D, K = 16, 2, 2, 128, 4
+    i32 = dict(dtype=torch.int32, device="cuda")
+    z = torch.zeros(8, **i32)
+    canary = torch.full((8,), 77, **i32)
+    q = torch.zeros(1, G, D, dtype=torch.bfloat16, device="cuda")[:0]
+    kv = torch.zeros(4 * H, P, D, dtype=torch.bfloat16, device="cuda")
+    cent = torch.zeros(4 * H, 1, D, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(1, G, D, dtype=torch.bfloat16, device="cuda")[:0]
+    sel = canary.clone()
+    _cabi.plan_decode(torch.zeros(1, **i32)[:0], torch.zeros(1, 64, **i32), torch.zeros(1, dtype=torch.int64, device="cuda")[:0],
+                      z, z.clone(), z.clone(), sel, z.clone(), z.clone(), z.clone(), z.clone(), z[:1].clone(), z[:1].clone(),
+                      P, H, K, 1, 1, 64, 16)
+    _cabi.indexer_fused(q, cent, z, z, z, sel, 0, K, 1, 1, 8)
+    _cabi.decode_gqa(q, kv, kv, out, z, z, z, 0, P, 0.1)
+    _cabi.sparse_layer_fused(q, cent, kv, kv, out, z, z, z, sel, z, 0, P, K, 1, 1, 8, 0.1)
+    empty_loc = torch.zeros(1, dtype=torch.int64, device="cuda")[:0]
+    nk = torch.zeros(1, H, D, dtype=torch.bfloat16, device="cuda")[:0]
+    before = kv.clone()
+    _cabi.set_kv(kv, kv.clone(), nk, nk, empty_loc, P)
+    _cabi.set_kv_cmean(kv, kv.clone(), nk, nk, cent, empty_loc, P)
+    _cabi.cmean(kv, cent, empty_loc, H, P)
+    torch.cuda.synchronize()
+    assert torch.equal(sel, canary) and torch.equal(kv, before) and _cabi.device_status() == 0

@@ -149,7 +149,9 @@ extern "C" int vtx_plan_decode(const int32_t* cached_seq_lens, const int32_t* re
                                int num_kv_heads, int topk_val, int page_reserved_bos,
                                int page_reserved_eos, int max_chunk_size, int min_chunk_size,
                                void* stream) {
-    if (!cached_seq_lens || !req_to_token || !req_indices || !dense_kv_indptr || !dense_kv_indices ||
+    // the two per-request inputs are empty (and may be null) for an empty batch
+    if (batch_size != 0 && (!cached_seq_lens || !req_indices)) return VTX_ERR_INVALID_ARGUMENT;
+    if (!req_to_token || !dense_kv_indptr || !dense_kv_indices ||
         !sparse_kv_indptr || !sparse_kv_indices || !winfo_q_indices ||
         !winfo_kv_offsets || !winfo_kv_lens || !winfo_num_workloads || !winfo_chunk_size)
         return VTX_ERR_INVALID_ARGUMENT;

@@ -228,6 +228,8 @@ def plan_decode(cached_seq_lens, req_to_token, req_indices, dense_kv_indptr, den
                 winfo_kv_lens, winfo_num_workloads, winfo_chunk_size, page_size, num_kv_heads, topk_val,
                 bos, eos, max_chunk_size, min_chunk_size, dense_page_table=None, dense_cache_seqlens=None,
                 sparse_page_table=None, sparse_cache_seqlens=None) -> None:
+    if cached_seq_lens.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(cached_seq_lens, torch.int32, "cached_seq_lens")
     want(req_to_token, torch.int32, "req_to_token")
     want(req_indices, torch.int64, "req_indices")
@@ -260,6 +262,8 @@ def plan_decode(cached_seq_lens, req_to_token, req_indices, dense_kv_indptr, den
 
 
 def set_kv(k_cache, v_cache, new_k, new_v, loc, page_size) -> None:
+    if new_k.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(loc, torch.int64, "loc")
     nnz, H, D = new_k.shape
     _limits(k_cache, kv=k_cache.shape[0], loc=_slots(k_cache, H, page_size))
@@ -269,6 +273,8 @@ def set_kv(k_cache, v_cache, new_k, new_v, loc, page_size) -> None:
 
 
 def cmean(x, out, loc, num_kv_heads, page_size) -> None:
+    if loc.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(loc, torch.int64, "loc")
     if out.dtype != x.dtype:
         raise TypeError("cmean: x and out must share a dtype")
@@ -279,6 +285,8 @@ def cmean(x, out, loc, num_kv_heads, page_size) -> None:
 
 
 def set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, page_size) -> None:
+    if new_k.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(loc, torch.int64, "loc")
     nnz, H, D = new_k.shape
     if not (k_cache.dtype == v_cache.dtype == new_k.dtype == new_v.dtype == centroids.dtype):
@@ -290,6 +298,8 @@ def set_kv_cmean(k_cache, v_cache, new_k, new_v, centroids, loc, page_size) -> N
 
 
 def gemv(q_mean, centroids, scores, dense_kv_indptr, dense_kv_indices, eff_bs, topk_val, bos, eos) -> None:
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if not (q_mean.dtype == centroids.dtype == scores.dtype):
         raise TypeError("gemv: q_mean, centroids and scores must share a dtype")
     _limits(q_mean, summary=centroids.shape[0])
@@ -301,6 +311,8 @@ def gemv(q_mean, centroids, scores, dense_kv_indptr, dense_kv_indices, eff_bs, t
 
 def topk(scores, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices, eff_bs, topk_val,
          bos, eos, max_pages_per_request) -> None:
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(sparse_kv_indices, torch.int32, "sparse_kv_indices")
     rc = lib.vtx_topk(ptr(scores), ptr(dense_kv_indptr), ptr(sparse_kv_indptr), ptr(dense_kv_indices),
                       ptr(sparse_kv_indices), int(eff_bs), int(topk_val), int(bos), int(eos),
@@ -310,6 +322,8 @@ def topk(scores, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_
 
 def indexer_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, dense_kv_indices, sparse_kv_indices,
                   eff_bs, topk_val, bos, eos, max_pages_per_request, sparse_page_table=None) -> None:
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if q.dtype != centroids.dtype:
         raise TypeError("indexer_fused: q and centroids must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
@@ -323,6 +337,8 @@ def indexer_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, dense_kv_indi
 
 def decode_gqa(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len, eff_bs, page_size,
                sm_scale) -> None:
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("decode_gqa: q, caches and out must share a dtype")
     _limits(q, kv=min(k_cache.shape[0], v_cache.shape[0]))
@@ -334,6 +350,8 @@ def decode_gqa(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_page_len
 
 def decode_mla(q, latent_cache, out, page_table, cache_seqlens, page_size, sm_scale) -> None:
     """q [bs, heads, latent_dim], latent_cache [rows, P, latent_dim], out [bs, heads, value_dim]."""
+    if q.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(page_table, torch.int32, "page_table")
     want(cache_seqlens, torch.int32, "cache_seqlens")
     if not (q.dtype == latent_cache.dtype == out.dtype):
@@ -349,6 +367,8 @@ def mla_sparse_layer(q, summary, latent_cache, out, dense_kv_indptr, sparse_kv_i
                      max_pages_per_request, sm_scale) -> None:
     """Page selection (as `indexer_fused` with ``sparse_page_table``) and `decode_mla` over the selected pages in
     one launch where the tcgen05 form allows it, else as the two launches; same results either way."""
+    if q.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(sparse_page_table, torch.int32, "sparse_page_table")
     want(sparse_cache_seqlens, torch.int32, "sparse_cache_seqlens")
     if not (q.dtype == summary.dtype == latent_cache.dtype == out.dtype):
@@ -412,6 +432,8 @@ def sparse_layer_fused(q, centroids, k_cache, v_cache, out, dense_kv_indptr, spa
     token write then maintains).  ``workspace``: zero-initialised device scratch of
     ``sparse_layer_workspace_bytes(...)`` bytes that lets long segments be scanned by several CTAs.
     ``early_prologue``: see ``VTX_LAYER_EARLY_PROLOGUE`` in the header."""
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if not (q.dtype == centroids.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("sparse_layer_fused: q, centroids, caches and out must share a dtype")
     H = 0
@@ -448,6 +470,8 @@ def decode_gqa_splitkv(q, k_cache, v_cache, out, kv_indptr, kv_indices, kv_last_
                        sm_scale, num_splits, workspace) -> None:
     """Split-KV form of `decode_gqa`; ``workspace`` is a device tensor of at least
     ``splitkv_workspace_bytes(...)`` bytes that the call overwrites."""
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if not (q.dtype == k_cache.dtype == v_cache.dtype == out.dtype):
         raise TypeError("decode_gqa_splitkv: q, caches and out must share a dtype")
     _limits(q, kv=min(k_cache.shape[0], v_cache.shape[0]))
@@ -462,6 +486,8 @@ def indexer_gqa_softmax_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, d
                               eff_bs, topk_val, bos, eos, max_pages_per_request, softmax_scale,
                               sparse_page_table=None) -> None:
     """GeMM -> Softmax(scale) over pages -> Max over heads -> topK of the gqa_block_sparse_attention flow."""
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if q.dtype != centroids.dtype:
         raise TypeError("indexer_gqa_softmax_fused: q and centroids must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
@@ -476,6 +502,8 @@ def indexer_gqa_softmax_fused(q, centroids, dense_kv_indptr, sparse_kv_indptr, d
 
 def creduce(x, out, loc, num_kv_heads, page_size, op: int) -> None:
     """Page-completion reduction over rows: op 0 mean, 1 max, 2 min."""
+    if loc.shape[0] == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     want(loc, torch.int64, "loc")
     if out.dtype != x.dtype:
         raise TypeError("creduce: x and out must share a dtype")
@@ -489,6 +517,8 @@ def indexer_quest_fused(q, cache_max, cache_min, dense_kv_indptr, sparse_kv_indp
                         sparse_kv_indices, eff_bs, topk_val, bos, eos, max_pages_per_request,
                         sparse_page_table=None) -> None:
     """Multiply x2 -> Maximum -> Sum(dim=2) -> Max(dim=1) -> topK of the gqa_quest_sparse_attention flow."""
+    if int(eff_bs) == 0:  # an empty batch: nothing to do (torch hands out null pointers for empty tensors)
+        return
     if not (q.dtype == cache_max.dtype == cache_min.dtype):
         raise TypeError("indexer_quest_fused: q and the two caches must share a dtype")
     stride = 0 if sparse_page_table is None else sparse_page_table.shape[1]
