@@ -273,6 +273,15 @@ __device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((
 // fault codes (bits of g_mla_fault): which kind of barrier a wait gave up on
 enum : unsigned { kFaultEmpty = 1, kFaultFull = 2, kFaultS = 4, kFaultP = 8, kFaultO = 16, kFaultFixed = 32, kFaultQ = 64, kFaultDrain = 128 };
 
+// Shared memory of one instance of the indexer body in the fused form: ring (two slots per warp), query mean,
+// keys and row ids of its candidates; rounded up so that the next instance starts 128-byte aligned.
+__host__ __device__ inline size_t fused_instance_bytes(int key_cap) {
+    using Gm = Geom<__nv_bfloat16, kDl, 4>;  // four lanes per row, 8-row batches
+    const size_t n = (size_t)4 * 2 * Gm::slot_bytes + (size_t)q_stage_bytes<__nv_bfloat16, kDl, 0, 1>() +
+                     (size_t)key_cap * (sizeof(KeyOf<__nv_bfloat16>::type) + sizeof(int32_t));
+    return (n + 127) & ~(size_t)127;
+}
+
 // FUSED: the request's page selection (query mean over the heads, scores of its candidate pages' summary rows,
 // top-K; the body of the stand-alone indexer kernel) runs first, on warps 0-3 with the tile ring as its scratch,
 // and writes the page-table row the decode then walks.  One launch instead of two, and none of the second
@@ -317,10 +326,54 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     vtx::pdl_wait();
     if constexpr (FUSED != 0) {
         // The ring and the q / P areas are idle until the first copy is issued below; barriers, the TMEM slot and
-        // the abort flag live behind them (kOffBars) and stay untouched: the host checked that the body's
-        // shared memory ends before kOffWmax.
-        if (warp < 4)
-            indexer_body<__nv_bfloat16, kDl, 0, NoHooks, 1, /*BAR=*/2, /*SLOTS=*/FUSED>(ia, gbase + kOffQuads, b, 0);
+        // the abort flag live behind them (kOffBars) and stay untouched: the host checked that everything used
+        // here ends before kOffWmax.  Two instances of the indexer body, warps 0-3 on the first half of the
+        // request's candidate pages and warps 4-7 on the second, each with its own ring, query mean and named
+        // barrier; each leaves the K best keys of its half in `part`, and warp 0 orders the union.
+        using Key = KeyOf<__nv_bfloat16>::type;
+        const int inst = warp >> 2;
+        const size_t inst_bytes = fused_instance_bytes(ia.key_cap);
+        unsigned char* scratch = gbase + kOffQuads + (size_t)inst * inst_bytes;
+        Key* part = reinterpret_cast<Key*>(gbase + kOffQuads + 2 * inst_bytes);
+        IndexerArgs mine = ia;
+        mine.part_keys = part;
+        indexer_body<__nv_bfloat16, kDl, 0, NoHooks, 1, /*BAR=*/2, /*SLOTS=*/2, /*LPR=*/4>(mine, scratch, b, inst);  // barriers 2, 3
+        __syncthreads();  // both halves' keys are in `part` (or the whole list was written: nothing to select)
+        const int beg = ia.dense_indptr[b] + ia.bos;
+        const int c = ia.dense_indptr[b + 1] - ia.eos - beg;
+        const int half = (c + 1) / 2;
+        if (warp == 0 && c > ia.K && half <= ia.key_cap) {  // else: nothing to select, or the body's overflow path ran
+            // 2 K keys (K <= 64) as 2 or 4 per lane; a full sort; the first K name the selected candidates
+            EmitSelection<__nv_bfloat16> emit;
+            emit.to_scratch = false;
+            emit.part = nullptr;
+            emit.ids = ia.dense_indices + beg;  // keys name candidates by their position in the segment
+            emit.out = ia.sparse_indices + ia.sparse_indptr[b] + ia.bos;
+            emit.out_pt = ia.sparse_pt ? ia.sparse_pt + (int64_t)b * ia.pt_stride + ia.bos : nullptr;
+            if (ia.K <= 32) {
+                Key u[2];
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int e = lane * 2 + r, h = e >> 5, k = e & 31;  // 32 places per half, K of them filled
+                    u[r] = k < ia.K ? part[h * ia.K + k] : (Key)0;
+                }
+                warp_bitonic_desc<Key, 2>(u, lane, 2);
+#pragma unroll
+                for (int r = 0; r < 2; ++r)
+                    if (lane * 2 + r < ia.K) emit(lane * 2 + r, u[r]);
+            } else {
+                Key u[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int e = lane * 4 + r, h = e >> 6, k = e & 63;
+                    u[r] = k < ia.K ? part[h * ia.K + k] : (Key)0;
+                }
+                warp_bitonic_desc<Key, 4>(u, lane, 2);
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+                    if (lane * 4 + r < ia.K) emit(lane * 4 + r, u[r]);
+            }
+        }
         __syncthreads();  // the page-table row of this request is complete and visible to the CTA
     }
     const int ntok = a.seqlens[b];
@@ -784,7 +837,6 @@ int launch_mla_sparse_layer_tc(const void* q, const void* summary, const void* l
                                int64_t page_table_stride, const int32_t* sparse_cache_seqlens, int batch_size,
                                int page_size, int topk_val, int bos, int eos, int max_pages, float sm_scale,
                                cudaStream_t stream) {
-    using Gm = Geom<__nv_bfloat16, mla::kDl>;
     vtxidx::IndexerArgs ia{};
     ia.q = q;
     ia.centroids = summary;
@@ -801,11 +853,13 @@ int launch_mla_sparse_layer_tc(const void* q, const void* summary, const void* l
     ia.eos = eos;
     ia.key_cap = key_capacity(max_pages);
     ia.status = device_status_word();
-    const size_t rest = (size_t)q_stage_bytes<__nv_bfloat16, mla::kDl, 0, 1>() +
-                        (size_t)ia.key_cap * (sizeof(KeyOf<__nv_bfloat16>::type) + sizeof(int32_t));
-    const size_t slot = (size_t)kWarps * Gm::slot_bytes;
-    const int slots = 2;  // three were measured and lose (see ring_slots)
-    if (stream_kpl(topk_val) == 0 || slots * slot + rest > (size_t)mla::kOffWmax) return VTX_ERR_UNSUPPORTED;
+    // every request's candidates are scanned in two halves by two instances of the body
+    ia.chunk = -2;
+    ia.nch_max = 2;
+    ia.key_cap = key_capacity((max_pages + 1) / 2);  // keys and row ids of one half
+    const int slots = 2;
+    const size_t need = 2 * mla::fused_instance_bytes(ia.key_cap) + 2 * (size_t)topk_val * sizeof(KeyOf<__nv_bfloat16>::type);
+    if (stream_kpl(topk_val) == 0 || need > (size_t)mla::kOffWmax) return VTX_ERR_UNSUPPORTED;
     return launch_tc(q, latent_cache, num_cache_pages, out, sparse_page_table, page_table_stride, sparse_cache_seqlens,
                      batch_size, page_size, sm_scale, &ia, slots, stream);
 }

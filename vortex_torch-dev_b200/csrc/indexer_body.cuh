@@ -85,12 +85,13 @@ constexpr int kMaxCandidates = 16384;
 constexpr int kRowsPerSlot = 16;
 
 // Barrier of the kThreads threads that run an indexer body.  BAR == 0: they are the whole CTA.  BAR > 0: they
-// are the first kThreads threads of a larger CTA (the body runs as a phase of another kernel) and meet at named
-// barrier BAR, which nothing else of that kernel may use during the phase.
+// are one group of kThreads consecutive threads of a larger CTA (the body runs as a phase of another kernel, one
+// instance per group, all from the same call site) and group g meets at named barrier BAR + g, which nothing
+// else of that kernel may use during the phase.
 template <int BAR>
 __device__ __forceinline__ void body_sync() {
     if constexpr (BAR == 0) __syncthreads();
-    else asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(kThreads) : "memory");
+    else asm volatile("bar.sync %0, %1;" ::"r"(BAR + (int)(threadIdx.x / kThreads)), "n"(kThreads) : "memory");
 }
 
 // ---- sortable keys: high bits order the score, low bits make lower positions win ties ----
@@ -350,18 +351,23 @@ __device__ __forceinline__ float exp_canonical(float x) {
 // no faster and the decode that follows is slower.)
 constexpr int ring_slots(int slot_b) { return slot_b * 3 * kWarps <= 96 * 1024 ? 3 : 2; }
 
-template <typename T, int D>
+template <typename T, int D, int LPR = 2>
 struct Geom {
     static constexpr int nchunk = D / 8;  // canonical chunks of 8 dims
     static constexpr int L = nchunk > 16 ? 32 : (nchunk > 8 ? 16 : (nchunk > 4 ? 8 : 4));
     static constexpr int row_bytes = D * (int)sizeof(T);
     static constexpr int pieces = row_bytes / 16;        // 16-byte pieces per row
     static constexpr int ppc = 8 * (int)sizeof(T) / 16;  // pieces per canonical chunk (1 bf16, 2 fp32)
-    static constexpr int slot_bytes = kRowsPerSlot * row_bytes;
+    // lanes that share a row while it is scored: two; four (half the rows per batch, half the slot) where two
+    // bodies have to fit side by side in one CTA's shared memory.  More, smaller batches cost a stand-alone scan
+    // of wide rows 2 us, so four is the choice of that one caller, not the rule.
+    static constexpr int lpr = LPR;
+    static constexpr int rows_per_slot = 32 / lpr;
+    static constexpr int slot_bytes = rows_per_slot * row_bytes;
     static constexpr int slots = ring_slots(slot_bytes);
     static constexpr size_t ring_bytes = (size_t)kWarps * slots * slot_bytes;
     static_assert(pieces % 8 == 0, "row must be a multiple of 128 bytes");
-    static_assert(nchunk % 2 == 0, "two threads share a row by parity of the partial sums");
+    static_assert(nchunk % lpr == 0 && L % lpr == 0, "the lanes of a row split its partial sums evenly");
     // the idle ring doubles as the sort's exchange buffer (2 x 2048 keys at most)
     static_assert(ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
 };
@@ -560,18 +566,19 @@ constexpr int q_stage_bytes() {
 
 // The gather-and-score loop of one warp.  KPL > 0: the warp's best 32 * KPL keys stay in `run` (registers);
 // KPL == 0: every key goes to keys[] in shared memory (MODE 0, 3) or every score to sbuf / global (MODE 2, 1).
-template <typename T, int D, int MODE, int GQ, int KPL, int SLOTS, int SLOT_B, typename Issue>
+template <typename T, int D, int MODE, int GQ, int KPL, int SLOTS, int SLOT_B, int LPRX, typename Issue>
 __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, const int my_batches, const int warp,
                                            const int lane, const unsigned char* my_ring, const T* qv, const float* qf32,
                                            typename KeyOf<T>::type* keys, __nv_bfloat16* sbuf, const int beg,
                                            const int lo, const int cnt,
                                            typename KeyOf<T>::type (&run)[KPL > 0 ? KPL : 1]) {
     using Key = typename KeyOf<T>::type;
-    using Gm = Geom<T, D>;
+    using Gm = Geom<T, D, LPRX>;
     constexpr int NQ = MODE >= 2 ? GQ : 1;
-    constexpr int L = Gm::L, HALF = L / 2;
+    constexpr int LPR = Gm::lpr;               // lanes per row
+    constexpr int L = Gm::L, HALF = L / LPR;   // partial sums of a row; those this thread owns
     constexpr int KP = KPL > 0 ? KPL : 1;
-    const int r_in = lane >> 1, par = lane & 1;  // row of the slot; parity of the partial sums this thread owns
+    const int r_in = lane / LPR, par = lane % LPR;  // row of the slot; residue of the partial sums this thread owns
     Key pend[KP];
 #pragma unroll
     for (int r = 0; r < KP; ++r) pend[r] = (Key)0;
@@ -583,7 +590,7 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
         cp_async_commit();
         const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
         const int sw = (r_in & 3) << 1;
-        const int i = (warp + ord * kWarps) * kRowsPerSlot + r_in;  // position inside this CTA's chunk
+        const int i = (warp + ord * kWarps) * Gm::rows_per_slot + r_in;  // position inside this CTA's chunk
         float best = -INFINITY;  // MODE 3: running maximum over the heads
         float row_score = 0.f;
 #pragma unroll
@@ -591,13 +598,13 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
             float acc[HALF];
 #pragma unroll
             for (int ii = 0; ii < HALF; ++ii) acc[ii] = 0.f;
-            // this thread owns partial sums 2*ii + par; partial l takes chunks l, l + L, ...
+            // this thread owns partial sums LPR*ii + par; partial l takes chunks l, l + L, ...
 #pragma unroll
             for (int k = 0; k * L < Gm::nchunk; ++k) {
 #pragma unroll
                 for (int ii = 0; ii < HALF; ++ii) {
-                    if (k * L + 2 * ii < Gm::nchunk) {  // nchunk is even, so the test holds for both parities
-                        const int ch = k * L + 2 * ii + par;
+                    if (k * L + LPR * ii < Gm::nchunk) {  // nchunk is a multiple of LPR: the test holds for every residue
+                        const int ch = k * L + LPR * ii + par;
                         // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
                         const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
                         if constexpr (MODE == 3)
@@ -617,7 +624,10 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
             for (int w = HALF / 2; w > 0; w >>= 1)
 #pragma unroll
                 for (int ii = 0; ii < w; ++ii) acc[ii] = __fadd_rn(acc[ii], acc[ii + w]);
-            const float total = __fadd_rn(acc[0], __shfl_xor_sync(0xffffffffu, acc[0], 1));
+            // the last folds (widths LPR/2 .. 1) cross the lanes of the row: v[i] += v[i + w] for i < w
+            float total = acc[0];
+#pragma unroll
+            for (int w = LPR / 2; w > 0; w >>= 1) total = __fadd_rn(total, __shfl_xor_sync(0xffffffffu, total, w));
             const float sc = vtx::round_to<T>(total);
             if (MODE == 3) best = fmaxf(best, sc);
             else row_score = sc;
@@ -631,14 +641,15 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
             if (KPL == 0) {
                 if (par == 0 && i < cnt) keys[i] = key;
             } else {
-                // two batches fill one 32-key row of pend: even batches in the even lanes, odd batches moved
-                // to the odd lanes
-                const Key moved = __shfl_up_sync(0xffffffffu, key, 1);
-                const Key mine = (filled & 1) ? (par ? moved : (Key)0) : key;
+                // LPR batches fill one 32-key row of pend: batch f of the row moves its keys (held by the lanes
+                // of residue 0) to the lanes of residue f
+                const int f = filled % LPR;
+                const Key moved = __shfl_up_sync(0xffffffffu, key, f);
+                const Key mine = par == f ? moved : (Key)0;
 #pragma unroll
                 for (int r = 0; r < KP; ++r)
-                    if (r == (filled >> 1)) pend[r] = pend[r] | mine;  // disjoint lanes: OR keeps both batches
-                if (++filled == 2 * KP) {
+                    if (r == filled / LPR) pend[r] = pend[r] | mine;  // disjoint lanes: OR keeps all batches
+                if (++filled == LPR * KP) {
                     warp_topk_merge<Key, KP>(run, pend, lane);
 #pragma unroll
                     for (int r = 0; r < KP; ++r) pend[r] = (Key)0;
@@ -659,7 +670,8 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
 // per head sum_d max(round(q_d*max_d), round(q_d*min_d)) in the canonical order, rounded, maximum over heads.
 // Returns true when this CTA leaves with the segment's page list complete (it is the only CTA of the
 // segment, or the last of its chunks to arrive), false when it has nothing more to do for the segment.
-template <typename T, int D, int MODE, typename HooksRef = NoHooks, int GQ = 1, int BAR = 0, int SLOTS_FORCE = 0>
+template <typename T, int D, int MODE, typename HooksRef = NoHooks, int GQ = 1, int BAR = 0, int SLOTS_FORCE = 0,
+          int LPRX = 2>
 __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char* smem_raw, const int s, const int j,
                                              HooksRef hooks = HooksRef()) {
     using Hooks = typename std::remove_reference<HooksRef>::type;
@@ -667,7 +679,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     constexpr int NSRC = MODE == 3 ? 2 : 1;                         // summary rows gathered per page
     constexpr int QBYTES = q_stage_bytes<T, D, MODE, GQ>();
     using Key = typename KeyOf<T>::type;
-    using Gm = Geom<T, D>;
+    using Gm = Geom<T, D, LPRX>;
     constexpr int SLOT_B = NSRC * Gm::slot_bytes;
     constexpr int SLOTS = SLOTS_FORCE ? SLOTS_FORCE : ring_slots(SLOT_B);
     constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
@@ -679,14 +691,18 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     __nv_bfloat16* sbuf = reinterpret_cast<__nv_bfloat16*>(ids + a.key_cap);  // MODE 2: [candidate][head] scores
     float* qf32 = reinterpret_cast<float*>(qbar);                               // MODE 2: [head][D]
     __shared__ int s_last_arrival;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // as a phase of a larger CTA (BAR > 0) the body's threads are numbered within their group of kThreads
+    const int tix = BAR == 0 ? (int)threadIdx.x : (int)(threadIdx.x & (kThreads - 1));
+    const int warp = tix >> 5, lane = tix & 31;
 
     const int beg = a.dense_indptr[s] + a.bos;
     const int c = a.dense_indptr[s + 1] - a.eos - beg;  // candidates of the whole segment
-    const bool split = MODE != 2 && a.chunk > 0 && c > a.chunk;
-    const int nch = split ? (c + a.chunk - 1) / a.chunk : 1;
+    // a.chunk > 0: chunks of that many candidates; a.chunk < 0: -a.chunk chunks of equal length per segment
+    const int chunk_len = a.chunk >= 0 ? a.chunk : (c + (-a.chunk) - 1) / (-a.chunk);
+    const bool split = MODE != 2 && chunk_len > 0 && c > chunk_len;
+    const int nch = split ? (c + chunk_len - 1) / chunk_len : 1;
     if (j >= nch) return false;
-    const bool overflow = split ? nch > a.nch_max : (MODE != 1 && c > a.key_cap);
+    const bool overflow = split ? (nch > a.nch_max || chunk_len > a.key_cap) : (MODE != 1 && c > a.key_cap);
     if (c <= a.K || overflow) {
         // Nothing to select (the block-table builder already wrote the whole list), or more candidates than
         // the caller's max_num_pages_per_request promised (shared memory or the grid cannot hold them: flag it
@@ -696,10 +712,10 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         const typename Hooks::Regs hr = hooks.load(warp, lane);
         hooks.finish(warp, lane, hr, nullptr);
         if (c > a.K) {
-            if (threadIdx.x == 0 && a.status) atomicOr(a.status, (uint32_t)VTX_STATUS_CANDIDATE_OVERFLOW);
+            if (tix == 0 && a.status) atomicOr(a.status, (uint32_t)VTX_STATUS_CANDIDATE_OVERFLOW);
             if (MODE != 1) {
                 const int o0 = a.sparse_indptr[s] + a.bos;
-                for (int e = threadIdx.x; e < a.K; e += kThreads) {
+                for (int e = tix; e < a.K; e += kThreads) {
                     const int32_t row = a.dense_indices[beg + e];
                     a.sparse_indices[o0 + e] = row;
                     if (a.sparse_pt) a.sparse_pt[(int64_t)s * a.pt_stride + a.bos + e] = row;
@@ -708,8 +724,8 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         }
         return true;
     }
-    const int lo = split ? j * a.chunk : 0;             // this CTA's candidates: [lo, lo + cnt)
-    const int cnt = split ? min(a.chunk, c - lo) : c;
+    const int lo = split ? j * chunk_len : 0;           // this CTA's candidates: [lo, lo + cnt)
+    const int cnt = split ? min(chunk_len, c - lo) : c;
     // Wide rows (1 KB and more: one CTA per SM, registers to spare, many query heads): the heads' chunks this
     // thread will average are requested now, so that their round trip overlaps the dependent loads below
     // (segment bounds -> row ids -> first gathers) instead of following them.
@@ -717,8 +733,8 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     constexpr int GW = 16;
     vtx::Vec8<T> qpre[WIDE ? GW : 1];
     if constexpr (WIDE) {
-        if ((int)threadIdx.x < Gm::nchunk) {
-            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + threadIdx.x * 8;
+        if (tix < Gm::nchunk) {
+            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + tix * 8;
 #pragma unroll
             for (int g = 0; g < GW; ++g)
                 if (g < a.G) qpre[g].load_cached(qs + (int64_t)g * D);
@@ -726,7 +742,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     }
     const int32_t* row_ids = a.dense_indices + beg + lo;
     if (MODE != 1) {
-        for (int i = threadIdx.x; i < cnt; i += kThreads) ids[i] = row_ids[i];
+        for (int i = tix; i < cnt; i += kThreads) ids[i] = row_ids[i];
         row_ids = ids;
     }
     body_sync<BAR>();  // row ids are staged
@@ -735,12 +751,12 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
     const unsigned char* cent = reinterpret_cast<const unsigned char*>(a.centroids);
     const unsigned char* cent2 = reinterpret_cast<const unsigned char*>(a.centroids2);
-    const int n_batches = (cnt + kRowsPerSlot - 1) / kRowsPerSlot;
+    const int n_batches = (cnt + Gm::rows_per_slot - 1) / Gm::rows_per_slot;
     const int my_batches = n_batches > warp ? (n_batches - warp + kWarps - 1) / kWarps : 0;
-    constexpr int pieces_per_slot = kRowsPerSlot * Gm::pieces;
+    constexpr int pieces_per_slot = Gm::rows_per_slot * Gm::pieces;
 
     auto issue = [&](int ord) {
-        const int row0 = (warp + ord * kWarps) * kRowsPerSlot;
+        const int row0 = (warp + ord * kWarps) * Gm::rows_per_slot;
         const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * SLOT_B);
 #pragma unroll
         for (int pc = lane; pc < pieces_per_slot; pc += 32) {
@@ -772,7 +788,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         // one canonical chunk per thread and pass; all loads of a pass are issued before anything is stored
         const typename Hooks::Regs hr = hooks.load(warp, lane);
         constexpr int GMAX = 8;
-        const int tid = shared_q ? (int)threadIdx.x : lane, nthr = shared_q ? kThreads : 32;
+        const int tid = shared_q ? tix : lane, nthr = shared_q ? kThreads : 32;
         for (int ch0 = 0; ch0 < Gm::nchunk; ch0 += nthr) {
             const int ch = ch0 + tid;
             const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * a.G * D + ch * 8;
@@ -846,13 +862,13 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     const int kpl = (MODE == 0 || MODE == 3) ? stream_kpl(a.K) : 0;
     Key run1[1] = {(Key)0}, run2[2] = {(Key)0, (Key)0};
     if (kpl == 1)
-        score_rows<T, D, MODE, GQ, 1, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+        score_rows<T, D, MODE, GQ, 1, SLOTS, SLOT_B, LPRX>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
                                                      cnt, run1);
     else if (kpl == 2)
-        score_rows<T, D, MODE, GQ, 2, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+        score_rows<T, D, MODE, GQ, 2, SLOTS, SLOT_B, LPRX>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
                                                      cnt, run2);
     else
-        score_rows<T, D, MODE, GQ, 0, SLOTS, SLOT_B>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
+        score_rows<T, D, MODE, GQ, 0, SLOTS, SLOT_B, LPRX>(a, issue, my_batches, warp, lane, my_ring, my_q, qf32, keys, sbuf, beg, lo,
                                                      cnt, run1);
     if constexpr (MODE == 2) {
         __syncthreads();  // all head scores written; the rings are idle and lend their space to the reductions
@@ -909,7 +925,8 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     }
     if (MODE != 1) {
         const int o0 = a.sparse_indptr[s] + a.bos;
-        Key* part = reinterpret_cast<Key*>(a.part_keys) + ((size_t)s * a.nch_max) * a.K;  // this segment's chunks
+        // this segment's chunks (as a phase of a larger CTA, part_keys is that CTA's own scratch)
+        Key* part = reinterpret_cast<Key*>(a.part_keys) + (BAR != 0 ? (size_t)0 : (size_t)s * a.nch_max * a.K);
         EmitSelection<T> emit;
         emit.part = part + (size_t)j * a.K;
         emit.ids = split ? a.dense_indices + beg : ids;  // keys name candidates by their position in the segment
