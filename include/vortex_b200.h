@@ -253,8 +253,9 @@ int vtx_sparse_layer_fused(const void* q, const void* centroids, const void* k_c
  *               (flow/algorithms.py:411-451).
  *   workspace   optional caller-owned device scratch of vtx_sparse_layer_workspace_bytes(...) bytes, ZEROED
  *               ONCE by the caller after allocation (every call leaves it zeroed where that matters).  With
- *               it, a segment with more than 512 candidate pages is scanned by several CTAs whose best keys
- *               the last of them to arrive merges; selections are the same bits as without it.  Without it
+ *               it, a segment with more than 512 candidate pages (768 in batches of at most 384 segments) is
+ *               scanned by several CTAs whose best keys the last of them to arrive merges; selections are the
+ *               same bits as without it.  Without it
  *               (or for VTX_SCORE_GQA_SOFTMAX, whose softmax spans the whole segment) one CTA scans a
  *               segment.  Calls that share a workspace must not overlap on the GPU.
  *   flags       VTX_LAYER_EARLY_PROLOGUE: when programmatic launch is on, the kernel stages its row ids and

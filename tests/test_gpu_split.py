@@ -37,7 +37,8 @@ def _workspace(dp, K, bos, eos, poison=True):
 
 @pytest.mark.parametrize("seq,H,G,K", [
     ([32768, 9000, 8208, 1024, 600, 17], 8, 4, 64),   # ragged batch incl. the longest request of config 3
-    ([8192 + 16 * 3, 8192], 8, 2, 30),                # just above / at one chunk of 512 candidates
+    ([16 * 771, 16 * 770], 8, 2, 30),                 # just above / at one chunk of 768 candidates (small batches)
+    ([8192 + 16 * 3, 8192] + [40] * 58, 8, 2, 30),    # 480 segments: chunks of 512; just above / at one chunk
     ([20000, 16400], 2, 8, 30),
 ])
 def test_sparse_layer_split_segments_match_oracle_and_unsplit(seq, H, G, K):

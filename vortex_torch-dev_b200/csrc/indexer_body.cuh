@@ -1030,16 +1030,18 @@ int check_common(const int32_t* dip, const int32_t* din, int eff_bs, int K, int 
 // Candidate capacity of one segment (sizes the key and row-id arrays in shared memory).
 int key_capacity(int max_pages) { return vtx::pow2_ceil(max_pages < 256 ? 256 : max_pages); }  // >= 4 warps x 64 keys
 
-// Candidates one CTA scans when a workspace allows a segment's scan to be split.
-constexpr int kChunk = 512;
+// Candidates one CTA scans when a workspace allows a segment's scan to be split: 512, or 768 for small batches
+// (fewer than ~1.5 segments per CTA slot of the GPU), where fewer, longer chunks keep the whole grid in one wave.
+// A function of the batch size alone, so that the workspace size is known before the lengths are.
+inline int chunk_rows(int eff_bs) { return eff_bs <= 384 ? 768 : 512; }
 
-int split_chunks(int max_pages, int bos, int eos) {
-    const int cand = max_pages - bos - eos;
-    return cand > kChunk ? (cand + kChunk - 1) / kChunk : 1;
+int split_chunks(int eff_bs, int max_pages, int bos, int eos) {
+    const int cand = max_pages - bos - eos, chunk = chunk_rows(eff_bs);
+    return cand > chunk ? (cand + chunk - 1) / chunk : 1;
 }
 
 int64_t split_workspace_bytes(int eff_bs, int max_pages, int K, int bos, int eos) {
-    const int nch = split_chunks(max_pages, bos, eos);
+    const int nch = split_chunks(eff_bs, max_pages, bos, eos);
     if (nch == 1) return 0;
     const int64_t tickets = ((int64_t)eff_bs * 4 + 255) / 256 * 256;
     return tickets + (int64_t)eff_bs * nch * K * 8;  // keys are at most 8 bytes
@@ -1049,12 +1051,12 @@ int64_t split_workspace_bytes(int eff_bs, int max_pages, int K, int bos, int eos
 // allows it; otherwise leave the one-CTA-per-segment form.
 void plan_split(IndexerArgs& a, int eff_bs, int max_pages, void* workspace, int64_t workspace_bytes) {
     a.status = vtx::device_status_word();
-    const int nch = split_chunks(max_pages, a.bos, a.eos);
+    const int nch = split_chunks(eff_bs, max_pages, a.bos, a.eos), chunk = chunk_rows(eff_bs);
     if (workspace == nullptr || nch == 1) return;
     if (workspace_bytes < split_workspace_bytes(eff_bs, max_pages, a.K, a.bos, a.eos)) return;
-    a.chunk = kChunk;
+    a.chunk = chunk;
     a.nch_max = nch;
-    a.key_cap = vtx::pow2_ceil(nch * a.K > kChunk ? nch * a.K : kChunk);
+    a.key_cap = vtx::pow2_ceil(nch * a.K > chunk ? nch * a.K : chunk);
     a.tickets = reinterpret_cast<int32_t*>(workspace);
     a.part_keys = reinterpret_cast<unsigned char*>(workspace) + ((int64_t)eff_bs * 4 + 255) / 256 * 256;
 }
