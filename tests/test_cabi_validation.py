@@ -87,3 +87,14 @@ def test_checked_entry_points_of_the_normal_library():
 def test_workspace_size_queries_refuse_bad_sizes():
     assert _cabi.lib.vtx_sparse_layer_workspace_bytes(-1, 64, 30, 1, 1) <= 0
     assert _cabi.lib.vtx_decode_gqa_splitkv_workspace_bytes(8, 4, 128, 0) <= 0
+
+
+def test_layer_workspace_size_follows_the_chunk_rule():
+    """Chunks of 768 candidates for batches of at most 384 segments, 512 above; no workspace when one chunk holds
+    the longest segment; tickets padded to 256 bytes, K eight-byte keys per (segment, chunk)."""
+    ws = _cabi.lib.vtx_sparse_layer_workspace_bytes
+    K = 64
+    assert ws(256, 2048, K, 1, 1) == 1024 + 256 * 3 * K * 8        # 2046 candidates -> 3 chunks of 768
+    assert ws(2048, 2048, K, 1, 1) == 8192 + 2048 * 4 * K * 8      # -> 4 chunks of 512
+    assert ws(512, 512, 30, 1, 1) == 0 and ws(512, 515, 30, 1, 1) > 0   # 510 candidates fit one chunk, 513 do not
+    assert ws(64, 770, 30, 1, 1) == 0 and ws(64, 771, 30, 1, 1) > 0     # small batch: 768 fit, 769 do not
