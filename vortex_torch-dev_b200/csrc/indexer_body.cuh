@@ -369,7 +369,7 @@ struct Geom {
     static_assert(pieces % 8 == 0, "row must be a multiple of 128 bytes");
     static_assert(nchunk % lpr == 0 && L % lpr == 0, "the lanes of a row split its partial sums evenly");
     // the idle ring doubles as the sort's exchange buffer (2 x 2048 keys at most)
-    static_assert(ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
+    static_assert(LPR != 2 || ring_bytes >= 2 * 2048 * sizeof(typename KeyOf<T>::type), "ring too small for the sort scratch");
 };
 
 
@@ -683,6 +683,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     constexpr int SLOT_B = NSRC * Gm::slot_bytes;
     constexpr int SLOTS = SLOTS_FORCE ? SLOTS_FORCE : ring_slots(SLOT_B);
     constexpr size_t RING_B = (size_t)kWarps * SLOTS * SLOT_B;
+    static_assert(BAR != 0 || RING_B >= 2 * 2048 * sizeof(Key), "the idle ring doubles as the sort's exchange buffer");
     // layout: [ring][query staging][keys][ids]
     unsigned char* ring = smem_raw;
     T* qbar = reinterpret_cast<T*>(smem_raw + RING_B);

@@ -80,7 +80,7 @@ struct LayerHooks {
 // from the per-page maximum and minimum caches, which the token write then maintains instead of the mean
 // (twice the summary bytes per page: two CTAs per SM instead of four).
 template <int D, int G, int MODE = 0>
-__global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
+__global__ void __launch_bounds__(kThreads, 4) sparse_layer_kernel(IndexerArgs ia, vtxdec::DecodeArgs da,
                                                                   AppendArgs ap, const int early) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     if (!early) vtx::pdl_wait();
@@ -97,8 +97,10 @@ __global__ void __launch_bounds__(kThreads, MODE == 3 ? 2 : 4) sparse_layer_kern
         s_pre[3] = dend > dbeg ? VTX_CHECK_KV_ROW(ia.dense_indices[dbeg]) : 0;
     }
     LayerHooks<D, G, MODE> hooks{ia, da, ap, smem_raw, s_pre, seg, chunk_no, early != 0, false};
-    const bool owner = indexer_body<__nv_bfloat16, D, MODE, LayerHooks<D, G, MODE>&, (MODE >= 2 ? G : 1)>(
-        ia, smem_raw, seg, chunk_no, hooks);
+    // quest mode gathers two summary rows per page: four lanes per row (8-row batches) keep its ring at the size
+    // of the other modes', so that four CTAs fit an SM in every mode
+    const bool owner = indexer_body<__nv_bfloat16, D, MODE, LayerHooks<D, G, MODE>&, (MODE >= 2 ? G : 1), 0, 0,
+                                    (MODE == 3 ? 4 : 2)>(ia, smem_raw, seg, chunk_no, hooks);
     const bool pre_issued = hooks.pre_issued;
     if (!owner) return;
     __syncthreads();  // the list is complete and visible to the CTA; rings and sort scratch are idle
@@ -110,7 +112,7 @@ int launch_sparse_layer_cfg(const IndexerArgs& ia, const vtxdec::DecodeArgs& da,
                             bool early, cudaStream_t st) {
     using Gm = Geom<__nv_bfloat16, D>;
     static_assert(vtxdec::kDecWarps * 32 == kThreads, "both phases use the same CTA shape");
-    constexpr int quest_slot_b = 2 * Gm::slot_bytes;
+    constexpr int quest_slot_b = 2 * Geom<__nv_bfloat16, D, 4>::slot_bytes;
     constexpr int quest_slots = ring_slots(quest_slot_b);
     size_t bytes = MODE == 2 ? Gm::ring_bytes + (size_t)G * D * 4 +
                                    (size_t)ia.key_cap * (sizeof(uint32_t) + sizeof(int32_t) + G * sizeof(__nv_bfloat16))
