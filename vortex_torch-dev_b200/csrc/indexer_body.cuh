@@ -298,18 +298,27 @@ __device__ __forceinline__ void add_products(float& acc, const float* row_chunk,
     acc = __fadd_rn(acc, __fmul_rn(r1.w, q1.w));
 }
 
-// bf16 row chunk times fp32 query chunk, products kept in fp32 (the GeMM operator's arithmetic).
-__device__ __forceinline__ void add_products_f32(float& acc, const __nv_bfloat16* row_chunk, const float* q_chunk) {
+// bf16 row chunk times bf16 query chunk, products kept in fp32 (the GeMM operator's arithmetic): the product of
+// two bf16 values has 16 significant bits, so it is exact in fp32 and the mixed-precision fused multiply-add of
+// sm_100 (bf16 x bf16 + fp32, one rounding) returns what a separate exact multiply and a rounded add return -
+// for every product inside fp32's normal range; below 2^-126 a separate multiply would round first.
+__device__ __forceinline__ float fma_bf16(uint16_t x, uint16_t y, float acc) {
+    float d;
+    asm("fma.rn.f32.bf16 %0, %1, %2, %3;" : "=f"(d) : "h"(x), "h"(y), "f"(acc));
+    return d;
+}
+__device__ __forceinline__ void add_products_f32(float& acc, const __nv_bfloat16* row_chunk, const __nv_bfloat16* q_chunk) {
     const uint4 r = *reinterpret_cast<const uint4*>(row_chunk);
-    const float4 q0 = *reinterpret_cast<const float4*>(q_chunk), q1 = *reinterpret_cast<const float4*>(q_chunk + 4);
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.x), q0.x));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.x), q0.y));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.y), q0.z));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.y), q0.w));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.z), q1.x));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.z), q1.y));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16lo(r.w), q1.z));
-    acc = __fadd_rn(acc, __fmul_rn(vtx::bf16hi(r.w), q1.w));
+    const uint4 q = *reinterpret_cast<const uint4*>(q_chunk);
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w}, qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint16_t r0, r1, q0, q1;
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(r0), "=h"(r1) : "r"(rr[i]));
+        asm("mov.b32 {%0, %1}, %2;" : "=h"(q0), "=h"(q1) : "r"(qq[i]));
+        acc = fma_bf16(r0, q0, acc);
+        acc = fma_bf16(r1, q1, acc);
+    }
 }
 
 // Quest upper bound for one chunk: max(round_bf16(q*hi), round_bf16(q*lo)) per dim, added one by one.
@@ -614,7 +623,7 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
                                              reinterpret_cast<const __nv_bfloat16*>(qv) + g * D + ch * 8);
                         else if constexpr (MODE == 2)
                             add_products_f32(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
-                                             qf32 + g * D + ch * 8);
+                                             reinterpret_cast<const __nv_bfloat16*>(qf32) + g * D + ch * 8);
                         else
                             add_products(acc[ii], src, qv + ch * 8);
                     }
@@ -843,16 +852,9 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
         if (MODE == 3) {  // the group's query heads as they are
             const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
             for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
-        } else {          // the group's query heads, widened to fp32
-            const T* qs = reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D;
-            for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) {
-                vtx::Vec8<T> v;
-                v.load_cached(qs + ch * 8);
-                float f[8];
-                v.unpack(f);
-#pragma unroll
-                for (int jj = 0; jj < 8; ++jj) qf32[ch * 8 + jj] = f[jj];
-            }
+        } else {          // the group's query heads as they are (the products are formed in fp32, see add_products_f32)
+            const uint4* qs = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.q) + (int64_t)s * GQ * D);
+            for (int ch = threadIdx.x; ch < GQ * Gm::nchunk; ch += kThreads) reinterpret_cast<uint4*>(qbar)[ch] = qs[ch];
         }
         if (hooks.needs_spare(warp)) cp_async_wait<0>();
         __syncwarp();
