@@ -118,6 +118,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
         for (int i = 0; i < 4; ++i) o[mt][i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;  // running max / partial sum of head `gid`
     float a0 = 1.f, a1 = 1.f;              // pending rescale of the O^T columns this lane holds
+    bool rescale = false;                  // warp-uniform: some factor of the pending rescale differs from 1
     uint32_t pb0 = 0u, pb1 = 0u;           // P^T of the current tile as the B operand
 
     const bool whole = pg_cnt < 0;
@@ -206,12 +207,14 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
             // the O^T columns of this lane are heads tid*2 and tid*2+1
             a0 = __shfl_sync(0xffffffffu, alpha, (tid * 2) << 2);
             a1 = __shfl_sync(0xffffffffu, alpha, (tid * 2 + 1) << 2);
+            // once the running maxima have settled every factor is exactly 1: the rescaling below is skipped
+            rescale = !__all_sync(0xffffffffu, alpha == 1.f);
         } else {
 #pragma unroll
             for (int mt = 0; mt < KSTEPS; ++mt) {
                 uint32_t va[4];
                 vtx::ldmatrix_x4_trans(va, tile_addr + ((((mt << 1) + lm_c) ^ (lm_t & 7)) << 4));
-                o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
+                if (rescale) { o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1; }
                 // A regs: (dims 0-7, tok 0-7), (dims 8-15, tok 0-7), (dims 0-7, tok 8-15), (dims 8-15, tok 8-15)
                 vtx::mma_bf16(o[mt], va[0], va[1], va[2], va[3], pb0, pb1);
             }
