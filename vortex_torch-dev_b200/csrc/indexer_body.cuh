@@ -372,6 +372,10 @@ struct Geom {
     // of wide rows 2 us, so four is the choice of that one caller, not the rule.
     static constexpr int lpr = LPR;
     static constexpr int rows_per_slot = 32 / lpr;
+    // A 16-byte read of a warp is served a quarter warp (8 lanes = 8 / lpr rows) at a time, and the rows of a slot
+    // start at the same bank; the piece index of row r is XORed with swizzle(r) so that the lpr consecutive
+    // pieces read by the lanes of one row never meet those of the other rows of its quarter warp.
+    __host__ __device__ static constexpr int swizzle(int r) { return (r % (8 / lpr)) * lpr; }
     static constexpr int slot_bytes = rows_per_slot * row_bytes;
     static constexpr int slots = ring_slots(slot_bytes);
     static constexpr size_t ring_bytes = (size_t)kWarps * slots * slot_bytes;
@@ -598,7 +602,7 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
         if (ord + SLOTS - 1 < my_batches) issue(ord + SLOTS - 1);
         cp_async_commit();
         const unsigned char* row_ptr = my_ring + (size_t)(ord % SLOTS) * SLOT_B + r_in * Gm::row_bytes;
-        const int sw = (r_in & 3) << 1;
+        const int sw = Gm::swizzle(r_in);
         const int i = (warp + ord * kWarps) * Gm::rows_per_slot + r_in;  // position inside this CTA's chunk
         float best = -INFINITY;  // MODE 3: running maximum over the heads
         float row_score = 0.f;
@@ -614,7 +618,7 @@ __device__ __forceinline__ void score_rows(const IndexerArgs& a, Issue& issue, c
                 for (int ii = 0; ii < HALF; ++ii) {
                     if (k * L + LPR * ii < Gm::nchunk) {  // nchunk is a multiple of LPR: the test holds for every residue
                         const int ch = k * L + LPR * ii + par;
-                        // a chunk is ppc adjacent 16-byte pieces; the swizzle flips piece bits 1-2 only
+                        // a chunk is ppc adjacent 16-byte pieces; the swizzle never flips piece bit 0
                         const T* src = reinterpret_cast<const T*>(row_ptr + (((ch * Gm::ppc) ^ sw) << 4));
                         if constexpr (MODE == 3)
                             add_quest_bounds(acc[ii], reinterpret_cast<const __nv_bfloat16*>(src),
@@ -774,7 +778,7 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
             const int i = row0 + r;
             const bool valid = i < cnt;
             const int64_t row = valid ? VTX_CHECK_SUMMARY_ROW(row_ids[i]) : 0;
-            const uint32_t off = r * Gm::row_bytes + ((pr ^ ((r & 3) << 1)) << 4);
+            const uint32_t off = r * Gm::row_bytes + ((pr ^ Gm::swizzle(r)) << 4);
             cp_async16(dst + off, cent + row * Gm::row_bytes + pr * 16, valid);
             if (NSRC == 2) cp_async16(dst + Gm::slot_bytes + off, cent2 + row * Gm::row_bytes + pr * 16, valid);
         }
