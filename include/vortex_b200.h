@@ -144,9 +144,10 @@ int vtx_creduce(const void* x, void* out, const int64_t* loc, int64_t nnz, int n
                 int rows, int cols, int page_size, int op, int dtype, void* stream);
 
 /*
- * KV write fused with the page-completion mean of K: same results as vtx_set_kv followed by
- * vtx_cmean(k_cache -> centroids) on the same loc, in one launch (the new row is averaged from
- * registers).  Replaces the pair set_kv_buffer_launcher (cache/triton_kernels/set_kv.py:39-62) +
+ * KV write together with the page-completion mean of K: same results as vtx_set_kv followed by
+ * vtx_cmean(k_cache -> centroids) on the same loc, in one call - one launch up to 16384 (token, head) items (a
+ * decode step), the streaming copy and the page reduction as two launches above that (a prefill), whichever
+ * was measured faster.  Replaces the pair set_kv_buffer_launcher (cache/triton_kernels/set_kv.py:39-62) +
  * reduce_pp Mean (cache/triton_kernels/reduce_impl.py:7-89) that the runtime issues back to back
  * for flows whose forward_cache is `CMean(dim=1)(cache["k"], cache["centroids"])`
  * (flow/algorithms.py:172-205).  centroids [num_pages*H, 1, D].

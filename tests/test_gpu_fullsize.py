@@ -40,10 +40,12 @@ def test_config4b_prefill_32768_tokens():
     assert torch.equal(out.cpu()[:, 0].view(torch.int16), vo.cmean_pages(k, rows).view(torch.int16))
 
 
-def test_config4b_prefill_write_and_centroids_in_one_launch():
-    """Prefill of a 32768-token request through the fused KV write + page mean: caches and all 2048 x 8
+@pytest.mark.parametrize("pages", [128, 2048])
+def test_config4b_prefill_write_and_centroids_in_one_call(pages):
+    """Prefill of a 2048- and of a 32768-token request through vtx_set_kv_cmean (one launch up to 16384 (token,
+    head) items, copy and reduction as two launches inside the call above that): caches and all pages x 8
     centroids equal set_kv followed by the mean, bit for bit, and equal the oracle."""
-    P, H, D, pages, extra = 16, 8, 128, 2048, 64
+    P, H, D, extra = 16, 8, 128, 64
     g = torch.Generator().manual_seed(44)
     perm = torch.randperm(pages + extra, generator=g)[:pages]       # physical pages of the request, in token order
     loc = (perm.view(-1, 1) * P + torch.arange(P).view(1, -1)).reshape(-1)

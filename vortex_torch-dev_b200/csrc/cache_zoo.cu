@@ -25,12 +25,14 @@ struct Item {
 };
 
 __device__ __forceinline__ Item item_of(const int64_t* loc, int64_t it, int H, int P) {
-    const int64_t i = it / H;
-    const int h = (int)(it - i * H);
+    const vtx::DivMod ih = vtx::divmod(it, H);
+    const int64_t i = ih.q;
+    const int h = ih.r;
     const int64_t t = VTX_CHECK_LOC(loc[i]);
     Item r;
-    r.active = (t + 1) % P == 0;
-    r.paged_row = (t / P) * H + h;
+    const vtx::PageSlot ps = vtx::page_slot(t, P);
+    r.active = ps.row == P - 1;
+    r.paged_row = ps.page * H + h;
     r.ragged_row = i * H + h;
     return r;
 }

@@ -261,13 +261,7 @@ __device__ __forceinline__ void cp_async_wait() {
 
 // ---- one chunk (8 dims) of products added one by one into acc ----
 // bf16: the packed multiply rounds each exact product once to bf16, as the canonical order asks.
-// acc + (the bf16 value x widened to fp32), rounded to nearest even: the mixed-precision add of sm_100 does the
-// (exact) widening and the addition in one instruction.
-__device__ __forceinline__ float add_bf16(float acc, uint16_t x) {
-    float d;
-    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(x), "f"(acc));
-    return d;
-}
+using vtx::add_bf16;
 __device__ __forceinline__ void add_pair(float& acc, uint32_t packed) {  // low half first, then the high half
     uint16_t lo, hi;
     asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(packed));
@@ -417,8 +411,9 @@ __device__ __forceinline__ void append_finish(const AppendArgs& ap, const int s,
     constexpr int NCH = D / 8;
     if (lane >= NCH) return;
     const int h = s % ap.H;
-    const int64_t pid = (in.slot / ap.P) * ap.H + h;
-    const int tok = (int)(in.slot % ap.P);
+    const vtx::PageSlot ps = vtx::page_slot(in.slot, ap.P);
+    const int64_t pid = ps.page * ap.H + h;
+    const int tok = ps.row;
     __nv_bfloat16* kpage = ap.k_cache + pid * (int64_t)ap.P * D;
     __nv_bfloat16* vpage = ap.v_cache + pid * (int64_t)ap.P * D;
     *reinterpret_cast<uint4*>(kpage + (int64_t)tok * D + lane * 8) = in.k;

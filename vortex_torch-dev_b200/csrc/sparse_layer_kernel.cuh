@@ -30,9 +30,10 @@ struct LayerHooks {
         if (!needs_spare(warp)) return;
         // loc is an input of the step that is final before the step's first launch, like the page lists
         const int64_t t = VTX_CHECK_LOC(ap.loc[seg / ap.H]);
-        if ((int)(t % ap.P) != ap.P - 1) return;  // the token does not close its page: nothing to average
+        const vtx::PageSlot ps = vtx::page_slot(t, ap.P);
+        if (ps.row != ap.P - 1) return;  // the token does not close its page: nothing to average
         const unsigned char* page = reinterpret_cast<const unsigned char*>(ap.k_cache) +
-                                    ((t / ap.P) * ap.H + seg % ap.H) * (int64_t)ap.P * (D * 2);
+                                    (ps.page * ap.H + seg % ap.H) * (int64_t)ap.P * (D * 2);
         constexpr int pieces = D * 2 / 16;
         for (int pc = lane; pc < (ap.P - 1) * pieces; pc += 32) cp_async16(spare + pc * 16, page + (size_t)pc * 16, true);
     }

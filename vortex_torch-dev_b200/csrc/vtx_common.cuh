@@ -115,6 +115,47 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Page and in-page row of cache slot t (>= 0) for pages of P tokens.  A 64-bit division by a run-time P costs a
+// thread on the order of a hundred instructions, and the cache kernels do one per (token, head) item: pages of
+// a power of two take a shift and a mask, other sizes a 32-bit division while the slot fits 32 bits.
+struct PageSlot {
+    int64_t page;
+    int row;
+};
+__device__ __forceinline__ PageSlot page_slot(int64_t t, int P) {
+    PageSlot r;
+    if ((P & (P - 1)) == 0) {
+        r.page = t >> (31 - __clz(P));
+        r.row = (int)(t & (int64_t)(P - 1));
+    } else if ((uint64_t)t <= 0xffffffffull) {
+        const uint32_t u = (uint32_t)t, q = u / (uint32_t)P;
+        r.page = q;
+        r.row = (int)(u - q * (uint32_t)P);
+    } else {
+        r.page = t / P;
+        r.row = (int)(t % P);
+    }
+    return r;
+}
+
+// a / b and a % b for a >= 0, b > 0, with a 32-bit division whenever a fits 32 bits.
+struct DivMod {
+    int64_t q;
+    int r;
+};
+__device__ __forceinline__ DivMod divmod(int64_t a, int b) {
+    DivMod d;
+    if ((uint64_t)a <= 0xffffffffull) {
+        const uint32_t u = (uint32_t)a, q = u / (uint32_t)b;
+        d.q = q;
+        d.r = (int)(u - q * (uint32_t)b);
+    } else {
+        d.q = a / b;
+        d.r = (int)(a % b);
+    }
+    return d;
+}
+
 __host__ __device__ inline int pow2_ceil(int n) {
     int p = 1;
     while (p < n) p <<= 1;
@@ -133,6 +174,21 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// acc + (the bf16 value x widened to fp32), rounded to nearest even: the mixed-precision add of sm_100 does the
+// (exact) widening and the addition in one instruction.
+__device__ __forceinline__ float add_bf16(float acc, uint16_t x) {
+    float d;
+    asm("add.rn.f32.bf16 %0, %1, %2;" : "=f"(d) : "h"(x), "f"(acc));
+    return d;
+}
+// acc0 += low half, acc1 += high half of a packed pair of bf16 values
+__device__ __forceinline__ void add_bf16x2(float& acc0, float& acc1, uint32_t packed) {
+    uint16_t lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(packed));
+    acc0 = add_bf16(acc0, lo);
+    acc1 = add_bf16(acc1, hi);
+}
+
 // Eight consecutive elements widened to fp32.
 template <typename T>
 struct Vec8;
@@ -145,6 +201,7 @@ struct Vec8<__nv_bfloat16> {
         raw = *reinterpret_cast<const uint4*>(p);
     }
     __device__ __forceinline__ void zero() { raw = make_uint4(0, 0, 0, 0); }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
     __device__ __forceinline__ void unpack(float (&f)[8]) const {
         f[0] = bf16lo(raw.x); f[1] = bf16hi(raw.x);
         f[2] = bf16lo(raw.y); f[3] = bf16hi(raw.y);
@@ -167,6 +224,10 @@ struct Vec8<float> {
     __device__ __forceinline__ void zero() {
         raw0 = make_uint4(0, 0, 0, 0);
         raw1 = raw0;
+    }
+    __device__ __forceinline__ void store(float* p) const {
+        *reinterpret_cast<uint4*>(p) = raw0;
+        *reinterpret_cast<uint4*>(p + 4) = raw1;
     }
     __device__ __forceinline__ void unpack(float (&f)[8]) const {
         f[0] = __uint_as_float(raw0.x); f[1] = __uint_as_float(raw0.y);
