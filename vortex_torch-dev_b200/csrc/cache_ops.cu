@@ -281,14 +281,20 @@ template <typename T, int OP>
 int launch_creduce_op(const void* x, void* out, const int64_t* loc, int64_t nnz, int H, int rows, int cols, int P,
                       cudaStream_t st) {
     const int64_t items = nnz * H;
-    if (cols <= 128) {
-        const int64_t blocks = (items + 15) / 16;
-        return vtx::launch(creduce_kernel<T, 16, OP>, dim3((unsigned)std::min<int64_t>(blocks, kMaxBlocks)), dim3(256), 0,
-                           st, (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+    const int groups = cols <= 128 ? 16 : 8;
+    // Decode-sized calls: every entry may close a page, one item per group.  Prefill-sized calls: an entry in
+    // page_size closes one, so a block takes the entries that keep all its groups busy.
+    int64_t blocks = (items + groups - 1) / groups;
+    if (items > kOneLaunchItems) {
+        const int64_t entries = std::max<int64_t>(1, (int64_t)groups * P / H);  // ~ `groups` (closed page, head) items
+        blocks = (nnz + entries - 1) / entries;
     }
-    const int64_t blocks = (items + 7) / 8;
-    return vtx::launch(creduce_kernel<T, 32, OP>, dim3((unsigned)std::min<int64_t>(blocks, kMaxBlocks)), dim3(256), 0, st,
-                       (const T*)x, (T*)out, loc, nnz, H, rows, cols, P);
+    blocks = std::min<int64_t>(blocks, kMaxBlocks);
+    if (cols <= 128)
+        return vtx::launch(creduce_kernel<T, 16, OP>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)x, (T*)out, loc,
+                           nnz, H, rows, cols, P);
+    return vtx::launch(creduce_kernel<T, 32, OP>, dim3((unsigned)blocks), dim3(256), 0, st, (const T*)x, (T*)out, loc, nnz,
+                       H, rows, cols, P);
 }
 
 template <typename T>
