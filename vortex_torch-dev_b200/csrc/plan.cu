@@ -66,6 +66,19 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     const int r = blockIdx.x, h = blockIdx.y, tx = threadIdx.x;
     const int budget = a.K + a.bos + a.eos;
 
+    // The segment's first kPre * kPlanThreads page entries are requested before the prefix sums below: the request
+    // row and the token slots depend only on r, so their two round trips overlap the sums and the block barrier.
+    constexpr int kPre = 8;
+    const int seq_early = a.seq_lens[r];
+    const int n_early = (seq_early + a.P - 1) / a.P;
+    const int32_t* toks_early = a.req_to_token + VTX_CHECK_REQ_ROW(a.req_indices[r]) * a.r2t_stride;
+    int32_t pre[kPre];
+#pragma unroll
+    for (int u = 0; u < kPre; ++u) {
+        const int p = tx + u * kPlanThreads;
+        pre[u] = p < n_early ? toks_early[(int64_t)p * a.P] : 0;
+    }
+
     int3 part = make_int3(0, 0, 0);
     for (int i = tx; i < r; i += kPlanThreads) {
         const int n = (a.seq_lens[i] + a.P - 1) / a.P;
@@ -109,8 +122,16 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     int32_t* spt = a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride : nullptr;
     const bool copy_all = n <= budget;
 
-    for (int p = tx; p < n; p += kPlanThreads) {
-        const int row = (VTX_CHECK_LOC(toks[(int64_t)p * a.P]) / a.P) * a.H + h;
+    for (int p = tx, u = 0; p < n; p += kPlanThreads, ++u) {
+        int32_t tok = 0;
+        if (u < kPre) {
+#pragma unroll
+            for (int w = 0; w < kPre; ++w)
+                if (w == u) tok = pre[w];
+        } else {
+            tok = toks[(int64_t)p * a.P];
+        }
+        const int row = (VTX_CHECK_LOC(tok) / a.P) * a.H + h;
         dense[p] = row;
         if (dpt) dpt[p] = row;
         int slot = -1;
