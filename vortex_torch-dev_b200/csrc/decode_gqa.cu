@@ -83,6 +83,9 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
     const int last_len = a.last_len[s];
     const int P = a.P;
     const int tiles_per_page = (P + kTileTokens - 1) / kTileTokens;
+    const bool tpp_pow2 = (tiles_per_page & (tiles_per_page - 1)) == 0;  // then the page of a pair is a shift
+    const int tpp_shift = 31 - __clz(tiles_per_page);
+    auto page_of = [&](int pair) { return tpp_pow2 ? (pair >> tpp_shift) : pair / tiles_per_page; };
 
     T* my_ring = ring + (size_t)warp * kSlots * TILE_ELEMS;
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
@@ -121,7 +124,7 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
     auto issue = [&](int item) {
         // item -> (page ordinal, tile, K or V)
         const int pair = item >> 1;
-        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int po = page_of(pair), tile = pair - po * tiles_per_page;
         const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
         const int pg = warp + kWarps * po;
         const int nvalid_page = (pg == npages - 1) ? last_len : P;
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
         {
             const int nxt = item + kSlots - 1;
             if (nxt < n_items) {
-                const int po = (nxt >> 1) / tiles_per_page;
+                const int po = page_of(nxt >> 1);
                 if (po - id_base >= 32) {  // refill the per-lane page ids (warp-uniform branch)
                     id_base += 32;
                     id_reg = (id_base + lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + warp + kWarps * (id_base + lane)]) : 0;
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__(kWarps * 32, (G >= 8 ? 2 : 4)) decode_gqa_simt
         }
         const T* tile_ptr = my_ring + (size_t)(item % kSlots) * TILE_ELEMS + sub * 8;
         const int pair = item >> 1;
-        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int po = page_of(pair), tile = pair - po * tiles_per_page;
         const int pg = warp + kWarps * po;
         const int nvalid = ((pg == npages - 1) ? last_len : P) - tile * kTileTokens;  // valid rows in this tile
         if ((item & 1) == 0) {

@@ -96,6 +96,11 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
     const int last_len = a.last_len[s];
     const int P = a.P;
     const int tiles_per_page = (P + kDecTileTokens - 1) / kDecTileTokens;
+    // page ordinal of a (K, V) pair: a division by a run-time value per item is ~20 instructions, three times per
+    // item; the usual page sizes give a power of two (16 tokens: one tile per page), which is a shift
+    const bool tpp_pow2 = (tiles_per_page & (tiles_per_page - 1)) == 0;
+    const int tpp_shift = 31 - __clz(tiles_per_page);
+    auto page_of = [&](int pair) { return tpp_pow2 ? (pair >> tpp_shift) : pair / tiles_per_page; };
 
     unsigned char* my_ring = smem_raw + (size_t)warp * kDecSlots * TILE_BYTES;
     const uint32_t my_ring_addr = (uint32_t)__cvta_generic_to_shared(my_ring);
@@ -134,7 +139,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
 
     auto issue = [&](int item) {
         const int pair = item >> 1;
-        const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+        const int po = page_of(pair), tile = pair - po * tiles_per_page;
         const int row = __shfl_sync(0xffffffffu, id_reg, (po - id_base) & 31);
         const int nvalid_page = (entry_of(po) == npages - 1) ? last_len : P;
         issue_tile<D>((item & 1) ? vc : kc, row, P, tile * kDecTileTokens, nvalid_page,
@@ -159,7 +164,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
         {
             const int nxt = item + kDecSlots - 1;
             if (nxt < n_items) {
-                const int po = (nxt >> 1) / tiles_per_page;
+                const int po = page_of(nxt >> 1);
                 if (po - id_base >= 32) {
                     id_base += 32;
                     id_reg = (id_base + lane < my_pages) ? VTX_CHECK_KV_ROW(a.indices[beg + entry_of(id_base + lane)]) : 0;
@@ -171,7 +176,7 @@ __device__ __forceinline__ void decode_mma_body(const DecodeArgs& a, unsigned ch
         const uint32_t tile_addr = my_ring_addr + (uint32_t)((item % kDecSlots) * TILE_BYTES) + lm_t * ROWB;
         if ((item & 1) == 0) {
             const int pair = item >> 1;
-            const int po = pair / tiles_per_page, tile = pair - po * tiles_per_page;
+            const int po = page_of(pair), tile = pair - po * tiles_per_page;
             const int nvalid = ((entry_of(po) == npages - 1) ? last_len : P) - tile * kDecTileTokens;
             float st[2][4];
 #pragma unroll
