@@ -41,6 +41,17 @@ __device__ __forceinline__ void issue_tile(const unsigned char* cache, int row, 
                                            uint32_t dst, int lane) {
     constexpr int ROWB = D * 2, CH_PER_ROW = ROWB / 16, CPL = kDecTileTokens * ROWB / 16 / 32;
     const unsigned char* src = cache + ((int64_t)row * P + tok0) * ROWB;
+    if constexpr (D == 128) {
+        // 256-byte rows: a lane takes one 16-byte chunk of eight consecutive token rows (lanes 0-15 rows 0-7,
+        // lanes 16-31 rows 8-15), so that the swizzle of its c-th row is a constant of the unrolled loop
+        const int tbase = (lane >> 4) * 8, cr = lane & 15;
+        const unsigned char* s0 = src + tbase * ROWB + cr * 16;
+        const uint32_t d0 = dst + (uint32_t)(tbase * ROWB);
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+            vtx::cp_async16(d0 + c * ROWB + ((cr ^ c) << 4), s0 + c * ROWB, tok0 + tbase + c < nvalid_page);
+        return;
+    }
 #pragma unroll
     for (int c = 0; c < CPL; ++c) {
         const int ch = c * 32 + lane;

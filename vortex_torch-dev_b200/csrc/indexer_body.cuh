@@ -767,6 +767,37 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
     auto issue = [&](int ord) {
         const int row0 = (warp + ord * kWarps) * Gm::rows_per_slot;
         const uint32_t dst = my_ring_addr + (uint32_t)((ord % SLOTS) * SLOT_B);
+        if constexpr (Gm::pieces == 16 && MODE != 1) {
+            // 256-byte rows: a lane takes one 16-byte piece of RPL consecutive rows (lanes 0-15 the first half of
+            // the batch, lanes 16-31 the second), so that its row ids are 16-byte reads of the staged list and the
+            // swizzle of its k-th row is a constant of the unrolled loop
+            constexpr int RPL = Gm::rows_per_slot / 2;  // 8, or 4 with four lanes per row
+            static_assert(RPL % 4 == 0, "row ids are read four at a time");
+            const int rbase = (lane >> 4) * RPL, pr = lane & 15;
+            const int i0 = row0 + rbase;
+            int rid[RPL];
+            if (i0 + RPL <= cnt) {
+#pragma unroll
+                for (int k = 0; k < RPL; k += 4) {
+                    const int4 v = *reinterpret_cast<const int4*>(row_ids + i0 + k);
+                    rid[k] = v.x; rid[k + 1] = v.y; rid[k + 2] = v.z; rid[k + 3] = v.w;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < RPL; ++k) rid[k] = i0 + k < cnt ? row_ids[i0 + k] : -1;
+            }
+            const unsigned char* src = cent + pr * 16;
+            const uint32_t d0 = dst + (uint32_t)(rbase * Gm::row_bytes);
+#pragma unroll
+            for (int k = 0; k < RPL; ++k) {
+                const bool valid = i0 + k < cnt;
+                const int64_t row = valid ? VTX_CHECK_SUMMARY_ROW(rid[k]) : 0;
+                const uint32_t off = k * Gm::row_bytes + ((pr ^ Gm::swizzle(k)) << 4);  // swizzle(rbase + k) == swizzle(k)
+                cp_async16(d0 + off, src + row * Gm::row_bytes, valid);
+                if (NSRC == 2) cp_async16(d0 + Gm::slot_bytes + off, cent2 + row * Gm::row_bytes + pr * 16, valid);
+            }
+            return;
+        }
 #pragma unroll
         for (int pc = lane; pc < pieces_per_slot; pc += 32) {
             const int r = pc / Gm::pieces, pr = pc - r * Gm::pieces;
