@@ -273,11 +273,16 @@ __device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((
 // fault codes (bits of g_mla_fault): which kind of barrier a wait gave up on
 enum : unsigned { kFaultEmpty = 1, kFaultFull = 2, kFaultS = 4, kFaultP = 8, kFaultO = 16, kFaultFixed = 32, kFaultQ = 64, kFaultDrain = 128 };
 
-// Shared memory of one instance of the indexer body in the fused form: ring (two slots per warp), query mean,
+// The selection phase of the fused form: four lanes per row (8-row batches of 9 KB) and two batches per warp, so
+// that two instances fit under the decode's idle tile ring.  Eight lanes per row with five 4-row batches per warp
+// fit too and select the same pages, but are no faster (69.0 against 68.4 us on 128 requests of 256 candidate
+// pages): while it streams, the scan already moves 5.5 TB/s; its cost is the latency before and after.
+constexpr int kFusedLpr = 4, kFusedSlots = 2;
+// Shared memory of one instance of the indexer body in the fused form: ring (kFusedSlots per warp), query mean,
 // keys and row ids of its candidates; rounded up so that the next instance starts 128-byte aligned.
 __host__ __device__ inline size_t fused_instance_bytes(int key_cap) {
-    using Gm = Geom<__nv_bfloat16, kDl, 4>;  // four lanes per row, 8-row batches
-    const size_t n = (size_t)4 * 2 * Gm::slot_bytes + (size_t)q_stage_bytes<__nv_bfloat16, kDl, 0, 1>() +
+    using Gm = Geom<__nv_bfloat16, kDl, kFusedLpr>;
+    const size_t n = (size_t)4 * kFusedSlots * Gm::slot_bytes + (size_t)q_stage_bytes<__nv_bfloat16, kDl, 0, 1>() +
                      (size_t)key_cap * (sizeof(KeyOf<__nv_bfloat16>::type) + sizeof(int32_t));
     return (n + 127) & ~(size_t)127;
 }
@@ -325,6 +330,17 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
     const uint32_t tmem = *tmem_slot;
     vtx::pdl_wait();
     if constexpr (FUSED != 0) {
+        // The pages the planner reserved (the request's first and last page: entries 0 and n - 1 of its page-table
+        // row, written before this launch) will be read by the decode whatever the selection finds.  Their tiles
+        // are pulled into L2 now: HBM is idle while every CTA of the launch walks the dependent loads that open
+        // the selection (segment bounds -> row ids -> first gathers), and the decode then finds them in L2.
+        if (warp == 7 && a.P == kTile && lane < 2 * 9) {
+            const int nt = (a.seqlens[b] + kTile - 1) / kTile;
+            const int which = lane / 9, blk = lane - which * 9;
+            const int entry = which == 0 ? 0 : nt - 1;
+            if ((which == 0 ? ia.bos > 0 : (ia.eos > 0 && nt > 1)) && nt > 0)
+                tma_prefetch_2d(&block_map, blk * kBlockDims, a.page_table[(int64_t)b * a.pt_stride + entry] * a.P);
+        }
         // The ring and the q / P areas are idle until the first copy is issued below; barriers, the TMEM slot and
         // the abort flag live behind them (kOffBars) and stay untouched: the host checked that everything used
         // here ends before kOffWmax.  Two instances of the indexer body, warps 0-3 on the first half of the
@@ -337,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mla_tc_kernel(TcArgs a, co
         Key* part = reinterpret_cast<Key*>(gbase + kOffQuads + 2 * inst_bytes);
         IndexerArgs mine = ia;
         mine.part_keys = part;
-        indexer_body<__nv_bfloat16, kDl, 0, NoHooks, 1, /*BAR=*/2, /*SLOTS=*/2, /*LPR=*/4>(mine, scratch, b, inst);  // barriers 2, 3
+        indexer_body<__nv_bfloat16, kDl, 0, NoHooks, 1, /*BAR=*/2, kFusedSlots, kFusedLpr>(mine, scratch, b, inst);  // barriers 2, 3
         __syncthreads();  // both halves' keys are in `part` (or the whole list was written: nothing to select)
         const int beg = ia.dense_indptr[b] + ia.bos;
         const int c = ia.dense_indptr[b + 1] - ia.eos - beg;
