@@ -913,13 +913,19 @@ __device__ __forceinline__ bool indexer_body(const IndexerArgs& a, unsigned char
 #pragma unroll
             for (int g = 0; g < NQ; ++g)
                 mx[g] = fmaxf(mx[g], __fmul_rn(__bfloat162float(sbuf[i * NQ + g]), a.scale));
+        // the maximum is exact in any order: warp shuffles, then the warps' results through shared memory
 #pragma unroll
-        for (int g = 0; g < NQ; ++g) red[g * kThreads + threadIdx.x] = mx[g];
+        for (int g = 0; g < NQ; ++g) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+            if (lane == 0) red[g * kWarps + warp] = mx[g];
+        }
         __syncthreads();
 #pragma unroll
         for (int g = 0; g < NQ; ++g) {
-            float m = red[g * kThreads];
-            for (int t = 1; t < kThreads; ++t) m = fmaxf(m, red[g * kThreads + t]);
+            float m = red[g * kWarps];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) m = fmaxf(m, red[g * kWarps + w]);
             mx[g] = m;
         }
         __syncthreads();
