@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     __shared__ int3 red[kPlanThreads / 32];
     vtx::pdl_wait();
     vtx::pdl_trigger();
-    const int r = blockIdx.x, tx = threadIdx.x;
+    const int r = blockIdx.x, h = blockIdx.y, tx = threadIdx.x;
     const int budget = a.K + a.bos + a.eos;
 
     // The segment's first kPre * kPlanThreads page entries are requested before the prefix sums below: the request
@@ -92,74 +92,67 @@ __global__ void __launch_bounds__(kPlanThreads) plan_decode_kernel(PlanArgs a) {
     const int n = (seq + a.P - 1) / a.P;
     const int m = min(budget, n);
     const int nch = chunks_of(n, a.bos, a.eos, a.K, a.max_chunk);
-    // page entry -> row id of head 0: one division per entry, whatever the number of heads this CTA writes
+    const int s = r * a.H + h;
+    const int d0 = a.H * before.x + h * n;
+    const int s0 = a.H * before.y + h * m;
+    const int w0 = a.H * before.z + h * nch;
+    const int rem = seq % a.P;
+    const int last_len = rem == 0 ? a.P : rem;
+
+    if (tx == 0) {
+        a.dense_indptr[s] = d0;
+        a.sparse_indptr[s] = s0;
+        if (a.last_page_len) a.last_page_len[s] = last_len;
+        if (a.dense_sl) {
+            a.dense_sl[s] = seq;
+            a.sparse_sl[s] = min((budget - 1) * a.P + last_len, seq);
+        }
+        if (r == a.bs - 1 && h == a.H - 1) {
+            a.dense_indptr[s + 1] = d0 + n;
+            a.sparse_indptr[s + 1] = s0 + m;
+            *a.w_num = w0 + nch;
+            *a.w_chunk = a.max_chunk;
+        }
+    }
+
+    const int32_t* toks = a.req_to_token + VTX_CHECK_REQ_ROW(a.req_indices[r]) * a.r2t_stride;
+    int32_t* dense = a.dense_indices + d0;
+    int32_t* sparse = a.sparse_indices + s0;
+    int32_t* dpt = a.dense_pt ? a.dense_pt + (int64_t)s * a.pt_stride : nullptr;
+    int32_t* spt = a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride : nullptr;
+    const bool copy_all = n <= budget;
+
+    for (int p = tx, u = 0; p < n; p += kPlanThreads, ++u) {
+        int32_t tok = 0;
+        if (u < kPre) {
 #pragma unroll
-    for (int u = 0; u < kPre; ++u) pre[u] = (VTX_CHECK_LOC(pre[u]) / a.P) * a.H;
-    // The request's heads blockIdx.y, blockIdx.y + gridDim.y, ...: a large batch gives every CTA several heads
-    // (entries and prefix sums are read once for all of them), a small one a CTA per (request, head).
-    for (int h = blockIdx.y; h < a.H; h += gridDim.y) {
-        const int s = r * a.H + h;
-        const int d0 = a.H * before.x + h * n;
-        const int s0 = a.H * before.y + h * m;
-        const int w0 = a.H * before.z + h * nch;
-        const int rem = seq % a.P;
-        const int last_len = rem == 0 ? a.P : rem;
-
-        if (tx == 0) {
-            a.dense_indptr[s] = d0;
-            a.sparse_indptr[s] = s0;
-            if (a.last_page_len) a.last_page_len[s] = last_len;
-            if (a.dense_sl) {
-                a.dense_sl[s] = seq;
-                a.sparse_sl[s] = min((budget - 1) * a.P + last_len, seq);
-            }
-            if (r == a.bs - 1 && h == a.H - 1) {
-                a.dense_indptr[s + 1] = d0 + n;
-                a.sparse_indptr[s + 1] = s0 + m;
-                *a.w_num = w0 + nch;
-                *a.w_chunk = a.max_chunk;
-            }
+            for (int w = 0; w < kPre; ++w)
+                if (w == u) tok = pre[w];
+        } else {
+            tok = toks[(int64_t)p * a.P];
         }
-
-        const int32_t* toks = a.req_to_token + VTX_CHECK_REQ_ROW(a.req_indices[r]) * a.r2t_stride;
-        int32_t* dense = a.dense_indices + d0;
-        int32_t* sparse = a.sparse_indices + s0;
-        int32_t* dpt = a.dense_pt ? a.dense_pt + (int64_t)s * a.pt_stride : nullptr;
-        int32_t* spt = a.sparse_pt ? a.sparse_pt + (int64_t)s * a.pt_stride : nullptr;
-        const bool copy_all = n <= budget;
-
-        for (int p = tx, u = 0; p < n; p += kPlanThreads, ++u) {
-            int32_t base = 0;
-            if (u < kPre) {
-#pragma unroll
-                for (int w = 0; w < kPre; ++w)
-                    if (w == u) base = pre[w];
-            } else {
-                base = (VTX_CHECK_LOC(toks[(int64_t)p * a.P]) / a.P) * a.H;
-            }
-            const int row = base + h;
-            dense[p] = row;
-            if (dpt) dpt[p] = row;
-            int slot = -1;
-            if (copy_all) slot = p;
-            else if (p < a.bos) slot = p;
-            else if (p >= n - a.eos) slot = budget - (n - p);
-            if (slot >= 0) {
-                sparse[slot] = row;
-                if (spt) spt[slot] = row;
-            }
+        const int row = (VTX_CHECK_LOC(tok) / a.P) * a.H + h;
+        dense[p] = row;
+        if (dpt) dpt[p] = row;
+        int slot = -1;
+        if (copy_all) slot = p;
+        else if (p < a.bos) slot = p;
+        else if (p >= n - a.eos) slot = budget - (n - p);
+        if (slot >= 0) {
+            sparse[slot] = row;
+            if (spt) spt[slot] = row;
         }
+    }
 
-        // workload chunks of this segment (consumed only by chunk-list style operators)
-        const int cand = n - a.bos - a.eos;
-        for (int j = tx; j < nch; j += kPlanThreads) {
-            int len = cand - j * a.max_chunk;
-            if (len > a.max_chunk) len = a.max_chunk;
-            a.w_q[w0 + j] = s;
-            a.w_len[w0 + j] = len;
-            a.w_off[w0 + j] = d0 + j * a.max_chunk + a.bos;
-        }
-    }  // heads of this CTA
+    // workload chunks of this segment (consumed only by chunk-list style operators)
+    const int cand = n - a.bos - a.eos;
+    for (int j = tx; j < nch; j += kPlanThreads) {
+        int len = cand - j * a.max_chunk;
+        if (len > a.max_chunk) len = a.max_chunk;
+        a.w_q[w0 + j] = s;
+        a.w_len[w0 + j] = len;
+        a.w_off[w0 + j] = d0 + j * a.max_chunk + a.bos;
+    }
 }
 
 }  // namespace
@@ -222,10 +215,6 @@ extern "C" int vtx_plan_decode(const int32_t* cached_seq_lens, const int32_t* re
     a.bos = page_reserved_bos;
     a.eos = page_reserved_eos;
     a.max_chunk = max_chunk_size;
-    // CTAs per request: the smallest divisor of the head count that still gives about two CTAs per SM
-    int per_req = num_kv_heads;
-    for (int d = 1; d <= num_kv_heads; ++d)
-        if (num_kv_heads % d == 0 && (int64_t)batch_size * d >= 2 * 148) { per_req = d; break; }
-    dim3 grid(batch_size, per_req);
+    dim3 grid(batch_size, num_kv_heads);
     return vtx::launch(plan_decode_kernel, grid, dim3(kPlanThreads), 0, (cudaStream_t)stream, a);
 }
